@@ -1,0 +1,387 @@
+// C ABI of libb200q.so: state, error plumbing, packed-weight handles, dispatch.
+// No CPU fallback exists: every compute entry point launches CUDA kernels or fails.
+#include <atomic>
+#include <mutex>
+#include <unordered_set>
+#include <vector>
+
+#include "common.cuh"
+
+namespace bq {
+
+static thread_local std::string t_err;
+static thread_local int t_last_path = BQ_PATH_AUTO;
+static std::atomic<int64_t> g_launches{0};
+static std::mutex g_mu;
+static std::unordered_set<void*> g_weights, g_moes;
+static int g_device = -1;
+static int g_sms = 0;
+static int* g_status = nullptr;
+// grow-only device staging for the host-buffer entry point
+static void* g_stage_x = nullptr; static size_t g_stage_x_bytes = 0;
+static void* g_stage_y = nullptr; static size_t g_stage_y_bytes = 0;
+
+int fail(int code, const std::string& msg) { t_err = msg; return code; }
+int fail_cuda(cudaError_t e, const char* what) {
+  t_err = std::string(what) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")";
+  return BQ_ERR_CUDA;
+}
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+void set_last_path(int p) { t_last_path = p; }
+int device_id() { return g_device; }
+int sm_count() { return g_sms > 0 ? g_sms : SM_COUNT_B200; }
+int* status_word() { return g_status; }
+
+Weight* get_weight(bq_weight_t h) {
+  void* p = reinterpret_cast<void*>(static_cast<uintptr_t>(h));
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (!p || !g_weights.count(p) || static_cast<Weight*>(p)->magic != WEIGHT_MAGIC) {
+    fail(BQ_ERR_HANDLE, "invalid weight handle");
+    return nullptr;
+  }
+  return static_cast<Weight*>(p);
+}
+Moe* get_moe(bq_moe_t h) {
+  void* p = reinterpret_cast<void*>(static_cast<uintptr_t>(h));
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (!p || !g_moes.count(p) || static_cast<Moe*>(p)->magic != MOE_MAGIC) {
+    fail(BQ_ERR_HANDLE, "invalid moe handle");
+    return nullptr;
+  }
+  return static_cast<Moe*>(p);
+}
+
+static int check_ready() {
+  if (g_device < 0) return fail(BQ_ERR_STATE, "bq_init() has not been called");
+  int cur = -1;
+  BQ_CUDA(cudaGetDevice(&cur));
+  if (cur != g_device) BQ_CUDA(cudaSetDevice(g_device));
+  return BQ_OK;
+}
+
+static int check_shape(int64_t N, int64_t K, int fmt) {
+  if (fmt != BQ_FMT_Q8G32 && fmt != BQ_FMT_Q4G32) return fail(BQ_ERR_ARG, "unknown weight format");
+  if (N < 0 || K <= 0) return fail(BQ_ERR_ARG, "N must be >= 0 and K > 0");
+  if (K % GROUP != 0) return fail(BQ_ERR_ARG, "K must be a multiple of 32 (the quantization group)");
+  if (N > (int64_t)1 << 31 || K > (int64_t)1 << 24) return fail(BQ_ERR_ARG, "N or K out of range");
+  return BQ_OK;
+}
+
+static int alloc_weight(int64_t N, int64_t K, int fmt, Weight** out) {
+  Weight* w = new Weight();
+  w->magic = WEIGHT_MAGIC;
+  w->fmt = fmt; w->N = N; w->K = K;
+  w->codes_bytes = (size_t)(N * (fmt == BQ_FMT_Q8G32 ? K : K / 2));
+  w->scales_bytes = (size_t)(N * (K / GROUP)) * sizeof(__half);
+  w->codes = nullptr; w->scales = nullptr;
+  // +256 bytes of slack so whole-16-byte vector reads past a ragged tail stay in bounds
+  cudaError_t e = cudaMalloc((void**)&w->codes, w->codes_bytes + 256);
+  if (e == cudaSuccess) e = cudaMalloc((void**)&w->scales, w->scales_bytes + 256);
+  if (e == cudaSuccess) e = cudaMemset(w->codes + w->codes_bytes, 0, 256);
+  if (e == cudaSuccess) e = cudaMemset((uint8_t*)w->scales + w->scales_bytes, 0, 256);
+  if (e != cudaSuccess) {
+    if (w->codes) cudaFree(w->codes);
+    if (w->scales) cudaFree(w->scales);
+    delete w;
+    return fail_cuda(e, "cudaMalloc(weight)");
+  }
+  *out = w;
+  return BQ_OK;
+}
+
+static bq_weight_t publish(Weight* w) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  g_weights.insert(w);
+  return static_cast<bq_weight_t>(reinterpret_cast<uintptr_t>(w));
+}
+
+static int ensure_stage(void** buf, size_t* have, size_t need) {
+  if (need <= *have) return BQ_OK;
+  if (*buf) BQ_CUDA(cudaFree(*buf));
+  *buf = nullptr; *have = 0;
+  size_t cap = need + need / 4 + 4096;
+  BQ_CUDA(cudaMalloc(buf, cap));
+  *have = cap;
+  return BQ_OK;
+}
+
+static size_t dt_size(int dt) { return dt == BQ_DT_F32 ? 4 : 2; }
+static bool dt_ok(int dt) { return dt == BQ_DT_F32 || dt == BQ_DT_BF16; }
+
+// Kernel-family choice.  SIMT = exact fp32 CUDA-core GEMV (M small or fp32 activations);
+// TENSOR = tcgen05 path (bf16 activations).
+static int choose_path(const Weight* w, int x_dtype, int64_t M, int requested) {
+  if (requested == BQ_PATH_SIMT) return BQ_PATH_SIMT;
+  const bool tc_ok = tc_supported(w->fmt, w->N, w->K, x_dtype, M);
+  if (requested == BQ_PATH_TENSOR) return tc_ok ? BQ_PATH_TENSOR : -1;
+  if (requested != BQ_PATH_AUTO) return -1;
+  if (tc_ok && M >= 2) return BQ_PATH_TENSOR;
+  return BQ_PATH_SIMT;
+}
+
+static int qlinear_impl(Weight* w, const void* x, int x_dtype, int64_t M, void* y, int y_dtype,
+                        int path, cudaStream_t s) {
+  if (!dt_ok(x_dtype) || !dt_ok(y_dtype)) return fail(BQ_ERR_ARG, "dtype must be BQ_DT_F32 or BQ_DT_BF16");
+  if (M < 0) return fail(BQ_ERR_ARG, "M must be >= 0");
+  if (M == 0 || w->N == 0) { set_last_path(BQ_PATH_AUTO); return BQ_OK; }
+  if (!x || !y) return fail(BQ_ERR_ARG, "x and y must not be null");
+  const int p = choose_path(w, x_dtype, M, path);
+  if (p < 0) return fail(BQ_ERR_UNSUPPORTED, "requested kernel path does not support this shape/dtype");
+  set_last_path(p);
+  if (p == BQ_PATH_TENSOR)
+    return launch_qlinear_tc(w->codes, w->scales, w->fmt, w->N, w->K, x, x_dtype, M, y, y_dtype, w->N, s);
+  return launch_qlinear_simt(w->codes, w->scales, w->fmt, w->N, w->K, x, x_dtype, M, y, y_dtype, w->N, s);
+}
+
+}  // namespace bq
+
+using namespace bq;
+
+extern "C" {
+
+int bq_version(void) { return 100; }
+
+const char* bq_last_error(void) { return t_err.c_str(); }
+
+int bq_init(int device) {
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaGetDeviceCount");
+  if (device < 0 || device >= n) return fail(BQ_ERR_ARG, "device index out of range");
+  if (g_device >= 0 && g_device != device)
+    return fail(BQ_ERR_STATE, "library already initialised on another device (one process per GPU)");
+  BQ_CUDA(cudaSetDevice(device));
+  if (g_device == device) return BQ_OK;
+  cudaDeviceProp prop;
+  BQ_CUDA(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10)
+    return fail(BQ_ERR_UNSUPPORTED, std::string("this library is built for sm_100a only; device is ") + prop.name);
+  g_sms = prop.multiProcessorCount;
+  BQ_CUDA(cudaMalloc((void**)&g_status, 256));
+  BQ_CUDA(cudaMemset(g_status, 0, 256));
+  g_device = device;
+  return BQ_OK;
+}
+
+int bq_status_poll(void) {
+  int rc = check_ready();
+  if (rc) return rc;
+  BQ_CUDA(cudaDeviceSynchronize());
+  int v = 0;
+  BQ_CUDA(cudaMemcpy(&v, g_status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (v != 0) {
+    BQ_CUDA(cudaMemset(g_status, 0, sizeof(int)));
+    return fail(v, "a kernel recorded a device-side anomaly (bounded wait expired)");
+  }
+  return BQ_OK;
+}
+
+int bq_weight_create(const void* codes, const void* scales, int64_t N, int64_t K, int fmt, bq_weight_t* out) {
+  int rc = check_ready();
+  if (rc) return rc;
+  if (!out) return fail(BQ_ERR_ARG, "out must not be null");
+  if ((rc = check_shape(N, K, fmt))) return rc;
+  if (N > 0 && (!codes || !scales)) return fail(BQ_ERR_ARG, "codes and scales must not be null");
+  Weight* w = nullptr;
+  if ((rc = alloc_weight(N, K, fmt, &w))) return rc;
+  cudaError_t e = cudaSuccess;
+  if (w->codes_bytes) e = cudaMemcpy(w->codes, codes, w->codes_bytes, cudaMemcpyHostToDevice);
+  if (e == cudaSuccess && w->scales_bytes) e = cudaMemcpy(w->scales, scales, w->scales_bytes, cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) {
+    cudaFree(w->codes); cudaFree(w->scales); delete w;
+    return fail_cuda(e, "cudaMemcpy(weight upload)");
+  }
+  *out = publish(w);
+  return BQ_OK;
+}
+
+int bq_weight_create_device(const void* d_codes, const void* d_scales, int64_t N, int64_t K, int fmt,
+                            void* stream, bq_weight_t* out) {
+  int rc = check_ready();
+  if (rc) return rc;
+  if (!out) return fail(BQ_ERR_ARG, "out must not be null");
+  if ((rc = check_shape(N, K, fmt))) return rc;
+  if (N > 0 && (!d_codes || !d_scales)) return fail(BQ_ERR_ARG, "codes and scales must not be null");
+  Weight* w = nullptr;
+  if ((rc = alloc_weight(N, K, fmt, &w))) return rc;
+  cudaStream_t s = (cudaStream_t)stream;
+  cudaError_t e = cudaSuccess;
+  if (w->codes_bytes) e = cudaMemcpyAsync(w->codes, d_codes, w->codes_bytes, cudaMemcpyDeviceToDevice, s);
+  if (e == cudaSuccess && w->scales_bytes)
+    e = cudaMemcpyAsync(w->scales, d_scales, w->scales_bytes, cudaMemcpyDeviceToDevice, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) {
+    cudaFree(w->codes); cudaFree(w->scales); delete w;
+    return fail_cuda(e, "cudaMemcpyAsync(weight copy)");
+  }
+  *out = publish(w);
+  return BQ_OK;
+}
+
+int bq_weight_destroy(bq_weight_t h) {
+  Weight* w = get_weight(h);
+  if (!w) return BQ_ERR_HANDLE;
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    g_weights.erase(w);
+  }
+  w->magic = 0;
+  cudaFree(w->codes);
+  cudaFree(w->scales);
+  delete w;
+  return BQ_OK;
+}
+
+int bq_weight_info(bq_weight_t h, int64_t* N, int64_t* K, int* fmt) {
+  Weight* w = get_weight(h);
+  if (!w) return BQ_ERR_HANDLE;
+  if (N) *N = w->N;
+  if (K) *K = w->K;
+  if (fmt) *fmt = w->fmt;
+  return BQ_OK;
+}
+
+int bq_weight_export(bq_weight_t h, void* codes_out, void* scales_out) {
+  int rc = check_ready();
+  if (rc) return rc;
+  Weight* w = get_weight(h);
+  if (!w) return BQ_ERR_HANDLE;
+  if (w->N > 0 && (!codes_out || !scales_out)) return fail(BQ_ERR_ARG, "output pointers must not be null");
+  if (w->codes_bytes) BQ_CUDA(cudaMemcpy(codes_out, w->codes, w->codes_bytes, cudaMemcpyDeviceToHost));
+  if (w->scales_bytes) BQ_CUDA(cudaMemcpy(scales_out, w->scales, w->scales_bytes, cudaMemcpyDeviceToHost));
+  return BQ_OK;
+}
+
+int bq_dequant(bq_weight_t h, void* out, int out_dtype, void* stream) {
+  int rc = check_ready();
+  if (rc) return rc;
+  Weight* w = get_weight(h);
+  if (!w) return BQ_ERR_HANDLE;
+  if (!dt_ok(out_dtype)) return fail(BQ_ERR_ARG, "out_dtype must be BQ_DT_F32 or BQ_DT_BF16");
+  if (w->N > 0 && !out) return fail(BQ_ERR_ARG, "out must not be null");
+  return launch_dequant(w, out, out_dtype, (cudaStream_t)stream);
+}
+
+int bq_unpack_codes(bq_weight_t h, void* out_i8, void* stream) {
+  int rc = check_ready();
+  if (rc) return rc;
+  Weight* w = get_weight(h);
+  if (!w) return BQ_ERR_HANDLE;
+  if (w->N > 0 && !out_i8) return fail(BQ_ERR_ARG, "out must not be null");
+  return launch_unpack(w, (int8_t*)out_i8, (cudaStream_t)stream);
+}
+
+int bq_qlinear_ex(bq_weight_t h, const void* x, int x_dtype, int64_t M, void* y, int y_dtype, int path,
+                  void* stream) {
+  int rc = check_ready();
+  if (rc) return rc;
+  Weight* w = get_weight(h);
+  if (!w) return BQ_ERR_HANDLE;
+  return qlinear_impl(w, x, x_dtype, M, y, y_dtype, path, (cudaStream_t)stream);
+}
+
+int bq_qlinear(bq_weight_t h, const void* x, int x_dtype, int64_t M, void* y, int y_dtype, void* stream) {
+  return bq_qlinear_ex(h, x, x_dtype, M, y, y_dtype, BQ_PATH_AUTO, stream);
+}
+
+int bq_qlinear_host(bq_weight_t h, const void* x_host, int x_dtype, int64_t M, void* y_host, int y_dtype) {
+  int rc = check_ready();
+  if (rc) return rc;
+  Weight* w = get_weight(h);
+  if (!w) return BQ_ERR_HANDLE;
+  if (!dt_ok(x_dtype) || !dt_ok(y_dtype)) return fail(BQ_ERR_ARG, "dtype must be BQ_DT_F32 or BQ_DT_BF16");
+  if (M < 0) return fail(BQ_ERR_ARG, "M must be >= 0");
+  if (M == 0 || w->N == 0) return BQ_OK;
+  if (!x_host || !y_host) return fail(BQ_ERR_ARG, "x and y must not be null");
+  const size_t xb = (size_t)M * w->K * dt_size(x_dtype), yb = (size_t)M * w->N * dt_size(y_dtype);
+  if ((rc = ensure_stage(&g_stage_x, &g_stage_x_bytes, xb))) return rc;
+  if ((rc = ensure_stage(&g_stage_y, &g_stage_y_bytes, yb))) return rc;
+  cudaStream_t s = cudaStreamPerThread;
+  BQ_CUDA(cudaMemcpyAsync(g_stage_x, x_host, xb, cudaMemcpyHostToDevice, s));
+  if ((rc = qlinear_impl(w, g_stage_x, x_dtype, M, g_stage_y, y_dtype, BQ_PATH_AUTO, s))) return rc;
+  BQ_CUDA(cudaMemcpyAsync(y_host, g_stage_y, yb, cudaMemcpyDeviceToHost, s));
+  BQ_CUDA(cudaStreamSynchronize(s));
+  return BQ_OK;
+}
+
+int bq_lm_head(bq_weight_t h, const void* x, int x_dtype, int64_t M, void* logits, int logits_dtype,
+               int32_t* argmax_out, void* stream) {
+  int rc = check_ready();
+  if (rc) return rc;
+  Weight* w = get_weight(h);
+  if (!w) return BQ_ERR_HANDLE;
+  if (M < 0) return fail(BQ_ERR_ARG, "M must be >= 0");
+  if (M == 0) return BQ_OK;
+  if (w->N == 0) return fail(BQ_ERR_ARG, "lm_head needs a non-empty vocabulary");
+  if (!logits && !argmax_out) return fail(BQ_ERR_ARG, "logits and argmax_out are both null");
+  cudaStream_t s = (cudaStream_t)stream;
+  void* lg = logits;
+  int ldt = logits_dtype;
+  if (!lg) {  // argmax only: logits live in the library's staging buffer
+    ldt = BQ_DT_F32;
+    if ((rc = ensure_stage(&g_stage_y, &g_stage_y_bytes, (size_t)M * w->N * 4))) return rc;
+    lg = g_stage_y;
+  }
+  if ((rc = qlinear_impl(w, x, x_dtype, M, lg, ldt, BQ_PATH_AUTO, s))) return rc;
+  if (argmax_out) return launch_argmax(lg, ldt, M, w->N, argmax_out, s);
+  return BQ_OK;
+}
+
+int bq_last_path(void) { return t_last_path; }
+int64_t bq_launch_count(void) { return g_launches.load(); }
+
+// ---- MoE expert set -------------------------------------------------------------------------
+int bq_moe_create(const bq_weight_t* gate, const bq_weight_t* up, const bq_weight_t* down, int E, bq_moe_t* out) {
+  int rc = check_ready();
+  if (rc) return rc;
+  if (!gate || !up || !down || !out || E <= 0) return fail(BQ_ERR_ARG, "bad arguments");
+  std::vector<const uint8_t*> pc[3];
+  std::vector<const __half*> ps[3];
+  int64_t H = 0, F = 0;
+  int fmt = -1;
+  for (int e = 0; e < E; ++e) {
+    Weight* g = get_weight(gate[e]); if (!g) return BQ_ERR_HANDLE;
+    Weight* u = get_weight(up[e]);   if (!u) return BQ_ERR_HANDLE;
+    Weight* d = get_weight(down[e]); if (!d) return BQ_ERR_HANDLE;
+    if (e == 0) { H = g->K; F = g->N; fmt = g->fmt; }
+    if (g->K != H || g->N != F || u->K != H || u->N != F || d->K != F || d->N != H || g->fmt != fmt ||
+        u->fmt != fmt || d->fmt != fmt)
+      return fail(BQ_ERR_ARG, "expert weights must share shapes gate/up [F,H], down [H,F] and one format");
+    pc[0].push_back(g->codes); ps[0].push_back(g->scales);
+    pc[1].push_back(u->codes); ps[1].push_back(u->scales);
+    pc[2].push_back(d->codes); ps[2].push_back(d->scales);
+  }
+  Moe* m = new Moe();
+  m->magic = MOE_MAGIC; m->E = E; m->H = H; m->F = F; m->fmt = fmt;
+  const uint8_t*** cdst[3] = {&m->gate_codes, &m->up_codes, &m->down_codes};
+  const __half*** sdst[3] = {&m->gate_scales, &m->up_scales, &m->down_scales};
+  for (int i = 0; i < 3; ++i) {
+    BQ_CUDA(cudaMalloc((void**)cdst[i], sizeof(void*) * E));
+    BQ_CUDA(cudaMalloc((void**)sdst[i], sizeof(void*) * E));
+    BQ_CUDA(cudaMemcpy((void*)*cdst[i], pc[i].data(), sizeof(void*) * E, cudaMemcpyHostToDevice));
+    BQ_CUDA(cudaMemcpy((void*)*sdst[i], ps[i].data(), sizeof(void*) * E, cudaMemcpyHostToDevice));
+  }
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    g_moes.insert(m);
+  }
+  *out = static_cast<bq_moe_t>(reinterpret_cast<uintptr_t>(m));
+  return BQ_OK;
+}
+
+int bq_moe_destroy(bq_moe_t h) {
+  Moe* m = get_moe(h);
+  if (!m) return BQ_ERR_HANDLE;
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    g_moes.erase(m);
+  }
+  m->magic = 0;
+  cudaFree((void*)m->gate_codes); cudaFree((void*)m->gate_scales);
+  cudaFree((void*)m->up_codes);   cudaFree((void*)m->up_scales);
+  cudaFree((void*)m->down_codes); cudaFree((void*)m->down_scales);
+  delete m;
+  return BQ_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,115 @@
+// Shared declarations for libb200q: weight record, error plumbing, small device helpers.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <string>
+
+#include "../../include/b200q.h"
+
+namespace bq {
+
+constexpr int GROUP = 32;
+constexpr int SM_COUNT_B200 = 148;
+
+// A packed weight resident in HBM.  Device layout = interface layout (row-major codes and
+// row-major scales, each in its own 256-byte aligned allocation): a block of consecutive
+// rows is one contiguous byte range, which is what the bulk-copy (TMA) pipeline wants.
+struct Weight {
+  uint32_t magic;        // 0xB200C0DE while alive
+  int fmt;
+  int64_t N, K;
+  uint8_t* codes;        // Q8: N*K bytes, Q4: N*K/2 bytes
+  __half* scales;        // N*K/32 fp16
+  size_t codes_bytes, scales_bytes;
+  int64_t row_bytes() const { return fmt == BQ_FMT_Q8G32 ? K : K / 2; }
+};
+constexpr uint32_t WEIGHT_MAGIC = 0xB200C0DEu;
+
+struct Moe {
+  uint32_t magic;        // 0xB2003E00 while alive
+  int E;
+  int64_t H, F;
+  int fmt;
+  // device arrays of per-expert pointers
+  const uint8_t** gate_codes; const __half** gate_scales;
+  const uint8_t** up_codes;   const __half** up_scales;
+  const uint8_t** down_codes; const __half** down_scales;
+};
+constexpr uint32_t MOE_MAGIC = 0xB2003E00u;
+
+// ---- host-side state / error plumbing (api.cu) -----------------------------------------
+int fail(int code, const std::string& msg);
+int fail_cuda(cudaError_t e, const char* what);
+void count_launch(int n = 1);
+void set_last_path(int p);
+Weight* get_weight(bq_weight_t h);     // nullptr (and error set) if invalid
+Moe* get_moe(bq_moe_t h);
+int device_id();
+int sm_count();
+int* status_word();                    // device int, 0 = fine
+
+#define BQ_CUDA(call)                                          \
+  do {                                                         \
+    cudaError_t e__ = (call);                                  \
+    if (e__ != cudaSuccess) return ::bq::fail_cuda(e__, #call); \
+  } while (0)
+
+// ---- kernel launchers implemented in the .cu files ----------------------------------------
+int launch_dequant(const Weight* w, void* out, int out_dtype, cudaStream_t s);
+int launch_unpack(const Weight* w, int8_t* out, cudaStream_t s);
+// SIMT (CUDA-core, exact fp32) path: any M (loops over row tiles of the activations)
+int launch_qlinear_simt(const uint8_t* codes, const __half* scales, int fmt, int64_t N, int64_t K,
+                        const void* x, int x_dtype, int64_t M, void* y, int y_dtype, int64_t ldy,
+                        cudaStream_t s);
+// tensor-core (tcgen05) path: bf16 activations
+int launch_qlinear_tc(const uint8_t* codes, const __half* scales, int fmt, int64_t N, int64_t K,
+                      const void* x, int x_dtype, int64_t M, void* y, int y_dtype, int64_t ldy,
+                      cudaStream_t s);
+bool tc_supported(int fmt, int64_t N, int64_t K, int x_dtype, int64_t M);
+int launch_argmax(const void* logits, int dtype, int64_t M, int64_t N, int32_t* out, cudaStream_t s);
+
+// ---- device helpers --------------------------------------------------------------------------
+#ifdef __CUDACC__
+__device__ __forceinline__ uint4 ldg_stream16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;  // (a & b) | c
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ float bf16_bits_to_float(uint16_t b) {
+  return __uint_as_float(((uint32_t)b) << 16);
+}
+template <typename T> __device__ __forceinline__ float to_float(T v);
+template <> __device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) {
+  return __bfloat162float(v);
+}
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+// Exact integer-code -> fp32 conversions without the (slow) I2F pipe.
+// Q8: `v` holds four int8 codes already XOR-ed with 0x80808080 (so each byte is code+128).
+// Byte `I` is dropped into the mantissa of 2^23, giving 8388608 + code + 128 exactly.
+template <int I> __device__ __forceinline__ float q8_byte_to_float(uint32_t v_xor80) {
+  constexpr uint32_t sel = 0x7650u | (uint32_t)I;
+  return __uint_as_float(__byte_perm(v_xor80, 0x4B000000u, sel)) - 8388736.0f;
+}
+// Q4: nibble `I` of the word is element I of the 8 it holds; stored value is code + 8.
+template <int I> __device__ __forceinline__ float q4_nibble_to_float(uint32_t v) {
+  uint32_t m = lop3_and_or(I == 0 ? v : (v >> (4 * I)), 0xFu, 0x4B000000u);
+  return __uint_as_float(m) - 8388616.0f;
+}
+#endif
+
+}  // namespace bq

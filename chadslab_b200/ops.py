@@ -1,0 +1,356 @@
+"""Operator surface of the quantized-matmul path.
+
+    PackedWeight.from_float(W, fmt) / .from_arrays(codes, scales, fmt)
+    QuantLinear(pw)(x) -> y          every attention / FFN projection
+    LMHead(pw)(x) -> logits          .greedy(x) -> token ids
+    MoEExperts(router_pw, gate_pws, up_pws, down_pws, top_k)(x) -> y
+    shard(pw, axis, rank, world)     column ('n') / row ('k') parallel slices
+
+The reference checkout has no operator surface for this path (no quantized linear, expert matmul
+or lm_head exists in it), so these names are this package's own; they are identical for every
+caller and the numerical contract is: dequantized weight = float(code) * float(scale) exactly,
+fp32 accumulation, outputs within 1e-3 (max error / max magnitude) of an fp32 numpy evaluation.
+
+x may be a CUDA torch tensor (device path: nothing leaves the GPU) or a host numpy array
+(host path: the C ABI copies in, computes, copies out).  All compute is in libb200q.so; if the
+library or a GPU is missing the calls raise — there is no CPU fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import numpy as np
+
+from . import _lib, packing
+from ._lib import BqError, DT_BF16, DT_F32, FMT_Q4, FMT_Q8, PATH_AUTO
+
+GROUP = packing.GROUP
+
+
+def _torch():
+    import torch
+    return torch
+
+
+def _stream_ptr() -> int:
+    return _torch().cuda.current_stream().cuda_stream
+
+
+def _dt_of_torch(t) -> int:
+    torch = _torch()
+    if t.dtype == torch.float32:
+        return DT_F32
+    if t.dtype == torch.bfloat16:
+        return DT_BF16
+    raise TypeError(f"activations must be float32 or bfloat16, got {t.dtype}")
+
+
+def _torch_dtype(dt: int):
+    torch = _torch()
+    return torch.float32 if dt == DT_F32 else torch.bfloat16
+
+
+def _np_dt(a: np.ndarray) -> int:
+    if a.dtype == np.float32:
+        return DT_F32
+    if a.dtype.name == "bfloat16":
+        return DT_BF16
+    raise TypeError(f"host activations must be float32 or ml_dtypes.bfloat16, got {a.dtype}")
+
+
+class PackedWeight:
+    """A block-quantized [N, K] weight: host arrays in the interface layout + a device handle."""
+
+    def __init__(self, codes: np.ndarray, scales: np.ndarray, fmt: int, *, upload: bool = True,
+                 device: Optional[int] = None):
+        if fmt not in (FMT_Q8, FMT_Q4):
+            raise ValueError(f"unknown format {fmt}")
+        codes = np.ascontiguousarray(codes)
+        scales = np.ascontiguousarray(scales)
+        if codes.ndim != 2 or scales.ndim != 2:
+            raise ValueError("codes and scales must be 2-D")
+        N = codes.shape[0]
+        K = codes.shape[1] * (2 if fmt == FMT_Q4 else 1)
+        if K <= 0 or K % GROUP:
+            raise ValueError(f"K={K} must be a positive multiple of {GROUP}")
+        if codes.dtype != packing.codes_dtype(fmt):
+            raise TypeError(f"codes dtype must be {packing.codes_dtype(fmt).__name__}")
+        if scales.dtype != np.float16 or scales.shape != (N, K // GROUP):
+            raise ValueError(f"scales must be float16 of shape {(N, K // GROUP)}")
+        self.codes, self.scales, self.fmt, self.N, self.K = codes, scales, fmt, N, K
+        self._handle = None
+        self._device = device
+        if upload:
+            self.upload(device)
+
+    # -- construction -------------------------------------------------------------------------
+    @classmethod
+    def from_float(cls, W, fmt: int, **kw) -> "PackedWeight":
+        codes, scales = packing.quantize(np.asarray(W, dtype=np.float32), fmt)
+        return cls(codes, scales, fmt, **kw)
+
+    @classmethod
+    def from_arrays(cls, codes, scales, fmt: int, **kw) -> "PackedWeight":
+        return cls(codes, scales, fmt, **kw)
+
+    @classmethod
+    def from_device(cls, d_codes, d_scales, fmt: int) -> "PackedWeight":
+        """Wrap device-resident torch tensors (codes int8/uint8 [N,K or K/2], scales fp16)."""
+        torch = _torch()
+        self = cls.__new__(cls)
+        N = d_codes.shape[0]
+        K = d_codes.shape[1] * (2 if fmt == FMT_Q4 else 1)
+        assert d_scales.dtype == torch.float16 and tuple(d_scales.shape) == (N, K // GROUP)
+        assert d_codes.is_contiguous() and d_scales.is_contiguous()
+        self.codes = self.scales = None
+        self.fmt, self.N, self.K = fmt, N, K
+        lib = _lib.init(d_codes.device.index or 0)
+        h = C.c_uint64(0)
+        _lib.check(lib.bq_weight_create_device(d_codes.data_ptr(), d_scales.data_ptr(), N, K, fmt,
+                                               _stream_ptr(), C.byref(h)))
+        self._handle = h.value
+        self._device = d_codes.device.index or 0
+        return self
+
+    def upload(self, device: Optional[int] = None) -> "PackedWeight":
+        if self._handle is not None:
+            return self
+        if device is None:
+            device = _torch().cuda.current_device() if _torch().cuda.is_available() else 0
+        lib = _lib.init(device)
+        h = C.c_uint64(0)
+        _lib.check(lib.bq_weight_create(self.codes.ctypes.data, self.scales.ctypes.data, self.N, self.K,
+                                        self.fmt, C.byref(h)))
+        self._handle, self._device = h.value, device
+        return self
+
+    @property
+    def handle(self) -> int:
+        if self._handle is None:
+            self.upload(self._device)
+        return self._handle
+
+    def close(self) -> None:
+        if self._handle is not None:
+            try:
+                _lib.load().bq_weight_destroy(self._handle)
+            finally:
+                self._handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- queries ---------------------------------------------------------------------------------
+    @property
+    def nbytes(self) -> int:
+        """Algorithmic bytes of the packed weight (codes + scales)."""
+        return int(self.N * self.K * packing.bytes_per_weight(self.fmt))
+
+    def export(self):
+        """Read the weight back from the device in the interface layout."""
+        codes = np.empty(packing.codes_shape(self.N, self.K, self.fmt), dtype=packing.codes_dtype(self.fmt))
+        scales = np.empty((self.N, self.K // GROUP), dtype=np.float16)
+        _lib.check(_lib.lib().bq_weight_export(self.handle, codes.ctypes.data, scales.ctypes.data))
+        return codes, scales
+
+    def dequantize(self, dtype=None):
+        """-> CUDA tensor [N,K]; float32 (exact) or bfloat16 (round-to-nearest-even of it)."""
+        torch = _torch()
+        dtype = dtype or torch.float32
+        out = torch.empty((self.N, self.K), dtype=dtype, device=f"cuda:{self._device or 0}")
+        _lib.check(_lib.lib().bq_dequant(self.handle, out.data_ptr(), _dt_of_torch(out), _stream_ptr()))
+        return out
+
+    def unpack(self):
+        """-> CUDA int8 tensor [N,K] of integer codes."""
+        torch = _torch()
+        h = self.handle
+        out = torch.empty((self.N, self.K), dtype=torch.int8, device=f"cuda:{self._device or 0}")
+        _lib.check(_lib.lib().bq_unpack_codes(h, out.data_ptr(), _stream_ptr()))
+        return out
+
+
+def shard(pw: PackedWeight, axis: str, rank: int, world: int, **kw) -> PackedWeight:
+    """Column-parallel ('n': split output rows) or row-parallel ('k': split K in multiples of 32,
+    so no quantization group straddles two ranks) slice of a packed weight."""
+    if pw.codes is None:
+        raise ValueError("shard() needs the host arrays of the weight")
+    if not (0 <= rank < world):
+        raise ValueError("rank out of range")
+    if axis == "n":
+        if pw.N % world:
+            raise ValueError(f"N={pw.N} is not divisible by world={world}")
+        n = pw.N // world
+        return PackedWeight(pw.codes[rank * n:(rank + 1) * n], pw.scales[rank * n:(rank + 1) * n], pw.fmt, **kw)
+    if axis == "k":
+        if pw.K % (world * GROUP):
+            raise ValueError(f"K={pw.K} is not divisible by world*32={world * GROUP}")
+        k = pw.K // world
+        div = 2 if pw.fmt == FMT_Q4 else 1
+        return PackedWeight(pw.codes[:, rank * k // div:(rank + 1) * k // div],
+                            pw.scales[:, rank * k // GROUP:(rank + 1) * k // GROUP], pw.fmt, **kw)
+    raise ValueError("axis must be 'n' or 'k'")
+
+
+class QuantLinear:
+    """y = x . dequant(W)^T for a packed weight; fp32 accumulate."""
+
+    def __init__(self, pw: PackedWeight, out_dtype=None, path: int = PATH_AUTO):
+        self.pw = pw
+        self.out_dtype = out_dtype
+        self.path = path
+
+    @property
+    def in_features(self) -> int:
+        return self.pw.K
+
+    @property
+    def out_features(self) -> int:
+        return self.pw.N
+
+    def __call__(self, x, out=None):
+        if isinstance(x, np.ndarray):
+            return self._host(x)
+        torch = _torch()
+        if not x.is_cuda:
+            raise BqError(_lib.ERR_ARG, "activations must be a CUDA tensor (or a host numpy array)")
+        lead = x.shape[:-1]
+        if x.shape[-1] != self.pw.K:
+            raise ValueError(f"x has K={x.shape[-1]}, weight has K={self.pw.K}")
+        x2 = x.reshape(-1, self.pw.K)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        M = x2.shape[0]
+        odt = self.out_dtype or torch.float32
+        if out is None:
+            out = torch.empty((M, self.pw.N), dtype=odt, device=x.device)
+        _lib.check(_lib.lib().bq_qlinear_ex(self.pw.handle, x2.data_ptr(), _dt_of_torch(x2), M, out.data_ptr(),
+                                            _dt_of_torch(out), self.path, _stream_ptr()))
+        return out.reshape(*lead, self.pw.N)
+
+    def _host(self, x: np.ndarray) -> np.ndarray:
+        x2 = np.ascontiguousarray(x).reshape(-1, self.pw.K)
+        y = np.empty((x2.shape[0], self.pw.N), dtype=np.float32)
+        _lib.check(_lib.lib().bq_qlinear_host(self.pw.handle, x2.ctypes.data, _np_dt(x2), x2.shape[0],
+                                              y.ctypes.data, DT_F32))
+        return y.reshape(*x.shape[:-1], self.pw.N)
+
+
+class LMHead(QuantLinear):
+    """Vocabulary projection; `greedy` returns argmax token ids (ties -> lower id)."""
+
+    def greedy(self, x, return_logits: bool = False):
+        torch = _torch()
+        x2 = x.reshape(-1, self.pw.K).contiguous()
+        M = x2.shape[0]
+        ids = torch.empty((M,), dtype=torch.int32, device=x.device)
+        logits = torch.empty((M, self.pw.N), dtype=torch.float32, device=x.device) if return_logits else None
+        _lib.check(_lib.lib().bq_lm_head(self.pw.handle, x2.data_ptr(), _dt_of_torch(x2), M,
+                                         logits.data_ptr() if return_logits else None, DT_F32,
+                                         ids.data_ptr(), _stream_ptr()))
+        return (ids, logits) if return_logits else ids
+
+
+def moe_route(logits, top_k: int, renormalise: bool = True):
+    torch = _torch()
+    logits = logits.contiguous().float()
+    T, E = logits.shape
+    idx = torch.empty((T, top_k), dtype=torch.int32, device=logits.device)
+    w = torch.empty((T, top_k), dtype=torch.float32, device=logits.device)
+    _lib.check(_lib.lib().bq_moe_route(logits.data_ptr(), T, E, top_k, int(renormalise), idx.data_ptr(),
+                                       w.data_ptr(), _stream_ptr()))
+    return idx, w
+
+
+def moe_permute(idx, n_experts: int):
+    torch = _torch()
+    idx = idx.contiguous()
+    T, k = idx.shape
+    A = T * k
+    lib = _lib.lib()
+    perm = torch.empty((A,), dtype=torch.int32, device=idx.device)
+    inv = torch.empty((A,), dtype=torch.int32, device=idx.device)
+    offsets = torch.empty((n_experts + 1,), dtype=torch.int32, device=idx.device)
+    sb = max(int(lib.bq_moe_permute_scratch_bytes(T, k, n_experts)), 16)
+    scratch = torch.empty((sb,), dtype=torch.uint8, device=idx.device)
+    _lib.check(lib.bq_moe_permute(idx.data_ptr(), T, k, n_experts, perm.data_ptr(), inv.data_ptr(),
+                                  offsets.data_ptr(), scratch.data_ptr(), _stream_ptr()))
+    return perm, inv, offsets
+
+
+def moe_gather(x, perm, top_k: int):
+    torch = _torch()
+    x = x.contiguous()
+    P = perm.numel()
+    xp = torch.empty((P, x.shape[1]), dtype=x.dtype, device=x.device)
+    _lib.check(_lib.lib().bq_moe_gather(x.data_ptr(), _dt_of_torch(x), x.shape[1], perm.data_ptr(), P, top_k,
+                                        xp.data_ptr(), _stream_ptr()))
+    return xp
+
+
+def moe_combine(out_p, inv, w, out_dtype=None):
+    torch = _torch()
+    T, k = w.shape
+    H = out_p.shape[1]
+    y = torch.empty((T, H), dtype=out_dtype or torch.float32, device=out_p.device)
+    _lib.check(_lib.lib().bq_moe_combine(out_p.data_ptr(), inv.data_ptr(), w.data_ptr(), T, k, H, y.data_ptr(),
+                                         _dt_of_torch(y), _stream_ptr()))
+    return y
+
+
+class MoEExperts:
+    """Sparse MoE layer: router linear -> softmax/top-k -> permute -> grouped SwiGLU experts ->
+    weighted combine.  Activations are bf16 between the matmuls, accumulation is fp32."""
+
+    def __init__(self, router_pw: PackedWeight, gate_pws: Sequence[PackedWeight], up_pws: Sequence[PackedWeight],
+                 down_pws: Sequence[PackedWeight], top_k: int, renormalise: bool = True, path: int = PATH_AUTO):
+        E = len(gate_pws)
+        if not (len(up_pws) == len(down_pws) == E) or E == 0:
+            raise ValueError("gate/up/down must hold one weight per expert")
+        if router_pw.N != E:
+            raise ValueError("router must have one output row per expert")
+        self.router = QuantLinear(router_pw)
+        self.gate, self.up, self.down = list(gate_pws), list(up_pws), list(down_pws)
+        self.E, self.top_k, self.renormalise, self.path = E, top_k, renormalise, path
+        self.H, self.F = gate_pws[0].K, gate_pws[0].N
+        arr = lambda pws: (C.c_uint64 * E)(*[p.handle for p in pws])
+        h = C.c_uint64(0)
+        _lib.check(_lib.lib().bq_moe_create(arr(self.gate), arr(self.up), arr(self.down), E, C.byref(h)))
+        self._handle = h.value
+
+    def close(self):
+        if getattr(self, "_handle", None):
+            _lib.load().bq_moe_destroy(self._handle)
+            self._handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def experts(self, xp, offsets):
+        """Grouped SwiGLU FFN on permuted bf16 rows xp[P,H] -> f32[P,H]."""
+        torch = _torch()
+        P = xp.shape[0]
+        hbuf = torch.empty((P, self.F), dtype=torch.bfloat16, device=xp.device)
+        out = torch.empty((P, self.H), dtype=torch.float32, device=xp.device)
+        _lib.check(_lib.lib().bq_moe_experts(self._handle, xp.data_ptr(), offsets.data_ptr(), P, hbuf.data_ptr(),
+                                             out.data_ptr(), self.path, _stream_ptr()))
+        return out
+
+    def __call__(self, x, return_aux: bool = False):
+        torch = _torch()
+        x = x.reshape(-1, self.H)
+        xb = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
+        logits = self.router(xb)
+        idx, w = moe_route(logits, self.top_k, self.renormalise)
+        perm, inv, offsets = moe_permute(idx, self.E)
+        xp = moe_gather(xb, perm, self.top_k)
+        out_p = self.experts(xp, offsets)
+        y = moe_combine(out_p, inv, w)
+        return (y, (idx, w, perm, inv, offsets)) if return_aux else y

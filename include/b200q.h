@@ -1,0 +1,139 @@
+/*
+ * b200q.h — C ABI of libb200q.so: block-quantized (group-32) weight matmuls on NVIDIA B200.
+ *
+ * Reference interface replaced: NONE EXISTS.  The reference checkout has no quantized
+ * linear / expert-matmul / lm_head code and no FFI for one (its README, lines 1-9, lists
+ * only unrelated projects; the nearest things to a plugin interface are the emulator
+ * callbacks in m6502/m6502.h:20-23 and the IFileIO vtable in m++/mpp.h:20-25, neither of
+ * which concerns this path).  Each entry point below therefore cites the sentence of the
+ * written specification it implements instead of a reference file:line.
+ *
+ * Conventions
+ *   - every function returns 0 (BQ_OK) or a negative BQ_ERR_* code; bq_last_error() returns
+ *     a thread-local message for the last failing call on the calling thread;
+ *   - no C++ exception crosses this boundary; argument errors are found on the host before
+ *     anything is launched;
+ *   - "device pointer" arguments are plain CUDA device addresses on the device selected by
+ *     bq_init(); `stream` is a cudaStream_t passed as void* (NULL = default stream);
+ *   - activations and outputs are row-major: x[M,K], y[M,N];
+ *   - the host layout of a packed weight is the interface layout:
+ *       Q8: codes int8[N,K],      scales fp16[N,K/32]
+ *       Q4: codes uint8[N,K/2],   scales fp16[N,K/32]; byte j = element 2j in bits 0-3 and
+ *           element 2j+1 in bits 4-7, each stored as (code + 8)
+ *     dequantized weight = float(code) * float(scale)   (exact in fp32).
+ *   - one process per GPU; a handle may be used from any thread, not concurrently.
+ */
+#ifndef B200Q_H
+#define B200Q_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef uint64_t bq_weight_t;      /* opaque handle to a packed weight resident in HBM   */
+typedef uint64_t bq_moe_t;         /* opaque handle to a set of MoE expert weights        */
+
+enum { BQ_FMT_Q8G32 = 0, BQ_FMT_Q4G32 = 1 };
+enum { BQ_DT_F32 = 0, BQ_DT_BF16 = 1 };
+
+enum {
+  BQ_OK = 0,
+  BQ_ERR_ARG = -1,        /* null pointer, bad enum, K % 32 != 0, size out of range ...  */
+  BQ_ERR_HANDLE = -2,     /* unknown or destroyed handle                                  */
+  BQ_ERR_CUDA = -3,       /* a CUDA runtime call failed (message has the CUDA error)      */
+  BQ_ERR_STATE = -4,      /* bq_init() not called, or wrong device                        */
+  BQ_ERR_TIMEOUT = -5,    /* a bounded device-side wait expired (status word set)         */
+  BQ_ERR_UNSUPPORTED = -6 /* valid request that this build has no kernel for              */
+};
+
+/* kernel selection for bq_qlinear_ex (bq_qlinear uses BQ_PATH_AUTO) */
+enum { BQ_PATH_AUTO = 0, BQ_PATH_SIMT = 1, BQ_PATH_TENSOR = 2, BQ_PATH_MMA = 3 };
+
+/* ---- library state ------------------------------------------------------------------ */
+int bq_init(int device);                 /* select device, create context-wide state      */
+const char* bq_last_error(void);
+int bq_version(void);
+/* Reads and clears the device status word (0 = no anomaly; else a BQ_ERR_* code that a
+ * kernel recorded, e.g. BQ_ERR_TIMEOUT from a bounded mbarrier wait).  Synchronises.     */
+int bq_status_poll(void);
+
+/* ---- packed weights (spec: "packed quantized weights ... int8 or 4-bit codes in groups
+ *      of 32 with an fp16 scale per group"; "weight packer/loader layout on device") ---- */
+/* codes/scales are HOST pointers in the interface layout, borrowed for the call only.    */
+int bq_weight_create(const void* codes, const void* scales_f16, int64_t N, int64_t K,
+                     int fmt, bq_weight_t* out);
+/* Same, from DEVICE pointers (device-to-device copy; used for large synthetic weights).  */
+int bq_weight_create_device(const void* d_codes, const void* d_scales_f16, int64_t N,
+                            int64_t K, int fmt, void* stream, bq_weight_t* out);
+int bq_weight_destroy(bq_weight_t w);
+int bq_weight_info(bq_weight_t w, int64_t* N, int64_t* K, int* fmt);
+/* Copies the weight back to HOST memory in the interface layout (undoes any device-side
+ * re-tiling; used to show the device layout is a pure permutation).                      */
+int bq_weight_export(bq_weight_t w, void* codes_out, void* scales_f16_out);
+
+/* ---- dequantize (spec: "bit-exact for code unpacking and dequantized weight values") -- */
+/* out: device [N,K] of out_dtype.  F32 is exact; BF16 is round-to-nearest-even of it.    */
+int bq_dequant(bq_weight_t w, void* out, int out_dtype, void* stream);
+/* out: device int8[N,K] — the unpacked integer codes.                                    */
+int bq_unpack_codes(bq_weight_t w, void* out_i8, void* stream);
+
+/* ---- quantized linear / lm_head (spec: "multiplied against bf16/fp32 activations for
+ *      every linear, MoE-expert and lm_head projection", fp32 accumulate) --------------- */
+/* y[M,N] = x[M,K] . W^T.  x, y: device pointers. x_dtype/y_dtype in {F32,BF16}.          */
+int bq_qlinear(bq_weight_t w, const void* x, int x_dtype, int64_t M, void* y, int y_dtype,
+               void* stream);
+int bq_qlinear_ex(bq_weight_t w, const void* x, int x_dtype, int64_t M, void* y,
+                  int y_dtype, int path, void* stream);
+/* Same with HOST buffers: copies x in, runs, copies y out, synchronises.                 */
+int bq_qlinear_host(bq_weight_t w, const void* x_host, int x_dtype, int64_t M,
+                    void* y_host, int y_dtype);
+/* lm_head + greedy argmax: logits may be NULL (then only argmax is produced).
+ * argmax_out: device int32[M]; ties resolve to the lower vocabulary index.               */
+int bq_lm_head(bq_weight_t w, const void* x, int x_dtype, int64_t M, void* logits,
+               int logits_dtype, int32_t* argmax_out, void* stream);
+/* which kernel family the last bq_qlinear* call on this thread launched (BQ_PATH_*) and
+ * how many kernels it launched                                                            */
+int bq_last_path(void);
+int64_t bq_launch_count(void);           /* kernels launched by this library so far       */
+
+/* ---- MoE (spec: "router top-k, a token permute/gather, a grouped quantized expert GEMM
+ *      and a weighted scatter-combine") ------------------------------------------------- */
+/* softmax over E router logits (device f32[T,E]) -> top-k ids (int32[T,k], descending
+ * probability, ties to the lower expert id) and weights f32[T,k]: the softmax probabilities,
+ * rescaled to sum to 1 over the k selected experts when renormalise != 0.
+ * Limits: E <= 1024, top_k <= 32.                                                        */
+int bq_moe_route(const float* logits, int64_t T, int E, int top_k, int renormalise,
+                 int32_t* idx_out, float* w_out, void* stream);
+/* Stable counting sort of the T*k assignments by expert.  perm int32[T*k]: sorted position
+ * p holds flat assignment t*k+slot; inv int32[T*k] (may be NULL): inv[t*k+slot] = p;
+ * offsets int32[E+1]: expert e owns positions offsets[e]..offsets[e+1].
+ * scratch: device memory of >= bq_moe_permute_scratch_bytes(T,k,E) bytes (per-chunk
+ * histograms); contents need not be initialised.  All pointers are device pointers.      */
+int64_t bq_moe_permute_scratch_bytes(int64_t T, int top_k, int E);
+int bq_moe_permute(const int32_t* idx, int64_t T, int top_k, int E, int32_t* perm,
+                   int32_t* inv, int32_t* offsets, void* scratch, void* stream);
+/* xp[p,:] = x[perm[p] / k, :]  (rows of H elements of `dtype`)                           */
+int bq_moe_gather(const void* x, int dtype, int64_t H, const int32_t* perm, int64_t P,
+                  int top_k, void* xp, void* stream);
+/* Expert weight set: E experts, each gate[F,H], up[F,H], down[H,F]; arrays of E handles.
+ * The set takes ownership of nothing: the handles must outlive it.                       */
+int bq_moe_create(const bq_weight_t* gate, const bq_weight_t* up, const bq_weight_t* down,
+                  int E, bq_moe_t* out);
+int bq_moe_destroy(bq_moe_t m);
+/* Grouped SwiGLU FFN over the permuted rows: for expert e and rows offsets[e]..offsets[e+1]
+ *   h = silu(xp . gate_e^T) * (xp . up_e^T)  (rounded to bf16),  out = h . down_e^T.
+ * xp: device bf16[P,H]; out: device f32[P,H]; hbuf: device bf16[P,F] workspace.
+ * offsets: DEVICE int32[E+1] (read by the kernel; no host sync).                          */
+int bq_moe_experts(bq_moe_t m, const void* xp_bf16, const int32_t* offsets, int64_t P,
+                   void* hbuf_bf16, float* out, int path, void* stream);
+/* y[t,:] = sum_{slot=0..k-1} w[t,slot] * out[inv[t*k+slot], :] in slot order (deterministic,
+ * no atomics).  inv as produced by bq_moe_permute.  y dtype F32 or BF16.                 */
+int bq_moe_combine(const float* out, const int32_t* inv, const float* w, int64_t T,
+                   int top_k, int64_t H, void* y, int y_dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200Q_H */
