@@ -110,9 +110,9 @@ static bool dt_ok(int dt) { return dt == BQ_DT_F32 || dt == BQ_DT_BF16; }
 
 // Kernel-family choice.  SIMT = exact fp32 CUDA-core GEMV (M small or fp32 activations);
 // TENSOR = tcgen05 path (bf16 activations).
-static int choose_path(const Weight* w, int x_dtype, int64_t M, int requested) {
+static int choose_path(const Weight* w, const void* x, int x_dtype, int64_t M, int requested) {
   if (requested == BQ_PATH_SIMT) return BQ_PATH_SIMT;
-  const bool tc_ok = tc_supported(w->fmt, w->N, w->K, x_dtype, M);
+  const bool tc_ok = tc_supported(w->fmt, w->N, w->K, x_dtype, M) && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
   if (requested == BQ_PATH_TENSOR) return tc_ok ? BQ_PATH_TENSOR : -1;
   if (requested != BQ_PATH_AUTO) return -1;
   if (tc_ok && M >= 2) return BQ_PATH_TENSOR;
@@ -125,7 +125,7 @@ static int qlinear_impl(Weight* w, const void* x, int x_dtype, int64_t M, void* 
   if (M < 0) return fail(BQ_ERR_ARG, "M must be >= 0");
   if (M == 0 || w->N == 0) { set_last_path(BQ_PATH_AUTO); return BQ_OK; }
   if (!x || !y) return fail(BQ_ERR_ARG, "x and y must not be null");
-  const int p = choose_path(w, x_dtype, M, path);
+  const int p = choose_path(w, x, x_dtype, M, path);
   if (p < 0) return fail(BQ_ERR_UNSUPPORTED, "requested kernel path does not support this shape/dtype");
   set_last_path(p);
   if (p == BQ_PATH_TENSOR)
@@ -191,6 +191,11 @@ int bq_weight_create(const void* codes, const void* scales, int64_t N, int64_t K
     cudaFree(w->codes); cudaFree(w->scales); delete w;
     return fail_cuda(e, "cudaMemcpy(weight upload)");
   }
+  if (fmt == BQ_FMT_Q4G32) {
+    rc = launch_q4_repack(w->codes, w->codes_bytes, true, 0);
+    if (rc == BQ_OK && cudaStreamSynchronize(0) != cudaSuccess) rc = fail(BQ_ERR_CUDA, "repack failed");
+    if (rc) { cudaFree(w->codes); cudaFree(w->scales); delete w; return rc; }
+  }
   *out = publish(w);
   return BQ_OK;
 }
@@ -209,6 +214,8 @@ int bq_weight_create_device(const void* d_codes, const void* d_scales, int64_t N
   if (w->codes_bytes) e = cudaMemcpyAsync(w->codes, d_codes, w->codes_bytes, cudaMemcpyDeviceToDevice, s);
   if (e == cudaSuccess && w->scales_bytes)
     e = cudaMemcpyAsync(w->scales, d_scales, w->scales_bytes, cudaMemcpyDeviceToDevice, s);
+  if (e == cudaSuccess && fmt == BQ_FMT_Q4G32 && launch_q4_repack(w->codes, w->codes_bytes, true, s) != BQ_OK)
+    e = cudaErrorUnknown;
   if (e == cudaSuccess) e = cudaStreamSynchronize(s);
   if (e != cudaSuccess) {
     cudaFree(w->codes); cudaFree(w->scales); delete w;
@@ -248,6 +255,15 @@ int bq_weight_export(bq_weight_t h, void* codes_out, void* scales_out) {
   if (!w) return BQ_ERR_HANDLE;
   if (w->N > 0 && (!codes_out || !scales_out)) return fail(BQ_ERR_ARG, "output pointers must not be null");
   if (w->codes_bytes) BQ_CUDA(cudaMemcpy(codes_out, w->codes, w->codes_bytes, cudaMemcpyDeviceToHost));
+  if (w->fmt == BQ_FMT_Q4G32) {   // undo the device nibble order (a pure permutation inside each 32-bit word)
+    uint32_t* p = static_cast<uint32_t*>(codes_out);
+    for (size_t i = 0; i < w->codes_bytes / 4; ++i) {
+      const uint32_t v = p[i];
+      uint32_t o = 0;
+      for (int j = 0; j < 8; ++j) o |= ((v >> (4 * j)) & 0xFu) << (4 * q4_elem(j));
+      p[i] = o;
+    }
+  }
   if (w->scales_bytes) BQ_CUDA(cudaMemcpy(scales_out, w->scales, w->scales_bytes, cudaMemcpyDeviceToHost));
   return BQ_OK;
 }
@@ -361,6 +377,8 @@ int bq_moe_create(const bq_weight_t* gate, const bq_weight_t* up, const bq_weigh
     BQ_CUDA(cudaMemcpy((void*)*cdst[i], pc[i].data(), sizeof(void*) * E, cudaMemcpyHostToDevice));
     BQ_CUDA(cudaMemcpy((void*)*sdst[i], ps[i].data(), sizeof(void*) * E, cudaMemcpyHostToDevice));
   }
+  m->tc_state = nullptr;
+  if (int rc2 = moe_tc_prepare(m, pc, ps)) return rc2;
   {
     std::lock_guard<std::mutex> lk(g_mu);
     g_moes.insert(m);
@@ -377,6 +395,7 @@ int bq_moe_destroy(bq_moe_t h) {
     g_moes.erase(m);
   }
   m->magic = 0;
+  moe_tc_release(m);
   cudaFree((void*)m->gate_codes); cudaFree((void*)m->gate_scales);
   cudaFree((void*)m->up_codes);   cudaFree((void*)m->up_scales);
   cudaFree((void*)m->down_codes); cudaFree((void*)m->down_scales);

@@ -5,6 +5,7 @@
 #include <cuda_bf16.h>
 #include <stdint.h>
 #include <string>
+#include <vector>
 
 #include "../../include/b200q.h"
 
@@ -36,6 +37,7 @@ struct Moe {
   const uint8_t** gate_codes; const __half** gate_scales;
   const uint8_t** up_codes;   const __half** up_scales;
   const uint8_t** down_codes; const __half** down_scales;
+  void* tc_state;        // tensor-core path: per-expert TMA descriptors + tile list (tc.cu)
 };
 constexpr uint32_t MOE_MAGIC = 0xB2003E00u;
 
@@ -68,6 +70,15 @@ int launch_qlinear_tc(const uint8_t* codes, const __half* scales, int fmt, int64
                       const void* x, int x_dtype, int64_t M, void* y, int y_dtype, int64_t ldy,
                       cudaStream_t s);
 bool tc_supported(int fmt, int64_t N, int64_t K, int x_dtype, int64_t M);
+bool moe_tc_supported(const Moe* m);
+int moe_tc_prepare(Moe* m, const std::vector<const uint8_t*>* codes, const std::vector<const __half*>* scales);
+void moe_tc_release(Moe* m);
+int launch_moe_experts_tc(const Moe* m, const void* xp, const int32_t* offsets, int64_t P, void* hbuf, float* out,
+                          cudaStream_t s);
+// Q4 device layout: within every 32-bit word the 8 nibbles are stored in the order
+// e0,e2,e4,e6,e1,e3,e5,e7 (element e_i of the interface layout), so that masking with 0x000F000F /
+// 0x00F000F0 yields adjacent element pairs.  A pure permutation; repack is its own inverse pair.
+int launch_q4_repack(uint8_t* codes, size_t bytes, bool to_device_layout, cudaStream_t s);
 int launch_argmax(const void* logits, int dtype, int64_t M, int64_t N, int32_t* out, cudaStream_t s);
 
 // ---- device helpers --------------------------------------------------------------------------
@@ -105,7 +116,8 @@ template <int I> __device__ __forceinline__ float q8_byte_to_float(uint32_t v_xo
   constexpr uint32_t sel = 0x7650u | (uint32_t)I;
   return __uint_as_float(__byte_perm(v_xor80, 0x4B000000u, sel)) - 8388736.0f;
 }
-// Q4: nibble `I` of the word is element I of the 8 it holds; stored value is code + 8.
+// Q4 (device layout): nibble `I` of the word holds element q4_elem(I) of the 8; stored value is code + 8.
+__host__ __device__ constexpr int q4_elem(int nib) { return nib < 4 ? 2 * nib : 2 * (nib - 4) + 1; }
 template <int I> __device__ __forceinline__ float q4_nibble_to_float(uint32_t v) {
   uint32_t m = lop3_and_or(I == 0 ? v : (v >> (4 * I)), 0xFu, 0x4B000000u);
   return __uint_as_float(m) - 8388616.0f;

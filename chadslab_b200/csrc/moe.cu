@@ -211,10 +211,10 @@ template <> struct WordDotM<BQ_FMT_Q8G32> {
 template <> struct WordDotM<BQ_FMT_Q4G32> {
   static constexpr int WPW = 8;
   __device__ static __forceinline__ void cvt(uint32_t v, float* f) {
-    f[0] = q4_nibble_to_float<0>(v); f[1] = q4_nibble_to_float<1>(v);
-    f[2] = q4_nibble_to_float<2>(v); f[3] = q4_nibble_to_float<3>(v);
-    f[4] = q4_nibble_to_float<4>(v); f[5] = q4_nibble_to_float<5>(v);
-    f[6] = q4_nibble_to_float<6>(v); f[7] = q4_nibble_to_float<7>(v);
+    f[q4_elem(0)] = q4_nibble_to_float<0>(v); f[q4_elem(1)] = q4_nibble_to_float<1>(v);
+    f[q4_elem(2)] = q4_nibble_to_float<2>(v); f[q4_elem(3)] = q4_nibble_to_float<3>(v);
+    f[q4_elem(4)] = q4_nibble_to_float<4>(v); f[q4_elem(5)] = q4_nibble_to_float<5>(v);
+    f[q4_elem(6)] = q4_nibble_to_float<6>(v); f[q4_elem(7)] = q4_nibble_to_float<7>(v);
   }
 };
 
@@ -338,9 +338,6 @@ static int moe_ffn_simt(const Moe* m, bool gated, const void* x, const int32_t* 
   return BQ_OK;
 }
 
-int launch_moe_experts_tc(const Moe* m, const void* xp, const int32_t* offsets, int64_t P, void* hbuf,
-                          float* out, cudaStream_t s);
-bool moe_tc_supported(const Moe* m);
 
 }  // namespace bq
 
@@ -433,7 +430,7 @@ int bq_moe_experts(bq_moe_t h, const void* xp_bf16, const int32_t* offsets, int6
   if (P == 0) return BQ_OK;
   if (!xp_bf16 || !offsets || !hbuf_bf16 || !out) return fail(BQ_ERR_ARG, "null pointer");
   cudaStream_t s = (cudaStream_t)stream;
-  const bool tc_ok = moe_tc_supported(m);
+  const bool tc_ok = m->tc_state != nullptr;
   if (path == BQ_PATH_TENSOR && !tc_ok) return fail(BQ_ERR_UNSUPPORTED, "tensor path unavailable for this expert shape");
   if ((path == BQ_PATH_AUTO && tc_ok) || path == BQ_PATH_TENSOR) {
     set_last_path(BQ_PATH_TENSOR);

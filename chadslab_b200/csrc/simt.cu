@@ -41,31 +41,47 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict_
         o[4 * q + 3] = from_float<OT>(q8_byte_to_float<3>(v) * s);
       } else {
         const uint32_t v = words[q];
-        o[8 * q + 0] = from_float<OT>(q4_nibble_to_float<0>(v) * s);
-        o[8 * q + 1] = from_float<OT>(q4_nibble_to_float<1>(v) * s);
-        o[8 * q + 2] = from_float<OT>(q4_nibble_to_float<2>(v) * s);
-        o[8 * q + 3] = from_float<OT>(q4_nibble_to_float<3>(v) * s);
-        o[8 * q + 4] = from_float<OT>(q4_nibble_to_float<4>(v) * s);
-        o[8 * q + 5] = from_float<OT>(q4_nibble_to_float<5>(v) * s);
-        o[8 * q + 6] = from_float<OT>(q4_nibble_to_float<6>(v) * s);
-        o[8 * q + 7] = from_float<OT>(q4_nibble_to_float<7>(v) * s);
+        o[8 * q + q4_elem(0)] = from_float<OT>(q4_nibble_to_float<0>(v) * s);
+        o[8 * q + q4_elem(1)] = from_float<OT>(q4_nibble_to_float<1>(v) * s);
+        o[8 * q + q4_elem(2)] = from_float<OT>(q4_nibble_to_float<2>(v) * s);
+        o[8 * q + q4_elem(3)] = from_float<OT>(q4_nibble_to_float<3>(v) * s);
+        o[8 * q + q4_elem(4)] = from_float<OT>(q4_nibble_to_float<4>(v) * s);
+        o[8 * q + q4_elem(5)] = from_float<OT>(q4_nibble_to_float<5>(v) * s);
+        o[8 * q + q4_elem(6)] = from_float<OT>(q4_nibble_to_float<6>(v) * s);
+        o[8 * q + q4_elem(7)] = from_float<OT>(q4_nibble_to_float<7>(v) * s);
       }
     }
   }
 }
 
+// one thread per 32-bit word of codes (row sizes are multiples of 16 bytes)
 template <int FMT>
 __global__ void __launch_bounds__(256) unpack_kernel(const uint8_t* __restrict__ codes,
                                                      int8_t* __restrict__ out, int64_t total_bytes) {
-  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total_bytes;
+  const int64_t words = total_bytes / 4;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < words;
        i += (int64_t)gridDim.x * blockDim.x) {
-    const uint8_t b = codes[i];
+    const uint32_t v = reinterpret_cast<const uint32_t*>(codes)[i];
     if (FMT == BQ_FMT_Q8G32) {
-      out[i] = (int8_t)b;
+      reinterpret_cast<uint32_t*>(out)[i] = v;
     } else {
-      out[2 * i] = (int8_t)((int)(b & 0xF) - 8);
-      out[2 * i + 1] = (int8_t)((int)(b >> 4) - 8);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) out[8 * i + q4_elem(j)] = (int8_t)((int)((v >> (4 * j)) & 0xF) - 8);
     }
+  }
+}
+
+// interface nibble order <-> device nibble order, in place, one thread per word
+__global__ void __launch_bounds__(256) q4_repack_kernel(uint32_t* __restrict__ words, int64_t n, int to_device) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const uint32_t v = words[i];
+    uint32_t o = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (to_device) o |= ((v >> (4 * q4_elem(j))) & 0xFu) << (4 * j);   // device nibble j <- element q4_elem(j)
+      else           o |= ((v >> (4 * j)) & 0xFu) << (4 * q4_elem(j));
+    }
+    words[i] = o;
   }
 }
 
@@ -98,10 +114,19 @@ int launch_dequant(const Weight* w, void* out, int out_dtype, cudaStream_t s) {
   return BQ_OK;
 }
 
+int launch_q4_repack(uint8_t* codes, size_t bytes, bool to_device_layout, cudaStream_t s) {
+  if (bytes == 0) return BQ_OK;
+  const int64_t n = (int64_t)(bytes / 4);
+  q4_repack_kernel<<<grid_for(n, 256), 256, 0, s>>>(reinterpret_cast<uint32_t*>(codes), n, to_device_layout ? 1 : 0);
+  count_launch();
+  BQ_CUDA(cudaGetLastError());
+  return BQ_OK;
+}
+
 int launch_unpack(const Weight* w, int8_t* out, cudaStream_t s) {
   const int64_t bytes = (int64_t)w->codes_bytes;
   if (bytes == 0) return BQ_OK;
-  const int grid = grid_for(bytes, 256);
+  const int grid = grid_for(bytes / 4, 256);
   if (w->fmt == BQ_FMT_Q8G32)
     unpack_kernel<BQ_FMT_Q8G32><<<grid, 256, 0, s>>>(w->codes, out, bytes);
   else
@@ -132,14 +157,14 @@ template <> struct WordDot<BQ_FMT_Q8G32> {
 template <> struct WordDot<BQ_FMT_Q4G32> {
   static constexpr int WPW = 8;
   __device__ static __forceinline__ float run(uint32_t v, const float* xv, float acc) {
-    acc = fmaf(q4_nibble_to_float<0>(v), xv[0], acc);
-    acc = fmaf(q4_nibble_to_float<1>(v), xv[1], acc);
-    acc = fmaf(q4_nibble_to_float<2>(v), xv[2], acc);
-    acc = fmaf(q4_nibble_to_float<3>(v), xv[3], acc);
-    acc = fmaf(q4_nibble_to_float<4>(v), xv[4], acc);
-    acc = fmaf(q4_nibble_to_float<5>(v), xv[5], acc);
-    acc = fmaf(q4_nibble_to_float<6>(v), xv[6], acc);
-    acc = fmaf(q4_nibble_to_float<7>(v), xv[7], acc);
+    acc = fmaf(q4_nibble_to_float<0>(v), xv[q4_elem(0)], acc);
+    acc = fmaf(q4_nibble_to_float<1>(v), xv[q4_elem(1)], acc);
+    acc = fmaf(q4_nibble_to_float<2>(v), xv[q4_elem(2)], acc);
+    acc = fmaf(q4_nibble_to_float<3>(v), xv[q4_elem(3)], acc);
+    acc = fmaf(q4_nibble_to_float<4>(v), xv[q4_elem(4)], acc);
+    acc = fmaf(q4_nibble_to_float<5>(v), xv[q4_elem(5)], acc);
+    acc = fmaf(q4_nibble_to_float<6>(v), xv[q4_elem(6)], acc);
+    acc = fmaf(q4_nibble_to_float<7>(v), xv[q4_elem(7)], acc);
     return acc;
   }
 };

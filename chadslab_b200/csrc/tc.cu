@@ -1,11 +1,685 @@
-// placeholder until the tcgen05 kernels land
+// Tensor-core path (sm_100a): dequantize-to-fp16 shared-memory tiles feeding tcgen05.mma with the
+// accumulator in tensor memory.
+//
+// Formulation ("swap-AB"): D[n, m] = sum_k W[n, k] * x[m, k].  The 128 weight rows of a tile are the
+// MMA M dimension, the batch (activation rows) is the MMA N dimension (BN = 16..256), so decode-sized
+// batches waste no tensor work on padding weight rows and the accumulator lane == output column n.
+//
+// Per CTA (one 128 x BN output tile, 320 threads):
+//   warp 0      producer : TMA (cp.async.bulk.tensor.2d) of packed codes [128 x 64k], activations
+//                          [BN x 64k, 128-byte swizzle = the UMMA K-major layout] and, every 4th
+//                          k-step, the fp16 scales [128 x 8 groups] into a ring of stages
+//   warps 2..9  converter: packed codes + scale -> fp16 = code * scale (exact product rounded once to
+//                          fp16), written into a 128-byte-swizzled K-major A tile; later the epilogue
+//   warp 1      issuer   : one thread issues 4 x tcgen05.mma (K = 16 each, kind::f16, A = B = fp16,
+//                          D = fp32 in TMEM) per k-step and commits to the "free" barriers
+//   epilogue             : tcgen05.ld of the 128 x BN fp32 tile, coalesced stores of y[m, n]
+// Every mbarrier wait is bounded; on expiry a status word is set and all roles drain and exit.
+//
+// Activations reach the tensor core as fp16: a pre-pass kernel scales every activation row by a power
+// of two that puts its largest magnitude in [2^14, 2^15) and rounds to fp16 (exact for bf16 inputs
+// down to 2^-29 of the row maximum); the epilogue multiplies the row back.  Both MMA operands then
+// have the same type.
+//
+// GATED variant (MoE experts / SwiGLU): two weight matrices share the activation tile, two
+// accumulators, epilogue writes silu(g) * u as bf16.
+#include <cuda.h>
+
 #include "common.cuh"
+
 namespace bq {
-bool tc_supported(int, int64_t, int64_t, int, int64_t) { return false; }
-int launch_qlinear_tc(const uint8_t*, const __half*, int, int64_t, int64_t, const void*, int, int64_t, void*, int,
-                      int64_t, cudaStream_t) { return fail(BQ_ERR_UNSUPPORTED, "tensor path not built"); }
-bool moe_tc_supported(const Moe*) { return false; }
-int launch_moe_experts_tc(const Moe*, const void*, const int32_t*, int64_t, void*, float*, cudaStream_t) {
-  return fail(BQ_ERR_UNSUPPORTED, "tensor path not built");
+
+constexpr int TC_ROWS = 128;        // weight rows per tile (UMMA M)
+constexpr int TC_BK = 64;           // k per pipeline step (one 128-byte swizzle row of 16-bit data)
+constexpr int TC_CONV_THREADS = 256;   // 8 converter warps
+constexpr int TC_THREADS = 64 + TC_CONV_THREADS;
+constexpr int TC_SC_SLOTS = 3;      // scale tiles in flight (each covers 4 k-steps)
+constexpr uint32_t TC_WAIT_LIMIT = 1u << 21;
+
+// ---- PTX wrappers -----------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false if the wait expired or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t it = 0; it < TC_WAIT_LIMIT; ++it) {
+    if (mbar_test(bar, parity)) return true;
+    if (it > 32) {
+      __nanosleep(40);
+      if (*abort_flag) return false;
+    }
+  }
+  *abort_flag = 1;
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(tmap), "r"(c0), "r"(c1), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major, 128-byte-swizzled shared-memory matrix descriptor: rows of 128 bytes, 8-row groups 1024
+// bytes apart; tile base 1024-byte aligned.  Advancing K by 16 elements = +32 bytes on the address.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);       // start address
+  d |= (uint64_t)1 << 16;                          // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset: 8 rows * 128 B
+  d |= (uint64_t)1 << 46;                          // descriptor version (sm_100)
+  d |= (uint64_t)2 << 61;                          // SWIZZLE_128B
+  return d;
+}
+// kind::f16 instruction descriptor: D = f32, A = B = f16, both K-major, M = 128, N = BN.
+__host__ __device__ constexpr uint32_t umma_idesc(int bn) {
+  return (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(TC_ROWS >> 4) << 24);
+}
+
+// ---- shared-memory plan -------------------------------------------------------------------------
+template <int FMT, int BN, bool GATED> struct TcPlan {
+  static constexpr int NW = GATED ? 2 : 1;
+  static constexpr int RAW_ROW = (FMT == BQ_FMT_Q8G32) ? 64 : 32;       // code bytes per row per k-step
+  static constexpr int RAW = TC_ROWS * RAW_ROW;                           // per weight
+  static constexpr int XT = BN * 128;                                     // activation tile bytes
+  static constexpr int AT = TC_ROWS * 128;                                // fp16 A tile bytes (16 KB)
+  static constexpr int SCT = TC_ROWS * 16;                                // scale tile: 8 fp16 per row
+  static constexpr int STAGE = ((NW * RAW + XT + 1023) / 1024) * 1024;
+  static constexpr int NA = (BN >= 128) ? 3 : 2;                          // A-tile ring
+  static constexpr int BUDGET = (BN >= 128 ? 200 : 100) * 1024;           // 1 or 2 CTAs per SM
+  static constexpr int FIXED = NA * NW * AT + TC_SC_SLOTS * NW * SCT + 1024 /*barriers*/ + 1024 /*align*/;
+  static constexpr int S_RAW = (BUDGET - FIXED) / STAGE;
+  static constexpr int S = S_RAW > 8 ? 8 : (S_RAW < 2 ? 2 : S_RAW);       // S <= 4*SC_SLOTS - 3 = 9
+  static constexpr int SMEM = FIXED + S * STAGE;
+  static constexpr int TMEM_COLS = (NW * BN <= 32) ? 32 : (NW * BN <= 64) ? 64 : (NW * BN <= 128) ? 128
+                                   : (NW * BN <= 256) ? 256 : 512;
+  static_assert(NW * BN <= 512, "accumulators exceed tensor memory");
+  static_assert(SMEM <= 227 * 1024, "shared memory plan too large");
+};
+
+struct TcArgs {
+  CUtensorMap tm_x;                  // pre-scaled activations [M or P, K] fp16, box 64 x BN, 128B swizzle
+  const float* xscale;               // per activation row: the power of two to multiply the result by
+  CUtensorMap tm_w[2];               // dense: codes of weight 0 / 1 (GATED), box RAW_ROW x 128
+  CUtensorMap tm_s[2];               // dense: scales fp16 [N, K/32], box 8 x 128
+  const CUtensorMap* tm_list;        // MoE: per expert {codes0, scales0, codes1, scales1}
+  const int32_t* offsets;            // MoE: expert row ranges
+  const int32_t* tiles;              // MoE: tiles[0] = count, then (expert, m0) pairs
+  void* out;                         // dense: y [M, ldy];  GATED: bf16 h [P, N];  MoE plain: f32 [P, N]
+  int64_t ldy;
+  int64_t N, K, M;
+  int out_dtype;
+  int moe;
+  int* status;
+};
+
+// ---- converters: 16 bytes of codes -> fp16 (code * scale) -------------------------------------------
+// Q8: 16 codes -> two 16-byte pieces of the A row.
+__device__ __forceinline__ void cvt_q8_chunk(const uint4 w, const __half2 s2, uint4& lo, uint4& hi) {
+  const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+  uint32_t o[8];
+  const __half2 off = __float2half2_rn(1152.0f);   // 1024 (magic) + 128 (sign offset)
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const uint32_t v = words[q] ^ 0x80808080u;
+    uint32_t p0 = __byte_perm(v, 0x64646464u, 0x4140);   // (1024 + b0, 1024 + b1) as fp16x2
+    uint32_t p1 = __byte_perm(v, 0x64646464u, 0x4342);   // (1024 + b2, 1024 + b3)
+    __half2 h0 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&p0), off), s2);
+    __half2 h1 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&p1), off), s2);
+    o[2 * q] = *reinterpret_cast<uint32_t*>(&h0);
+    o[2 * q + 1] = *reinterpret_cast<uint32_t*>(&h1);
+  }
+  lo = make_uint4(o[0], o[1], o[2], o[3]);
+  hi = make_uint4(o[4], o[5], o[6], o[7]);
+}
+// Q4: one 32-bit word in the device nibble order (e0,e2,e4,e6,e1,e3,e5,e7) -> 8 fp16 in element
+// order.  Masks 0x000F000F / 0x00F000F0 pick the adjacent element pairs (e0,e1) / (e2,e3) straight
+// into fp16 mantissas (1024 + n, resp. 1024 + 16 n); one shift serves the upper half of the word.
+__device__ __forceinline__ uint4 cvt_q4_word(const uint32_t v, const __half2 s2) {
+  const __half2 off = __float2half2_rn(1032.0f);       // 1024 (magic) + 8 (zero point)
+  const __half2 sixteenth = __float2half2_rn(0.0625f);
+  const __half2 off16 = __float2half2_rn(-72.0f);      // -(1024/16 + 8)
+  const uint32_t v8 = v >> 8;
+  uint32_t t0 = lop3_and_or(v, 0x000F000Fu, 0x64006400u);    // 1024 + (e0, e1)
+  uint32_t t1 = lop3_and_or(v, 0x00F000F0u, 0x64006400u);    // 1024 + 16 * (e2, e3)
+  uint32_t t2 = lop3_and_or(v8, 0x000F000Fu, 0x64006400u);   // 1024 + (e4, e5)
+  uint32_t t3 = lop3_and_or(v8, 0x00F000F0u, 0x64006400u);   // 1024 + 16 * (e6, e7)
+  __half2 h01 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&t0), off), s2);
+  __half2 h23 = __hmul2(__hfma2(*reinterpret_cast<__half2*>(&t1), sixteenth, off16), s2);
+  __half2 h45 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&t2), off), s2);
+  __half2 h67 = __hmul2(__hfma2(*reinterpret_cast<__half2*>(&t3), sixteenth, off16), s2);
+  return make_uint4(*reinterpret_cast<uint32_t*>(&h01), *reinterpret_cast<uint32_t*>(&h23),
+                    *reinterpret_cast<uint32_t*>(&h45), *reinterpret_cast<uint32_t*>(&h67));
+}
+
+// ---- the kernel ----------------------------------------------------------------------------------------
+template <int FMT, int BN, bool GATED>
+__global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_constant__ TcArgs args) {
+  using P = TcPlan<FMT, BN, GATED>;
+  constexpr int NW = P::NW, S = P::S, NA = P::NA;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  // layout: [A tiles NA*NW*16K][stages S*STAGE][scale tiles][barriers]
+  uint8_t* a_tiles = smem;
+  uint8_t* stages = a_tiles + NA * NW * P::AT;
+  uint8_t* sc_tiles = stages + S * P::STAGE;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sc_tiles + TC_SC_SLOTS * NW * P::SCT);
+  // barrier indices
+  uint64_t* full = bars;               // [S]   TMA landed (tx)
+  uint64_t* empty = bars + S;          // [S]   converters (128) + MMA commit (1)
+  uint64_t* a_full = bars + 2 * S;     // [NA]  converters (128)
+  uint64_t* a_empty = a_full + NA;     // [NA]  MMA commit (1)
+  uint64_t* acc_full = a_empty + NA;   // [1]
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(acc_full + 1);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // ---- which tile ------------------------------------------------------------------------------------
+  int64_t n0 = (int64_t)blockIdx.y * TC_ROWS;
+  int64_t m0, m_end;
+  const CUtensorMap *tmw0, *tms0, *tmw1, *tms1;
+  if (args.moe) {
+    const int ntiles = args.tiles[0];
+    if ((int)blockIdx.x >= ntiles) return;           // uniform across the CTA, before any barrier
+    const int e = args.tiles[1 + 2 * blockIdx.x];
+    m0 = args.tiles[2 + 2 * blockIdx.x];
+    m_end = args.offsets[e + 1];
+    const CUtensorMap* l = args.tm_list + (int64_t)e * 4;
+    tmw0 = l; tms0 = l + 1; tmw1 = l + 2; tms1 = l + 3;
+  } else {
+    m0 = (int64_t)blockIdx.x * BN;
+    m_end = args.M;
+    tmw0 = &args.tm_w[0]; tms0 = &args.tm_s[0]; tmw1 = &args.tm_w[1]; tms1 = &args.tm_s[1];
+  }
+  const int ksteps = (int)((args.K + TC_BK - 1) / TC_BK);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < S; ++i) { mbar_init(smem_u32(&full[i]), 1); mbar_init(smem_u32(&empty[i]), TC_CONV_THREADS + 1); }
+    for (int i = 0; i < NA; ++i) { mbar_init(smem_u32(&a_full[i]), TC_CONV_THREADS); mbar_init(smem_u32(&a_empty[i]), 1); }
+    mbar_init(smem_u32(acc_full), 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {   // TMEM allocation by one full warp
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"((uint32_t)P::TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ================= producer =================
+    if (lane == 0) {
+      for (int ks = 0; ks < ksteps; ++ks) {
+        const int s = ks % S;
+        const uint32_t ph = (uint32_t)(ks / S) & 1u;
+        if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1u, abort_flag)) break;
+        const bool with_scales = (ks & 3) == 0;
+        const uint32_t bytes = NW * P::RAW + P::XT + (with_scales ? NW * P::SCT : 0);
+        const uint32_t fb = smem_u32(&full[s]);
+        mbar_expect_tx(fb, bytes);
+        uint8_t* st = stages + s * P::STAGE;
+        tma_load_2d(smem_u32(st), &args.tm_x, ks * TC_BK, (int)m0, fb);
+        tma_load_2d(smem_u32(st + P::XT), tmw0, ks * P::RAW_ROW, (int)n0, fb);
+        if (GATED) tma_load_2d(smem_u32(st + P::XT + P::RAW), tmw1, ks * P::RAW_ROW, (int)n0, fb);
+        if (with_scales) {
+          uint8_t* sc = sc_tiles + ((ks >> 2) % TC_SC_SLOTS) * NW * P::SCT;
+          tma_load_2d(smem_u32(sc), tms0, (ks >> 2) * 8, (int)n0, fb);
+          if (GATED) tma_load_2d(smem_u32(sc + P::SCT), tms1, (ks >> 2) * 8, (int)n0, fb);
+        }
+      }
+      if (*abort_flag) {   // give copies already in flight time to land before the CTA exits
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ================= MMA issuer =================
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(BN);
+      bool ok = true;
+      for (int ks = 0; ks < ksteps && ok; ++ks) {
+        const int s = ks % S, a = ks % NA;
+        const uint32_t ph = (uint32_t)(ks / S) & 1u, aph = (uint32_t)(ks / NA) & 1u;
+        ok = mbar_wait(smem_u32(&full[s]), ph, abort_flag) && mbar_wait(smem_u32(&a_full[a]), aph, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint64_t bdesc = umma_desc_sw128(smem_u32(stages + s * P::STAGE));
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+          const uint64_t adesc = umma_desc_sw128(smem_u32(a_tiles + (a * NW + w) * P::AT));
+#pragma unroll
+          for (int kk = 0; kk < TC_BK / 16; ++kk)
+            tc_mma_f16(tmem_base + (uint32_t)(w * BN), adesc + (uint64_t)(2 * kk), bdesc + (uint64_t)(2 * kk), idesc,
+                       (ks > 0 || kk > 0) ? 1u : 0u);
+        }
+        tc_commit(smem_u32(&a_empty[a]));
+        tc_commit(smem_u32(&empty[s]));
+      }
+      if (ok) tc_commit(smem_u32(acc_full));
+    }
+  } else {
+    // ================= converters, then epilogue =================
+    const int t = threadIdx.x - 64;   // 0..TC_CONV_THREADS-1
+    bool ok = true;
+    for (int ks = 0; ks < ksteps && ok; ++ks) {
+      const int s = ks % S, a = ks % NA;
+      const uint32_t ph = (uint32_t)(ks / S) & 1u, aph = (uint32_t)(ks / NA) & 1u;
+      ok = mbar_wait(smem_u32(&full[s]), ph, abort_flag) && mbar_wait(smem_u32(&a_empty[a]), aph ^ 1u, abort_flag);
+      if (!ok) break;
+      const uint8_t* st = stages + s * P::STAGE + P::XT;
+      const uint8_t* sc = sc_tiles + ((ks >> 2) % TC_SC_SLOTS) * NW * P::SCT;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) {
+        const uint8_t* raw = st + w * P::RAW;
+        const __half* scw = reinterpret_cast<const __half*>(sc + w * P::SCT);
+        uint8_t* at = a_tiles + (a * NW + w) * P::AT;
+        if (FMT == BQ_FMT_Q8G32) {
+          // 512 pieces of 16 bytes: piece j -> row j>>2, 16-code column c = j&3 (group c>>1)
+#pragma unroll
+          for (int i = 0; i < 512 / TC_CONV_THREADS; ++i) {
+            const int j = t + TC_CONV_THREADS * i;
+            const int row = j >> 2, c = j & 3;
+            const uint4 wv = *reinterpret_cast<const uint4*>(raw + j * 16);
+            const __half sh = scw[row * 8 + (ks & 3) * 2 + (c >> 1)];
+            uint4 lo, hi;
+            cvt_q8_chunk(wv, __half2half2(sh), lo, hi);
+            uint8_t* rowp = at + row * 128;
+            *reinterpret_cast<uint4*>(rowp + (((2 * c) ^ (row & 7)) << 4)) = lo;
+            *reinterpret_cast<uint4*>(rowp + (((2 * c + 1) ^ (row & 7)) << 4)) = hi;
+          }
+        } else {
+          // 256 pieces of 16 bytes: piece j -> row j>>1, group c = j&1 (32 codes)
+#pragma unroll
+          for (int i = 0; i < 256 / TC_CONV_THREADS; ++i) {
+            const int j = t + TC_CONV_THREADS * i;
+            const int row = j >> 1, c = j & 1;
+            const uint4 wv = *reinterpret_cast<const uint4*>(raw + j * 16);
+            const __half2 s2 = __half2half2(scw[row * 8 + (ks & 3) * 2 + c]);
+            uint8_t* rowp = at + row * 128;
+            *reinterpret_cast<uint4*>(rowp + (((4 * c + 0) ^ (row & 7)) << 4)) = cvt_q4_word(wv.x, s2);
+            *reinterpret_cast<uint4*>(rowp + (((4 * c + 1) ^ (row & 7)) << 4)) = cvt_q4_word(wv.y, s2);
+            *reinterpret_cast<uint4*>(rowp + (((4 * c + 2) ^ (row & 7)) << 4)) = cvt_q4_word(wv.z, s2);
+            *reinterpret_cast<uint4*>(rowp + (((4 * c + 3) ^ (row & 7)) << 4)) = cvt_q4_word(wv.w, s2);
+          }
+        }
+      }
+      fence_async_smem();                       // generic-proxy writes -> visible to the tensor core
+      mbar_arrive(smem_u32(&a_full[a]));
+      mbar_arrive(smem_u32(&empty[s]));
+    }
+    // ---- epilogue: warp w reads TMEM lanes 32*(w%4) .. +31 = weight rows -------------------------------
+    if (ok) ok = mbar_wait(smem_u32(acc_full), 0u, abort_flag);
+    if (ok) {
+      tc_fence_after();
+      const int lg = warp & 3;                 // two warps share a lane group and alternate column chunks
+      const int half = (warp - 2) >> 2;
+      const int64_t n = n0 + lg * 32 + lane;
+      const uint32_t tbase = tmem_base + ((uint32_t)(lg * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 16 * half; c0 < BN; c0 += 32) {
+        if (m0 + c0 >= m_end) break;             // warp-uniform
+        uint32_t v[16], u[16];
+        tc_ld16(tbase + (uint32_t)c0, v);
+        if (GATED) tc_ld16(tbase + (uint32_t)(BN + c0), u);
+        tc_ld_wait();
+        if (n < args.N) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int64_t m = m0 + c0 + j;
+            if (m < m_end) {
+              const float rs = args.xscale[m];
+              const float f = __uint_as_float(v[j]) * rs;
+              if (GATED) {
+                const float h = f / (1.0f + __expf(-f)) * (__uint_as_float(u[j]) * rs);
+                reinterpret_cast<__nv_bfloat16*>(args.out)[m * args.ldy + n] = __float2bfloat16_rn(h);
+              } else if (args.out_dtype == BQ_DT_F32) {
+                reinterpret_cast<float*>(args.out)[m * args.ldy + n] = f;
+              } else {
+                reinterpret_cast<__nv_bfloat16*>(args.out)[m * args.ldy + n] = __float2bfloat16_rn(f);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ---- teardown ------------------------------------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(args.status, BQ_ERR_TIMEOUT);
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)P::TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// Activation pre-pass: one block per row.  scale_back[m] = 2^e with e = floor(log2(rowmax)) - 14, and
+// x16[m, k] = fp16(x[m, k] * 2^-e).  Rows that are all zero (or hold inf / nan) use e = 0.
+template <typename XT>
+__global__ void __launch_bounds__(256) x_prep_kernel(const XT* __restrict__ x, int64_t K, __half* __restrict__ x16,
+                                                     float* __restrict__ scale_back) {
+  const XT* row = x + (int64_t)blockIdx.x * K;
+  __half* orow = x16 + (int64_t)blockIdx.x * K;
+  float mx = 0.0f;
+  for (int64_t k = threadIdx.x; k < K; k += blockDim.x) mx = fmaxf(mx, fabsf(to_float<XT>(row[k])));
+  __shared__ float red[8];
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  mx = red[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) mx = fmaxf(mx, red[i]);
+  int e = 0;
+  if (mx > 0.0f && mx < INFINITY) e = (int)((__float_as_uint(mx) >> 23) & 0xFF) - 127 - 14;   // floor(log2) - 14
+  if (e < -100) e = -100;                                   // denormal row maxima: keep 2^-e finite
+  const float down = __uint_as_float((uint32_t)(127 - e) << 23);   // 2^-e
+  for (int64_t k = threadIdx.x; k < K; k += blockDim.x) orow[k] = __float2half_rn(to_float<XT>(row[k]) * down);
+  if (threadIdx.x == 0) scale_back[blockIdx.x] = __uint_as_float((uint32_t)(127 + e) << 23);
+}
+
+// library-owned scratch for the pre-scaled activations (grow-only; calls are serialised per process)
+static __half* g_x16 = nullptr; static size_t g_x16_elems = 0;
+static float* g_xs = nullptr;   static size_t g_xs_elems = 0;
+static int ensure_x_scratch(int64_t rows, int64_t K) {
+  const size_t need = (size_t)rows * K + 64;
+  if (need > g_x16_elems) {
+    if (g_x16) BQ_CUDA(cudaFree(g_x16));
+    g_x16 = nullptr; g_x16_elems = 0;
+    BQ_CUDA(cudaMalloc((void**)&g_x16, (need + need / 8) * sizeof(__half)));
+    g_x16_elems = need + need / 8;
+  }
+  if ((size_t)rows + 64 > g_xs_elems) {
+    if (g_xs) BQ_CUDA(cudaFree(g_xs));
+    g_xs = nullptr; g_xs_elems = 0;
+    BQ_CUDA(cudaMalloc((void**)&g_xs, ((size_t)rows * 2 + 64) * sizeof(float)));
+    g_xs_elems = (size_t)rows * 2 + 64;
+  }
+  return BQ_OK;
+}
+static int launch_x_prep(const void* x, int x_dtype, int64_t rows, int64_t K, cudaStream_t s) {
+  int rc = ensure_x_scratch(rows, K);
+  if (rc) return rc;
+  if (x_dtype == BQ_DT_BF16)
+    x_prep_kernel<__nv_bfloat16><<<(unsigned)rows, 256, 0, s>>>((const __nv_bfloat16*)x, K, g_x16, g_xs);
+  else
+    return fail(BQ_ERR_UNSUPPORTED, "tensor path takes bf16 activations");
+  count_launch();
+  BQ_CUDA(cudaGetLastError());
+  return BQ_OK;
+}
+
+// small kernel: MoE tile list from expert offsets.  tiles[0] = count, then (expert, m0) pairs.
+__global__ void __launch_bounds__(1024) moe_tile_list_kernel(const int32_t* __restrict__ offsets, int E, int bn,
+                                                             int32_t* __restrict__ tiles) {
+  __shared__ int32_t pre[1024];
+  const int e = threadIdx.x;
+  int32_t cnt = 0;
+  if (e < E) cnt = (offsets[e + 1] - offsets[e] + bn - 1) / bn;
+  pre[e] = cnt;
+  __syncthreads();
+  for (int off = 1; off < 1024; off <<= 1) {
+    const int32_t add = e >= off ? pre[e - off] : 0;
+    __syncthreads();
+    pre[e] += add;
+    __syncthreads();
+  }
+  if (e < E) {
+    const int32_t base = pre[e] - cnt;
+    const int32_t a = offsets[e];
+    for (int i = 0; i < cnt; ++i) {
+      tiles[1 + 2 * (base + i)] = e;
+      tiles[2 + 2 * (base + i)] = a + i * bn;
+    }
+  }
+  if (e == E - 1) tiles[0] = pre[e];
+}
+
+// ---- host side --------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+static int make_map_2d(CUtensorMap* tm, CUtensorMapDataType dt, int elem_bytes, const void* base, uint64_t inner,
+                       uint64_t outer, uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer,
+                       CUtensorMapSwizzle sw) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(BQ_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  (void)elem_bytes;
+  CUresult r = fn(tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(BQ_ERR_CUDA, "cuTensorMapEncodeTiled failed (code " + std::to_string((int)r) + ")");
+  return BQ_OK;
+}
+
+int tc_weight_maps(const uint8_t* codes, const __half* scales, int fmt, int64_t N, int64_t K, CUtensorMap* tm_codes,
+                   CUtensorMap* tm_scales) {
+  const uint64_t rb = fmt == BQ_FMT_Q8G32 ? K : K / 2;
+  int rc = make_map_2d(tm_codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, codes, rb, (uint64_t)N, rb,
+                       fmt == BQ_FMT_Q8G32 ? 64 : 32, TC_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (rc) return rc;
+  return make_map_2d(tm_scales, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, scales, (uint64_t)(K / GROUP), (uint64_t)N,
+                     (uint64_t)(K / GROUP) * 2, 8, TC_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
+}
+
+static int x_map(CUtensorMap* tm, const void* x, int64_t rows, int64_t K, int bn) {
+  return make_map_2d(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x, (uint64_t)K, (uint64_t)rows, (uint64_t)K * 2, 64,
+                     (uint32_t)bn, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+bool tc_shape_ok(int64_t N, int64_t K) {
+  // scale rows must be 16-byte multiples for the TMA descriptor: K % 256 == 0
+  return N >= 1 && K >= 256 && (K % 256) == 0 && N < ((int64_t)1 << 31) && K < ((int64_t)1 << 31);
+}
+
+bool tc_supported(int fmt, int64_t N, int64_t K, int x_dtype, int64_t M) {
+  (void)fmt;
+  return x_dtype == BQ_DT_BF16 && M >= 1 && M < ((int64_t)1 << 31) && tc_shape_ok(N, K);
+}
+
+template <int FMT, int BN, bool GATED>
+static int tc_launch(const TcArgs& a, dim3 grid, cudaStream_t s) {
+  using P = TcPlan<FMT, BN, GATED>;
+  auto kern = qgemm_tc_kernel<FMT, BN, GATED>;
+  static bool configured = false;
+  if (!configured) {
+    BQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P::SMEM));
+    configured = true;
+  }
+  kern<<<grid, TC_THREADS, P::SMEM, s>>>(a);
+  count_launch();
+  BQ_CUDA(cudaGetLastError());
+  return BQ_OK;
+}
+
+template <int FMT>
+static int tc_dense_dispatch(const TcArgs& a, int bn, dim3 grid, cudaStream_t s) {
+  switch (bn) {
+    case 16:  return tc_launch<FMT, 16, false>(a, grid, s);
+    case 32:  return tc_launch<FMT, 32, false>(a, grid, s);
+    case 64:  return tc_launch<FMT, 64, false>(a, grid, s);
+    case 128: return tc_launch<FMT, 128, false>(a, grid, s);
+    default:  return tc_launch<FMT, 256, false>(a, grid, s);
+  }
+}
+
+static int pick_bn(int64_t M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
+
+int launch_qlinear_tc(const uint8_t* codes, const __half* scales, int fmt, int64_t N, int64_t K, const void* x,
+                      int x_dtype, int64_t M, void* y, int y_dtype, int64_t ldy, cudaStream_t s) {
+  if (x_dtype != BQ_DT_BF16) return fail(BQ_ERR_UNSUPPORTED, "tensor path takes bf16 activations");
+  if ((reinterpret_cast<uintptr_t>(x) & 15) != 0) return fail(BQ_ERR_ARG, "activations must be 16-byte aligned");
+  TcArgs a;
+  memset(&a, 0, sizeof(a));
+  const int bn = pick_bn(M);
+  int rc = launch_x_prep(x, x_dtype, M, K, s);
+  if (rc) return rc;
+  if ((rc = x_map(&a.tm_x, g_x16, M, K, bn))) return rc;
+  a.xscale = g_xs;
+  if ((rc = tc_weight_maps(codes, scales, fmt, N, K, &a.tm_w[0], &a.tm_s[0]))) return rc;
+  a.tm_w[1] = a.tm_w[0];
+  a.tm_s[1] = a.tm_s[0];
+  a.out = y; a.ldy = ldy; a.N = N; a.K = K; a.M = M; a.out_dtype = y_dtype; a.moe = 0; a.status = status_word();
+  dim3 grid((unsigned)((M + bn - 1) / bn), (unsigned)((N + TC_ROWS - 1) / TC_ROWS));
+  return fmt == BQ_FMT_Q8G32 ? tc_dense_dispatch<BQ_FMT_Q8G32>(a, bn, grid, s)
+                             : tc_dense_dispatch<BQ_FMT_Q4G32>(a, bn, grid, s);
+}
+
+// ---- MoE grouped experts ---------------------------------------------------------------------------------
+struct MoeTcState {           // device-side per-expert tensor maps + tile list, owned by the library
+  CUtensorMap* gate_up;       // [E][4] = {gate codes, gate scales, up codes, up scales}
+  CUtensorMap* down;          // [E][4] = {down codes, down scales, (unused) x2}
+  int32_t* tiles; int64_t tiles_cap;
+};
+static std::string g_dummy;
+
+bool moe_tc_supported(const Moe* m) { return tc_shape_ok(m->F, m->H) && tc_shape_ok(m->H, m->F); }
+
+int moe_tc_prepare(Moe* m, const std::vector<const uint8_t*>* codes, const std::vector<const __half*>* scales) {
+  // codes/scales: [0]=gate, [1]=up, [2]=down host-side pointer lists (device addresses)
+  if (!moe_tc_supported(m)) { m->tc_state = nullptr; return BQ_OK; }
+  MoeTcState* st = new MoeTcState();
+  memset(st, 0, sizeof(*st));
+  std::vector<CUtensorMap> gu((size_t)m->E * 4), dn((size_t)m->E * 4);
+  for (int e = 0; e < m->E; ++e) {
+    int rc = tc_weight_maps(codes[0][e], scales[0][e], m->fmt, m->F, m->H, &gu[e * 4 + 0], &gu[e * 4 + 1]);
+    if (!rc) rc = tc_weight_maps(codes[1][e], scales[1][e], m->fmt, m->F, m->H, &gu[e * 4 + 2], &gu[e * 4 + 3]);
+    if (!rc) rc = tc_weight_maps(codes[2][e], scales[2][e], m->fmt, m->H, m->F, &dn[e * 4 + 0], &dn[e * 4 + 1]);
+    if (rc) { delete st; return rc; }
+    dn[e * 4 + 2] = dn[e * 4 + 0];
+    dn[e * 4 + 3] = dn[e * 4 + 1];
+  }
+  const size_t bytes = sizeof(CUtensorMap) * (size_t)m->E * 4;
+  BQ_CUDA(cudaMalloc((void**)&st->gate_up, bytes));
+  BQ_CUDA(cudaMalloc((void**)&st->down, bytes));
+  BQ_CUDA(cudaMemcpy(st->gate_up, gu.data(), bytes, cudaMemcpyHostToDevice));
+  BQ_CUDA(cudaMemcpy(st->down, dn.data(), bytes, cudaMemcpyHostToDevice));
+  m->tc_state = st;
+  return BQ_OK;
+}
+
+void moe_tc_release(Moe* m) {
+  MoeTcState* st = static_cast<MoeTcState*>(m->tc_state);
+  if (!st) return;
+  cudaFree(st->gate_up); cudaFree(st->down); cudaFree(st->tiles);
+  delete st;
+  m->tc_state = nullptr;
+}
+
+template <int FMT, bool GATED>
+static int tc_moe_dispatch(const TcArgs& a, int bn, dim3 grid, cudaStream_t s) {
+  switch (bn) {
+    case 16:  return tc_launch<FMT, 16, GATED>(a, grid, s);
+    case 64:  return tc_launch<FMT, 64, GATED>(a, grid, s);
+    default:  return tc_launch<FMT, 128, GATED>(a, grid, s);
+  }
+}
+
+int launch_moe_experts_tc(const Moe* m, const void* xp, const int32_t* offsets, int64_t P, void* hbuf, float* out,
+                          cudaStream_t s) {
+  MoeTcState* st = static_cast<MoeTcState*>(m->tc_state);
+  if (!st) return fail(BQ_ERR_UNSUPPORTED, "tensor path unavailable for this expert shape");
+  if ((reinterpret_cast<uintptr_t>(xp) & 15) != 0 || (reinterpret_cast<uintptr_t>(hbuf) & 15) != 0)
+    return fail(BQ_ERR_ARG, "activation buffers must be 16-byte aligned");
+  // rows per expert ~ P / E: pick the batch tile for the average segment
+  const int64_t avg = (P + m->E - 1) / m->E;
+  const int bn = avg <= 16 ? 16 : avg <= 64 ? 64 : 128;
+  const int64_t max_tiles = (P + bn - 1) / bn + m->E;
+  if (max_tiles > st->tiles_cap) {
+    if (st->tiles) BQ_CUDA(cudaFree(st->tiles));
+    st->tiles = nullptr; st->tiles_cap = 0;
+    BQ_CUDA(cudaMalloc((void**)&st->tiles, sizeof(int32_t) * (size_t)(2 * max_tiles + 1 + 64)));
+    st->tiles_cap = max_tiles;
+  }
+  moe_tile_list_kernel<<<1, 1024, 0, s>>>(offsets, m->E, bn, st->tiles);
+  count_launch();
+  BQ_CUDA(cudaGetLastError());
+  // gate|up -> h (bf16)
+  TcArgs a;
+  memset(&a, 0, sizeof(a));
+  int rc = launch_x_prep(xp, BQ_DT_BF16, P, m->H, s);
+  if (rc) return rc;
+  if ((rc = x_map(&a.tm_x, g_x16, P, m->H, bn))) return rc;
+  a.xscale = g_xs;
+  a.tm_list = st->gate_up; a.offsets = offsets; a.tiles = st->tiles; a.out = hbuf; a.ldy = m->F; a.N = m->F;
+  a.K = m->H; a.M = P; a.out_dtype = BQ_DT_BF16; a.moe = 1; a.status = status_word();
+  dim3 g1((unsigned)max_tiles, (unsigned)((m->F + TC_ROWS - 1) / TC_ROWS));
+  rc = m->fmt == BQ_FMT_Q8G32 ? tc_moe_dispatch<BQ_FMT_Q8G32, true>(a, bn, g1, s)
+                              : tc_moe_dispatch<BQ_FMT_Q4G32, true>(a, bn, g1, s);
+  if (rc) return rc;
+  // down -> out (f32)
+  TcArgs b;
+  memset(&b, 0, sizeof(b));
+  if ((rc = launch_x_prep(hbuf, BQ_DT_BF16, P, m->F, s))) return rc;   // stream order: gate|up GEMM is done with the scratch
+  if ((rc = x_map(&b.tm_x, g_x16, P, m->F, bn))) return rc;
+  b.xscale = g_xs;
+  b.tm_list = st->down; b.offsets = offsets; b.tiles = st->tiles; b.out = out; b.ldy = m->H; b.N = m->H;
+  b.K = m->F; b.M = P; b.out_dtype = BQ_DT_F32; b.moe = 1; b.status = status_word();
+  dim3 g2((unsigned)max_tiles, (unsigned)((m->H + TC_ROWS - 1) / TC_ROWS));
+  return m->fmt == BQ_FMT_Q8G32 ? tc_moe_dispatch<BQ_FMT_Q8G32, false>(b, bn, g2, s)
+                                : tc_moe_dispatch<BQ_FMT_Q4G32, false>(b, bn, g2, s);
+}
+
+}  // namespace bq
