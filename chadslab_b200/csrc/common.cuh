@@ -70,6 +70,11 @@ int launch_qlinear_tc(const uint8_t* codes, const __half* scales, int fmt, int64
                       const void* x, int x_dtype, int64_t M, void* y, int y_dtype, int64_t ldy,
                       cudaStream_t s);
 bool tc_supported(int fmt, int64_t N, int64_t K, int x_dtype, int64_t M);
+// tensor-core GEMV with exact group scaling (mma.sync), 1..4 activation rows
+int launch_qlinear_mma(const uint8_t* codes, const __half* scales, int fmt, int64_t N, int64_t K,
+                       const void* x, int x_dtype, int64_t M, void* y, int y_dtype, int64_t ldy,
+                       cudaStream_t s);
+bool gemv_mma_supported(int fmt, int64_t N, int64_t K, int x_dtype, int64_t M);
 bool moe_tc_supported(const Moe* m);
 int moe_tc_prepare(Moe* m, const std::vector<const uint8_t*>* codes, const std::vector<const __half*>* scales);
 void moe_tc_release(Moe* m);

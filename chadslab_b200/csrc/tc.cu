@@ -34,7 +34,8 @@ constexpr int TC_BK = 64;           // k per pipeline step (one 128-byte swizzle
 constexpr int TC_CONV_THREADS = 256;   // 8 converter warps
 constexpr int TC_THREADS = 64 + TC_CONV_THREADS;
 constexpr int TC_SC_SLOTS = 3;      // scale tiles in flight (each covers 4 k-steps)
-constexpr uint32_t TC_WAIT_LIMIT = 1u << 21;
+constexpr uint64_t TC_WAIT_NS = 2000000000ull;   // every device-side wait gives up after 2 s
+constexpr int TC_CONV_WARPS = TC_CONV_THREADS / 32;
 
 // ---- PTX wrappers -----------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -47,28 +48,46 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+// One try: the hardware may suspend the thread up to `hint_ns` while the phase is incomplete.
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns false if the wait expired or another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t it = 0; it < TC_WAIT_LIMIT; ++it) {
-    if (mbar_test(bar, parity)) return true;
-    if (it > 32) {
-      __nanosleep(40);
-      if (*abort_flag) return false;
-    }
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait by one thread (at most ~TC_WAIT_NS).  Returns false if the wait expired or another
+// role already gave up; on expiry the CTA-wide abort flag is raised.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  const uint64_t t0 = global_ns();
+  for (;;) {
+    for (int i = 0; i < 16; ++i)
+      if (mbar_try(bar, parity, 2000u)) return true;
+    if (*abort_flag) return false;
+    if (global_ns() - t0 > TC_WAIT_NS) { *abort_flag = 1; return false; }
   }
-  *abort_flag = 1;
-  return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try(bar, parity, 2000u)) return true;
+  return mbar_wait_slow(bar, parity, abort_flag);
+}
+// Warp-collective wait: lane 0 does the waiting, the result is broadcast, then every lane performs
+// one (already satisfied) test of its own so that it has observed the phase itself.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int lane) {
+  uint32_t ok = 0;
+  if (lane == 0) ok = mbar_wait(bar, parity, abort_flag) ? 1u : 0u;
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  if (ok && lane != 0) ok = mbar_try(bar, parity, 0u) ? 1u : 0u;
+  return __all_sync(0xffffffffu, ok != 0);
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int c0, int c1, uint32_t bar) {
   asm volatile(
@@ -193,6 +212,17 @@ __device__ __forceinline__ uint4 cvt_q4_word(const uint32_t v, const __half2 s2)
                     *reinterpret_cast<uint32_t*>(&h45), *reinterpret_cast<uint32_t*>(&h67));
 }
 
+// Optional timeline of CTA (0,0) for tuning builds (-DBQ_TC_TRACE): role x k-step x point -> SM clock.
+#ifdef BQ_TC_TRACE
+__device__ long long g_tc_trace[3][64][6];
+#define TC_TRACE(role, ks, pt)                                                                     \
+  do {                                                                                             \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && (ks) < 64) g_tc_trace[role][ks][pt] = clock64();     \
+  } while (0)
+#else
+#define TC_TRACE(role, ks, pt) do {} while (0)
+#endif
+
 // ---- the kernel ----------------------------------------------------------------------------------------
 template <int FMT, int BN, bool GATED>
 __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_constant__ TcArgs args) {
@@ -207,8 +237,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
   uint64_t* bars = reinterpret_cast<uint64_t*>(sc_tiles + TC_SC_SLOTS * NW * P::SCT);
   // barrier indices
   uint64_t* full = bars;               // [S]   TMA landed (tx)
-  uint64_t* empty = bars + S;          // [S]   converters (128) + MMA commit (1)
-  uint64_t* a_full = bars + 2 * S;     // [NA]  converters (128)
+  uint64_t* empty = bars + S;          // [S]   converter warps (8) + MMA commit (1)
+  uint64_t* a_full = bars + 2 * S;     // [NA]  converter warps (8)
   uint64_t* a_empty = a_full + NA;     // [NA]  MMA commit (1)
   uint64_t* acc_full = a_empty + NA;   // [1]
   volatile int* abort_flag = reinterpret_cast<volatile int*>(acc_full + 1);
@@ -236,8 +266,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
   const int ksteps = (int)((args.K + TC_BK - 1) / TC_BK);
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < S; ++i) { mbar_init(smem_u32(&full[i]), 1); mbar_init(smem_u32(&empty[i]), TC_CONV_THREADS + 1); }
-    for (int i = 0; i < NA; ++i) { mbar_init(smem_u32(&a_full[i]), TC_CONV_THREADS); mbar_init(smem_u32(&a_empty[i]), 1); }
+    for (int i = 0; i < S; ++i) { mbar_init(smem_u32(&full[i]), 1); mbar_init(smem_u32(&empty[i]), TC_CONV_WARPS + 1); }
+    for (int i = 0; i < NA; ++i) { mbar_init(smem_u32(&a_full[i]), TC_CONV_WARPS); mbar_init(smem_u32(&a_empty[i]), 1); }
     mbar_init(smem_u32(acc_full), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -260,6 +290,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
         const int s = ks % S;
         const uint32_t ph = (uint32_t)(ks / S) & 1u;
         if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1u, abort_flag)) break;
+        TC_TRACE(0, ks, 0);
         const bool with_scales = (ks & 3) == 0;
         const uint32_t bytes = NW * P::RAW + P::XT + (with_scales ? NW * P::SCT : 0);
         const uint32_t fb = smem_u32(&full[s]);
@@ -273,6 +304,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
           tma_load_2d(smem_u32(sc), tms0, (ks >> 2) * 8, (int)n0, fb);
           if (GATED) tma_load_2d(smem_u32(sc + P::SCT), tms1, (ks >> 2) * 8, (int)n0, fb);
         }
+        TC_TRACE(0, ks, 1);
       }
       if (*abort_flag) {   // give copies already in flight time to land before the CTA exits
         for (int i = 0; i < 64; ++i) __nanosleep(1000);
@@ -286,8 +318,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
       for (int ks = 0; ks < ksteps && ok; ++ks) {
         const int s = ks % S, a = ks % NA;
         const uint32_t ph = (uint32_t)(ks / S) & 1u, aph = (uint32_t)(ks / NA) & 1u;
-        ok = mbar_wait(smem_u32(&full[s]), ph, abort_flag) && mbar_wait(smem_u32(&a_full[a]), aph, abort_flag);
+        ok = mbar_wait(smem_u32(&a_full[a]), aph, abort_flag);
+        TC_TRACE(1, ks, 0);
+        ok = ok && mbar_wait(smem_u32(&full[s]), ph, abort_flag);   // activation tile (completed before a_full)
         if (!ok) break;
+        TC_TRACE(1, ks, 1);
         tc_fence_after();
         const uint64_t bdesc = umma_desc_sw128(smem_u32(stages + s * P::STAGE));
 #pragma unroll
@@ -298,8 +333,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
             tc_mma_f16(tmem_base + (uint32_t)(w * BN), adesc + (uint64_t)(2 * kk), bdesc + (uint64_t)(2 * kk), idesc,
                        (ks > 0 || kk > 0) ? 1u : 0u);
         }
+        TC_TRACE(1, ks, 2);
         tc_commit(smem_u32(&a_empty[a]));
         tc_commit(smem_u32(&empty[s]));
+        TC_TRACE(1, ks, 3);
       }
       if (ok) tc_commit(smem_u32(acc_full));
     }
@@ -310,8 +347,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
     for (int ks = 0; ks < ksteps && ok; ++ks) {
       const int s = ks % S, a = ks % NA;
       const uint32_t ph = (uint32_t)(ks / S) & 1u, aph = (uint32_t)(ks / NA) & 1u;
-      ok = mbar_wait(smem_u32(&full[s]), ph, abort_flag) && mbar_wait(smem_u32(&a_empty[a]), aph ^ 1u, abort_flag);
+      ok = mbar_wait_warp(smem_u32(&full[s]), ph, abort_flag, lane);
+      if (t == 0) TC_TRACE(2, ks, 0);
+      ok = ok && mbar_wait_warp(smem_u32(&a_empty[a]), aph ^ 1u, abort_flag, lane);
       if (!ok) break;
+      if (t == 0) TC_TRACE(2, ks, 1);
       const uint8_t* st = stages + s * P::STAGE + P::XT;
       const uint8_t* sc = sc_tiles + ((ks >> 2) % TC_SC_SLOTS) * NW * P::SCT;
 #pragma unroll
@@ -349,12 +389,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
           }
         }
       }
+      if (t == 0) TC_TRACE(2, ks, 2);
       fence_async_smem();                       // generic-proxy writes -> visible to the tensor core
-      mbar_arrive(smem_u32(&a_full[a]));
-      mbar_arrive(smem_u32(&empty[s]));
+      if (t == 0) TC_TRACE(2, ks, 3);
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(smem_u32(&a_full[a]));
+        mbar_arrive(smem_u32(&empty[s]));
+      }
+      if (t == 0) TC_TRACE(2, ks, 4);
     }
     // ---- epilogue: warp w reads TMEM lanes 32*(w%4) .. +31 = weight rows -------------------------------
-    if (ok) ok = mbar_wait(smem_u32(acc_full), 0u, abort_flag);
+    if (ok) ok = mbar_wait_warp(smem_u32(acc_full), 0u, abort_flag, lane);
     if (ok) {
       tc_fence_after();
       const int lg = warp & 3;                 // two warps share a lane group and alternate column chunks
@@ -683,3 +729,9 @@ int launch_moe_experts_tc(const Moe* m, const void* xp, const int32_t* offsets, 
 }
 
 }  // namespace bq
+
+#ifdef BQ_TC_TRACE
+extern "C" int bq_debug_tc_trace(long long* out) {
+  return cudaMemcpyFromSymbol(out, bq::g_tc_trace, sizeof(bq::g_tc_trace)) == cudaSuccess ? 0 : -3;
+}
+#endif

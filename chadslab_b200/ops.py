@@ -333,15 +333,15 @@ class MoEExperts:
         except Exception:
             pass
 
-    def experts(self, xp, offsets):
-        """Grouped SwiGLU FFN on permuted bf16 rows xp[P,H] -> f32[P,H]."""
+    def experts(self, xp, offsets, return_h: bool = False):
+        """Grouped SwiGLU FFN on permuted bf16 rows xp[P,H] -> f32[P,H] (and the bf16 hidden h[P,F])."""
         torch = _torch()
         P = xp.shape[0]
         hbuf = torch.empty((P, self.F), dtype=torch.bfloat16, device=xp.device)
         out = torch.empty((P, self.H), dtype=torch.float32, device=xp.device)
         _lib.check(_lib.lib().bq_moe_experts(self._handle, xp.data_ptr(), offsets.data_ptr(), P, hbuf.data_ptr(),
                                              out.data_ptr(), self.path, _stream_ptr()))
-        return out
+        return (out, hbuf) if return_h else out
 
     def __call__(self, x, return_aux: bool = False):
         torch = _torch()

@@ -66,35 +66,71 @@ def test_combine_matches_oracle_order(cuda_lib):
     assert np.array_equal(y.cpu().numpy(), ref)                # same order, separate mul/add: bit-exact
 
 
+def _check_layer(cb, torch, layer, x, E, k, gate, up, down, fmt, golden_y=None):
+    """Stage-wise parity.  The layer rounds the hidden activation h to bf16 between its two matmuls, so a
+    1e-4 difference in the first matmul can flip a bf16 rounding (2^-8 relative) of an element of h; each
+    matmul is therefore checked against the oracle on the inputs that matmul actually saw."""
+    xt = torch.from_numpy(x).cuda().to(torch.bfloat16)
+    y, (idx, w, perm, inv, offsets) = layer(xt, return_aux=True)
+    gi, gw = idx.cpu().numpy(), w.cpu().numpy()
+    p2, o2 = spec.moe_permute(gi, E)
+    assert np.array_equal(perm.cpu().numpy(), p2) and np.array_equal(offsets.cpu().numpy(), o2)
+    xp = cb.moe_gather(xt, perm, k)
+    out_p, h = layer.experts(xp, offsets, return_h=True)
+    h = h.float().cpu().numpy()
+    xp_np = x[p2 // k]
+    # (1) gate/up matmuls + SwiGLU: h within one bf16 rounding step of the oracle's h
+    h_ref = np.zeros_like(h)
+    for e in range(E):
+        a, b = int(o2[e]), int(o2[e + 1])
+        if a < b:
+            g_ = spec.qlinear(xp_np[a:b], gate[e][0], gate[e][1], fmt, f64=True)
+            u_ = spec.qlinear(xp_np[a:b], up[e][0], up[e][1], fmt, f64=True)
+            h_ref[a:b] = (g_ / (1 + np.exp(-g_)) * u_).astype(np.float32)
+    assert np.abs(h - h_ref).max() <= 2.0 ** -8 * np.abs(h_ref).max() + TOL * np.abs(h_ref).max()
+    assert spec.rel_err(h, h_ref) <= 2.0 ** -8 + TOL
+    # (2) down matmul on the kernel's own h
+    out_ref = np.zeros((len(p2), layer.H), dtype=np.float64)
+    for e in range(E):
+        a, b = int(o2[e]), int(o2[e + 1])
+        if a < b:
+            out_ref[a:b] = spec.qlinear(h[a:b], down[e][0], down[e][1], fmt, f64=True)
+    assert spec.rel_err(out_p.cpu().numpy(), out_ref) <= TOL
+    # (3) combine of the kernel's expert outputs, same order as the oracle: bit-exact
+    assert np.array_equal(y.cpu().numpy(), spec.moe_combine(out_p.cpu().numpy(), p2, gw))
+    # (4) whole layer against the oracle layer (includes the bf16 flips of h): loose bound
+    if golden_y is not None and np.array_equal(gi, golden_y[1]):
+        assert spec.rel_err(y.cpu().numpy(), golden_y[0]) <= 4 * TOL
+    return gi
+
+
 @pytest.mark.parametrize("fmt,tag", [(0, "q8"), (1, "q4")])
 def test_moe_layer_golden(cuda_lib, moegolden, fmt, tag):
     import torch
     import chadslab_b200 as cb
     E = moegolden[f"{tag}/gate_codes"].shape[0]
-    mk = lambda nm: [cb.PackedWeight.from_arrays(moegolden[f"{tag}/{nm}_codes"][e], moegolden[f"{tag}/{nm}_scales"][e], fmt)
-                     for e in range(E)]
+    pick = lambda nm: [(moegolden[f"{tag}/{nm}_codes"][e], moegolden[f"{tag}/{nm}_scales"][e]) for e in range(E)]
+    mk = lambda lst: [cb.PackedWeight.from_arrays(c, s_, fmt) for c, s_ in lst]
     router = cb.PackedWeight.from_arrays(moegolden[f"{tag}/router_codes"], moegolden[f"{tag}/router_scales"], fmt)
+    x = spec.from_bf16_bits(moegolden["x_bf16"])
     for path in (cb.PATH_SIMT, cb.PATH_AUTO):
-        layer = cb.MoEExperts(router, mk("gate"), mk("up"), mk("down"), top_k=2, path=path)
-        x = torch.from_numpy(moegolden["x_bf16"].astype(np.int16)).cuda().view(torch.bfloat16)
-        y, (idx, w, perm, inv, offsets) = layer(x, return_aux=True)
-        assert np.array_equal(idx.cpu().numpy(), moegolden[f"{tag}/idx"])
-        assert np.array_equal(perm.cpu().numpy(), moegolden[f"{tag}/perm"])
-        assert np.array_equal(offsets.cpu().numpy(), moegolden[f"{tag}/offsets"])
-        assert spec.rel_err(y.cpu().numpy(), moegolden[f"{tag}/y"]) <= TOL
+        layer = cb.MoEExperts(router, mk(pick("gate")), mk(pick("up")), mk(pick("down")), top_k=2, path=path)
+        gi = _check_layer(cb, torch, layer, x, E, 2, pick("gate"), pick("up"), pick("down"), fmt,
+                          golden_y=(moegolden[f"{tag}/y"], moegolden[f"{tag}/idx"]))
+        assert np.array_equal(gi, moegolden[f"{tag}/idx"])
 
 
 @pytest.mark.parametrize("fmt", [0, 1])
 @pytest.mark.parametrize("T", [3, 64, 300])
 def test_moe_layer_random(cuda_lib, fmt, T):
-    """16 experts of the benchmark's expert shape family (hidden 256, ffn 96..., top-4), some experts empty."""
+    """16 experts, hidden 256, ffn 256, top-4; one expert is (almost) never chosen -> empty segment."""
     import torch
     import chadslab_b200 as cb
     rng = np.random.default_rng(100 + T + fmt)
-    E, H, F, k = 16, 256, 192, 4
+    E, H, F, k = 16, 256, 256, 4
     x = spec.bf16_round(rng.normal(0, 1, (T, H)).astype(np.float32))
     Wr = rng.normal(0, 0.3, (E, H)).astype(np.float32)
-    Wr[5] = -10.0 * np.abs(Wr[5])        # expert 5 is (almost) never chosen -> empty segment
+    Wr[5] = -10.0 * np.abs(Wr[5])
     q = lambda W: spec.quantize(W, fmt)
     router = q(Wr)
     gate = [q(rng.normal(0, 0.05, (F, H)).astype(np.float32)) for _ in range(E)]
@@ -102,14 +138,7 @@ def test_moe_layer_random(cuda_lib, fmt, T):
     down = [q(rng.normal(0, 0.05, (H, F)).astype(np.float32)) for _ in range(E)]
     ref, (ridx, rw, rperm, roff) = spec.moe_forward(x, router, gate, up, down, fmt, k)
     pw = lambda cs: cb.PackedWeight.from_arrays(cs[0], cs[1], fmt)
-    for path in (cb.PATH_SIMT, cb.PATH_AUTO):
+    for path in (cb.PATH_SIMT, cb.PATH_TENSOR):
         layer = cb.MoEExperts(pw(router), [pw(g) for g in gate], [pw(u) for u in up], [pw(d) for d in down], top_k=k,
                               path=path)
-        y, (idx, w, perm, inv, offsets) = layer(torch.from_numpy(x).cuda().to(torch.bfloat16), return_aux=True)
-        if np.array_equal(idx.cpu().numpy(), ridx):
-            assert spec.rel_err(y.cpu().numpy(), ref) <= TOL
-        else:                                # a router near-tie flipped: compare with the oracle fed the kernel's routing
-            gi, gw = idx.cpu().numpy(), w.cpu().numpy()
-            p2, o2 = spec.moe_permute(gi, E)
-            out_p = spec.moe_experts(x[p2 // k], o2, gate, up, down, fmt)
-            assert spec.rel_err(y.cpu().numpy(), spec.moe_combine(out_p, p2, gw)) <= TOL
+        _check_layer(cb, torch, layer, x, E, k, gate, up, down, fmt, golden_y=(ref, ridx))
