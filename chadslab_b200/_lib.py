@@ -51,6 +51,8 @@ PROTOTYPES = {
     "bq_moe_route": (_i32, [_vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp]),
     "bq_moe_permute_scratch_bytes": (_i64, [_i64, _i32, _i32]),
     "bq_moe_permute": (_i32, [_vp, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp]),
+    "bq_moe_permute_noalloc_max_bytes": (_i64, []),
+    "bq_moe_permute_noalloc": (_i32, [_vp, _i64, _i32, _i32, _vp, _vp, _vp, _vp]),
     "bq_moe_gather": (_i32, [_vp, _i32, _i64, _vp, _i64, _i32, _vp, _vp]),
     "bq_moe_create": (_i32, [C.POINTER(_h), C.POINTER(_h), C.POINTER(_h), _i32, C.POINTER(_h)]),
     "bq_moe_destroy": (_i32, [_h]),

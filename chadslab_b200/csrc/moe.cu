@@ -401,6 +401,45 @@ int bq_moe_permute(const int32_t* idx, int64_t T, int top_k, int E, int32_t* per
   return BQ_OK;
 }
 
+// ---- permute without any allocation ---------------------------------------------------------------------
+// Some hosts of this library may not allocate device memory at the point where they sort tokens: a serving
+// loop that has handed every free byte of HBM to its KV-cache pool, a plugin that runs under an allocator
+// it does not own, or a latency-critical section where a cudaMalloc (which synchronises the device) is
+// forbidden.  For them the per-chunk histograms of the counting sort live in this fixed array, which every
+// GPU that loads the library holds (512 KiB) until the process exits.
+constexpr int64_t PERMUTE_STATIC_INTS = 131072;   // 512 KiB: chunks * experts may not exceed this
+static __device__ __align__(256) int32_t g_permute_scratch[PERMUTE_STATIC_INTS];
+// The array's name is only a host-side handle; kernels need its device address, fetched once per device.
+static int32_t* g_permute_scratch_addr[64] = {nullptr};
+
+int64_t bq_moe_permute_noalloc_max_bytes(void) { return PERMUTE_STATIC_INTS * (int64_t)sizeof(int32_t); }
+
+int bq_moe_permute_noalloc(const int32_t* idx, int64_t T, int top_k, int E, int32_t* perm, int32_t* inv,
+                           int32_t* offsets, void* stream) {
+  int rc = ready();
+  if (rc) return rc;
+  if (T < 0 || E <= 0 || E > 1024 || top_k <= 0) return fail(BQ_ERR_ARG, "need T >= 0, 1 <= E <= 1024, top_k >= 1");
+  if (T * top_k > 0x7fffffff) return fail(BQ_ERR_ARG, "T * top_k exceeds int32 range");
+  const int64_t need = bq_moe_permute_scratch_bytes(T, top_k, E);
+  if (need > bq_moe_permute_noalloc_max_bytes())
+    return fail(BQ_ERR_ARG, "bq_moe_permute_noalloc: this T*top_k and E need " + std::to_string(need) +
+                                " bytes of histogram scratch, the built-in array holds " +
+                                std::to_string(bq_moe_permute_noalloc_max_bytes()) +
+                                "; use bq_moe_permute with caller-provided scratch");
+  const int dev = device_id();
+  if (dev < 0 || dev >= 64) return fail(BQ_ERR_STATE, "device index out of range for the built-in scratch table");
+  if (!g_permute_scratch_addr[dev]) {     // first call on this device: resolve the symbol's device address
+    int cur = -1;
+    BQ_CUDA(cudaGetDevice(&cur));
+    if (cur != dev) BQ_CUDA(cudaSetDevice(dev));
+    void* p = nullptr;
+    BQ_CUDA(cudaGetSymbolAddress(&p, g_permute_scratch));
+    g_permute_scratch_addr[dev] = static_cast<int32_t*>(p);
+  }
+  // Nothing in the array has to start at zero: the histogram kernel writes every cell the later kernels read.
+  return bq_moe_permute(idx, T, top_k, E, perm, inv, offsets, g_permute_scratch_addr[dev], stream);
+}
+
 int bq_moe_gather(const void* x, int dtype, int64_t H, const int32_t* perm, int64_t P, int top_k, void* xp,
                   void* stream) {
   int rc = ready();

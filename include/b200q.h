@@ -114,6 +114,23 @@ int bq_moe_route(const float* logits, int64_t T, int E, int top_k, int renormali
 int64_t bq_moe_permute_scratch_bytes(int64_t T, int top_k, int E);
 int bq_moe_permute(const int32_t* idx, int64_t T, int top_k, int E, int32_t* perm,
                    int32_t* inv, int32_t* offsets, void* scratch, void* stream);
+/* bq_moe_permute for callers that cannot allocate device memory.  No counterpart in the
+ * reference: it exists for hosts that have given all free HBM to a KV-cache / arena they do
+ * not control, or that sort tokens inside a section where cudaMalloc (a device-wide
+ * synchronisation) is not allowed.  Same arguments and results as bq_moe_permute minus the
+ * scratch pointer: the per-chunk histograms live in a fixed 512 KiB array inside the library
+ * (held by every GPU that loads it, until the process exits).  Calls no cudaMalloc/cudaFree.
+ *   - limit: bq_moe_permute_scratch_bytes(T, top_k, E) <= bq_moe_permute_noalloc_max_bytes()
+ *     (any T*top_k when E <= 128; T*top_k <= 65536 when E = 512); larger requests return
+ *     BQ_ERR_ARG and launch nothing;
+ *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress);
+ *     make that first call before any stream capture begins;
+ *   - all calls share the one array and it keeps the previous call's contents (nothing in it
+ *     needs to start at zero): two calls whose kernels overlap on the GPU — different streams
+ *     without an event between them — race on it.                                           */
+int64_t bq_moe_permute_noalloc_max_bytes(void);
+int bq_moe_permute_noalloc(const int32_t* idx, int64_t T, int top_k, int E, int32_t* perm,
+                           int32_t* inv, int32_t* offsets, void* stream);
 /* xp[p,:] = x[perm[p] / k, :]  (rows of H elements of `dtype`)                           */
 int bq_moe_gather(const void* x, int dtype, int64_t H, const int32_t* perm, int64_t P,
                   int top_k, void* xp, void* stream);
