@@ -1,0 +1,144 @@
+"""Tensor- and expert-parallel sharding of the quantized-matmul path (one process per GPU).
+
+Collectives happen only at shard boundaries and go through `torch.distributed` (NCCL on GPUs; the
+same code runs on the `gloo` backend with CPU tensors, which is how the host logic is tested):
+
+    ColumnParallelLinear   shard N (q/k/v, gate/up): no communication, optional all-gather
+    RowParallelLinear      shard K in multiples of 32 (o, down): all-reduce(sum) of the partial outputs
+    VocabParallelHead      shard the vocabulary: greedy decode exchanges one (max, argmax) pair per rank
+    ExpertParallelMoE      experts E/world per rank, tokens stay data-parallel: all-to-all of routed rows
+                           to the owning rank, grouped experts there, all-to-all back, weighted combine
+
+Every class takes *callables* for the compute (`QuantLinear`, `MoEExperts.experts`, the permute /
+gather / combine kernels), so the communication logic is independent of where the math runs.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+
+def _world(group=None):
+    return dist.get_world_size(group), dist.get_rank(group)
+
+
+class ColumnParallelLinear:
+    """y_local = x . W[rank*N/world : (rank+1)*N/world]^T ; gather_output concatenates along N."""
+
+    def __init__(self, linear: Callable, gather_output: bool = False, group=None):
+        self.linear, self.gather_output, self.group = linear, gather_output, group
+
+    def __call__(self, x):
+        y = self.linear(x)
+        if not self.gather_output:
+            return y
+        world, _ = _world(self.group)
+        parts = [torch.empty_like(y) for _ in range(world)]
+        dist.all_gather(parts, y.contiguous(), group=self.group)
+        return torch.cat(parts, dim=-1)
+
+
+class RowParallelLinear:
+    """x is this rank's K slice (K/world columns, a multiple of 32); partial outputs are summed."""
+
+    def __init__(self, linear: Callable, group=None):
+        self.linear, self.group = linear, group
+
+    def __call__(self, x_local):
+        y = self.linear(x_local)
+        dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
+        return y
+
+
+class VocabParallelHead:
+    """Vocabulary-sharded lm_head.  `head(x)` -> local logits [M, V/world]."""
+
+    def __init__(self, head: Callable, vocab_local: int, group=None):
+        self.head, self.vocab_local, self.group = head, vocab_local, group
+
+    def logits(self, x):
+        return ColumnParallelLinear(self.head, gather_output=True, group=self.group)(x)
+
+    def greedy(self, x):
+        """Global argmax ids (ties -> lower id) exchanging 2 numbers per row and rank."""
+        world, rank = _world(self.group)
+        local = self.head(x).float()
+        mx, am = local.max(dim=-1)
+        pair = torch.stack([mx, (am + rank * self.vocab_local).to(mx.dtype)], dim=-1).contiguous()   # [M, 2]
+        pairs = [torch.empty_like(pair) for _ in range(world)]
+        dist.all_gather(pairs, pair, group=self.group)
+        allp = torch.stack(pairs, dim=0)                     # [world, M, 2]
+        vals, ids = allp[..., 0], allp[..., 1]
+        best = vals.max(dim=0).values
+        # lowest id among the ranks that hold the maximum
+        cand = torch.where(vals == best.unsqueeze(0), ids, torch.full_like(ids, float("inf")))
+        return cand.min(dim=0).values.to(torch.int64)
+
+
+class MoEBackend:
+    """The five MoE kernels as callables (defaults: the CUDA ones from chadslab_b200.ops)."""
+
+    def __init__(self, route=None, permute=None, gather=None, combine=None):
+        from . import ops
+        self.route = route or ops.moe_route
+        self.permute = permute or ops.moe_permute
+        self.gather = gather or ops.moe_gather
+        self.combine = combine or ops.moe_combine
+
+
+class ExpertParallelMoE:
+    """router (replicated) -> top-k -> sort by global expert -> all-to-all rows to the owning rank ->
+    local sort by local expert -> grouped experts -> inverse -> all-to-all back -> weighted combine.
+
+    router:      callable x[T,H] -> logits[T,E]           (replicated weights)
+    experts:     callable (xp[P,H], offsets[E_local+1]) -> out[P,H] float32   (this rank's experts)
+    """
+
+    def __init__(self, router: Callable, experts: Callable, n_experts: int, top_k: int, backend: Optional[MoEBackend] = None,
+                 renormalise: bool = True, group=None, act_dtype=torch.bfloat16):
+        self.router, self.experts, self.E, self.top_k = router, experts, n_experts, top_k
+        self.backend = backend or MoEBackend()
+        self.renormalise, self.group, self.act_dtype = renormalise, group, act_dtype
+        world, _ = _world(group)
+        if n_experts % world:
+            raise ValueError(f"{n_experts} experts do not divide over {world} ranks")
+        self.E_local = n_experts // world
+
+    def __call__(self, x):
+        be, k = self.backend, self.top_k
+        world, rank = _world(self.group)
+        El = self.E_local
+        xb = x if x.dtype == self.act_dtype else x.to(self.act_dtype)
+        idx, w = be.route(self.router(xb), k, self.renormalise)                # [T,k]
+        perm, inv, offsets = be.permute(idx, self.E)                            # sorted by global expert
+        xp = be.gather(xb, perm, k)                                             # [T*k, H], grouped by owner rank
+        # rows per (destination rank, local expert) and the counts exchange
+        counts = (offsets[1:] - offsets[:-1]).to(torch.int64).reshape(world, El)        # what I send
+        recv_counts = torch.empty_like(counts)
+        dist.all_to_all_single(recv_counts, counts.contiguous(), group=self.group)       # [src, local expert]
+        send_rows = counts.sum(dim=1).tolist()
+        recv_rows = recv_counts.sum(dim=1).tolist()
+        xr = torch.empty((int(sum(recv_rows)), xp.shape[1]), dtype=xp.dtype, device=xp.device)
+        dist.all_to_all_single(xr, xp.contiguous(), output_split_sizes=recv_rows, input_split_sizes=send_rows,
+                               group=self.group)
+        # received rows are ordered (source rank, local expert); regroup by local expert, sources in rank order
+        eid = torch.repeat_interleave(torch.arange(El, device=xr.device).repeat(world), recv_counts.reshape(-1))
+        lperm, linv, loffsets = be.permute(eid.to(torch.int32).reshape(-1, 1), El)
+        xl = be.gather(xr, lperm, 1)
+        out_l = self.experts(xl, loffsets)                                      # float32 [P_local, H]
+        out_r = out_l[linv.long()] if out_l.shape[0] else out_l                 # back to (source, expert) order
+        out_p = torch.empty((xp.shape[0], out_r.shape[1]), dtype=out_r.dtype, device=out_r.device)
+        dist.all_to_all_single(out_p, out_r.contiguous(), output_split_sizes=send_rows, input_split_sizes=recv_rows,
+                               group=self.group)
+        return be.combine(out_p, inv, w)
+
+
+def shard_experts(items: Sequence, rank: int, world: int):
+    """The contiguous block of experts a rank owns."""
+    n = len(items)
+    if n % world:
+        raise ValueError(f"{n} experts do not divide over {world} ranks")
+    per = n // world
+    return list(items[rank * per:(rank + 1) * per])
