@@ -1,0 +1,199 @@
+"""Decoder driver around the quantized-matmul path (the caller side of the path).
+
+Every projection (q/k/v/o, gate/up/down, lm_head) is a `QuantLinear` on packed weights; the glue between
+them — RMSNorm, rotate-half RoPE, causal GQA attention over a KV cache, GeGLU, residuals, embedding lookup —
+is plain PyTorch.  With `world > 1` the projections are tensor-parallel (`parallel.py`): q/k/v and gate/up
+column-sharded, o and down row-sharded with an all-reduce, the head vocabulary-sharded.
+Architecture choices the specification leaves open follow oracle/model.py's header (weights multiply the
+normalised value directly, eps 1e-6, no embedding scaling, no soft-capping, RoPE base 10000).
+"""
+from __future__ import annotations
+
+import math
+import zlib
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+from . import parallel
+from .ops import LMHead, PackedWeight, QuantLinear, shard
+from .synth import make_device_weight
+
+
+@dataclass
+class DecoderConfig:
+    layers: int
+    hidden: int
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int
+    ffn: int
+    vocab: int
+    fmt: int = 0
+    rope_base: float = 10000.0
+    eps: float = 1e-6
+
+    def as_dict(self):
+        return dict(self.__dict__)
+
+
+GEMMA_2B_SHAPE = DecoderConfig(18, 2048, 8, 1, 256, 16384, 256000, fmt=0)
+GEMMA_7B_SHAPE = DecoderConfig(28, 3072, 16, 16, 256, 24576, 256000, fmt=1)
+
+
+def _rmsnorm(x, w, eps):
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w).to(x.dtype)
+
+
+def _rope(x, pos, base):
+    """x [B, T, heads, d], pos [T]."""
+    d = x.shape[-1]
+    inv = 1.0 / (base ** (torch.arange(0, d, 2, device=x.device, dtype=torch.float32) / d))
+    ang = pos.float()[:, None] * inv[None, :]
+    cos, sin = ang.cos()[None, :, None, :], ang.sin()[None, :, None, :]
+    xf = x.float()
+    x1, x2 = xf[..., : d // 2], xf[..., d // 2:]
+    return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1).to(x.dtype)
+
+
+class QuantDecoder:
+    def __init__(self, cfg: DecoderConfig, lin: dict, embed, norms: dict, act_dtype=torch.bfloat16, rank: int = 0,
+                 world: int = 1, max_seq: int = 4096, max_batch: int = 1):
+        self.cfg, self.lin, self.embed, self.norms = cfg, lin, embed, norms
+        self.act_dtype, self.rank, self.world = act_dtype, rank, world
+        self.kv_sharded = cfg.n_kv_heads % world == 0 and cfg.n_kv_heads >= world
+        self.h_local = cfg.n_heads // world
+        self.kv_local = cfg.n_kv_heads // world if self.kv_sharded else cfg.n_kv_heads
+        dev = embed.device
+        self.k_cache = [torch.zeros((max_batch, max_seq, self.kv_local, cfg.head_dim), dtype=act_dtype, device=dev)
+                        for _ in range(cfg.layers)]
+        self.v_cache = [torch.zeros_like(self.k_cache[0]) for _ in range(cfg.layers)]
+        self.pos = 0
+
+    # ---- construction -------------------------------------------------------------------------------
+    @staticmethod
+    def _wrap(cfg, get, rank, world):
+        """get(name, axis) -> PackedWeight shard.  Builds the (possibly tensor-parallel) projection objects."""
+        lin = {}
+        kv_sharded = cfg.n_kv_heads % world == 0 and cfg.n_kv_heads >= world
+        for l in range(cfg.layers):
+            lin[f"l{l}.q"] = QuantLinear(get(f"l{l}.q", "n"))
+            lin[f"l{l}.k"] = QuantLinear(get(f"l{l}.k", "n" if kv_sharded else None))
+            lin[f"l{l}.v"] = QuantLinear(get(f"l{l}.v", "n" if kv_sharded else None))
+            lin[f"l{l}.gate"] = QuantLinear(get(f"l{l}.gate", "n"))
+            lin[f"l{l}.up"] = QuantLinear(get(f"l{l}.up", "n"))
+            o, d = QuantLinear(get(f"l{l}.o", "k")), QuantLinear(get(f"l{l}.down", "k"))
+            lin[f"l{l}.o"] = parallel.RowParallelLinear(o) if world > 1 else o
+            lin[f"l{l}.down"] = parallel.RowParallelLinear(d) if world > 1 else d
+        head = LMHead(get("lm_head", "n"))
+        lin["lm_head"] = head
+        return lin
+
+    @classmethod
+    def from_numpy(cls, cfg: DecoderConfig, w: dict, act_dtype=torch.float32, rank=0, world=1, **kw):
+        """w: name -> (codes, scales) for projections, arrays for 'embed', norms (as oracle.model.random_weights)."""
+        def get(name, axis):
+            pw = PackedWeight(w[name][0], w[name][1], cfg.fmt, upload=(world == 1 or axis is None))
+            return pw if (world == 1 or axis is None) else shard(pw, axis, rank, world)
+        lin = cls._wrap(cfg, get, rank, world)
+        dev = torch.device("cuda", torch.cuda.current_device())
+        embed = torch.from_numpy(w["embed"]).to(dev)
+        norms = {k: torch.from_numpy(v).to(dev) for k, v in w.items() if "norm" in k}
+        return cls(cfg, lin, embed, norms, act_dtype, rank, world, **kw)
+
+    @classmethod
+    def random(cls, cfg: DecoderConfig, seed=0, act_dtype=torch.bfloat16, rank=0, world=1, **kw):
+        """Random-init N(0,0.02) packed weights generated on the device, shard by shard (synthetic benchmark
+        weights: each shard has its own seed, so a sharded model is not a slice of the unsharded one)."""
+        shapes = {"q": (cfg.n_heads * cfg.head_dim, cfg.hidden), "k": (cfg.n_kv_heads * cfg.head_dim, cfg.hidden),
+                  "v": (cfg.n_kv_heads * cfg.head_dim, cfg.hidden), "o": (cfg.hidden, cfg.n_heads * cfg.head_dim),
+                  "gate": (cfg.ffn, cfg.hidden), "up": (cfg.ffn, cfg.hidden), "down": (cfg.hidden, cfg.ffn),
+                  "lm_head": (cfg.vocab, cfg.hidden)}
+
+        def get(name, axis):
+            N, K = shapes[name.split(".")[-1]]
+            if world > 1 and axis == "n":
+                N //= world
+            if world > 1 and axis == "k":
+                K //= world
+            gen = torch.Generator(device="cuda").manual_seed(zlib.crc32(f"{seed}:{name}:{rank if axis else 0}".encode()))
+            codes, scales = make_device_weight(torch, N, K, cfg.fmt, gen)
+            return PackedWeight.from_device(codes, scales, cfg.fmt)
+        lin = cls._wrap(cfg, get, rank, world)
+        dev = torch.device("cuda", torch.cuda.current_device())
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        embed = torch.randn((cfg.vocab, cfg.hidden), device=dev, generator=g, dtype=torch.float32).to(act_dtype)
+        norms = {f"l{l}.norm{i}": torch.ones(cfg.hidden, device=dev) for l in range(cfg.layers) for i in (1, 2)}
+        norms["norm_f"] = torch.ones(cfg.hidden, device=dev)
+        return cls(cfg, lin, embed, norms, act_dtype, rank, world, **kw)
+
+    # ---- forward ---------------------------------------------------------------------------------------
+    def reset(self):
+        self.pos = 0
+
+    def hidden_states(self, tokens):
+        """tokens int64 [B, T] -> final normalised hidden states [B, T, hidden]; appends to the KV cache."""
+        c = self.cfg
+        B, T = tokens.shape
+        x = self.embed[tokens].to(self.act_dtype)
+        pos = torch.arange(self.pos, self.pos + T, device=x.device)
+        S = self.pos + T
+        for l in range(c.layers):
+            h = _rmsnorm(x, self.norms[f"l{l}.norm1"], c.eps)
+            q = self.lin[f"l{l}.q"](h).to(self.act_dtype).reshape(B, T, self.h_local, c.head_dim)
+            k = self.lin[f"l{l}.k"](h).to(self.act_dtype).reshape(B, T, self.kv_local, c.head_dim)
+            v = self.lin[f"l{l}.v"](h).to(self.act_dtype).reshape(B, T, self.kv_local, c.head_dim)
+            q, k = _rope(q, pos, c.rope_base), _rope(k, pos, c.rope_base)
+            self.k_cache[l][:B, self.pos:S] = k
+            self.v_cache[l][:B, self.pos:S] = v
+            kk, vv = self.k_cache[l][:B, :S], self.v_cache[l][:B, :S]
+            rep = self.h_local // self.kv_local
+            if rep > 1:
+                kk, vv = kk.repeat_interleave(rep, dim=2), vv.repeat_interleave(rep, dim=2)
+            mask = (torch.arange(S, device=x.device)[None, :] <= pos[:, None])      # [T, S]
+            o = F.scaled_dot_product_attention(q.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2), attn_mask=mask)
+            o = o.transpose(1, 2).reshape(B, T, self.h_local * c.head_dim)
+            x = x + self.lin[f"l{l}.o"](o.contiguous()).to(self.act_dtype)
+            h = _rmsnorm(x, self.norms[f"l{l}.norm2"], c.eps)
+            a = F.gelu(self.lin[f"l{l}.gate"](h), approximate="tanh") * self.lin[f"l{l}.up"](h)
+            x = x + self.lin[f"l{l}.down"](a.to(self.act_dtype)).to(self.act_dtype)
+        self.pos = S
+        return _rmsnorm(x, self.norms["norm_f"], c.eps)
+
+    def logits(self, tokens):
+        h = self.hidden_states(tokens)
+        B, T, _ = h.shape
+        lg = self.lin["lm_head"](h.reshape(B * T, -1))
+        if self.world > 1:
+            parts = [torch.empty_like(lg) for _ in range(self.world)]
+            torch.distributed.all_gather(parts, lg.contiguous())
+            lg = torch.cat(parts, dim=-1)
+        return lg.reshape(B, T, -1)
+
+    def next_tokens(self, tokens):
+        """Greedy next token for every sequence: tokens [B, T] -> ids [B] (only the last position is projected)."""
+        h = self.hidden_states(tokens)[:, -1].contiguous()
+        head = self.lin["lm_head"]
+        if self.world > 1:
+            return parallel.VocabParallelHead(head, self.cfg.vocab // self.world).greedy(h)
+        return head.greedy(h).long()
+
+    def generate(self, prompt, n_new):
+        """prompt int64 [B, T] -> generated ids [B, n_new] (greedy)."""
+        tok = self.next_tokens(prompt)
+        out = []
+        for _ in range(n_new):
+            out.append(tok)
+            tok = self.next_tokens(tok[:, None])
+        return torch.stack(out, dim=1)
+
+    def linear_bytes_per_token(self) -> float:
+        """Algorithmic packed-weight bytes every decoded token streams on this rank (codes + scales)."""
+        tot = 0
+        for name, l in self.lin.items():
+            q = l.linear if isinstance(l, parallel.RowParallelLinear) else l
+            tot += q.pw.nbytes
+        return float(tot)

@@ -1,0 +1,55 @@
+"""End-to-end decoder (quantized linears + PyTorch glue) against the numpy decoder oracle, and the
+tensor-parallel decoder on 2 GPUs (NCCL) against the single-GPU one."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from oracle import model as omodel
+from oracle import spec
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+SMALL = dict(layers=2, hidden=256, n_heads=4, n_kv_heads=1, head_dim=64, ffn=512, vocab=1024)
+
+
+@pytest.mark.parametrize("fmt", [0, 1])
+def test_decoder_logits_and_greedy_tokens(cuda_lib, fmt):
+    import torch
+    from chadslab_b200.decoder import DecoderConfig, QuantDecoder
+    cfg = dict(SMALL, fmt=fmt)
+    w = omodel.random_weights(cfg, seed=3)
+    rng = np.random.default_rng(0)
+    prompt = rng.integers(0, cfg["vocab"], 8)
+    ref = omodel.OracleDecoder(cfg, w)
+    ref_tokens, ref_logits = ref.generate(list(prompt), 4)            # logits of the last prompt position + 4 steps
+    dec = QuantDecoder.from_numpy(DecoderConfig(**cfg), w, act_dtype=torch.float32, max_seq=64)
+    pt = torch.from_numpy(prompt)[None].cuda()
+    lg = dec.logits(pt)[0, -1].cpu().numpy()
+    assert spec.rel_err(lg, ref_logits[0]) <= 1e-3                     # tolerance stated by the specification
+    toks = []
+    tok = int(np.argmax(lg))
+    for i in range(4):
+        toks.append(tok)
+        lg = dec.logits(torch.tensor([[tok]], device="cuda"))[0, -1].cpu().numpy()
+        assert spec.rel_err(lg, ref_logits[i + 1]) <= 1e-3
+        tok = int(np.argmax(lg))
+    assert toks == ref_tokens
+    # the fused greedy entry gives the same tokens
+    dec.reset()
+    out = dec.generate(pt, 4)[0].cpu().numpy().tolist()
+    assert out == ref_tokens
+
+
+def test_tensor_parallel_decoder_two_gpus(cuda_lib):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29531",
+                        os.path.join(ROOT, "tests", "tp_worker.py")], capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "tp_worker ok" in r.stdout
