@@ -9,7 +9,7 @@ import os
 import threading
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libb200q.so")
+LIB_PATH = os.environ.get("B200Q_LIB") or os.path.join(HERE, "libb200q.so")   # B200Q_LIB: load another build (A/B tuning)
 
 FMT_Q8, FMT_Q4 = 0, 1
 DT_F32, DT_BF16 = 0, 1

@@ -196,8 +196,8 @@ int bq_weight_create(const void* codes, const void* scales, int64_t N, int64_t K
     cudaFree(w->codes); cudaFree(w->scales); delete w;
     return fail_cuda(e, "cudaMemcpy(weight upload)");
   }
-  if (fmt == BQ_FMT_Q4G32) {
-    rc = launch_q4_repack(w->codes, w->codes_bytes, true, 0);
+  {
+    rc = launch_device_encode(w->codes, w->codes_bytes, fmt, true, 0);
     if (rc == BQ_OK && cudaStreamSynchronize(0) != cudaSuccess) rc = fail(BQ_ERR_CUDA, "repack failed");
     if (rc) { cudaFree(w->codes); cudaFree(w->scales); delete w; return rc; }
   }
@@ -219,7 +219,7 @@ int bq_weight_create_device(const void* d_codes, const void* d_scales, int64_t N
   if (w->codes_bytes) e = cudaMemcpyAsync(w->codes, d_codes, w->codes_bytes, cudaMemcpyDeviceToDevice, s);
   if (e == cudaSuccess && w->scales_bytes)
     e = cudaMemcpyAsync(w->scales, d_scales, w->scales_bytes, cudaMemcpyDeviceToDevice, s);
-  if (e == cudaSuccess && fmt == BQ_FMT_Q4G32 && launch_q4_repack(w->codes, w->codes_bytes, true, s) != BQ_OK)
+  if (e == cudaSuccess && launch_device_encode(w->codes, w->codes_bytes, fmt, true, s) != BQ_OK)
     e = cudaErrorUnknown;
   if (e == cudaSuccess) e = cudaStreamSynchronize(s);
   if (e != cudaSuccess) {
@@ -260,7 +260,10 @@ int bq_weight_export(bq_weight_t h, void* codes_out, void* scales_out) {
   if (!w) return BQ_ERR_HANDLE;
   if (w->N > 0 && (!codes_out || !scales_out)) return fail(BQ_ERR_ARG, "output pointers must not be null");
   if (w->codes_bytes) BQ_CUDA(cudaMemcpy(codes_out, w->codes, w->codes_bytes, cudaMemcpyDeviceToHost));
-  if (w->fmt == BQ_FMT_Q4G32) {   // undo the device nibble order (a pure permutation inside each 32-bit word)
+  if (w->fmt == BQ_FMT_Q8G32) {   // device bytes are code + 128
+    uint32_t* p = static_cast<uint32_t*>(codes_out);
+    for (size_t i = 0; i < w->codes_bytes / 4; ++i) p[i] ^= 0x80808080u;
+  } else {                        // undo the device nibble order (a pure permutation inside each 32-bit word)
     uint32_t* p = static_cast<uint32_t*>(codes_out);
     for (size_t i = 0; i < w->codes_bytes / 4; ++i) {
       const uint32_t v = p[i];

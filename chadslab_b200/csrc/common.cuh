@@ -80,10 +80,11 @@ int moe_tc_prepare(Moe* m, const std::vector<const uint8_t*>* codes, const std::
 void moe_tc_release(Moe* m);
 int launch_moe_experts_tc(const Moe* m, const void* xp, const int32_t* offsets, int64_t P, void* hbuf, float* out,
                           cudaStream_t s);
-// Q4 device layout: within every 32-bit word the 8 nibbles are stored in the order
-// e0,e2,e4,e6,e1,e3,e5,e7 (element e_i of the interface layout), so that masking with 0x000F000F /
-// 0x00F000F0 yields adjacent element pairs.  A pure permutation; repack is its own inverse pair.
-int launch_q4_repack(uint8_t* codes, size_t bytes, bool to_device_layout, cudaStream_t s);
+// Device encoding of the codes (a bijection of the interface bytes, undone by bq_weight_export):
+//   Q4: within every 32-bit word the 8 nibbles are stored in the order e0,e2,e4,e6,e1,e3,e5,e7 (element
+//       e_i of the interface layout), so that masking with 0x000F000F / 0x00F000F0 yields adjacent pairs;
+//   Q8: every byte holds code + 128 (sign bit flipped), so mantissa insertion needs no sign fix-up.
+int launch_device_encode(uint8_t* codes, size_t bytes, int fmt, bool to_device_layout, cudaStream_t s);
 int launch_argmax(const void* logits, int dtype, int64_t M, int64_t N, int32_t* out, cudaStream_t s);
 
 // ---- device helpers --------------------------------------------------------------------------
@@ -115,7 +116,7 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(f
 }
 
 // Exact integer-code -> fp32 conversions without the (slow) I2F pipe.
-// Q8: `v` holds four int8 codes already XOR-ed with 0x80808080 (so each byte is code+128).
+// Q8: `v` holds four device bytes, each code + 128.
 // Byte `I` is dropped into the mantissa of 2^23, giving 8388608 + code + 128 exactly.
 template <int I> __device__ __forceinline__ float q8_byte_to_float(uint32_t v_xor80) {
   constexpr uint32_t sel = 0x7650u | (uint32_t)I;

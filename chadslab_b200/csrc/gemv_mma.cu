@@ -35,9 +35,9 @@ __device__ __forceinline__ void mma_f16_16816(float* d, const uint32_t* a, uint3
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// 4 int8 codes (one word) -> two fp16x2 registers holding the exact codes (c0,c1), (c2,c3)
-__device__ __forceinline__ void q8_word_to_h2(uint32_t w, uint32_t& lo, uint32_t& hi) {
-  const uint32_t v = w ^ 0x80808080u;
+// 4 int8 codes (one word, stored as code + 128 on the device) -> two fp16x2 registers holding the exact
+// codes (c0,c1), (c2,c3): 0x6400 | byte = 1024 + byte, minus 1152
+__device__ __forceinline__ void q8_word_to_h2(uint32_t v, uint32_t& lo, uint32_t& hi) {
   uint32_t p0 = __byte_perm(v, 0x64646464u, 0x4140);
   uint32_t p1 = __byte_perm(v, 0x64646464u, 0x4342);
   const __half2 off = __float2half2_rn(1152.0f);

@@ -203,7 +203,7 @@ template <int FMT> struct WordDotM;
 template <> struct WordDotM<BQ_FMT_Q8G32> {
   static constexpr int WPW = 4;
   __device__ static __forceinline__ void cvt(uint32_t word, float* f) {
-    const uint32_t v = word ^ 0x80808080u;
+    const uint32_t v = word;   // device bytes are code + 128
     f[0] = q8_byte_to_float<0>(v); f[1] = q8_byte_to_float<1>(v);
     f[2] = q8_byte_to_float<2>(v); f[3] = q8_byte_to_float<3>(v);
   }

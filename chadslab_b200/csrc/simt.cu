@@ -34,7 +34,7 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict_
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       if (FMT == BQ_FMT_Q8G32) {
-        const uint32_t v = words[q] ^ 0x80808080u;
+        const uint32_t v = words[q];   // device bytes are code + 128
         o[4 * q + 0] = from_float<OT>(q8_byte_to_float<0>(v) * s);
         o[4 * q + 1] = from_float<OT>(q8_byte_to_float<1>(v) * s);
         o[4 * q + 2] = from_float<OT>(q8_byte_to_float<2>(v) * s);
@@ -63,7 +63,7 @@ __global__ void __launch_bounds__(256) unpack_kernel(const uint8_t* __restrict__
        i += (int64_t)gridDim.x * blockDim.x) {
     const uint32_t v = reinterpret_cast<const uint32_t*>(codes)[i];
     if (FMT == BQ_FMT_Q8G32) {
-      reinterpret_cast<uint32_t*>(out)[i] = v;
+      reinterpret_cast<uint32_t*>(out)[i] = v ^ 0x80808080u;   // device bytes are code + 128
     } else {
 #pragma unroll
       for (int j = 0; j < 8; ++j) out[8 * i + q4_elem(j)] = (int8_t)((int)((v >> (4 * j)) & 0xF) - 8);
@@ -71,10 +71,13 @@ __global__ void __launch_bounds__(256) unpack_kernel(const uint8_t* __restrict__
   }
 }
 
-// interface nibble order <-> device nibble order, in place, one thread per word
-__global__ void __launch_bounds__(256) q4_repack_kernel(uint32_t* __restrict__ words, int64_t n, int to_device) {
+// interface encoding <-> device encoding, in place, one thread per word.
+// Q8: every byte is stored as code + 128 (flip the sign bit), so unpacking needs no sign fix-up.
+// Q4: nibble order inside the word (see q4_elem).
+__global__ void __launch_bounds__(256) q4_repack_kernel(uint32_t* __restrict__ words, int64_t n, int to_device, int q8) {
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
     const uint32_t v = words[i];
+    if (q8) { words[i] = v ^ 0x80808080u; continue; }
     uint32_t o = 0;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -114,10 +117,11 @@ int launch_dequant(const Weight* w, void* out, int out_dtype, cudaStream_t s) {
   return BQ_OK;
 }
 
-int launch_q4_repack(uint8_t* codes, size_t bytes, bool to_device_layout, cudaStream_t s) {
+int launch_device_encode(uint8_t* codes, size_t bytes, int fmt, bool to_device_layout, cudaStream_t s) {
   if (bytes == 0) return BQ_OK;
   const int64_t n = (int64_t)(bytes / 4);
-  q4_repack_kernel<<<grid_for(n, 256), 256, 0, s>>>(reinterpret_cast<uint32_t*>(codes), n, to_device_layout ? 1 : 0);
+  q4_repack_kernel<<<grid_for(n, 256), 256, 0, s>>>(reinterpret_cast<uint32_t*>(codes), n, to_device_layout ? 1 : 0,
+                                                    fmt == BQ_FMT_Q8G32 ? 1 : 0);
   count_launch();
   BQ_CUDA(cudaGetLastError());
   return BQ_OK;
@@ -146,7 +150,7 @@ template <int FMT> struct WordDot;
 template <> struct WordDot<BQ_FMT_Q8G32> {
   static constexpr int WPW = 4;  // weights per word
   __device__ static __forceinline__ float run(uint32_t word, const float* xv, float acc) {
-    const uint32_t v = word ^ 0x80808080u;
+    const uint32_t v = word;   // device bytes are code + 128
     acc = fmaf(q8_byte_to_float<0>(v), xv[0], acc);
     acc = fmaf(q8_byte_to_float<1>(v), xv[1], acc);
     acc = fmaf(q8_byte_to_float<2>(v), xv[2], acc);

@@ -181,7 +181,7 @@ __device__ __forceinline__ void cvt_q8_chunk(const uint4 w, const __half2 s2, ui
   const __half2 off = __float2half2_rn(1152.0f);   // 1024 (magic) + 128 (sign offset)
 #pragma unroll
   for (int q = 0; q < 4; ++q) {
-    const uint32_t v = words[q] ^ 0x80808080u;
+    const uint32_t v = words[q];   // device bytes are code + 128
     uint32_t p0 = __byte_perm(v, 0x64646464u, 0x4140);   // (1024 + b0, 1024 + b1) as fp16x2
     uint32_t p1 = __byte_perm(v, 0x64646464u, 0x4342);   // (1024 + b2, 1024 + b3)
     __half2 h0 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&p0), off), s2);
