@@ -80,14 +80,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   if (mbar_try(bar, parity, 2000u)) return true;
   return mbar_wait_slow(bar, parity, abort_flag);
 }
-// Warp-collective wait: lane 0 does the waiting, the result is broadcast, then every lane performs
-// one (already satisfied) test of its own so that it has observed the phase itself.
+// Warp-collective wait: lane 0 does the waiting (32 lanes polling one mbarrier word serialise on it and
+// cost ~300 cycles even when the phase is complete); __syncwarp orders the other lanes' later reads of
+// the data behind lane 0's observation of the phase.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int lane) {
   uint32_t ok = 0;
   if (lane == 0) ok = mbar_wait(bar, parity, abort_flag) ? 1u : 0u;
   ok = __shfl_sync(0xffffffffu, ok, 0);
-  if (ok && lane != 0) ok = mbar_try(bar, parity, 0u) ? 1u : 0u;
-  return __all_sync(0xffffffffu, ok != 0);
+  return ok != 0;
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int c0, int c1, uint32_t bar) {
   asm volatile(
@@ -137,8 +137,10 @@ __host__ __device__ constexpr uint32_t umma_idesc(int bn) {
 }
 
 // ---- shared-memory plan -------------------------------------------------------------------------
-template <int FMT, int BN, bool GATED> struct TcPlan {
-  static constexpr int NW = GATED ? 2 : 1;
+// MODE: 0 = one weight tile; 1 = GATED (gate and up matrices, SwiGLU epilogue); 2 = DUAL (rows n0..n0+127 and
+// n0+128..n0+255 of the same matrix share the activation tile: halves the activation traffic per MAC)
+template <int FMT, int BN, int MODE> struct TcPlan {
+  static constexpr int NW = MODE ? 2 : 1;
   static constexpr int RAW_ROW = (FMT == BQ_FMT_Q8G32) ? 64 : 32;       // code bytes per row per k-step
   static constexpr int RAW = TC_ROWS * RAW_ROW;                           // per weight
   static constexpr int XT = BN * 128;                                     // activation tile bytes
@@ -224,9 +226,10 @@ __device__ long long g_tc_trace[3][64][6];
 #endif
 
 // ---- the kernel ----------------------------------------------------------------------------------------
-template <int FMT, int BN, bool GATED>
+template <int FMT, int BN, int MODE>
 __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_constant__ TcArgs args) {
-  using P = TcPlan<FMT, BN, GATED>;
+  using P = TcPlan<FMT, BN, MODE>;
+  constexpr bool GATED = MODE == 1, DUAL = MODE == 2, TWO = MODE != 0;
   constexpr int NW = P::NW, S = P::S, NA = P::NA;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -247,7 +250,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   // ---- which tile ------------------------------------------------------------------------------------
-  int64_t n0 = (int64_t)blockIdx.y * TC_ROWS;
+  int64_t n0 = (int64_t)blockIdx.y * TC_ROWS * (DUAL ? 2 : 1);
+  const int n1_off = DUAL ? TC_ROWS : 0;      // row offset of the second weight tile
   int64_t m0, m_end;
   const CUtensorMap *tmw0, *tms0, *tmw1, *tms1;
   if (args.moe) {
@@ -298,11 +302,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
         uint8_t* st = stages + s * P::STAGE;
         tma_load_2d(smem_u32(st), &args.tm_x, ks * TC_BK, (int)m0, fb);
         tma_load_2d(smem_u32(st + P::XT), tmw0, ks * P::RAW_ROW, (int)n0, fb);
-        if (GATED) tma_load_2d(smem_u32(st + P::XT + P::RAW), tmw1, ks * P::RAW_ROW, (int)n0, fb);
+        if (TWO) tma_load_2d(smem_u32(st + P::XT + P::RAW), tmw1, ks * P::RAW_ROW, (int)n0 + n1_off, fb);
         if (with_scales) {
           uint8_t* sc = sc_tiles + ((ks >> 2) % TC_SC_SLOTS) * NW * P::SCT;
           tma_load_2d(smem_u32(sc), tms0, (ks >> 2) * 8, (int)n0, fb);
-          if (GATED) tma_load_2d(smem_u32(sc + P::SCT), tms1, (ks >> 2) * 8, (int)n0, fb);
+          if (TWO) tma_load_2d(smem_u32(sc + P::SCT), tms1, (ks >> 2) * 8, (int)n0 + n1_off, fb);
         }
         TC_TRACE(0, ks, 1);
       }
@@ -412,8 +416,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
         if (m0 + c0 >= m_end) break;             // warp-uniform
         uint32_t v[16], u[16];
         tc_ld16(tbase + (uint32_t)c0, v);
-        if (GATED) tc_ld16(tbase + (uint32_t)(BN + c0), u);
+        if (TWO) tc_ld16(tbase + (uint32_t)(BN + c0), u);
         tc_ld_wait();
+        if (DUAL && n + TC_ROWS < args.N) {       // second tile: output rows n + 128
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int64_t m = m0 + c0 + j;
+            if (m < m_end) {
+              const float f2 = __uint_as_float(u[j]) * args.xscale[m];
+              if (args.out_dtype == BQ_DT_F32) reinterpret_cast<float*>(args.out)[m * args.ldy + n + TC_ROWS] = f2;
+              else reinterpret_cast<__nv_bfloat16*>(args.out)[m * args.ldy + n + TC_ROWS] = __float2bfloat16_rn(f2);
+            }
+          }
+        }
         if (n < args.N) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
@@ -437,6 +452,266 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
   }
 
   // ---- teardown ------------------------------------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(args.status, BQ_ERR_TIMEOUT);
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)P::TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// =================================================================================================
+// Variant with the A operand in tensor memory (decode / mid-size batches, BN <= 128).
+//
+// Differences from qgemm_tc_kernel: a pipeline step covers 128 k (half as many barrier round trips per
+// byte); the converted fp16 weights never touch shared memory — every converter thread owns one weight
+// row (its TMEM lane), reads that row's 64 bytes of codes from the (TMA-swizzled, so bank-conflict-free)
+// stage, converts them in registers and writes them with tcgen05.st into one of two A buffers in TMEM;
+// the issuer uses the tensor-memory form of tcgen05.mma (A from TMEM, B from shared memory).  Shared
+// memory then only holds packed codes, activations and scales, so two CTAs fit on an SM.
+// TMEM columns: [0, BN) accumulator, then two A buffers of 64 columns (= 128 k) at 128 / 192 (BN <= 128,
+// 256 columns allocated, two CTAs per SM) or at 256 / 320 (BN = 256, 512 columns allocated).
+// =================================================================================================
+constexpr int T2_BK = 128;
+constexpr int T2_ACOLS = 64;
+
+// NW = 2: the CTA converts two 128-row weight tiles (rows n0.. and n0+128..) per activation tile, which halves
+// the activation bytes fetched per multiply-add (the activation tiles come from L2, the scarcer resource of
+// large batches); then BN = 128 and all 512 TMEM columns are in use (2 accumulators + 2 x 2 A buffers).
+template <int FMT, int BN, int NW> struct T2Plan {
+  static constexpr int RAW_ROW = (FMT == BQ_FMT_Q8G32) ? 128 : 64;      // code bytes per row per step
+  static constexpr int RAW = TC_ROWS * RAW_ROW;
+  static constexpr int XT = 2 * BN * 128;                                 // two 64-k swizzle atoms
+  static constexpr int SCT = TC_ROWS * 16;                                // 8 fp16 scales per row = 256 k = 2 steps
+  static constexpr int STAGE = ((NW * RAW + XT + 1023) / 1024) * 1024;
+  static constexpr int FIXED = TC_SC_SLOTS * NW * SCT + 1024 + 1024;
+  static constexpr int BUDGET = (NW * BN <= 128 ? 100 : 200) * 1024;      // two CTAs per SM up to BN = 128
+  static constexpr int S_RAW = (BUDGET - FIXED) / STAGE;
+  static constexpr int S = S_RAW > 4 ? 4 : (S_RAW < 2 ? 2 : S_RAW);       // S <= 2*SC_SLOTS - 1 = 5
+  static constexpr int SMEM = FIXED + S * STAGE;
+  static constexpr int ACOL0 = NW * BN <= 128 ? 128 : 256;                // first A-buffer column
+  static constexpr int TMEM_COLS = NW * BN <= 128 ? 256 : 512;
+  static_assert(NW * BN <= 256 && BN % 16 == 0, "accumulators must fit below the A buffers");
+  static_assert(SMEM <= 227 * 1024, "shared memory plan too large");
+};
+
+struct T2Args {
+  CUtensorMap tm_x;      // fp16 activations [M, K], box 64 x BN, 128B swizzle
+  CUtensorMap tm_w;      // codes: Q8 box 128 B x 128 rows (128B swizzle); Q4 box 64 B x 128 rows (64B swizzle)
+  CUtensorMap tm_s;      // scales fp16 [N, K/32], box 8 x 128
+  const float* xscale;
+  void* out;
+  int64_t ldy, N, K, M;
+  int out_dtype;
+  int* status;
+};
+
+__device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]),
+        "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]),
+        "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
+__device__ __forceinline__ void tc_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+template <int FMT, int BN, int NW>
+__global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tmem_kernel(const __grid_constant__ T2Args args) {
+  using P = T2Plan<FMT, BN, NW>;
+  constexpr int S = P::S, NA = 2;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* stages = smem;                                  // per stage: [x atom 0][x atom 1][codes tile 0][codes tile 1]
+  uint8_t* sc_tiles = stages + S * P::STAGE;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sc_tiles + TC_SC_SLOTS * NW * P::SCT);
+  uint64_t* full = bars;               // [S]  TMA landed
+  uint64_t* empty = bars + S;          // [S]  converter warps (8) + MMA commit (1)
+  uint64_t* a_full = bars + 2 * S;     // [NA] converter warps (8)
+  uint64_t* a_empty = a_full + NA;     // [NA] MMA commit (1)
+  uint64_t* acc_full = a_empty + NA;   // [1]
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(acc_full + 1);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t n0 = (int64_t)blockIdx.y * TC_ROWS * NW;
+  const int64_t m0 = (int64_t)blockIdx.x * BN;
+  const int64_t m_end = args.M;
+  const int ksteps = (int)(args.K / T2_BK);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < S; ++i) { mbar_init(smem_u32(&full[i]), 1); mbar_init(smem_u32(&empty[i]), TC_CONV_WARPS + 1); }
+    for (int i = 0; i < NA; ++i) { mbar_init(smem_u32(&a_full[i]), TC_CONV_WARPS); mbar_init(smem_u32(&a_empty[i]), 1); }
+    mbar_init(smem_u32(acc_full), 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"((uint32_t)P::TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ================= producer =================
+    if (lane == 0) {
+      for (int ks = 0; ks < ksteps; ++ks) {
+        const int s = ks % S;
+        const uint32_t ph = (uint32_t)(ks / S) & 1u;
+        if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1u, abort_flag)) break;
+        const bool with_scales = (ks & 1) == 0;
+        const uint32_t fb = smem_u32(&full[s]);
+        mbar_expect_tx(fb, NW * P::RAW + P::XT + (with_scales ? NW * P::SCT : 0));
+        uint8_t* st = stages + s * P::STAGE;
+        tma_load_2d(smem_u32(st), &args.tm_x, ks * T2_BK, (int)m0, fb);
+        tma_load_2d(smem_u32(st + BN * 128), &args.tm_x, ks * T2_BK + 64, (int)m0, fb);
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+          tma_load_2d(smem_u32(st + P::XT + w * P::RAW), &args.tm_w, ks * P::RAW_ROW, (int)n0 + w * TC_ROWS, fb);
+          if (with_scales)
+            tma_load_2d(smem_u32(sc_tiles + (((ks >> 1) % TC_SC_SLOTS) * NW + w) * P::SCT), &args.tm_s, (ks >> 1) * 8,
+                        (int)n0 + w * TC_ROWS, fb);
+        }
+      }
+      if (*abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ================= MMA issuer =================
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(BN);
+      const uint64_t bdesc_stage0 = umma_desc_sw128(smem_u32(stages));
+      bool ok = true;
+      for (int ks = 0; ks < ksteps && ok; ++ks) {
+        const int s = ks % S, a = ks & 1;
+        const uint32_t aph = (uint32_t)(ks >> 1) & 1u;
+        ok = mbar_wait(smem_u32(&a_full[a]), aph, abort_flag);   // implies the stage (and its activations) landed
+        if (!ok) break;
+        TC_TRACE(1, ks, 1);
+        tc_fence_after();
+        const uint64_t bdesc0 = bdesc_stage0 + (uint64_t)((uint32_t)(s * P::STAGE) >> 4);   // stage offsets are < 256 KB
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+          const uint32_t a_tmem = tmem_base + (uint32_t)(P::ACOL0 + (w * NA + a) * T2_ACOLS);
+          const uint32_t d_tmem = tmem_base + (uint32_t)(w * BN);
+          tc_mma_f16_ts(d_tmem, a_tmem, bdesc0, idesc, ks > 0 ? 1u : 0u);
+#pragma unroll
+          for (int kk = 1; kk < T2_BK / 16; ++kk)
+            tc_mma_f16_ts(d_tmem, a_tmem + (uint32_t)(8 * kk),
+                          bdesc0 + (uint64_t)((((kk >> 2) * BN * 128) >> 4) + 2 * (kk & 3)), idesc, 1u);
+        }
+        TC_TRACE(1, ks, 2);
+        tc_commit(smem_u32(&a_empty[a]));
+        tc_commit(smem_u32(&empty[s]));
+        TC_TRACE(1, ks, 3);
+      }
+      if (ok) tc_commit(smem_u32(acc_full));
+    }
+  } else {
+    // ================= converters (one weight row per thread), then epilogue =================
+    const int lg = warp & 3;                 // TMEM lane group this warp may touch
+    const int half = (warp - 2) >> 2;        // which 64 k of the 128-k step this warp converts
+    const int row = lg * 32 + lane;
+    bool ok = true;
+    for (int ks = 0; ks < ksteps && ok; ++ks) {
+      const int s = ks % S, a = ks & 1;
+      const uint32_t ph = (uint32_t)(ks / S) & 1u, aph = (uint32_t)(ks >> 1) & 1u;
+      ok = mbar_wait_warp(smem_u32(&full[s]), ph, abort_flag, lane);
+      if (threadIdx.x == 64) TC_TRACE(2, ks, 0);
+      ok = ok && mbar_wait_warp(smem_u32(&a_empty[a]), aph ^ 1u, abort_flag, lane);
+      if (!ok) break;
+      if (threadIdx.x == 64) TC_TRACE(2, ks, 1);
+#pragma unroll
+      for (int w = 0; w < NW; ++w) {
+      const uint8_t* raw = stages + s * P::STAGE + P::XT + w * P::RAW + row * P::RAW_ROW;
+      const __half* scw = reinterpret_cast<const __half*>(sc_tiles + (((ks >> 1) % TC_SC_SLOTS) * NW + w) * P::SCT) + row * 8 + (ks & 1) * 4;
+      uint32_t regs[32];
+      if (FMT == BQ_FMT_Q8G32) {
+        // 64 codes = 4 chunks of 16; chunk c of the row sits at 16-byte slot c ^ (row & 7)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int c = 4 * half + i;
+          const uint4 wv = *reinterpret_cast<const uint4*>(raw + ((c ^ (row & 7)) << 4));
+          uint4 lo, hi;
+          cvt_q8_chunk(wv, __half2half2(scw[c >> 1]), lo, hi);
+          regs[8 * i + 0] = lo.x; regs[8 * i + 1] = lo.y; regs[8 * i + 2] = lo.z; regs[8 * i + 3] = lo.w;
+          regs[8 * i + 4] = hi.x; regs[8 * i + 5] = hi.y; regs[8 * i + 6] = hi.z; regs[8 * i + 7] = hi.w;
+        }
+      } else {
+        // 64 codes = 2 chunks of 32 (one group each); chunk c sits at 16-byte slot c ^ ((row >> 1) & 3)
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int c = 2 * half + i;
+          const uint4 wv = *reinterpret_cast<const uint4*>(raw + ((c ^ ((row >> 1) & 3)) << 4));
+          const __half2 s2 = __half2half2(scw[c]);
+          const uint4 q0 = cvt_q4_word(wv.x, s2), q1 = cvt_q4_word(wv.y, s2), q2 = cvt_q4_word(wv.z, s2),
+                      q3 = cvt_q4_word(wv.w, s2);
+          uint32_t* r = regs + 16 * i;
+          r[0] = q0.x; r[1] = q0.y; r[2] = q0.z; r[3] = q0.w; r[4] = q1.x; r[5] = q1.y; r[6] = q1.z; r[7] = q1.w;
+          r[8] = q2.x; r[9] = q2.y; r[10] = q2.z; r[11] = q2.w; r[12] = q3.x; r[13] = q3.y; r[14] = q3.z; r[15] = q3.w;
+        }
+      }
+      if (threadIdx.x == 64) TC_TRACE(2, ks, 2);
+      tc_st32(tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)(P::ACOL0 + (w * NA + a) * T2_ACOLS + 32 * half), regs);
+      }
+      tc_st_wait();
+      tc_fence_before();
+      if (threadIdx.x == 64) TC_TRACE(2, ks, 3);
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(smem_u32(&a_full[a]));
+        mbar_arrive(smem_u32(&empty[s]));
+      }
+      if (threadIdx.x == 64) TC_TRACE(2, ks, 4);
+    }
+    if (ok) ok = mbar_wait_warp(smem_u32(acc_full), 0u, abort_flag, lane);
+    if (ok) {
+      tc_fence_after();
+      const int64_t n = n0 + row;
+      const uint32_t tbase = tmem_base + ((uint32_t)(lg * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 16 * half; c0 < BN; c0 += 32) {
+        if (m0 + c0 >= m_end) break;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+          uint32_t v[16];
+          tc_ld16(tbase + (uint32_t)(w * BN + c0), v);
+          tc_ld_wait();
+          const int64_t nn = n + w * TC_ROWS;
+          if (nn < args.N) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int64_t m = m0 + c0 + j;
+              if (m < m_end) {
+                const float f = __uint_as_float(v[j]) * args.xscale[m];
+                if (args.out_dtype == BQ_DT_F32) reinterpret_cast<float*>(args.out)[m * args.ldy + nn] = f;
+                else reinterpret_cast<__nv_bfloat16*>(args.out)[m * args.ldy + nn] = __float2bfloat16_rn(f);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
   tc_fence_before();
   __syncthreads();
   if (threadIdx.x == 0 && *abort_flag) atomicExch(args.status, BQ_ERR_TIMEOUT);
@@ -585,10 +860,10 @@ bool tc_supported(int fmt, int64_t N, int64_t K, int x_dtype, int64_t M) {
   return x_dtype == BQ_DT_BF16 && M >= 1 && M < ((int64_t)1 << 31) && tc_shape_ok(N, K);
 }
 
-template <int FMT, int BN, bool GATED>
+template <int FMT, int BN, int MODE>
 static int tc_launch(const TcArgs& a, dim3 grid, cudaStream_t s) {
-  using P = TcPlan<FMT, BN, GATED>;
-  auto kern = qgemm_tc_kernel<FMT, BN, GATED>;
+  using P = TcPlan<FMT, BN, MODE>;
+  auto kern = qgemm_tc_kernel<FMT, BN, MODE>;
   static bool configured = false;
   if (!configured) {
     BQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P::SMEM));
@@ -603,15 +878,60 @@ static int tc_launch(const TcArgs& a, dim3 grid, cudaStream_t s) {
 template <int FMT>
 static int tc_dense_dispatch(const TcArgs& a, int bn, dim3 grid, cudaStream_t s) {
   switch (bn) {
-    case 16:  return tc_launch<FMT, 16, false>(a, grid, s);
-    case 32:  return tc_launch<FMT, 32, false>(a, grid, s);
-    case 64:  return tc_launch<FMT, 64, false>(a, grid, s);
-    case 128: return tc_launch<FMT, 128, false>(a, grid, s);
-    default:  return tc_launch<FMT, 256, false>(a, grid, s);
+    case 16:  return tc_launch<FMT, 16, 0>(a, grid, s);
+    case 32:  return tc_launch<FMT, 32, 0>(a, grid, s);
+    case 64:  return tc_launch<FMT, 64, 0>(a, grid, s);
+    case 128: return tc_launch<FMT, 128, 0>(a, grid, s);
+    case 256: return tc_launch<FMT, 256, 0>(a, grid, s);
+    default:  return tc_launch<FMT, 256, 2>(a, grid, s);      // 512: DUAL, 256 weight rows x 256 batch rows
   }
 }
 
 static int pick_bn(int64_t M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
+
+template <int FMT, int BN, int NW>
+static int t2_launch(const T2Args& a, dim3 grid, cudaStream_t s) {
+  using P = T2Plan<FMT, BN, NW>;
+  auto kern = qgemm_tmem_kernel<FMT, BN, NW>;
+  static bool configured = false;
+  if (!configured) {
+    BQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P::SMEM));
+    configured = true;
+  }
+  kern<<<grid, TC_THREADS, P::SMEM, s>>>(a);
+  count_launch();
+  BQ_CUDA(cudaGetLastError());
+  return BQ_OK;
+}
+template <int FMT>
+static int t2_dispatch(const T2Args& a, int bn, dim3 grid, cudaStream_t s) {
+  switch (bn) {
+    case 16:  return t2_launch<FMT, 16, 1>(a, grid, s);
+    case 32:  return t2_launch<FMT, 32, 1>(a, grid, s);
+    case 64:  return t2_launch<FMT, 64, 1>(a, grid, s);
+    case 128: return t2_launch<FMT, 128, 1>(a, grid, s);
+    case 256: return t2_launch<FMT, 256, 1>(a, grid, s);
+    default:  return t2_launch<FMT, 128, 2>(a, grid, s);      // 512: two weight tiles x 128 batch rows
+  }
+}
+static int dual_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("BQ_TC_DUAL");
+    v = e ? (atoi(e) != 0) : 1;
+  }
+  return v;
+}
+// BQ_TC_TMEM (tuning switch): 0 = shared-memory A tiles for every batch size, 1 = tensor-memory A for batches up
+// to 128, 2 (default) = tensor-memory A everywhere, 3 = same but never two weight tiles per CTA
+static int tmem_variant_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("BQ_TC_TMEM");
+    v = e ? atoi(e) : 2;
+  }
+  return v;
+}
 
 int launch_qlinear_tc(const uint8_t* codes, const __half* scales, int fmt, int64_t N, int64_t K, const void* x,
                       int x_dtype, int64_t M, void* y, int y_dtype, int64_t ldy, cudaStream_t s) {
@@ -622,15 +942,39 @@ int launch_qlinear_tc(const uint8_t* codes, const __half* scales, int fmt, int64
   const int bn = pick_bn(M);
   int rc = launch_x_prep(x, x_dtype, M, K, s);
   if (rc) return rc;
+  if (tmem_variant_enabled() >= (bn <= 128 ? 1 : 2)) {     // BQ_TC_TMEM: 1 = batches <= 128, 2 = all
+    T2Args t;
+    memset(&t, 0, sizeof(t));
+    // large batches are bound by the L2 -> SM traffic of codes + activations per multiply-add: 4-bit weights do
+    // better with 256 weight rows x 128 batch rows per CTA, int8 with 128 x 256 (measured)
+    const bool two = bn == 256 && fmt == BQ_FMT_Q4G32 && N >= 2 * TC_ROWS && tmem_variant_enabled() != 3;
+    const int bx = two ? 128 : bn;
+    if ((rc = x_map(&t.tm_x, g_x16, M, K, bx))) return rc;
+    const uint64_t rb = fmt == BQ_FMT_Q8G32 ? K : K / 2;
+    if ((rc = make_map_2d(&t.tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, codes, rb, (uint64_t)N, rb,
+                          fmt == BQ_FMT_Q8G32 ? 128 : 64, TC_ROWS,
+                          fmt == BQ_FMT_Q8G32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B))) return rc;
+    if ((rc = make_map_2d(&t.tm_s, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, scales, (uint64_t)(K / GROUP), (uint64_t)N,
+                          (uint64_t)(K / GROUP) * 2, 8, TC_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
+    t.xscale = g_xs; t.out = y; t.ldy = ldy; t.N = N; t.K = K; t.M = M; t.out_dtype = y_dtype; t.status = status_word();
+    const int rows_cta = two ? 2 * TC_ROWS : TC_ROWS;
+    dim3 grid2((unsigned)((M + bx - 1) / bx), (unsigned)((N + rows_cta - 1) / rows_cta));
+    const int sel = two ? 512 : bn;
+    return fmt == BQ_FMT_Q8G32 ? t2_dispatch<BQ_FMT_Q8G32>(t, sel, grid2, s) : t2_dispatch<BQ_FMT_Q4G32>(t, sel, grid2, s);
+  }
   if ((rc = x_map(&a.tm_x, g_x16, M, K, bn))) return rc;
   a.xscale = g_xs;
   if ((rc = tc_weight_maps(codes, scales, fmt, N, K, &a.tm_w[0], &a.tm_s[0]))) return rc;
   a.tm_w[1] = a.tm_w[0];
   a.tm_s[1] = a.tm_s[0];
   a.out = y; a.ldy = ldy; a.N = N; a.K = K; a.M = M; a.out_dtype = y_dtype; a.moe = 0; a.status = status_word();
-  dim3 grid((unsigned)((M + bn - 1) / bn), (unsigned)((N + TC_ROWS - 1) / TC_ROWS));
-  return fmt == BQ_FMT_Q8G32 ? tc_dense_dispatch<BQ_FMT_Q8G32>(a, bn, grid, s)
-                             : tc_dense_dispatch<BQ_FMT_Q4G32>(a, bn, grid, s);
+  // batches of 256 rows and more: each CTA converts 256 weight rows for one activation tile (DUAL)
+  const bool dual = bn == 256 && N >= 2 * TC_ROWS && dual_enabled();
+  const int rows_per_cta = dual ? 2 * TC_ROWS : TC_ROWS;
+  dim3 grid((unsigned)((M + bn - 1) / bn), (unsigned)((N + rows_per_cta - 1) / rows_per_cta));
+  const int sel = dual ? 512 : bn;
+  return fmt == BQ_FMT_Q8G32 ? tc_dense_dispatch<BQ_FMT_Q8G32>(a, sel, grid, s)
+                             : tc_dense_dispatch<BQ_FMT_Q4G32>(a, sel, grid, s);
 }
 
 // ---- MoE grouped experts ---------------------------------------------------------------------------------
@@ -674,7 +1018,7 @@ void moe_tc_release(Moe* m) {
   m->tc_state = nullptr;
 }
 
-template <int FMT, bool GATED>
+template <int FMT, int GATED>
 static int tc_moe_dispatch(const TcArgs& a, int bn, dim3 grid, cudaStream_t s) {
   switch (bn) {
     case 16:  return tc_launch<FMT, 16, GATED>(a, grid, s);
@@ -712,8 +1056,8 @@ int launch_moe_experts_tc(const Moe* m, const void* xp, const int32_t* offsets, 
   a.tm_list = st->gate_up; a.offsets = offsets; a.tiles = st->tiles; a.out = hbuf; a.ldy = m->F; a.N = m->F;
   a.K = m->H; a.M = P; a.out_dtype = BQ_DT_BF16; a.moe = 1; a.status = status_word();
   dim3 g1((unsigned)max_tiles, (unsigned)((m->F + TC_ROWS - 1) / TC_ROWS));
-  rc = m->fmt == BQ_FMT_Q8G32 ? tc_moe_dispatch<BQ_FMT_Q8G32, true>(a, bn, g1, s)
-                              : tc_moe_dispatch<BQ_FMT_Q4G32, true>(a, bn, g1, s);
+  rc = m->fmt == BQ_FMT_Q8G32 ? tc_moe_dispatch<BQ_FMT_Q8G32, 1>(a, bn, g1, s)
+                              : tc_moe_dispatch<BQ_FMT_Q4G32, 1>(a, bn, g1, s);
   if (rc) return rc;
   // down -> out (f32)
   TcArgs b;
@@ -724,8 +1068,8 @@ int launch_moe_experts_tc(const Moe* m, const void* xp, const int32_t* offsets, 
   b.tm_list = st->down; b.offsets = offsets; b.tiles = st->tiles; b.out = out; b.ldy = m->H; b.N = m->H;
   b.K = m->F; b.M = P; b.out_dtype = BQ_DT_F32; b.moe = 1; b.status = status_word();
   dim3 g2((unsigned)max_tiles, (unsigned)((m->H + TC_ROWS - 1) / TC_ROWS));
-  return m->fmt == BQ_FMT_Q8G32 ? tc_moe_dispatch<BQ_FMT_Q8G32, false>(b, bn, g2, s)
-                                : tc_moe_dispatch<BQ_FMT_Q4G32, false>(b, bn, g2, s);
+  return m->fmt == BQ_FMT_Q8G32 ? tc_moe_dispatch<BQ_FMT_Q8G32, 0>(b, bn, g2, s)
+                                : tc_moe_dispatch<BQ_FMT_Q4G32, 0>(b, bn, g2, s);
 }
 
 }  // namespace bq
