@@ -28,6 +28,24 @@ namespace bq {
 constexpr int GM_WARPS = 8;
 constexpr int GM_THREADS = GM_WARPS * 32;
 
+// ---- thread-block cluster helpers (split-K across the CTAs of a cluster, summed through distributed shared memory)
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(const float* local_ptr, uint32_t rank) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(local_ptr);
+  uint32_t ra;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(a), "r"(rank));
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
+  return v;
+}
+
 __device__ __forceinline__ void mma_f16_16816(float* d, const uint32_t* a, uint32_t b0, uint32_t b1) {
   asm volatile(
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -74,7 +92,7 @@ __device__ __forceinline__ void q4_word_to_h2(uint32_t v, uint32_t* o) {
 template <int FMT, int NV, int KSPLIT, typename XT, typename YT>
 __global__ void __launch_bounds__(GM_THREADS)
 qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ scales, const XT* __restrict__ x,
-                 YT* __restrict__ y, int64_t N, int64_t K, int m_rows, int64_t ldy) {
+                 YT* __restrict__ y, int64_t N, int64_t K, int m_rows, int64_t ldy, int kc) {
   constexpr bool Q8 = FMT == BQ_FMT_Q8G32;
   constexpr bool XF32 = sizeof(XT) == 4;
   constexpr int GROUPS_PER_STEP = Q8 ? 2 : 4;          // groups covered by a quad per step
@@ -88,6 +106,9 @@ qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ s
   __half* xs = reinterpret_cast<__half*>(gm_smem);                       // [NV][K]
   float* xscale = reinterpret_cast<float*>(gm_smem + (size_t)NV * K * 2);  // [NV] power-of-two back-scale
   float* red = xscale + 8;                                                 // [GM_WARPS][16][NV] partials
+  float* cred = red + GM_WARPS * 16 * NV;                                  // [RB_PER_CTA][16][NV] per-CTA sums (cluster)
+  // kc > 1: the kc CTAs of a cluster (gridDim.y = kc) split K; rank 0 adds the others' sums through DSMEM
+  const int cy = kc > 1 ? (int)cluster_ctarank() : 0;
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
@@ -97,9 +118,23 @@ qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ s
     __shared__ float wmax[GM_WARPS];
     constexpr int ROWS = XF32 ? NV / 2 : NV;
     for (int r = 0; r < ROWS; ++r) {
+      // 16-byte loads: 8 bf16 or 4 fp32 per thread and trip (rows start 16-byte aligned: K % 128 == 0)
+      constexpr int VEC = XF32 ? 4 : 8;
+      const bool vec_ok = (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+      const XT* xrow = x + (int64_t)r * K;
       float mx = 0.0f;
-      if (r < m_rows)
-        for (int64_t k = threadIdx.x; k < K; k += GM_THREADS) mx = fmaxf(mx, fabsf(to_float<XT>(x[(int64_t)r * K + k])));
+      if (r < m_rows) {
+        if (vec_ok) {
+          for (int64_t k = (int64_t)threadIdx.x * VEC; k < K; k += GM_THREADS * VEC) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(xrow + k);
+            const XT* e = reinterpret_cast<const XT*>(&raw);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) mx = fmaxf(mx, fabsf(to_float<XT>(e[i])));
+          }
+        } else {
+          for (int64_t k = threadIdx.x; k < K; k += GM_THREADS) mx = fmaxf(mx, fabsf(to_float<XT>(xrow[k])));
+        }
+      }
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
       __syncthreads();
@@ -112,15 +147,37 @@ qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ s
       if (mx > 0.0f && mx < INFINITY) e = (int)((__float_as_uint(mx) >> 23) & 0xFF) - 127 - 14;
       if (e < -100) e = -100;
       const float down = __uint_as_float((uint32_t)(127 - e) << 23);
-      for (int64_t k = threadIdx.x; k < K; k += GM_THREADS) {
-        const float v = r < m_rows ? to_float<XT>(x[(int64_t)r * K + k]) * down : 0.0f;
-        if (XF32) {
-          const __half hi = __float2half_rn(v);
-          const float rem = (v - __half2float(hi)) * 2048.0f;
-          xs[(int64_t)(2 * r) * K + k] = hi;
-          xs[(int64_t)(2 * r + 1) * K + k] = __float2half_rn(rem);
-        } else {
-          xs[(int64_t)r * K + k] = __float2half_rn(v);
+      const int64_t steps_all = K / KSTEP;
+      const int64_t k_lo = (steps_all * cy / kc) * KSTEP, k_hi = (steps_all * (cy + 1) / kc) * KSTEP;   // this CTA's K slice
+      if (vec_ok && r < m_rows) {
+        for (int64_t k = k_lo + (int64_t)threadIdx.x * VEC; k < k_hi; k += GM_THREADS * VEC) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(xrow + k);
+          const XT* el = reinterpret_cast<const XT*>(&raw);
+          __half hi[VEC], lo[VEC];
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) {
+            const float v = to_float<XT>(el[i]) * down;
+            hi[i] = __float2half_rn(v);
+            if (XF32) lo[i] = __float2half_rn((v - __half2float(hi[i])) * 2048.0f);
+          }
+          if (XF32) {
+            *reinterpret_cast<uint2*>(xs + (int64_t)(2 * r) * K + k) = *reinterpret_cast<const uint2*>(hi);
+            *reinterpret_cast<uint2*>(xs + (int64_t)(2 * r + 1) * K + k) = *reinterpret_cast<const uint2*>(lo);
+          } else {
+            *reinterpret_cast<uint4*>(xs + (int64_t)r * K + k) = *reinterpret_cast<const uint4*>(hi);
+          }
+        }
+      } else {
+        for (int64_t k = k_lo + threadIdx.x; k < k_hi; k += GM_THREADS) {
+          const float v = r < m_rows ? to_float<XT>(xrow[k]) * down : 0.0f;
+          if (XF32) {
+            const __half hi = __float2half_rn(v);
+            const float rem = (v - __half2float(hi)) * 2048.0f;
+            xs[(int64_t)(2 * r) * K + k] = hi;
+            xs[(int64_t)(2 * r + 1) * K + k] = __float2half_rn(rem);
+          } else {
+            xs[(int64_t)r * K + k] = __float2half_rn(v);
+          }
         }
       }
       if (threadIdx.x == 0) {
@@ -137,7 +194,9 @@ qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ s
   const int rb_in_cta = warp / KSPLIT;
   const int ksp = warp % KSPLIT;
   const int64_t steps_total = K / KSTEP;
-  const int64_t s_begin = steps_total * ksp / KSPLIT, s_end = steps_total * (ksp + 1) / KSPLIT;
+  const int64_t cs_begin = steps_total * cy / kc, cs_end = steps_total * (cy + 1) / kc;   // this CTA's steps
+  const int64_t s_begin = cs_begin + (cs_end - cs_begin) * ksp / KSPLIT;
+  const int64_t s_end = cs_begin + (cs_end - cs_begin) * (ksp + 1) / KSPLIT;
 
   // which activation vector / group-column this lane feeds into B: column n = g.
   //   Q8: column n = 2*v + h, h = group half (0/1); this lane's k-slots are in half (t >> 1)
@@ -262,6 +321,9 @@ qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ s
       }
       __syncthreads();
     }
+    float racc0[NB], racc1[NB];
+#pragma unroll
+    for (int b = 0; b < NB; ++b) racc0[b] = racc1[b] = 0.0f;
     if (KSPLIT == 1 || ksp == 0) {      // warp-uniform
 #pragma unroll
       for (int b = 0; b < NB; ++b) {
@@ -275,6 +337,28 @@ qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ s
               a0 += red[((rb_in_cta * KSPLIT + i) * 16 + g) * NV + v];
               a1 += red[((rb_in_cta * KSPLIT + i) * 16 + g + 8) * NV + v];
             }
+          }
+        }
+        if (kc > 1) {                       // park this CTA's sums where the cluster's rank 0 can read them
+          if (v < NV && (Q8 || (t & 1) == 0)) {
+            cred[(rb_in_cta * 16 + g) * NV + v] = a0;
+            cred[(rb_in_cta * 16 + g + 8) * NV + v] = a1;
+          }
+        }
+        racc0[b] = a0;
+        racc1[b] = a1;
+      }
+    }
+    if (kc > 1) cluster_sync_all();         // every CTA of the cluster runs the same number of trips
+    if ((KSPLIT == 1 || ksp == 0) && cy == 0) {
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        const int v = Q8 ? (b * VPM + t) : (b * VPM + (t >> 1));
+        float a0 = racc0[b], a1 = racc1[b];
+        if (kc > 1 && v < NV) {
+          for (int r = 1; r < kc; ++r) {    // fixed order: deterministic
+            a0 += ld_cluster_f32(&cred[(rb_in_cta * 16 + g) * NV + v], (uint32_t)r);
+            a1 += ld_cluster_f32(&cred[(rb_in_cta * 16 + g + 8) * NV + v], (uint32_t)r);
           }
         }
         const float back = v < NV ? xscale[v] : 0.0f;
@@ -294,6 +378,7 @@ qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ s
       }
     }
     if (KSPLIT > 1) __syncthreads();
+    if (kc > 1) cluster_sync_all();         // rank 0 is done reading before anybody overwrites or exits
   }
 }
 
@@ -308,7 +393,7 @@ template <int FMT, int NV, int KSPLIT, typename XT, typename YT>
 static int gm_launch(const uint8_t* codes, const __half* scales, const XT* x, YT* y, int64_t N, int64_t K, int m_rows,
                      int64_t ldy, cudaStream_t s) {
   auto kern = qgemv_mma_kernel<FMT, NV, KSPLIT, XT, YT>;
-  const size_t smem = (size_t)NV * K * 2 + 32 + (size_t)GM_WARPS * 16 * NV * sizeof(float);
+  const size_t smem = (size_t)NV * K * 2 + 32 + 2 * (size_t)GM_WARPS * 16 * NV * sizeof(float);
   static size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
     BQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
@@ -321,8 +406,30 @@ static int gm_launch(const uint8_t* codes, const __half* scales, const XT* x, YT
   if (per_sm > 6) per_sm = 6;
   if (per_sm < 1) per_sm = 1;
   const int64_t cap = (int64_t)sm_count() * per_sm;
+  // Few row blocks but a long K (e.g. 2048 x 16384): the CTAs above cannot fill the machine.  Split K further
+  // across a thread-block cluster of kc CTAs (summed through distributed shared memory, fixed order) while every
+  // warp keeps at least 4 steps to stream.
+  const int64_t steps_per_warp = K / (FMT == BQ_FMT_Q8G32 ? 64 : 128) / KSPLIT;
+  int kc = 1;
+  while (kc < 8 && grid * kc * 2 <= (int64_t)sm_count() * 3 && steps_per_warp / (kc * 2) >= 4) kc *= 2;
   if (grid > cap) grid = cap;
-  kern<<<(unsigned)grid, GM_THREADS, smem, s>>>(codes, scales, x, y, N, K, m_rows, ldy);
+  if (kc == 1) {
+    kern<<<(unsigned)grid, GM_THREADS, smem, s>>>(codes, scales, x, y, N, K, m_rows, ldy, 1);
+  } else {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid, (unsigned)kc, 1);
+    cfg.blockDim = dim3(GM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = (unsigned)kc;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    BQ_CUDA(cudaLaunchKernelEx(&cfg, kern, codes, scales, x, y, N, K, m_rows, ldy, kc));
+  }
   count_launch();
   BQ_CUDA(cudaGetLastError());
   return BQ_OK;

@@ -190,6 +190,69 @@ class QuantDecoder:
             tok = self.next_tokens(tok[:, None])
         return torch.stack(out, dim=1)
 
+    # ---- static-shape decode step (capturable in a CUDA graph) -----------------------------------------
+    def _step_static(self, tokens, pos_t):
+        """One greedy decode step with every shape fixed: `tokens` int64 [B] and `pos_t` int64 [1] live on the
+        device and are updated in place (tokens <- next ids, pos_t += 1).  Attention runs over the whole KV buffer
+        under a position mask, so nothing depends on the host-side position."""
+        c = self.cfg
+        B = tokens.shape[0]
+        x = self.embed[tokens].to(self.act_dtype)[:, None, :]
+        S = self.k_cache[0].shape[1]
+        mask = (torch.arange(S, device=x.device) <= pos_t)[None, :]              # [1, S]
+        for l in range(c.layers):
+            h = _rmsnorm(x, self.norms[f"l{l}.norm1"], c.eps)
+            q = self.lin[f"l{l}.q"](h).to(self.act_dtype).reshape(B, 1, self.h_local, c.head_dim)
+            k = self.lin[f"l{l}.k"](h).to(self.act_dtype).reshape(B, 1, self.kv_local, c.head_dim)
+            v = self.lin[f"l{l}.v"](h).to(self.act_dtype).reshape(B, 1, self.kv_local, c.head_dim)
+            q, k = _rope(q, pos_t, c.rope_base), _rope(k, pos_t, c.rope_base)
+            self.k_cache[l][:B].index_copy_(1, pos_t, k)
+            self.v_cache[l][:B].index_copy_(1, pos_t, v)
+            o = F.scaled_dot_product_attention(q.transpose(1, 2), self.k_cache[l][:B].transpose(1, 2),
+                                               self.v_cache[l][:B].transpose(1, 2), attn_mask=mask,
+                                               enable_gqa=self.h_local != self.kv_local)
+            o = o.transpose(1, 2).reshape(B, 1, self.h_local * c.head_dim)
+            x = x + self.lin[f"l{l}.o"](o.contiguous()).to(self.act_dtype)
+            h = _rmsnorm(x, self.norms[f"l{l}.norm2"], c.eps)
+            a = F.gelu(self.lin[f"l{l}.gate"](h), approximate="tanh") * self.lin[f"l{l}.up"](h)
+            x = x + self.lin[f"l{l}.down"](a.to(self.act_dtype)).to(self.act_dtype)
+        hfin = _rmsnorm(x, self.norms["norm_f"], c.eps)[:, 0].contiguous()
+        head = self.lin["lm_head"]
+        if self.world > 1:
+            ids = parallel.VocabParallelHead(head, c.vocab // self.world).greedy(hfin)
+        else:
+            ids = head.greedy(hfin).long()
+        tokens.copy_(ids)
+        pos_t.add_(1)
+
+    def make_graph_stepper(self, batch: int, first_tokens, start_pos: int):
+        """Capture `_step_static` in a CUDA graph.  Returns (step, tokens): calling step() advances every sequence
+        by one token; `tokens` (int64 [B], device) then holds the ids just generated."""
+        dev = self.embed.device
+        tokens = first_tokens.to(dev).long().clone()
+        pos_t = torch.tensor([start_pos], device=dev, dtype=torch.int64)
+        keep = (tokens.clone(), pos_t.clone(), [k.clone() for k in self.k_cache], [v.clone() for v in self.v_cache])
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):                      # warm-up outside capture (sizes library scratch)
+            self._step_static(tokens, pos_t)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            self._step_static(tokens, pos_t)
+        # restore the state the two trial steps consumed
+        tokens.copy_(keep[0]); pos_t.copy_(keep[1])
+        for dst, src in zip(self.k_cache, keep[2]):
+            dst.copy_(src)
+        for dst, src in zip(self.v_cache, keep[3]):
+            dst.copy_(src)
+        self.pos = start_pos
+
+        def step():
+            graph.replay()
+            self.pos += 1
+        return step, tokens
+
     def linear_bytes_per_token(self) -> float:
         """Algorithmic packed-weight bytes every decoded token streams on this rank (codes + scales)."""
         tot = 0
