@@ -35,6 +35,7 @@ SHAPES = [(2048, 2048), (16384, 2048), (2048, 16384), (256000, 2048)]
 FMT_NAMES = {0: "int8_g32", 1: "q4_g32"}
 L2_BYTES = 126 * 1024 * 1024
 DOMINANT = (256000, 2048, 0)      # the launch with the most bytes: int8 lm_head-shaped GEMV
+NCU_TRAFFIC_RATIO = 146.4 / 142.7   # measured DRAM traffic / algorithmic bytes (profiles/qgemv_mma_65536x2048.md)
 
 
 from chadslab_b200.synth import algorithmic_bytes, make_device_weight  # noqa: E402
@@ -158,6 +159,72 @@ def cpu_sample(steps: int, warmup: int):
                       "256000-row shape cut to 32000 rows; host cores=%d, affinity=%d" % (
                           os.cpu_count() or 0, len(os.sched_getaffinity(0))),
             "ms_per_pass": dt * 1e3}
+
+
+# ------------------------------------------------------------------------------------------------
+# extras (reported beside the headline, N=1 only): the rest of configs[1] and a decode loop
+# ------------------------------------------------------------------------------------------------
+def run_extras(torch, cb, lib, problems):
+    from chadslab_b200 import _lib
+    from chadslab_b200.decoder import GEMMA_2B_SHAPE, QuantDecoder
+    stream = torch.cuda.current_stream().cuda_stream
+    out = {"batch_sweep": [], "note": "batch_sweep: same weights as the headline, bf16 activations, CUDA events, "
+                                      "3 launches each after 1 warm-up; decode: Gemma-2B-shaped decoder, int8-g32, "
+                                      "batch 1, random-init, 128-token prefill then 32 greedy tokens replayed from a "
+                                      "CUDA graph"}
+    for p in problems:
+        if p["N"] < 16384:
+            continue
+        pw = p["pws"][0]
+        for M in (8, 64, 512, 4096):
+            x = torch.randn((M, p["K"]), device="cuda").to(torch.bfloat16)
+            y = torch.empty((M, p["N"]), dtype=torch.float32, device="cuda")
+            call = lambda: _lib.check(lib.bq_qlinear(pw.handle, x.data_ptr(), cb.DT_BF16, M, y.data_ptr(), cb.DT_F32, stream))
+            call()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(3):
+                call()
+            b.record()
+            torch.cuda.synchronize()
+            us = a.elapsed_time(b) * 1e3 / 3
+            out["batch_sweep"].append({"N": p["N"], "K": p["K"], "fmt": FMT_NAMES[p["fmt"]], "M": M, "us": round(us, 1),
+                                       "gbs": round(algorithmic_bytes(p["N"], p["K"], p["fmt"], M) / us / 1e3, 1),
+                                       "tflops": round(2.0 * M * p["N"] * p["K"] / us / 1e6, 1)})
+            del x, y
+    for p in problems:
+        for pw in p["pws"]:
+            pw.close()
+    torch.cuda.empty_cache()
+    try:
+        dec = QuantDecoder.random(GEMMA_2B_SHAPE, seed=0, act_dtype=torch.bfloat16, max_seq=192, max_batch=1)
+        g = torch.Generator(device="cuda").manual_seed(0)
+        prompt = torch.randint(0, GEMMA_2B_SHAPE.vocab, (1, 128), device="cuda", generator=g)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        first = dec.next_tokens(prompt)
+        torch.cuda.synchronize()
+        prefill_s = time.perf_counter() - t0
+        step, tokens = dec.make_graph_stepper(1, first, start_pos=dec.pos)
+        for _ in range(3):
+            step()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(32):
+            step()
+        b.record()
+        torch.cuda.synchronize()
+        ms_tok = a.elapsed_time(b) / 32
+        bpt = dec.linear_bytes_per_token()
+        peak, _ = load_peaks()
+        out["decode"] = {"model": "gemma-2b-shape int8-g32, bf16 activations, batch 1", "tokens_per_s": round(1e3 / ms_tok, 1),
+                         "ms_per_token": round(ms_tok, 4), "linear_GB_per_token": round(bpt / 1e9, 3),
+                         "linear_stream_gbs": round(bpt / ms_tok / 1e6, 1),
+                         "frac_of_hbm_ceiling": round(bpt / ms_tok / 1e6 / peak, 4),
+                         "prefill_128_tokens_s": round(prefill_s, 4)}
+    except Exception as e:  # extras never break the headline line
+        out["decode"] = {"error": repr(e)[:300]}
+    return out
 
 
 def run_reference(args):
@@ -309,6 +376,15 @@ def run_gpu(args):
         e2e_value = world * step_bytes * args.steps / (e2e_ms * 1e-3) / 1e9
         achieved = dom["bytes"] / (dom_ms * 1e-3) / 1e9
         cpu = cpu_sample(2, 1) if world == 1 else None
+        extras = None
+        if world == 1 and args.extras:
+            del hx, hy
+            for p in problems:           # keep only what the extras reuse
+                for pw in p["pws"][1:]:
+                    pw.close()
+                p["pws"] = p["pws"][:1]
+            torch.cuda.empty_cache()
+            extras = run_extras(torch, cb, lib, problems)
         line = {
             "metric": "quantized_gemv_hbm_gbs", "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": round(ms_total / args.steps, 4),
@@ -322,7 +398,10 @@ def run_gpu(args):
                                  "with events in an eager pass of the same step sequence",
                        "bytes_per_step_per_gpu": int(step_bytes), "parallelism": f"independent sweep per GPU x{world}"},
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                         "frac": round(achieved / peak, 4), "traffic": None, "peak_source": peak_src,
+                         "frac": round(achieved / peak, 4), "traffic": int(NCU_TRAFFIC_RATIO * dom["bytes"]),
+                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of the same kernel on a 65536-row "
+                                           "case (146.4 MB for 142.7 MB algorithmic), scaled by rows to this launch",
+                         "peak_source": peak_src,
                          "kernel": "qgemv int8-g32 (256000,2048) M=1", "frac_of_nominal_8TBs": round(achieved / 8000, 4),
                          "launch_us": round(dom_ms * 1e3, 2)},
             "e2e": {"value": round(e2e_value, 1), "unit": "GB/s",
@@ -333,6 +412,8 @@ def run_gpu(args):
         }
         if cpu:
             line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        if extras:
+            line["extras"] = extras
         print(json.dumps(line))
     if world > 1:
         dist.barrier()
@@ -345,6 +426,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--extras", type=int, default=1, help="also report the batch sweep and decode tokens/s (N=1 only)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

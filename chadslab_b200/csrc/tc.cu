@@ -479,7 +479,8 @@ constexpr int T2_ACOLS = 64;
 // NW = 2: the CTA converts two 128-row weight tiles (rows n0.. and n0+128..) per activation tile, which halves
 // the activation bytes fetched per multiply-add (the activation tiles come from L2, the scarcer resource of
 // large batches); then BN = 128 and all 512 TMEM columns are in use (2 accumulators + 2 x 2 A buffers).
-template <int FMT, int BN, int NW> struct T2Plan {
+template <int FMT, int BN, int MODE> struct T2Plan {
+  static constexpr int NW = MODE ? 2 : 1;                                 // MODE: 0 single, 1 gated (gate|up), 2 dual
   static constexpr int RAW_ROW = (FMT == BQ_FMT_Q8G32) ? 128 : 64;      // code bytes per row per step
   static constexpr int RAW = TC_ROWS * RAW_ROW;
   static constexpr int XT = 2 * BN * 128;                                 // two 64-k swizzle atoms
@@ -505,6 +506,11 @@ struct T2Args {
   int64_t ldy, N, K, M;
   int out_dtype;
   int* status;
+  // MoE (grouped experts): per expert {codes0, scales0, codes1, scales1} descriptors, row ranges, tile list
+  const CUtensorMap* tm_list;
+  const int32_t* offsets;
+  const int32_t* tiles;
+  int moe;
 };
 
 __device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
@@ -528,10 +534,11 @@ __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t* v) {
 }
 __device__ __forceinline__ void tc_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-template <int FMT, int BN, int NW>
+template <int FMT, int BN, int MODE>
 __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tmem_kernel(const __grid_constant__ T2Args args) {
-  using P = T2Plan<FMT, BN, NW>;
-  constexpr int S = P::S, NA = 2;
+  using P = T2Plan<FMT, BN, MODE>;
+  constexpr int S = P::S, NA = 2, NW = P::NW;
+  constexpr bool GATED = MODE == 1, DUAL = MODE == 2;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* stages = smem;                                  // per stage: [x atom 0][x atom 1][codes tile 0][codes tile 1]
@@ -546,9 +553,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tmem_kernel(const __grid_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t n0 = (int64_t)blockIdx.y * TC_ROWS * NW;
-  const int64_t m0 = (int64_t)blockIdx.x * BN;
-  const int64_t m_end = args.M;
+  const int64_t n0 = (int64_t)blockIdx.y * TC_ROWS * (DUAL ? 2 : 1);
+  int64_t m0 = (int64_t)blockIdx.x * BN, m_end = args.M;
+  const CUtensorMap* tmw[2] = {&args.tm_w, &args.tm_w};
+  const CUtensorMap* tms[2] = {&args.tm_s, &args.tm_s};
+  if (args.moe) {
+    if ((int)blockIdx.x >= args.tiles[0]) return;     // uniform across the CTA, before any barrier
+    const int e = args.tiles[1 + 2 * blockIdx.x];
+    m0 = args.tiles[2 + 2 * blockIdx.x];
+    m_end = args.offsets[e + 1];
+    const CUtensorMap* l = args.tm_list + (int64_t)e * 4;
+    tmw[0] = l; tms[0] = l + 1; tmw[1] = GATED ? l + 2 : l; tms[1] = GATED ? l + 3 : l + 1;
+  }
   const int ksteps = (int)(args.K / T2_BK);
 
   if (threadIdx.x == 0) {
@@ -584,10 +600,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tmem_kernel(const __grid_
         tma_load_2d(smem_u32(st + BN * 128), &args.tm_x, ks * T2_BK + 64, (int)m0, fb);
 #pragma unroll
         for (int w = 0; w < NW; ++w) {
-          tma_load_2d(smem_u32(st + P::XT + w * P::RAW), &args.tm_w, ks * P::RAW_ROW, (int)n0 + w * TC_ROWS, fb);
+          const int nrow = (int)n0 + (DUAL ? w * TC_ROWS : 0);
+          tma_load_2d(smem_u32(st + P::XT + w * P::RAW), tmw[w], ks * P::RAW_ROW, nrow, fb);
           if (with_scales)
-            tma_load_2d(smem_u32(sc_tiles + (((ks >> 1) % TC_SC_SLOTS) * NW + w) * P::SCT), &args.tm_s, (ks >> 1) * 8,
-                        (int)n0 + w * TC_ROWS, fb);
+            tma_load_2d(smem_u32(sc_tiles + (((ks >> 1) % TC_SC_SLOTS) * NW + w) * P::SCT), tms[w], (ks >> 1) * 8, nrow, fb);
         }
       }
       if (*abort_flag) {
@@ -690,6 +706,25 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tmem_kernel(const __grid_
 #pragma unroll 1
       for (int c0 = 16 * half; c0 < BN; c0 += 32) {
         if (m0 + c0 >= m_end) break;
+        if (GATED) {                               // h = silu(gate) * up, rounded to bf16
+          uint32_t v[16], u[16];
+          tc_ld16(tbase + (uint32_t)c0, v);
+          tc_ld16(tbase + (uint32_t)(BN + c0), u);
+          tc_ld_wait();
+          if (n < args.N) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int64_t m = m0 + c0 + j;
+              if (m < m_end) {
+                const float rs = args.xscale[m];
+                const float f = __uint_as_float(v[j]) * rs;
+                const float h = f / (1.0f + __expf(-f)) * (__uint_as_float(u[j]) * rs);
+                reinterpret_cast<__nv_bfloat16*>(args.out)[m * args.ldy + n] = __float2bfloat16_rn(h);
+              }
+            }
+          }
+          continue;
+        }
 #pragma unroll
         for (int w = 0; w < NW; ++w) {
           uint32_t v[16];
@@ -889,10 +924,10 @@ static int tc_dense_dispatch(const TcArgs& a, int bn, dim3 grid, cudaStream_t s)
 
 static int pick_bn(int64_t M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
 
-template <int FMT, int BN, int NW>
+template <int FMT, int BN, int MODE>
 static int t2_launch(const T2Args& a, dim3 grid, cudaStream_t s) {
-  using P = T2Plan<FMT, BN, NW>;
-  auto kern = qgemm_tmem_kernel<FMT, BN, NW>;
+  using P = T2Plan<FMT, BN, MODE>;
+  auto kern = qgemm_tmem_kernel<FMT, BN, MODE>;
   static bool configured = false;
   if (!configured) {
     BQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P::SMEM));
@@ -906,11 +941,11 @@ static int t2_launch(const T2Args& a, dim3 grid, cudaStream_t s) {
 template <int FMT>
 static int t2_dispatch(const T2Args& a, int bn, dim3 grid, cudaStream_t s) {
   switch (bn) {
-    case 16:  return t2_launch<FMT, 16, 1>(a, grid, s);
-    case 32:  return t2_launch<FMT, 32, 1>(a, grid, s);
-    case 64:  return t2_launch<FMT, 64, 1>(a, grid, s);
-    case 128: return t2_launch<FMT, 128, 1>(a, grid, s);
-    case 256: return t2_launch<FMT, 256, 1>(a, grid, s);
+    case 16:  return t2_launch<FMT, 16, 0>(a, grid, s);
+    case 32:  return t2_launch<FMT, 32, 0>(a, grid, s);
+    case 64:  return t2_launch<FMT, 64, 0>(a, grid, s);
+    case 128: return t2_launch<FMT, 128, 0>(a, grid, s);
+    case 256: return t2_launch<FMT, 256, 0>(a, grid, s);
     default:  return t2_launch<FMT, 128, 2>(a, grid, s);      // 512: two weight tiles x 128 batch rows
   }
 }
@@ -981,8 +1016,22 @@ int launch_qlinear_tc(const uint8_t* codes, const __half* scales, int fmt, int64
 struct MoeTcState {           // device-side per-expert tensor maps + tile list, owned by the library
   CUtensorMap* gate_up;       // [E][4] = {gate codes, gate scales, up codes, up scales}
   CUtensorMap* down;          // [E][4] = {down codes, down scales, (unused) x2}
+  CUtensorMap* gate_up2;      // same for the tensor-memory kernel (128-k boxes, swizzled codes)
+  CUtensorMap* down2;
   int32_t* tiles; int64_t tiles_cap;
 };
+
+// descriptors of one weight for qgemm_tmem_kernel: codes box = one 128-k step of 128 rows (swizzled), scales as before
+static int t2_weight_maps(const uint8_t* codes, const __half* scales, int fmt, int64_t N, int64_t K, CUtensorMap* tm_codes,
+                          CUtensorMap* tm_scales) {
+  const uint64_t rb = fmt == BQ_FMT_Q8G32 ? K : K / 2;
+  int rc = make_map_2d(tm_codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, codes, rb, (uint64_t)N, rb,
+                       fmt == BQ_FMT_Q8G32 ? 128 : 64, TC_ROWS,
+                       fmt == BQ_FMT_Q8G32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
+  if (rc) return rc;
+  return make_map_2d(tm_scales, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, scales, (uint64_t)(K / GROUP), (uint64_t)N,
+                     (uint64_t)(K / GROUP) * 2, 8, TC_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
+}
 static std::string g_dummy;
 
 bool moe_tc_supported(const Moe* m) { return tc_shape_ok(m->F, m->H) && tc_shape_ok(m->H, m->F); }
@@ -992,9 +1041,15 @@ int moe_tc_prepare(Moe* m, const std::vector<const uint8_t*>* codes, const std::
   if (!moe_tc_supported(m)) { m->tc_state = nullptr; return BQ_OK; }
   MoeTcState* st = new MoeTcState();
   memset(st, 0, sizeof(*st));
-  std::vector<CUtensorMap> gu((size_t)m->E * 4), dn((size_t)m->E * 4);
+  std::vector<CUtensorMap> gu((size_t)m->E * 4), dn((size_t)m->E * 4), gu2((size_t)m->E * 4), dn2((size_t)m->E * 4);
   for (int e = 0; e < m->E; ++e) {
-    int rc = tc_weight_maps(codes[0][e], scales[0][e], m->fmt, m->F, m->H, &gu[e * 4 + 0], &gu[e * 4 + 1]);
+    int rc = t2_weight_maps(codes[0][e], scales[0][e], m->fmt, m->F, m->H, &gu2[e * 4 + 0], &gu2[e * 4 + 1]);
+    if (!rc) rc = t2_weight_maps(codes[1][e], scales[1][e], m->fmt, m->F, m->H, &gu2[e * 4 + 2], &gu2[e * 4 + 3]);
+    if (!rc) rc = t2_weight_maps(codes[2][e], scales[2][e], m->fmt, m->H, m->F, &dn2[e * 4 + 0], &dn2[e * 4 + 1]);
+    if (rc) { delete st; return rc; }
+    dn2[e * 4 + 2] = dn2[e * 4 + 0];
+    dn2[e * 4 + 3] = dn2[e * 4 + 1];
+    rc = tc_weight_maps(codes[0][e], scales[0][e], m->fmt, m->F, m->H, &gu[e * 4 + 0], &gu[e * 4 + 1]);
     if (!rc) rc = tc_weight_maps(codes[1][e], scales[1][e], m->fmt, m->F, m->H, &gu[e * 4 + 2], &gu[e * 4 + 3]);
     if (!rc) rc = tc_weight_maps(codes[2][e], scales[2][e], m->fmt, m->H, m->F, &dn[e * 4 + 0], &dn[e * 4 + 1]);
     if (rc) { delete st; return rc; }
@@ -1006,6 +1061,10 @@ int moe_tc_prepare(Moe* m, const std::vector<const uint8_t*>* codes, const std::
   BQ_CUDA(cudaMalloc((void**)&st->down, bytes));
   BQ_CUDA(cudaMemcpy(st->gate_up, gu.data(), bytes, cudaMemcpyHostToDevice));
   BQ_CUDA(cudaMemcpy(st->down, dn.data(), bytes, cudaMemcpyHostToDevice));
+  BQ_CUDA(cudaMalloc((void**)&st->gate_up2, bytes));
+  BQ_CUDA(cudaMalloc((void**)&st->down2, bytes));
+  BQ_CUDA(cudaMemcpy(st->gate_up2, gu2.data(), bytes, cudaMemcpyHostToDevice));
+  BQ_CUDA(cudaMemcpy(st->down2, dn2.data(), bytes, cudaMemcpyHostToDevice));
   m->tc_state = st;
   return BQ_OK;
 }
@@ -1013,9 +1072,18 @@ int moe_tc_prepare(Moe* m, const std::vector<const uint8_t*>* codes, const std::
 void moe_tc_release(Moe* m) {
   MoeTcState* st = static_cast<MoeTcState*>(m->tc_state);
   if (!st) return;
-  cudaFree(st->gate_up); cudaFree(st->down); cudaFree(st->tiles);
+  cudaFree(st->gate_up); cudaFree(st->down); cudaFree(st->gate_up2); cudaFree(st->down2); cudaFree(st->tiles);
   delete st;
   m->tc_state = nullptr;
+}
+
+template <int FMT, int MODE>
+static int t2_moe_dispatch(const T2Args& a, int bn, dim3 grid, cudaStream_t s) {
+  switch (bn) {
+    case 16:  return t2_launch<FMT, 16, MODE>(a, grid, s);
+    case 64:  return t2_launch<FMT, 64, MODE>(a, grid, s);
+    default:  return t2_launch<FMT, 128, MODE>(a, grid, s);
+  }
 }
 
 template <int FMT, int GATED>
@@ -1046,6 +1114,26 @@ int launch_moe_experts_tc(const Moe* m, const void* xp, const int32_t* offsets, 
   moe_tile_list_kernel<<<1, 1024, 0, s>>>(offsets, m->E, bn, st->tiles);
   count_launch();
   BQ_CUDA(cudaGetLastError());
+  if (tmem_variant_enabled()) {     // tensor-memory kernel: gate|up -> h (bf16), then down -> out (f32)
+    T2Args a;
+    memset(&a, 0, sizeof(a));
+    int rc = launch_x_prep(xp, BQ_DT_BF16, P, m->H, s);
+    if (rc) return rc;
+    if ((rc = x_map(&a.tm_x, g_x16, P, m->H, bn))) return rc;
+    a.xscale = g_xs; a.tm_list = st->gate_up2; a.offsets = offsets; a.tiles = st->tiles; a.out = hbuf; a.ldy = m->F;
+    a.N = m->F; a.K = m->H; a.M = P; a.out_dtype = BQ_DT_BF16; a.moe = 1; a.status = status_word();
+    dim3 g1((unsigned)max_tiles, (unsigned)((m->F + TC_ROWS - 1) / TC_ROWS));
+    rc = m->fmt == BQ_FMT_Q8G32 ? t2_moe_dispatch<BQ_FMT_Q8G32, 1>(a, bn, g1, s) : t2_moe_dispatch<BQ_FMT_Q4G32, 1>(a, bn, g1, s);
+    if (rc) return rc;
+    T2Args b;
+    memset(&b, 0, sizeof(b));
+    if ((rc = launch_x_prep(hbuf, BQ_DT_BF16, P, m->F, s))) return rc;   // stream order: the first GEMM is done with the scratch
+    if ((rc = x_map(&b.tm_x, g_x16, P, m->F, bn))) return rc;
+    b.xscale = g_xs; b.tm_list = st->down2; b.offsets = offsets; b.tiles = st->tiles; b.out = out; b.ldy = m->H;
+    b.N = m->H; b.K = m->F; b.M = P; b.out_dtype = BQ_DT_F32; b.moe = 1; b.status = status_word();
+    dim3 g2((unsigned)max_tiles, (unsigned)((m->H + TC_ROWS - 1) / TC_ROWS));
+    return m->fmt == BQ_FMT_Q8G32 ? t2_moe_dispatch<BQ_FMT_Q8G32, 0>(b, bn, g2, s) : t2_moe_dispatch<BQ_FMT_Q4G32, 0>(b, bn, g2, s);
+  }
   // gate|up -> h (bf16)
   TcArgs a;
   memset(&a, 0, sizeof(a));

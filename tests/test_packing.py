@@ -64,3 +64,22 @@ def test_packed_weight_and_shard_bookkeeping():
         PackedWeight(np.zeros((2, 32), np.int8), np.zeros((2, 2), np.float16), 0, upload=False)
     with pytest.raises(TypeError):
         PackedWeight(np.zeros((2, 32), np.uint8), np.zeros((2, 1), np.float16), 0, upload=False)
+
+
+def test_container_round_trip(tmp_path):
+    from chadslab_b200 import container
+    rng = np.random.default_rng(9)
+    ws = {"l0.q": PackedWeight.from_float(rng.normal(0, 0.02, (24, 64)).astype(np.float32), 0, upload=False),
+          "l0.down": PackedWeight.from_float(rng.normal(0, 0.02, (8, 96)).astype(np.float32), 1, upload=False)}
+    extra = {"embed": rng.normal(0, 1, (10, 8)).astype(np.float32)}
+    path = str(tmp_path / "w.safetensors")
+    container.save_packed(path, ws, extra)
+    got, tensors = container.load_packed(path, upload=False)
+    assert set(got) == set(ws) and set(tensors) == {"embed"}
+    for k in ws:
+        assert got[k].fmt == ws[k].fmt and (got[k].N, got[k].K) == (ws[k].N, ws[k].K)
+        assert np.array_equal(got[k].codes, ws[k].codes)
+        assert np.array_equal(got[k].scales.view(np.uint16), ws[k].scales.view(np.uint16))
+    assert np.array_equal(tensors["embed"], extra["embed"])
+    with pytest.raises(ValueError):
+        container.save_packed(path, ws, {"x.codes": extra["embed"]})
