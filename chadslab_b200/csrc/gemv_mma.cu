@@ -89,10 +89,13 @@ __device__ __forceinline__ void q4_word_to_h2(uint32_t v, uint32_t* o) {
 // KSPLIT     warps that split K for one 16-row block (1, 2, 4 or 8); GM_WARPS/KSPLIT row blocks per CTA
 // Columns of an MMA: Q8 -> 2 groups per 64-k step, so 4 vectors per MMA; Q4 -> 4 groups per 128-k step,
 // so 2 vectors per MMA.  NB = MMAs (column sets) needed for NV vectors.
-template <int FMT, int NV, int KSPLIT, typename XT, typename YT>
+// CL         launched as a thread-block cluster of kc_arg CTAs that split K (compile-time switch so the plain
+//            instantiation carries no cluster code at all)
+template <int FMT, int NV, int KSPLIT, typename XT, typename YT, bool CL>
 __global__ void __launch_bounds__(GM_THREADS)
 qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ scales, const XT* __restrict__ x,
-                 YT* __restrict__ y, int64_t N, int64_t K, int m_rows, int64_t ldy, int kc) {
+                 YT* __restrict__ y, int64_t N, int64_t K, int m_rows, int64_t ldy, int kc_arg) {
+  const int kc = CL ? kc_arg : 1;
   constexpr bool Q8 = FMT == BQ_FMT_Q8G32;
   constexpr bool XF32 = sizeof(XT) == 4;
   constexpr int GROUPS_PER_STEP = Q8 ? 2 : 4;          // groups covered by a quad per step
@@ -108,7 +111,7 @@ qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ s
   float* red = xscale + 8;                                                 // [GM_WARPS][16][NV] partials
   float* cred = red + GM_WARPS * 16 * NV;                                  // [RB_PER_CTA][16][NV] per-CTA sums (cluster)
   // kc > 1: the kc CTAs of a cluster (gridDim.y = kc) split K; rank 0 adds the others' sums through DSMEM
-  const int cy = kc > 1 ? (int)cluster_ctarank() : 0;
+  const int cy = CL ? (int)cluster_ctarank() : 0;
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
@@ -339,7 +342,7 @@ qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ s
             }
           }
         }
-        if (kc > 1) {                       // park this CTA's sums where the cluster's rank 0 can read them
+        if (CL) {                           // park this CTA's sums where the cluster's rank 0 can read them
           if (v < NV && (Q8 || (t & 1) == 0)) {
             cred[(rb_in_cta * 16 + g) * NV + v] = a0;
             cred[(rb_in_cta * 16 + g + 8) * NV + v] = a1;
@@ -349,13 +352,13 @@ qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ s
         racc1[b] = a1;
       }
     }
-    if (kc > 1) cluster_sync_all();         // every CTA of the cluster runs the same number of trips
+    if (CL) cluster_sync_all();             // every CTA of the cluster runs the same number of trips
     if ((KSPLIT == 1 || ksp == 0) && cy == 0) {
 #pragma unroll
       for (int b = 0; b < NB; ++b) {
         const int v = Q8 ? (b * VPM + t) : (b * VPM + (t >> 1));
         float a0 = racc0[b], a1 = racc1[b];
-        if (kc > 1 && v < NV) {
+        if (CL && v < NV) {
           for (int r = 1; r < kc; ++r) {    // fixed order: deterministic
             a0 += ld_cluster_f32(&cred[(rb_in_cta * 16 + g) * NV + v], (uint32_t)r);
             a1 += ld_cluster_f32(&cred[(rb_in_cta * 16 + g + 8) * NV + v], (uint32_t)r);
@@ -378,7 +381,7 @@ qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ s
       }
     }
     if (KSPLIT > 1) __syncthreads();
-    if (kc > 1) cluster_sync_all();         // rank 0 is done reading before anybody overwrites or exits
+    if (CL) cluster_sync_all();             // rank 0 is done reading before anybody overwrites or exits
   }
 }
 
@@ -392,11 +395,13 @@ bool gemv_mma_supported(int fmt, int64_t N, int64_t K, int x_dtype, int64_t M) {
 template <int FMT, int NV, int KSPLIT, typename XT, typename YT>
 static int gm_launch(const uint8_t* codes, const __half* scales, const XT* x, YT* y, int64_t N, int64_t K, int m_rows,
                      int64_t ldy, cudaStream_t s) {
-  auto kern = qgemv_mma_kernel<FMT, NV, KSPLIT, XT, YT>;
+  auto kern = qgemv_mma_kernel<FMT, NV, KSPLIT, XT, YT, false>;
+  auto kern_cl = qgemv_mma_kernel<FMT, NV, KSPLIT, XT, YT, true>;
   const size_t smem = (size_t)NV * K * 2 + 32 + 2 * (size_t)GM_WARPS * 16 * NV * sizeof(float);
   static size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
     BQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    BQ_CUDA(cudaFuncSetAttribute(kern_cl, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     configured = 200 * 1024;
   }
   const int64_t rb = (N + 15) / 16;
@@ -428,7 +433,7 @@ static int gm_launch(const uint8_t* codes, const __half* scales, const XT* x, YT
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    BQ_CUDA(cudaLaunchKernelEx(&cfg, kern, codes, scales, x, y, N, K, m_rows, ldy, kc));
+    BQ_CUDA(cudaLaunchKernelEx(&cfg, kern_cl, codes, scales, x, y, N, K, m_rows, ldy, kc));
   }
   count_launch();
   BQ_CUDA(cudaGetLastError());
