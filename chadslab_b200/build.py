@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200q.so")
-SOURCES = ["api.cu", "simt.cu", "gemv_mma.cu", "moe.cu", "tc.cu"]
+SOURCES = ["api.cu", "simt.cu", "gemv_mma.cu", "moe.cu", "tc.cu", "glue.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-shared", "-Xcompiler", "-fPIC",

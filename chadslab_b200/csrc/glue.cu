@@ -1,0 +1,293 @@
+// Decode-step glue between the quantized matmuls, as a handful of kernels so that one token is ~10 launches
+// per layer instead of ~40 framework ops: residual add + RMSNorm, rotate-half RoPE + KV-cache append,
+// single-query (decode) attention over the KV cache, and the gated activation (GeGLU / SwiGLU).
+// All arithmetic is fp32; T is the activation storage type (float or bf16).
+#include "common.cuh"
+
+namespace bq {
+
+// x[r,:] += delta[r,:] (if delta), then out[r,:] = x[r,:] * rsqrt(mean(x^2) + eps) * w[:]
+// One block per row; each thread keeps up to RN_CACHE of its elements in registers, so x and delta are read once.
+constexpr int RN_THREADS = 256;
+constexpr int RN_CACHE = 16;
+template <typename T>
+__global__ void __launch_bounds__(RN_THREADS) add_rmsnorm_kernel(T* __restrict__ x, const float* __restrict__ delta,
+                                                                 const float* __restrict__ w, T* __restrict__ out,
+                                                                 int64_t H, float eps) {
+  T* xr = x + (int64_t)blockIdx.x * H;
+  const float* dr = delta ? delta + (int64_t)blockIdx.x * H : nullptr;
+  T* orow = out + (int64_t)blockIdx.x * H;
+  float cache[RN_CACHE];
+  float ss = 0.0f;
+#pragma unroll
+  for (int j = 0; j < RN_CACHE; ++j) {
+    const int64_t i = threadIdx.x + (int64_t)j * RN_THREADS;
+    float v = 0.0f;
+    if (i < H) {
+      v = to_float<T>(xr[i]);
+      if (dr) {
+        v = to_float<T>(from_float<T>(v + dr[i]));   // the residual stream is stored in T
+        xr[i] = from_float<T>(v);
+      }
+    }
+    cache[j] = v;
+    ss += v * v;
+  }
+  for (int64_t i = threadIdx.x + (int64_t)RN_CACHE * RN_THREADS; i < H; i += RN_THREADS) {   // rows longer than the cache
+    float v = to_float<T>(xr[i]);
+    if (dr) {
+      v = to_float<T>(from_float<T>(v + dr[i]));
+      xr[i] = from_float<T>(v);
+    }
+    ss += v * v;
+  }
+  __shared__ float red[RN_THREADS / 32];
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.0f;
+#pragma unroll
+  for (int i = 0; i < RN_THREADS / 32; ++i) tot += red[i];
+  const float inv = rsqrtf(tot / (float)H + eps);
+#pragma unroll
+  for (int j = 0; j < RN_CACHE; ++j) {
+    const int64_t i = threadIdx.x + (int64_t)j * RN_THREADS;
+    if (i < H) orow[i] = from_float<T>(cache[j] * inv * w[i]);
+  }
+  for (int64_t i = threadIdx.x + (int64_t)RN_CACHE * RN_THREADS; i < H; i += RN_THREADS)
+    orow[i] = from_float<T>(to_float<T>(xr[i]) * inv * w[i]);
+}
+
+// qkv: fp32 [B, (Hq + 2*Hkv) * D] (output of the fused q|k|v projection).  Writes q (rotated) as T [B, Hq, D],
+// and k (rotated), v into the caches [B, S, Hkv, D] at position *pos.  One block per (b, head).
+template <typename T>
+__global__ void __launch_bounds__(128) rope_kv_append_kernel(const float* __restrict__ qkv, const int64_t* __restrict__ pos_p,
+                                                             T* __restrict__ q_out, T* __restrict__ k_cache,
+                                                             T* __restrict__ v_cache, int Hq, int Hkv, int D, int64_t S,
+                                                             float base) {
+  const int b = blockIdx.y, h = blockIdx.x;            // h in [0, Hq + 2*Hkv)
+  const int64_t pos = *pos_p;
+  const float* src = qkv + ((int64_t)b * (Hq + 2 * Hkv) + h) * D;
+  const int half = D / 2;
+  T* dst;
+  bool rot = true;
+  if (h < Hq) dst = q_out + ((int64_t)b * Hq + h) * D;
+  else if (h < Hq + Hkv) dst = k_cache + (((int64_t)b * S + pos) * Hkv + (h - Hq)) * D;
+  else { dst = v_cache + (((int64_t)b * S + pos) * Hkv + (h - Hq - Hkv)) * D; rot = false; }
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    // values pass through T once before the rotation, as a runtime that stores q/k in T would do
+    const float x1 = to_float<T>(from_float<T>(src[i])), x2 = to_float<T>(from_float<T>(src[i + half]));
+    if (rot) {
+      const float inv = 1.0f / powf(base, (float)(2 * i) / (float)D);
+      float sn, cs;
+      sincosf((float)pos * inv, &sn, &cs);
+      dst[i] = from_float<T>(x1 * cs - x2 * sn);
+      dst[i + half] = from_float<T>(x2 * cs + x1 * sn);
+    } else {
+      dst[i] = from_float<T>(x1);
+      dst[i + half] = from_float<T>(x2);
+    }
+  }
+}
+
+// Single-query attention: out[b, h, :] = softmax(q[b,h,:] . K[b, 0..pos, kv(h), :] / sqrt(D)) . V[b, 0..pos, kv(h), :]
+// One block (8 warps) per (b, h).  A lane owns 8 consecutive head-dim elements (D <= 256, D % 8 == 0), so a warp
+// reads one K or V row with a single coalesced vector load per lane; a warp takes 4 positions per trip (4 K rows and
+// 4 V rows in flight) and keeps an online softmax; the 8 partial (max, sum, acc) states merge through shared memory.
+constexpr int ATT_WARPS = 8;
+constexpr int ATT_MAXD = 256;
+constexpr int ATT_EPL = 8;
+constexpr int ATT_PB = 4;
+template <typename T> __device__ __forceinline__ void load8(const T* p, float* f);
+template <> __device__ __forceinline__ void load8<float>(const float* p, float* f) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float* f) {
+  const uint4 r = *reinterpret_cast<const uint4*>(p);
+  const uint32_t wds[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(wds[i] << 16);
+    f[2 * i + 1] = __uint_as_float(wds[i] & 0xFFFF0000u);
+  }
+}
+template <typename T>
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
+                        const int64_t* __restrict__ pos_p, T* __restrict__ out, int Hq, int Hkv, int D, int64_t S) {
+  const int b = blockIdx.y, h = blockIdx.x;
+  const int kv = h / (Hq / Hkv);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t n_pos = *pos_p + 1;
+  const int d0 = lane * ATT_EPL;
+  const bool live = d0 < D;
+  float qv[ATT_EPL], acc[ATT_EPL];
+  const float scale = rsqrtf((float)D);
+#pragma unroll
+  for (int i = 0; i < ATT_EPL; ++i) { qv[i] = 0.0f; acc[i] = 0.0f; }
+  if (live) {
+    load8<T>(q + ((int64_t)b * Hq + h) * D + d0, qv);
+#pragma unroll
+    for (int i = 0; i < ATT_EPL; ++i) qv[i] *= scale;
+  }
+  float mx = -INFINITY, sum = 0.0f;
+  const int64_t row_stride = (int64_t)Hkv * D;
+  const T* kbase = k_cache + ((int64_t)b * S * Hkv + kv) * D + d0;
+  const T* vbase = v_cache + ((int64_t)b * S * Hkv + kv) * D + d0;
+  for (int64_t s0 = (int64_t)warp * ATT_PB; s0 < n_pos; s0 += ATT_WARPS * ATT_PB) {
+    float kf[ATT_PB][ATT_EPL], dot[ATT_PB];
+#pragma unroll
+    for (int j = 0; j < ATT_PB; ++j) {
+      const int64_t sidx = s0 + j < n_pos ? s0 + j : n_pos - 1;       // clamp: masked below
+      if (live) load8<T>(kbase + sidx * row_stride, kf[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < ATT_PB; ++j) {
+      float dsum = 0.0f;
+      if (live) {
+#pragma unroll
+        for (int i = 0; i < ATT_EPL; ++i) dsum += qv[i] * kf[j][i];
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) dsum += __shfl_xor_sync(0xffffffffu, dsum, off);
+      dot[j] = s0 + j < n_pos ? dsum : -INFINITY;
+    }
+    float nm = mx;
+#pragma unroll
+    for (int j = 0; j < ATT_PB; ++j) nm = fmaxf(nm, dot[j]);
+    const float corr = __expf(mx - nm);
+    sum *= corr;
+#pragma unroll
+    for (int i = 0; i < ATT_EPL; ++i) acc[i] *= corr;
+#pragma unroll
+    for (int j = 0; j < ATT_PB; ++j) {
+      const int64_t sidx = s0 + j < n_pos ? s0 + j : n_pos - 1;
+      const float p = __expf(dot[j] - nm);                                   // 0 for masked positions
+      sum += p;
+      if (live) {
+        float vf[ATT_EPL];
+        load8<T>(vbase + sidx * row_stride, vf);
+#pragma unroll
+        for (int i = 0; i < ATT_EPL; ++i) acc[i] += p * vf[i];
+      }
+    }
+    mx = nm;
+  }
+  __shared__ float s_mx[ATT_WARPS], s_sum[ATT_WARPS], s_acc[ATT_WARPS][ATT_MAXD];
+  if (lane == 0) { s_mx[warp] = mx; s_sum[warp] = sum; }
+#pragma unroll
+  for (int i = 0; i < ATT_EPL; ++i) s_acc[warp][d0 + i] = acc[i];
+  __syncthreads();
+  float gm = -INFINITY;
+#pragma unroll
+  for (int w = 0; w < ATT_WARPS; ++w) gm = fmaxf(gm, s_mx[w]);
+  float gs = 0.0f;
+#pragma unroll
+  for (int w = 0; w < ATT_WARPS; ++w) gs += s_mx[w] == -INFINITY ? 0.0f : s_sum[w] * __expf(s_mx[w] - gm);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float o = 0.0f;
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS; ++w) o += s_mx[w] == -INFINITY ? 0.0f : s_acc[w][d] * __expf(s_mx[w] - gm);
+    out[((int64_t)b * Hq + h) * D + d] = from_float<T>(o / gs);
+  }
+}
+
+// gu: fp32 [rows, 2F] = (gate | up) from the fused projection; out[r, f] = act(gate) * up, stored as T.
+// act: 0 = gelu (tanh approximation), 1 = silu
+template <typename T>
+__global__ void __launch_bounds__(256) gated_act_kernel(const float* __restrict__ gu, T* __restrict__ out, int64_t rows,
+                                                        int64_t F, int act) {
+  const int64_t total = rows * F;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / F, f = i - r * F;
+    const float g = gu[r * 2 * F + f], u = gu[r * 2 * F + F + f];
+    float a;
+    if (act == 0) a = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    else a = g / (1.0f + __expf(-g));
+    out[i] = from_float<T>(a * u);
+  }
+}
+
+}  // namespace bq
+
+using namespace bq;
+
+static int glue_ready(int dtype) {
+  if (device_id() < 0) return fail(BQ_ERR_STATE, "bq_init() has not been called");
+  if (dtype != BQ_DT_F32 && dtype != BQ_DT_BF16) return fail(BQ_ERR_ARG, "dtype must be BQ_DT_F32 or BQ_DT_BF16");
+  return BQ_OK;
+}
+
+extern "C" {
+
+int bq_add_rmsnorm(void* x, const float* delta, const float* weight, void* out, int64_t rows, int64_t H, float eps,
+                   int dtype, void* stream) {
+  int rc = glue_ready(dtype);
+  if (rc) return rc;
+  if (rows < 0 || H <= 0) return fail(BQ_ERR_ARG, "bad sizes");
+  if (rows == 0) return BQ_OK;
+  if (!x || !weight || !out) return fail(BQ_ERR_ARG, "null pointer");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == BQ_DT_F32) add_rmsnorm_kernel<float><<<(unsigned)rows, RN_THREADS, 0, s>>>((float*)x, delta, weight, (float*)out, H, eps);
+  else add_rmsnorm_kernel<__nv_bfloat16><<<(unsigned)rows, RN_THREADS, 0, s>>>((__nv_bfloat16*)x, delta, weight, (__nv_bfloat16*)out, H, eps);
+  count_launch();
+  BQ_CUDA(cudaGetLastError());
+  return BQ_OK;
+}
+
+int bq_rope_kv_append(const float* qkv, const int64_t* pos, void* q_out, void* k_cache, void* v_cache, int64_t B, int Hq,
+                      int Hkv, int D, int64_t S, float rope_base, int dtype, void* stream) {
+  int rc = glue_ready(dtype);
+  if (rc) return rc;
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || (D & 1) || S <= 0) return fail(BQ_ERR_ARG, "bad sizes");
+  if (!qkv || !pos || !q_out || !k_cache || !v_cache) return fail(BQ_ERR_ARG, "null pointer");
+  dim3 grid((unsigned)(Hq + 2 * Hkv), (unsigned)B);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == BQ_DT_F32)
+    rope_kv_append_kernel<float><<<grid, 128, 0, s>>>(qkv, pos, (float*)q_out, (float*)k_cache, (float*)v_cache, Hq, Hkv, D, S, rope_base);
+  else
+    rope_kv_append_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>(qkv, pos, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache,
+                                                               (__nv_bfloat16*)v_cache, Hq, Hkv, D, S, rope_base);
+  count_launch();
+  BQ_CUDA(cudaGetLastError());
+  return BQ_OK;
+}
+
+int bq_decode_attention(const void* q, const void* k_cache, const void* v_cache, const int64_t* pos, void* out, int64_t B,
+                        int Hq, int Hkv, int D, int64_t S, int dtype, void* stream) {
+  int rc = glue_ready(dtype);
+  if (rc) return rc;
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || D <= 0 || D > ATT_MAXD || (D % 8) || S <= 0)
+    return fail(BQ_ERR_ARG, "bad sizes (head_dim <= 256 and a multiple of 8, Hq a multiple of Hkv)");
+  if (!q || !k_cache || !v_cache || !pos || !out) return fail(BQ_ERR_ARG, "null pointer");
+  dim3 grid((unsigned)Hq, (unsigned)B);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == BQ_DT_F32)
+    decode_attention_kernel<float><<<grid, ATT_WARPS * 32, 0, s>>>((const float*)q, (const float*)k_cache, (const float*)v_cache, pos, (float*)out, Hq, Hkv, D, S);
+  else
+    decode_attention_kernel<__nv_bfloat16><<<grid, ATT_WARPS * 32, 0, s>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache,
+                                                                           (const __nv_bfloat16*)v_cache, pos, (__nv_bfloat16*)out, Hq, Hkv, D, S);
+  count_launch();
+  BQ_CUDA(cudaGetLastError());
+  return BQ_OK;
+}
+
+int bq_gated_act(const float* gate_up, void* out, int64_t rows, int64_t F, int act, int dtype, void* stream) {
+  int rc = glue_ready(dtype);
+  if (rc) return rc;
+  if (rows < 0 || F <= 0 || (act != 0 && act != 1)) return fail(BQ_ERR_ARG, "bad arguments");
+  if (rows == 0) return BQ_OK;
+  if (!gate_up || !out) return fail(BQ_ERR_ARG, "null pointer");
+  int64_t grid = (rows * F + 255) / 256;
+  if (grid > (int64_t)sm_count() * 8) grid = (int64_t)sm_count() * 8;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == BQ_DT_F32) gated_act_kernel<float><<<(unsigned)grid, 256, 0, s>>>(gate_up, (float*)out, rows, F, act);
+  else gated_act_kernel<__nv_bfloat16><<<(unsigned)grid, 256, 0, s>>>(gate_up, (__nv_bfloat16*)out, rows, F, act);
+  count_launch();
+  BQ_CUDA(cudaGetLastError());
+  return BQ_OK;
+}
+
+}  // extern "C"

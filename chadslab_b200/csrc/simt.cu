@@ -376,8 +376,82 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const T* __restrict__ logi
   }
 }
 
+// Large vocabularies: stage 1 reduces ARG_CHUNKS slices of every row to (value, index) pairs, stage 2 reduces the pairs.
+constexpr int ARG_CHUNKS = 128;
+template <typename T>
+__global__ void __launch_bounds__(256) argmax_partial_kernel(const T* __restrict__ logits, int64_t N, float* __restrict__ pv,
+                                                             int32_t* __restrict__ pi) {
+  const T* row = logits + (int64_t)blockIdx.y * N;
+  const int64_t per = (N + ARG_CHUNKS - 1) / ARG_CHUNKS;
+  const int64_t lo = (int64_t)blockIdx.x * per, hi = min(N, lo + per);
+  float best = -INFINITY;
+  int32_t bi = 0x7fffffff;
+  for (int64_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    const float v = to_float<T>(row[i]);
+    if (v > best || (v == best && (int32_t)i < bi)) { best = v; bi = (int32_t)i; }
+  }
+  __shared__ float sv[8];
+  __shared__ int32_t si[8];
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, off);
+    const int32_t oi = __shfl_xor_sync(0xffffffffu, bi, off);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w)
+      if (sv[w] > best || (sv[w] == best && si[w] < bi)) { best = sv[w]; bi = si[w]; }
+    pv[(int64_t)blockIdx.y * ARG_CHUNKS + blockIdx.x] = best;
+    pi[(int64_t)blockIdx.y * ARG_CHUNKS + blockIdx.x] = bi;
+  }
+}
+__global__ void __launch_bounds__(ARG_CHUNKS) argmax_final_kernel(const float* __restrict__ pv, const int32_t* __restrict__ pi,
+                                                                  int32_t* __restrict__ out) {
+  float best = pv[(int64_t)blockIdx.x * ARG_CHUNKS + threadIdx.x];
+  int32_t bi = pi[(int64_t)blockIdx.x * ARG_CHUNKS + threadIdx.x];
+  __shared__ float sv[ARG_CHUNKS / 32];
+  __shared__ int32_t si[ARG_CHUNKS / 32];
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, off);
+    const int32_t oi = __shfl_xor_sync(0xffffffffu, bi, off);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < ARG_CHUNKS / 32; ++w)
+      if (sv[w] > best || (sv[w] == best && si[w] < bi)) { best = sv[w]; bi = si[w]; }
+    out[blockIdx.x] = (bi == 0x7fffffff) ? 0 : bi;
+  }
+}
+
+static float* g_arg_pv = nullptr;          // grow-only scratch for the stage-1 pairs
+static int32_t* g_arg_pi = nullptr;
+static int64_t g_arg_rows = 0;
+
 int launch_argmax(const void* logits, int dtype, int64_t M, int64_t N, int32_t* out, cudaStream_t s) {
   if (M == 0) return BQ_OK;
+  if (N >= 32768 && M <= 65535) {
+    if (M > g_arg_rows) {
+      if (g_arg_pv) BQ_CUDA(cudaFree(g_arg_pv));
+      if (g_arg_pi) BQ_CUDA(cudaFree(g_arg_pi));
+      g_arg_pv = nullptr; g_arg_pi = nullptr; g_arg_rows = 0;
+      const int64_t rows = M + 64;
+      BQ_CUDA(cudaMalloc((void**)&g_arg_pv, sizeof(float) * rows * ARG_CHUNKS));
+      BQ_CUDA(cudaMalloc((void**)&g_arg_pi, sizeof(int32_t) * rows * ARG_CHUNKS));
+      g_arg_rows = rows;
+    }
+    dim3 grid(ARG_CHUNKS, (unsigned)M);
+    if (dtype == BQ_DT_F32) argmax_partial_kernel<float><<<grid, 256, 0, s>>>((const float*)logits, N, g_arg_pv, g_arg_pi);
+    else argmax_partial_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)logits, N, g_arg_pv, g_arg_pi);
+    argmax_final_kernel<<<(unsigned)M, ARG_CHUNKS, 0, s>>>(g_arg_pv, g_arg_pi, out);
+    count_launch(2);
+    BQ_CUDA(cudaGetLastError());
+    return BQ_OK;
+  }
   if (dtype == BQ_DT_F32)
     argmax_kernel<float><<<(int)M, 1024, 0, s>>>((const float*)logits, N, out);
   else

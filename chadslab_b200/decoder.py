@@ -67,6 +67,7 @@ class QuantDecoder:
         self.kv_sharded = cfg.n_kv_heads % world == 0 and cfg.n_kv_heads >= world
         self.h_local = cfg.n_heads // world
         self.kv_local = cfg.n_kv_heads // world if self.kv_sharded else cfg.n_kv_heads
+        self.ffn_local = cfg.ffn // world
         dev = embed.device
         self.k_cache = [torch.zeros((max_batch, max_seq, self.kv_local, cfg.head_dim), dtype=act_dtype, device=dev)
                         for _ in range(cfg.layers)]
@@ -79,12 +80,11 @@ class QuantDecoder:
         """get(name, axis) -> PackedWeight shard.  Builds the (possibly tensor-parallel) projection objects."""
         lin = {}
         kv_sharded = cfg.n_kv_heads % world == 0 and cfg.n_kv_heads >= world
+        kv_axis = "n" if kv_sharded else None
         for l in range(cfg.layers):
-            lin[f"l{l}.q"] = QuantLinear(get(f"l{l}.q", "n"))
-            lin[f"l{l}.k"] = QuantLinear(get(f"l{l}.k", "n" if kv_sharded else None))
-            lin[f"l{l}.v"] = QuantLinear(get(f"l{l}.v", "n" if kv_sharded else None))
-            lin[f"l{l}.gate"] = QuantLinear(get(f"l{l}.gate", "n"))
-            lin[f"l{l}.up"] = QuantLinear(get(f"l{l}.up", "n"))
+            # q|k|v and gate|up are each one packed weight (rows concatenated): one launch instead of three / two
+            lin[f"l{l}.qkv"] = QuantLinear(get([f"l{l}.q", f"l{l}.k", f"l{l}.v"], ["n", kv_axis, kv_axis]))
+            lin[f"l{l}.gate_up"] = QuantLinear(get([f"l{l}.gate", f"l{l}.up"], ["n", "n"]))
             o, d = QuantLinear(get(f"l{l}.o", "k")), QuantLinear(get(f"l{l}.down", "k"))
             lin[f"l{l}.o"] = parallel.RowParallelLinear(o) if world > 1 else o
             lin[f"l{l}.down"] = parallel.RowParallelLinear(d) if world > 1 else d
@@ -95,9 +95,16 @@ class QuantDecoder:
     @classmethod
     def from_numpy(cls, cfg: DecoderConfig, w: dict, act_dtype=torch.float32, rank=0, world=1, **kw):
         """w: name -> (codes, scales) for projections, arrays for 'embed', norms (as oracle.model.random_weights)."""
+        def get_one(name, axis, upload):
+            pw = PackedWeight(w[name][0], w[name][1], cfg.fmt, upload=upload and (world == 1 or axis is None))
+            return pw if (world == 1 or axis is None) else shard(pw, axis, rank, world, upload=upload)
+
         def get(name, axis):
-            pw = PackedWeight(w[name][0], w[name][1], cfg.fmt, upload=(world == 1 or axis is None))
-            return pw if (world == 1 or axis is None) else shard(pw, axis, rank, world)
+            if isinstance(name, str):
+                return get_one(name, axis, True)
+            parts = [get_one(n_, a_, False) for n_, a_ in zip(name, axis)]
+            return PackedWeight(np.concatenate([p_.codes for p_ in parts], 0), np.concatenate([p_.scales for p_ in parts], 0),
+                                cfg.fmt)
         lin = cls._wrap(cfg, get, rank, world)
         dev = torch.device("cuda", torch.cuda.current_device())
         embed = torch.from_numpy(w["embed"]).to(dev)
@@ -114,11 +121,13 @@ class QuantDecoder:
                   "lm_head": (cfg.vocab, cfg.hidden)}
 
         def get(name, axis):
-            N, K = shapes[name.split(".")[-1]]
-            if world > 1 and axis == "n":
-                N //= world
-            if world > 1 and axis == "k":
+            names, axes = ([name], [axis]) if isinstance(name, str) else (name, axis)
+            N, K = 0, shapes[names[0].split(".")[-1]][1]
+            for n_, a_ in zip(names, axes):
+                N += shapes[n_.split(".")[-1]][0] // (world if (world > 1 and a_ == "n") else 1)
+            if world > 1 and axes[0] == "k":
                 K //= world
+            name, axis = "+".join(names), axes[0]
             gen = torch.Generator(device="cuda").manual_seed(zlib.crc32(f"{seed}:{name}:{rank if axis else 0}".encode()))
             codes, scales = make_device_weight(torch, N, K, cfg.fmt, gen)
             return PackedWeight.from_device(codes, scales, cfg.fmt)
@@ -143,9 +152,11 @@ class QuantDecoder:
         S = self.pos + T
         for l in range(c.layers):
             h = _rmsnorm(x, self.norms[f"l{l}.norm1"], c.eps)
-            q = self.lin[f"l{l}.q"](h).to(self.act_dtype).reshape(B, T, self.h_local, c.head_dim)
-            k = self.lin[f"l{l}.k"](h).to(self.act_dtype).reshape(B, T, self.kv_local, c.head_dim)
-            v = self.lin[f"l{l}.v"](h).to(self.act_dtype).reshape(B, T, self.kv_local, c.head_dim)
+            nq, nkv = self.h_local * c.head_dim, self.kv_local * c.head_dim
+            qkv = self.lin[f"l{l}.qkv"](h).to(self.act_dtype)
+            q = qkv[..., :nq].reshape(B, T, self.h_local, c.head_dim)
+            k = qkv[..., nq:nq + nkv].reshape(B, T, self.kv_local, c.head_dim)
+            v = qkv[..., nq + nkv:].reshape(B, T, self.kv_local, c.head_dim)
             q, k = _rope(q, pos, c.rope_base), _rope(k, pos, c.rope_base)
             self.k_cache[l][:B, self.pos:S] = k
             self.v_cache[l][:B, self.pos:S] = v
@@ -158,7 +169,8 @@ class QuantDecoder:
             o = o.transpose(1, 2).reshape(B, T, self.h_local * c.head_dim)
             x = x + self.lin[f"l{l}.o"](o.contiguous()).to(self.act_dtype)
             h = _rmsnorm(x, self.norms[f"l{l}.norm2"], c.eps)
-            a = F.gelu(self.lin[f"l{l}.gate"](h), approximate="tanh") * self.lin[f"l{l}.up"](h)
+            gu = self.lin[f"l{l}.gate_up"](h)
+            a = F.gelu(gu[..., :self.ffn_local], approximate="tanh") * gu[..., self.ffn_local:]
             x = x + self.lin[f"l{l}.down"](a.to(self.act_dtype)).to(self.act_dtype)
         self.pos = S
         return _rmsnorm(x, self.norms["norm_f"], c.eps)
@@ -193,35 +205,45 @@ class QuantDecoder:
     # ---- static-shape decode step (capturable in a CUDA graph) -----------------------------------------
     def _step_static(self, tokens, pos_t):
         """One greedy decode step with every shape fixed: `tokens` int64 [B] and `pos_t` int64 [1] live on the
-        device and are updated in place (tokens <- next ids, pos_t += 1).  Attention runs over the whole KV buffer
-        under a position mask, so nothing depends on the host-side position."""
-        c = self.cfg
+        device and are updated in place (tokens <- next ids, pos_t += 1).  Between the quantized matmuls the step
+        runs the library's glue kernels (residual add + RMSNorm, RoPE + KV append, single-query attention, gated
+        activation), all of which read the position from device memory, so the step is graph-capturable."""
+        from . import _lib
+        from .ops import _dt_of_torch, _stream_ptr
+        c, lib, st = self.cfg, _lib.lib(), _stream_ptr()
         B = tokens.shape[0]
-        x = self.embed[tokens].to(self.act_dtype)[:, None, :]
+        dt = _dt_of_torch(self.k_cache[0])
+        dev = tokens.device
+        x = self.embed[tokens].to(self.act_dtype).contiguous()                    # residual stream [B, hidden]
+        h = torch.empty_like(x)
         S = self.k_cache[0].shape[1]
-        mask = (torch.arange(S, device=x.device) <= pos_t)[None, :]              # [1, S]
+        q = torch.empty((B, self.h_local, c.head_dim), dtype=self.act_dtype, device=dev)
+        att = torch.empty_like(q)
+        act = torch.empty((B, self.ffn_local), dtype=self.act_dtype, device=dev)
+        delta = None
         for l in range(c.layers):
-            h = _rmsnorm(x, self.norms[f"l{l}.norm1"], c.eps)
-            q = self.lin[f"l{l}.q"](h).to(self.act_dtype).reshape(B, 1, self.h_local, c.head_dim)
-            k = self.lin[f"l{l}.k"](h).to(self.act_dtype).reshape(B, 1, self.kv_local, c.head_dim)
-            v = self.lin[f"l{l}.v"](h).to(self.act_dtype).reshape(B, 1, self.kv_local, c.head_dim)
-            q, k = _rope(q, pos_t, c.rope_base), _rope(k, pos_t, c.rope_base)
-            self.k_cache[l][:B].index_copy_(1, pos_t, k)
-            self.v_cache[l][:B].index_copy_(1, pos_t, v)
-            o = F.scaled_dot_product_attention(q.transpose(1, 2), self.k_cache[l][:B].transpose(1, 2),
-                                               self.v_cache[l][:B].transpose(1, 2), attn_mask=mask,
-                                               enable_gqa=self.h_local != self.kv_local)
-            o = o.transpose(1, 2).reshape(B, 1, self.h_local * c.head_dim)
-            x = x + self.lin[f"l{l}.o"](o.contiguous()).to(self.act_dtype)
-            h = _rmsnorm(x, self.norms[f"l{l}.norm2"], c.eps)
-            a = F.gelu(self.lin[f"l{l}.gate"](h), approximate="tanh") * self.lin[f"l{l}.up"](h)
-            x = x + self.lin[f"l{l}.down"](a.to(self.act_dtype)).to(self.act_dtype)
-        hfin = _rmsnorm(x, self.norms["norm_f"], c.eps)[:, 0].contiguous()
+            _lib.check(lib.bq_add_rmsnorm(x.data_ptr(), delta.data_ptr() if delta is not None else None,
+                                          self.norms[f"l{l}.norm1"].data_ptr(), h.data_ptr(), B, c.hidden, c.eps, dt, st))
+            qkv = self.lin[f"l{l}.qkv"](h)                                        # fp32 [B, (Hq + 2 Hkv) D]
+            _lib.check(lib.bq_rope_kv_append(qkv.data_ptr(), pos_t.data_ptr(), q.data_ptr(), self.k_cache[l].data_ptr(),
+                                             self.v_cache[l].data_ptr(), B, self.h_local, self.kv_local, c.head_dim, S,
+                                             c.rope_base, dt, st))
+            _lib.check(lib.bq_decode_attention(q.data_ptr(), self.k_cache[l].data_ptr(), self.v_cache[l].data_ptr(),
+                                               pos_t.data_ptr(), att.data_ptr(), B, self.h_local, self.kv_local,
+                                               c.head_dim, S, dt, st))
+            delta = self.lin[f"l{l}.o"](att.reshape(B, -1))                       # fp32 (all-reduced when sharded)
+            _lib.check(lib.bq_add_rmsnorm(x.data_ptr(), delta.data_ptr(), self.norms[f"l{l}.norm2"].data_ptr(),
+                                          h.data_ptr(), B, c.hidden, c.eps, dt, st))
+            gu = self.lin[f"l{l}.gate_up"](h)
+            _lib.check(lib.bq_gated_act(gu.data_ptr(), act.data_ptr(), B, self.ffn_local, 0, dt, st))
+            delta = self.lin[f"l{l}.down"](act)
+        _lib.check(lib.bq_add_rmsnorm(x.data_ptr(), delta.data_ptr(), self.norms["norm_f"].data_ptr(), h.data_ptr(), B,
+                                      c.hidden, c.eps, dt, st))
         head = self.lin["lm_head"]
         if self.world > 1:
-            ids = parallel.VocabParallelHead(head, c.vocab // self.world).greedy(hfin)
+            ids = parallel.VocabParallelHead(head, c.vocab // self.world).greedy(h)
         else:
-            ids = head.greedy(hfin).long()
+            ids = head.greedy(h).long()
         tokens.copy_(ids)
         pos_t.add_(1)
 

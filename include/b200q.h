@@ -98,6 +98,25 @@ int bq_lm_head(bq_weight_t w, const void* x, int x_dtype, int64_t M, void* logit
 int bq_last_path(void);
 int64_t bq_launch_count(void);           /* kernels launched by this library so far       */
 
+/* ---- decode-step glue between the quantized matmuls (the callers on either side of the path; the
+ *      reference has no counterpart).  dtype = storage type of activations / KV cache (F32 or BF16);
+ *      arithmetic is fp32.  `pos` is a DEVICE int64: the position being written, so a captured CUDA
+ *      graph can be replayed for every token. ------------------------------------------------------ */
+/* x[rows,H] += delta[rows,H] (fp32, may be NULL); out = x * rsqrt(mean(x^2) + eps) * weight[H]      */
+int bq_add_rmsnorm(void* x, const float* delta, const float* weight, void* out, int64_t rows,
+                   int64_t H, float eps, int dtype, void* stream);
+/* qkv: fp32 [B, (Hq + 2*Hkv) * D] from a fused q|k|v projection.  Rotate-half RoPE on q and k at
+ * position *pos; q -> q_out [B,Hq,D]; k, v -> caches [B,S,Hkv,D] at row *pos.                        */
+int bq_rope_kv_append(const float* qkv, const int64_t* pos, void* q_out, void* k_cache, void* v_cache,
+                      int64_t B, int Hq, int Hkv, int D, int64_t S, float rope_base, int dtype,
+                      void* stream);
+/* out[B,Hq,D] = softmax(q . K[0..*pos] / sqrt(D)) . V[0..*pos], grouped-query (Hq % Hkv == 0), D <= 256 */
+int bq_decode_attention(const void* q, const void* k_cache, const void* v_cache, const int64_t* pos,
+                        void* out, int64_t B, int Hq, int Hkv, int D, int64_t S, int dtype, void* stream);
+/* gate_up: fp32 [rows, 2F] (gate | up); out[rows,F] = act(gate) * up; act 0 = gelu(tanh), 1 = silu    */
+int bq_gated_act(const float* gate_up, void* out, int64_t rows, int64_t F, int act, int dtype,
+                 void* stream);
+
 /* ---- MoE (spec: "router top-k, a token permute/gather, a grouped quantized expert GEMM
  *      and a weighted scatter-combine") ------------------------------------------------- */
 /* softmax over E router logits (device f32[T,E]) -> top-k ids (int32[T,k], descending

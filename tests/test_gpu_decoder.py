@@ -56,14 +56,16 @@ def test_tensor_parallel_decoder_two_gpus(cuda_lib):
 
 
 @pytest.mark.parametrize("fmt", [0, 1])
-def test_cuda_graph_decode_matches_eager(cuda_lib, fmt):
-    """The static-shape decode step replayed from a CUDA graph generates the same greedy tokens."""
+@pytest.mark.parametrize("adt", ["float32", "bfloat16"])
+def test_cuda_graph_decode_matches_eager(cuda_lib, fmt, adt):
+    """The decode step built from the library's glue kernels (add+RMSNorm, RoPE+KV append, single-query attention,
+    gated activation) and replayed from a CUDA graph generates the same greedy tokens as the eager PyTorch glue."""
     import torch
     from chadslab_b200.decoder import DecoderConfig, QuantDecoder
     cfg = dict(SMALL, fmt=fmt)
     w = omodel.random_weights(cfg, seed=7)
     prompt = torch.from_numpy(np.random.default_rng(2).integers(0, cfg["vocab"], (2, 5))).cuda()
-    dec = QuantDecoder.from_numpy(DecoderConfig(**cfg), w, act_dtype=torch.bfloat16, max_seq=32, max_batch=2)
+    dec = QuantDecoder.from_numpy(DecoderConfig(**cfg), w, act_dtype=getattr(torch, adt), max_seq=32, max_batch=2)
     eager = dec.generate(prompt, 6).cpu().numpy()
     dec.reset()
     first = dec.next_tokens(prompt)                      # prefill, first generated token

@@ -121,7 +121,7 @@ def test_lm_head_greedy(cuda_lib, fmt):
     import torch
     import chadslab_b200 as cb
     rng = np.random.default_rng(9)
-    V, K = 32000, 256
+    V, K = 40000, 256          # > 32768: exercises the two-stage argmax; rows 123 and 777 fall in different slices
     W = rng.normal(0, 0.02, (V, K)).astype(np.float32)
     W[777] = W[123]                                           # exact tie between two vocabulary rows
     codes, scales = spec.quantize(W, fmt)
