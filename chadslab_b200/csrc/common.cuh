@@ -86,9 +86,39 @@ int launch_moe_experts_tc(const Moe* m, const void* xp, const int32_t* offsets, 
 //   Q8: every byte holds code + 128 (sign bit flipped), so mantissa insertion needs no sign fix-up.
 int launch_device_encode(uint8_t* codes, size_t bytes, int fmt, bool to_device_layout, cudaStream_t s);
 int launch_argmax(const void* logits, int dtype, int64_t M, int64_t N, int32_t* out, cudaStream_t s);
+bool pdl_enabled();     // BQ_PDL environment switch (default on)
+
+#ifdef __CUDACC__
+// Launch with the programmatic-stream-serialization attribute (the kernel must call pdl_wait() before it reads or
+// writes anything a preceding kernel on the stream may still be using).  `cluster_y` > 1 adds a cluster dimension.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chain(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, int cluster_y,
+                                Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = s;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  if (pdl_enabled()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (cluster_y > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = 1; attr[n].val.clusterDim.y = (unsigned)cluster_y; attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  cfg.attrs = attr; cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+#endif
 
 // ---- device helpers --------------------------------------------------------------------------
 #ifdef __CUDACC__
+// Programmatic dependent launch: a kernel lets its successor start launching right away and itself waits for its
+// predecessor (completion + memory visibility) before it touches anything the predecessor may have written.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ uint4 ldg_stream16(const void* p) {
   uint4 v;
   asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"

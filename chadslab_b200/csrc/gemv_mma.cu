@@ -115,6 +115,10 @@ qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ s
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
+  // Launched with programmatic stream serialization: it may start while a preceding (small, early-triggering) kernel
+  // still runs, so wait before touching x / y.  It never triggers its own successor early: CTAs of a following GEMV
+  // parked on the SMs cost this one bandwidth (measured).
+  pdl_wait();
 
   // ---- activations -> scaled fp16 vectors in shared memory ------------------------------------------
   {
@@ -418,23 +422,11 @@ static int gm_launch(const uint8_t* codes, const __half* scales, const XT* x, YT
   int kc = 1;
   while (kc < 8 && grid * kc * 2 <= (int64_t)sm_count() * 3 && steps_per_warp / (kc * 2) >= 4) kc *= 2;
   if (grid > cap) grid = cap;
-  if (kc == 1) {
-    kern<<<(unsigned)grid, GM_THREADS, smem, s>>>(codes, scales, x, y, N, K, m_rows, ldy, 1);
-  } else {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid, (unsigned)kc, 1);
-    cfg.blockDim = dim3(GM_THREADS, 1, 1);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = (unsigned)kc;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    BQ_CUDA(cudaLaunchKernelEx(&cfg, kern_cl, codes, scales, x, y, N, K, m_rows, ldy, kc));
-  }
+  if (kc == 1)
+    BQ_CUDA(launch_chain(kern, dim3((unsigned)grid), dim3(GM_THREADS), smem, s, 1, codes, scales, x, y, N, K, m_rows, ldy, 1));
+  else
+    BQ_CUDA(launch_chain(kern_cl, dim3((unsigned)grid, (unsigned)kc), dim3(GM_THREADS), smem, s, kc, codes, scales, x, y, N, K,
+                         m_rows, ldy, kc));
   count_launch();
   BQ_CUDA(cudaGetLastError());
   return BQ_OK;

@@ -14,6 +14,8 @@ template <typename T>
 __global__ void __launch_bounds__(RN_THREADS) add_rmsnorm_kernel(T* __restrict__ x, const float* __restrict__ delta,
                                                                  const float* __restrict__ w, T* __restrict__ out,
                                                                  int64_t H, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   T* xr = x + (int64_t)blockIdx.x * H;
   const float* dr = delta ? delta + (int64_t)blockIdx.x * H : nullptr;
   T* orow = out + (int64_t)blockIdx.x * H;
@@ -67,6 +69,8 @@ __global__ void __launch_bounds__(128) rope_kv_append_kernel(const float* __rest
                                                              T* __restrict__ v_cache, int Hq, int Hkv, int D, int64_t S,
                                                              float base) {
   const int b = blockIdx.y, h = blockIdx.x;            // h in [0, Hq + 2*Hkv)
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t pos = *pos_p;
   const float* src = qkv + ((int64_t)b * (Hq + 2 * Hkv) + h) * D;
   const int half = D / 2;
@@ -120,6 +124,8 @@ decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
   const int b = blockIdx.y, h = blockIdx.x;
   const int kv = h / (Hq / Hkv);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t n_pos = *pos_p + 1;
   const int d0 = lane * ATT_EPL;
   const bool live = d0 < D;
@@ -199,6 +205,8 @@ decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
 template <typename T>
 __global__ void __launch_bounds__(256) gated_act_kernel(const float* __restrict__ gu, T* __restrict__ out, int64_t rows,
                                                         int64_t F, int act) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t total = rows * F;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t r = i / F, f = i - r * F;
@@ -230,8 +238,11 @@ int bq_add_rmsnorm(void* x, const float* delta, const float* weight, void* out, 
   if (rows == 0) return BQ_OK;
   if (!x || !weight || !out) return fail(BQ_ERR_ARG, "null pointer");
   cudaStream_t s = (cudaStream_t)stream;
-  if (dtype == BQ_DT_F32) add_rmsnorm_kernel<float><<<(unsigned)rows, RN_THREADS, 0, s>>>((float*)x, delta, weight, (float*)out, H, eps);
-  else add_rmsnorm_kernel<__nv_bfloat16><<<(unsigned)rows, RN_THREADS, 0, s>>>((__nv_bfloat16*)x, delta, weight, (__nv_bfloat16*)out, H, eps);
+  if (dtype == BQ_DT_F32)
+    BQ_CUDA(launch_chain(add_rmsnorm_kernel<float>, dim3((unsigned)rows), dim3(RN_THREADS), 0, s, 1, (float*)x, delta, weight, (float*)out, H, eps));
+  else
+    BQ_CUDA(launch_chain(add_rmsnorm_kernel<__nv_bfloat16>, dim3((unsigned)rows), dim3(RN_THREADS), 0, s, 1, (__nv_bfloat16*)x, delta, weight,
+                         (__nv_bfloat16*)out, H, eps));
   count_launch();
   BQ_CUDA(cudaGetLastError());
   return BQ_OK;
@@ -246,10 +257,11 @@ int bq_rope_kv_append(const float* qkv, const int64_t* pos, void* q_out, void* k
   dim3 grid((unsigned)(Hq + 2 * Hkv), (unsigned)B);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == BQ_DT_F32)
-    rope_kv_append_kernel<float><<<grid, 128, 0, s>>>(qkv, pos, (float*)q_out, (float*)k_cache, (float*)v_cache, Hq, Hkv, D, S, rope_base);
+    BQ_CUDA(launch_chain(rope_kv_append_kernel<float>, grid, dim3(128), 0, s, 1, qkv, pos, (float*)q_out, (float*)k_cache,
+                         (float*)v_cache, Hq, Hkv, D, S, rope_base));
   else
-    rope_kv_append_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>(qkv, pos, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache,
-                                                               (__nv_bfloat16*)v_cache, Hq, Hkv, D, S, rope_base);
+    BQ_CUDA(launch_chain(rope_kv_append_kernel<__nv_bfloat16>, grid, dim3(128), 0, s, 1, qkv, pos, (__nv_bfloat16*)q_out,
+                         (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, Hq, Hkv, D, S, rope_base));
   count_launch();
   BQ_CUDA(cudaGetLastError());
   return BQ_OK;
@@ -265,10 +277,11 @@ int bq_decode_attention(const void* q, const void* k_cache, const void* v_cache,
   dim3 grid((unsigned)Hq, (unsigned)B);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == BQ_DT_F32)
-    decode_attention_kernel<float><<<grid, ATT_WARPS * 32, 0, s>>>((const float*)q, (const float*)k_cache, (const float*)v_cache, pos, (float*)out, Hq, Hkv, D, S);
+    BQ_CUDA(launch_chain(decode_attention_kernel<float>, grid, dim3(ATT_WARPS * 32), 0, s, 1, (const float*)q, (const float*)k_cache,
+                         (const float*)v_cache, pos, (float*)out, Hq, Hkv, D, S));
   else
-    decode_attention_kernel<__nv_bfloat16><<<grid, ATT_WARPS * 32, 0, s>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache,
-                                                                           (const __nv_bfloat16*)v_cache, pos, (__nv_bfloat16*)out, Hq, Hkv, D, S);
+    BQ_CUDA(launch_chain(decode_attention_kernel<__nv_bfloat16>, grid, dim3(ATT_WARPS * 32), 0, s, 1, (const __nv_bfloat16*)q,
+                         (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, pos, (__nv_bfloat16*)out, Hq, Hkv, D, S));
   count_launch();
   BQ_CUDA(cudaGetLastError());
   return BQ_OK;
@@ -283,8 +296,11 @@ int bq_gated_act(const float* gate_up, void* out, int64_t rows, int64_t F, int a
   int64_t grid = (rows * F + 255) / 256;
   if (grid > (int64_t)sm_count() * 8) grid = (int64_t)sm_count() * 8;
   cudaStream_t s = (cudaStream_t)stream;
-  if (dtype == BQ_DT_F32) gated_act_kernel<float><<<(unsigned)grid, 256, 0, s>>>(gate_up, (float*)out, rows, F, act);
-  else gated_act_kernel<__nv_bfloat16><<<(unsigned)grid, 256, 0, s>>>(gate_up, (__nv_bfloat16*)out, rows, F, act);
+  if (dtype == BQ_DT_F32)
+    BQ_CUDA(launch_chain(gated_act_kernel<float>, dim3((unsigned)grid), dim3(256), 0, s, 1, gate_up, (float*)out, rows, F, act));
+  else
+    BQ_CUDA(launch_chain(gated_act_kernel<__nv_bfloat16>, dim3((unsigned)grid), dim3(256), 0, s, 1, gate_up, (__nv_bfloat16*)out,
+                         rows, F, act));
   count_launch();
   BQ_CUDA(cudaGetLastError());
   return BQ_OK;

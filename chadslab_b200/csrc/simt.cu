@@ -381,6 +381,8 @@ constexpr int ARG_CHUNKS = 128;
 template <typename T>
 __global__ void __launch_bounds__(256) argmax_partial_kernel(const T* __restrict__ logits, int64_t N, float* __restrict__ pv,
                                                              int32_t* __restrict__ pi) {
+  pdl_launch_dependents();
+  pdl_wait();
   const T* row = logits + (int64_t)blockIdx.y * N;
   const int64_t per = (N + ARG_CHUNKS - 1) / ARG_CHUNKS;
   const int64_t lo = (int64_t)blockIdx.x * per, hi = min(N, lo + per);
@@ -409,6 +411,8 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(const T* __restrict
 }
 __global__ void __launch_bounds__(ARG_CHUNKS) argmax_final_kernel(const float* __restrict__ pv, const int32_t* __restrict__ pi,
                                                                   int32_t* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
   float best = pv[(int64_t)blockIdx.x * ARG_CHUNKS + threadIdx.x];
   int32_t bi = pi[(int64_t)blockIdx.x * ARG_CHUNKS + threadIdx.x];
   __shared__ float sv[ARG_CHUNKS / 32];
@@ -445,9 +449,13 @@ int launch_argmax(const void* logits, int dtype, int64_t M, int64_t N, int32_t* 
       g_arg_rows = rows;
     }
     dim3 grid(ARG_CHUNKS, (unsigned)M);
-    if (dtype == BQ_DT_F32) argmax_partial_kernel<float><<<grid, 256, 0, s>>>((const float*)logits, N, g_arg_pv, g_arg_pi);
-    else argmax_partial_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)logits, N, g_arg_pv, g_arg_pi);
-    argmax_final_kernel<<<(unsigned)M, ARG_CHUNKS, 0, s>>>(g_arg_pv, g_arg_pi, out);
+    if (dtype == BQ_DT_F32)
+      BQ_CUDA(launch_chain(argmax_partial_kernel<float>, grid, dim3(256), 0, s, 1, (const float*)logits, N, g_arg_pv, g_arg_pi));
+    else
+      BQ_CUDA(launch_chain(argmax_partial_kernel<__nv_bfloat16>, grid, dim3(256), 0, s, 1, (const __nv_bfloat16*)logits, N, g_arg_pv,
+                           g_arg_pi));
+    BQ_CUDA(launch_chain(argmax_final_kernel, dim3((unsigned)M), dim3(ARG_CHUNKS), 0, s, 1, (const float*)g_arg_pv,
+                         (const int32_t*)g_arg_pi, out));
     count_launch(2);
     BQ_CUDA(cudaGetLastError());
     return BQ_OK;
