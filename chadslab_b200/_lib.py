@@ -62,6 +62,15 @@ PROTOTYPES = {
     "bq_moe_destroy": (_i32, [_h]),
     "bq_moe_experts": (_i32, [_h, _vp, _vp, _i64, _vp, _vp, _i32, _vp]),
     "bq_moe_combine": (_i32, [_vp, _vp, _vp, _i64, _i32, _i64, _vp, _i32, _vp]),
+    "bq_comm_create": (_i32, [_i32, _i32, _i64, C.POINTER(_h)]),
+    "bq_comm_handle": (_i32, [_h, _vp]),
+    "bq_comm_connect": (_i32, [_h, _vp]),
+    "bq_comm_connect_loopback": (_i32, [_h]),
+    "bq_comm_set_timeout_ms": (_i32, [_h, _i32]),
+    "bq_comm_destroy": (_i32, [_h]),
+    "bq_qlinear_push": (_i32, [_h, _vp, _i32, _i64, _h, _vp]),
+    "bq_allreduce": (_i32, [_h, _vp, _vp, _i64, _vp]),
+    "bq_allreduce_add_rmsnorm": (_i32, [_h, _vp, _vp, _vp, _vp, _i64, _i64, C.c_float, _i32, _vp]),
 }
 
 _lock = threading.Lock()

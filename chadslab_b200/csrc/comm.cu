@@ -1,0 +1,397 @@
+// Peer-memory communicator for the tensor-parallel shard boundary: a one-shot all-reduce over NVLink written as
+// plain stores into the other ranks' HBM plus flags, fused with what precedes it (the row-parallel GEMV deposits
+// its partial sums directly in the peers' receive slots, gemv_push.cu) and with what follows it (residual add +
+// RMSNorm of the reduced row).  One process per GPU; the buffers are exchanged as CUDA IPC handles by the host
+// code (which carries the 64-byte handles over its own process group).
+//
+// Protocol, per call (epoch e, parity p = e & 1), identical on every rank:
+//   1. deposit: rank s stores its contribution into slot [p][s] of EVERY rank's buffer (its own included);
+//   2. signal:  after a system-scope fence, rank s stores e into flag [s][chunk] of every rank (release);
+//   3. wait:    a rank polls its own flags [r][chunk] for all r until they reach e (acquire) -- bounded: after
+//               the communicator's time limit (5 s unless changed) the kernel records BQ_ERR_TIMEOUT in the library's status word and carries on;
+//   4. sum:     slots [p][0..world) are added in rank order, so every rank gets bit-identical results;
+//   5. the last CTA to finish advances the epoch (device-side, so a replayed CUDA graph keeps working).
+// Two parities suffice: a rank can only be one call ahead of the slowest (it needs everybody's flag of call e to
+// finish call e), and it deposits call e+1 in the other parity.  Flags only grow; "reached e" is (int)(flag - e) >= 0.
+// Nothing here uses multicast or multimem: plain ld / st on peer-mapped memory only.
+#include <cstring>
+#include <mutex>
+#include <unordered_set>
+
+#include "common.cuh"
+
+namespace bq {
+
+constexpr int COMM_WAIT_MS_DEFAULT = 5000;
+constexpr int COMM_HEADER_BYTES = 256;
+constexpr uint32_t COMM_MAGIC = 0xB200C033u;
+constexpr int AR_THREADS = 256;
+constexpr int AR_CACHE = 16;                        // row elements a thread keeps in registers (rows <= 4096)
+
+struct Comm {
+  uint32_t magic;
+  int rank, world;
+  int64_t slot_elems;
+  size_t bytes;
+  uint8_t* local;                       // this rank's buffer (cudaMalloc)
+  void* peer[COMM_MAX_WORLD];           // mappings of the other ranks' buffers (nullptr for self / not connected)
+  CommDev* dev;                         // device copy of the descriptor
+  int wait_ms;
+  bool connected;
+  bool loopback;                        // peers are private stand-in buffers of this process (bq_comm_connect_loopback)
+};
+
+static std::mutex c_mu;
+static std::unordered_set<void*> c_comms;
+
+static Comm* get_comm(bq_comm_t h) {
+  void* p = reinterpret_cast<void*>(static_cast<uintptr_t>(h));
+  std::lock_guard<std::mutex> lk(c_mu);
+  if (!p || !c_comms.count(p) || static_cast<Comm*>(p)->magic != COMM_MAGIC) {
+    fail(BQ_ERR_HANDLE, "invalid communicator handle");
+    return nullptr;
+  }
+  return static_cast<Comm*>(p);
+}
+
+static size_t comm_flag_bytes() { return (size_t)COMM_MAX_WORLD * COMM_MAX_CHUNKS * sizeof(uint32_t); }
+static size_t comm_total_bytes(int world, int64_t slot_elems) {
+  return COMM_HEADER_BYTES + comm_flag_bytes() + (size_t)2 * world * slot_elems * sizeof(float);
+}
+
+// ---- device side ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint64_t comm_now_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Steps 2 and 3 for one chunk.  Called by every thread of the CTA after its deposits were issued.
+__device__ __forceinline__ void comm_signal_wait(const CommDev* d, uint32_t e, int chunk, int* status) {
+  __syncthreads();
+  if ((int)threadIdx.x < d->world) {
+    const int r = threadIdx.x;
+    __threadfence_system();
+    st_release_sys(d->flags[r] + (int64_t)d->rank * COMM_MAX_CHUNKS + chunk, e);
+    const uint32_t* mine = d->flags[d->rank] + (int64_t)r * COMM_MAX_CHUNKS + chunk;
+    const uint64_t t0 = comm_now_ns();
+    uint32_t spins = 0;
+    while ((int32_t)(ld_acquire_sys(mine) - e) < 0) {
+      if ((++spins & 255u) == 0 && comm_now_ns() - t0 > d->wait_ns) {
+        atomicExch(status, (int)BQ_ERR_TIMEOUT);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+}
+
+// Step 5.  Called by every thread of the CTA when its reads of the slots are done.
+__device__ __forceinline__ void comm_finish(const CommDev* d, uint32_t e) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t done = atomicAdd(d->state + 1, 1u);
+    if (done == gridDim.x - 1) {
+      d->state[1] = 0;
+      __threadfence();
+      *reinterpret_cast<volatile uint32_t*>(d->state) = e + 1;
+    }
+  }
+}
+
+__device__ __forceinline__ float ld_slot(const float* p) { return __ldcg(p); }   // L2 only: the line was written remotely
+
+// out[i] = sum over ranks of in_r[i].  `in` == nullptr: the contributions were already deposited by the kernel
+// before this one (the PUSH GEMV).  One chunk of `chunk` elements per CTA.
+__global__ void __launch_bounds__(AR_THREADS) allreduce_sum_kernel(const CommDev* __restrict__ d, const float* __restrict__ in,
+                                                                   float* __restrict__ out, int64_t count, int64_t chunk,
+                                                                   int* status) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint32_t e = *reinterpret_cast<const volatile uint32_t*>(d->state);
+  const int world = d->world;
+  const int64_t lo = (int64_t)blockIdx.x * chunk;
+  const int64_t hi = lo + chunk < count ? lo + chunk : count;
+  const int64_t par = (int64_t)(e & 1u) * world;
+  if (in) {
+    const int64_t off = (par + d->rank) * d->slot_elems;
+    for (int64_t i = lo + threadIdx.x; i < hi; i += AR_THREADS) {
+      const float v = in[i];
+      for (int r = 0; r < world; ++r) d->data[r][off + i] = v;
+    }
+  }
+  comm_signal_wait(d, e, blockIdx.x, status);
+  const float* mine = d->data[d->rank];
+  for (int64_t i = lo + threadIdx.x; i < hi; i += AR_THREADS) {
+    float s = ld_slot(mine + par * d->slot_elems + i);
+    for (int r = 1; r < world; ++r) s += ld_slot(mine + (par + r) * d->slot_elems + i);
+    out[i] = s;
+  }
+  comm_finish(d, e);
+}
+
+// One CTA per row of H elements: delta = sum over ranks of the deposited rows; x <- T(x + delta) (the residual
+// stream, stored in T); normed = T(x * rsqrt(mean(x^2) + eps) * gamma).  Same arithmetic and rounding as the
+// single-GPU add + RMSNorm kernel.  `in` as above.
+template <typename T>
+__global__ void __launch_bounds__(AR_THREADS) allreduce_add_rmsnorm_kernel(const CommDev* __restrict__ d,
+                                                                           const float* __restrict__ in, T* __restrict__ x,
+                                                                           const float* __restrict__ gamma,
+                                                                           T* __restrict__ normed, int64_t H, float eps,
+                                                                           int* status) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint32_t e = *reinterpret_cast<const volatile uint32_t*>(d->state);
+  const int world = d->world;
+  const int64_t row0 = (int64_t)blockIdx.x * H;
+  const int64_t par = (int64_t)(e & 1u) * world;
+  if (in) {
+    const int64_t off = (par + d->rank) * d->slot_elems + row0;
+    for (int64_t i = threadIdx.x; i < H; i += AR_THREADS) {
+      const float v = in[row0 + i];
+      for (int r = 0; r < world; ++r) d->data[r][off + i] = v;
+    }
+  }
+  comm_signal_wait(d, e, blockIdx.x, status);
+  const float* mine = d->data[d->rank] + row0;
+  T* xr = x + row0;
+  T* orow = normed + row0;
+  float cache[AR_CACHE];
+  float ss = 0.0f;
+#pragma unroll
+  for (int j = 0; j < AR_CACHE; ++j) {
+    const int64_t i = threadIdx.x + (int64_t)j * AR_THREADS;
+    float v = 0.0f;
+    if (i < H) {
+      float s = ld_slot(mine + par * d->slot_elems + i);
+      for (int r = 1; r < world; ++r) s += ld_slot(mine + (par + r) * d->slot_elems + i);
+      v = to_float<T>(from_float<T>(to_float<T>(xr[i]) + s));
+      xr[i] = from_float<T>(v);
+    }
+    cache[j] = v;
+    ss += v * v;
+  }
+  __shared__ float red[AR_THREADS / 32];
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.0f;
+#pragma unroll
+  for (int i = 0; i < AR_THREADS / 32; ++i) tot += red[i];
+  const float inv = rsqrtf(tot / (float)H + eps);
+#pragma unroll
+  for (int j = 0; j < AR_CACHE; ++j) {
+    const int64_t i = threadIdx.x + (int64_t)j * AR_THREADS;
+    if (i < H) orow[i] = from_float<T>(cache[j] * inv * gamma[i]);
+  }
+  comm_finish(d, e);
+}
+
+static int comm_ready() {
+  if (device_id() < 0) return fail(BQ_ERR_STATE, "bq_init() has not been called");
+  return BQ_OK;
+}
+
+static int upload_desc(Comm* c) {
+  CommDev h = {};
+  for (int r = 0; r < c->world; ++r) {
+    uint8_t* base = r == c->rank ? c->local : static_cast<uint8_t*>(c->peer[r]);
+    if (!base) return fail(BQ_ERR_STATE, "communicator is not connected to every rank");
+    h.flags[r] = reinterpret_cast<uint32_t*>(base + COMM_HEADER_BYTES);
+    h.data[r] = reinterpret_cast<float*>(base + COMM_HEADER_BYTES + comm_flag_bytes());
+  }
+  h.state = reinterpret_cast<uint32_t*>(c->local);
+  h.slot_elems = c->slot_elems;
+  h.wait_ns = (uint64_t)c->wait_ms * 1000000ull;
+  h.rank = c->rank;
+  h.world = c->world;
+  BQ_CUDA(cudaMemcpy(c->dev, &h, sizeof(h), cudaMemcpyHostToDevice));
+  return BQ_OK;
+}
+
+}  // namespace bq
+
+using namespace bq;
+
+extern "C" {
+
+int bq_comm_create(int rank, int world, int64_t max_elems, bq_comm_t* out) {
+  int rc = comm_ready();
+  if (rc) return rc;
+  if (!out) return fail(BQ_ERR_ARG, "null pointer");
+  if (world < 1 || world > COMM_MAX_WORLD || rank < 0 || rank >= world) return fail(BQ_ERR_ARG, "bad rank / world (world <= 8)");
+  if (max_elems <= 0 || max_elems > ((int64_t)1 << 28)) return fail(BQ_ERR_ARG, "max_elems out of range");
+  Comm* c = new Comm();
+  c->magic = COMM_MAGIC;
+  c->rank = rank; c->world = world;
+  c->slot_elems = (max_elems + 63) / 64 * 64;
+  c->bytes = comm_total_bytes(world, c->slot_elems);
+  c->local = nullptr; c->dev = nullptr; c->connected = false; c->loopback = false; c->wait_ms = COMM_WAIT_MS_DEFAULT;
+  for (int r = 0; r < COMM_MAX_WORLD; ++r) c->peer[r] = nullptr;
+  cudaError_t e = cudaMalloc((void**)&c->local, c->bytes);
+  if (e == cudaSuccess) e = cudaMalloc((void**)&c->dev, sizeof(CommDev));
+  if (e == cudaSuccess) e = cudaMemset(c->local, 0, c->bytes);
+  const uint32_t one = 1;
+  if (e == cudaSuccess) e = cudaMemcpy(c->local, &one, sizeof(one), cudaMemcpyHostToDevice);   // epoch starts at 1
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) {
+    if (c->local) cudaFree(c->local);
+    if (c->dev) cudaFree(c->dev);
+    delete c;
+    return fail_cuda(e, "cudaMalloc(communicator)");
+  }
+  if (world == 1) {
+    rc = upload_desc(c);
+    if (rc) { cudaFree(c->local); cudaFree(c->dev); delete c; return rc; }
+    c->connected = true;
+  }
+  {
+    std::lock_guard<std::mutex> lk(c_mu);
+    c_comms.insert(c);
+  }
+  *out = static_cast<bq_comm_t>(reinterpret_cast<uintptr_t>(c));
+  return BQ_OK;
+}
+
+int bq_comm_handle(bq_comm_t comm, void* out64) {
+  Comm* c = get_comm(comm);
+  if (!c) return BQ_ERR_HANDLE;
+  if (!out64) return fail(BQ_ERR_ARG, "null pointer");
+  static_assert(sizeof(cudaIpcMemHandle_t) == BQ_COMM_HANDLE_BYTES, "IPC handle size");
+  cudaIpcMemHandle_t h;
+  BQ_CUDA(cudaIpcGetMemHandle(&h, c->local));
+  memcpy(out64, &h, sizeof(h));
+  return BQ_OK;
+}
+
+int bq_comm_connect(bq_comm_t comm, const void* handles) {
+  Comm* c = get_comm(comm);
+  if (!c) return BQ_ERR_HANDLE;
+  if (!handles) return fail(BQ_ERR_ARG, "null pointer");
+  if (c->connected) return fail(BQ_ERR_STATE, "communicator is already connected");
+  for (int r = 0; r < c->world; ++r) {
+    if (r == c->rank) continue;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, static_cast<const uint8_t*>(handles) + (size_t)r * BQ_COMM_HANDLE_BYTES, sizeof(h));
+    BQ_CUDA(cudaIpcOpenMemHandle(&c->peer[r], h, cudaIpcMemLazyEnablePeerAccess));
+  }
+  int rc = upload_desc(c);
+  if (rc) return rc;
+  c->connected = true;
+  return BQ_OK;
+}
+
+int bq_comm_connect_loopback(bq_comm_t comm) {
+  Comm* c = get_comm(comm);
+  if (!c) return BQ_ERR_HANDLE;
+  if (c->connected) return fail(BQ_ERR_STATE, "communicator is already connected");
+  for (int r = 0; r < c->world; ++r) {
+    if (r == c->rank) continue;
+    BQ_CUDA(cudaMalloc(&c->peer[r], c->bytes));
+    BQ_CUDA(cudaMemset(c->peer[r], 0, c->bytes));
+  }
+  c->loopback = true;
+  int rc = upload_desc(c);
+  if (rc) return rc;
+  c->connected = true;
+  return BQ_OK;
+}
+
+int bq_comm_set_timeout_ms(bq_comm_t comm, int ms) {
+  Comm* c = get_comm(comm);
+  if (!c) return BQ_ERR_HANDLE;
+  if (ms < 1 || ms > 60000) return fail(BQ_ERR_ARG, "time limit must be 1..60000 ms");
+  c->wait_ms = ms;
+  if (c->connected) {
+    BQ_CUDA(cudaDeviceSynchronize());
+    return upload_desc(c);
+  }
+  return BQ_OK;
+}
+
+int bq_comm_destroy(bq_comm_t comm) {
+  Comm* c = get_comm(comm);
+  if (!c) return BQ_ERR_HANDLE;
+  {
+    std::lock_guard<std::mutex> lk(c_mu);
+    c_comms.erase(c);
+  }
+  cudaDeviceSynchronize();
+  for (int r = 0; r < c->world; ++r)
+    if (c->peer[r]) {
+      if (c->loopback) cudaFree(c->peer[r]);
+      else cudaIpcCloseMemHandle(c->peer[r]);
+    }
+  cudaFree(c->local);
+  cudaFree(c->dev);
+  c->magic = 0;
+  delete c;
+  return BQ_OK;
+}
+
+int bq_allreduce(bq_comm_t comm, const float* in, float* out, int64_t count, void* stream) {
+  Comm* c = get_comm(comm);
+  if (!c) return BQ_ERR_HANDLE;
+  if (!c->connected) return fail(BQ_ERR_STATE, "communicator is not connected");
+  if (count < 0 || count > c->slot_elems) return fail(BQ_ERR_ARG, "count exceeds the communicator's max_elems");
+  if (count == 0) return BQ_OK;
+  if (!out) return fail(BQ_ERR_ARG, "null pointer");
+  int64_t chunk = (count + COMM_MAX_CHUNKS - 1) / COMM_MAX_CHUNKS;
+  if (chunk < 2048) chunk = 2048;
+  const int64_t grid = (count + chunk - 1) / chunk;
+  BQ_CUDA(launch_chain(allreduce_sum_kernel, dim3((unsigned)grid), dim3(AR_THREADS), 0, (cudaStream_t)stream, 1,
+                       (const CommDev*)c->dev, in, out, count, chunk, status_word()));
+  count_launch();
+  BQ_CUDA(cudaGetLastError());
+  return BQ_OK;
+}
+
+int bq_allreduce_add_rmsnorm(bq_comm_t comm, const float* in, void* x, const float* gamma, void* normed, int64_t rows,
+                             int64_t H, float eps, int dtype, void* stream) {
+  Comm* c = get_comm(comm);
+  if (!c) return BQ_ERR_HANDLE;
+  if (!c->connected) return fail(BQ_ERR_STATE, "communicator is not connected");
+  if (dtype != BQ_DT_F32 && dtype != BQ_DT_BF16) return fail(BQ_ERR_ARG, "dtype must be BQ_DT_F32 or BQ_DT_BF16");
+  if (rows < 0 || H <= 0) return fail(BQ_ERR_ARG, "bad sizes");
+  if (H > (int64_t)AR_THREADS * AR_CACHE) return fail(BQ_ERR_UNSUPPORTED, "rows longer than 4096 elements");
+  if (rows > COMM_MAX_CHUNKS || rows * H > c->slot_elems) return fail(BQ_ERR_ARG, "rows * H exceeds the communicator's max_elems");
+  if (rows == 0) return BQ_OK;
+  if (!x || !gamma || !normed) return fail(BQ_ERR_ARG, "null pointer");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == BQ_DT_F32)
+    BQ_CUDA(launch_chain(allreduce_add_rmsnorm_kernel<float>, dim3((unsigned)rows), dim3(AR_THREADS), 0, s, 1,
+                         (const CommDev*)c->dev, in, (float*)x, gamma, (float*)normed, H, eps, status_word()));
+  else
+    BQ_CUDA(launch_chain(allreduce_add_rmsnorm_kernel<__nv_bfloat16>, dim3((unsigned)rows), dim3(AR_THREADS), 0, s, 1,
+                         (const CommDev*)c->dev, in, (__nv_bfloat16*)x, gamma, (__nv_bfloat16*)normed, H, eps, status_word()));
+  count_launch();
+  BQ_CUDA(cudaGetLastError());
+  return BQ_OK;
+}
+
+int bq_qlinear_push(bq_weight_t weight, const void* x, int x_dtype, int64_t M, bq_comm_t comm, void* stream) {
+  Comm* c = get_comm(comm);
+  if (!c) return BQ_ERR_HANDLE;
+  Weight* w = get_weight(weight);
+  if (!w) return BQ_ERR_HANDLE;
+  if (!c->connected) return fail(BQ_ERR_STATE, "communicator is not connected");
+  if (x_dtype != BQ_DT_F32 && x_dtype != BQ_DT_BF16) return fail(BQ_ERR_ARG, "x dtype must be BQ_DT_F32 or BQ_DT_BF16");
+  if (M <= 0 || !x) return fail(BQ_ERR_ARG, "bad arguments");
+  if (M * w->N > c->slot_elems) return fail(BQ_ERR_ARG, "M * N exceeds the communicator's max_elems");
+  if (!gemv_mma_supported(w->fmt, w->N, w->K, x_dtype, M))
+    return fail(BQ_ERR_UNSUPPORTED, "only decode-sized calls (the tensor-core GEMV's shapes) can deposit directly");
+  set_last_path(BQ_PATH_MMA);
+  return launch_qlinear_mma_push(w->codes, w->scales, w->fmt, w->N, w->K, x, x_dtype, M, c->dev, (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -41,6 +41,21 @@ struct Moe {
 };
 constexpr uint32_t MOE_MAGIC = 0xB2003E00u;
 
+// Peer-memory communicator (comm.cu): what the kernels read.  Every rank owns one buffer (flags + receive slots)
+// that all ranks of the node map through CUDA IPC.  Rank s deposits its contribution to a sum in slot
+// [parity][s] of EVERY rank's buffer and then raises flag [s][chunk] there; the receiver adds the slots in rank
+// order.  `state[0]` is the call counter (epoch, starts at 1; parity = epoch & 1), `state[1]` counts finished CTAs.
+constexpr int COMM_MAX_WORLD = 8;
+constexpr int COMM_MAX_CHUNKS = 1024;
+struct CommDev {
+  float* data[COMM_MAX_WORLD];        // rank r's receive slots: [2][world][slot_elems] floats
+  uint32_t* flags[COMM_MAX_WORLD];    // rank r's flags: [world][COMM_MAX_CHUNKS]
+  uint32_t* state;                    // this rank's {epoch, finished-CTA counter}
+  int64_t slot_elems;
+  uint64_t wait_ns;                   // bound of the flag wait
+  int rank, world;
+};
+
 // ---- host-side state / error plumbing (api.cu) -----------------------------------------
 int fail(int code, const std::string& msg);
 int fail_cuda(cudaError_t e, const char* what);
@@ -75,6 +90,9 @@ int launch_qlinear_mma(const uint8_t* codes, const __half* scales, int fmt, int6
                        const void* x, int x_dtype, int64_t M, void* y, int y_dtype, int64_t ldy,
                        cudaStream_t s);
 bool gemv_mma_supported(int fmt, int64_t N, int64_t K, int x_dtype, int64_t M);
+// same GEMV, fp32 partial sums pushed into every rank's receive slot of a peer-memory communicator (gemv_push.cu)
+int launch_qlinear_mma_push(const uint8_t* codes, const __half* scales, int fmt, int64_t N, int64_t K,
+                            const void* x, int x_dtype, int64_t M, const CommDev* comm_dev, cudaStream_t s);
 bool moe_tc_supported(const Moe* m);
 int moe_tc_prepare(Moe* m, const std::vector<const uint8_t*>* codes, const std::vector<const __half*>* scales);
 void moe_tc_release(Moe* m);
@@ -115,6 +133,14 @@ inline cudaError_t launch_chain(void (*kern)(KArgs...), dim3 grid, dim3 block, s
 
 // ---- device helpers --------------------------------------------------------------------------
 #ifdef __CUDACC__
+// Deposit one partial sum (element `idx` of this call's vector) in every rank's receive slot for this rank.
+__device__ __forceinline__ void comm_push_store(const void* desc, int64_t idx, float v) {
+  const CommDev* d = reinterpret_cast<const CommDev*>(desc);
+  const uint32_t e = *reinterpret_cast<const volatile uint32_t*>(d->state);
+  const int64_t off = ((int64_t)(e & 1u) * d->world + d->rank) * d->slot_elems + idx;
+  for (int r = 0; r < d->world; ++r) d->data[r][off] = v;
+  __threadfence_system();             // the deposits are on their way before this kernel can be seen as finished
+}
 // Programmatic dependent launch: a kernel lets its successor start launching right away and itself waits for its
 // predecessor (completion + memory visibility) before it touches anything the predecessor may have written.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }

@@ -61,8 +61,11 @@ def _rope(x, pos, base):
 
 class QuantDecoder:
     def __init__(self, cfg: DecoderConfig, lin: dict, embed, norms: dict, act_dtype=torch.bfloat16, rank: int = 0,
-                 world: int = 1, max_seq: int = 4096, max_batch: int = 1):
+                 world: int = 1, max_seq: int = 4096, max_batch: int = 1, comm=None):
         self.cfg, self.lin, self.embed, self.norms = cfg, lin, embed, norms
+        # ops.PeerComm (optional, world > 1): the static decode step then sums the row-parallel partial products
+        # through peer memory (GEMV deposits -> fused sum + residual add + RMSNorm) instead of NCCL all-reduces
+        self.comm = comm
         self.act_dtype, self.rank, self.world = act_dtype, rank, world
         self.kv_sharded = cfg.n_kv_heads % world == 0 and cfg.n_kv_heads >= world
         self.h_local = cfg.n_heads // world
@@ -220,10 +223,25 @@ class QuantDecoder:
         q = torch.empty((B, self.h_local, c.head_dim), dtype=self.act_dtype, device=dev)
         att = torch.empty_like(q)
         act = torch.empty((B, self.ffn_local), dtype=self.act_dtype, device=dev)
+        comm = self.comm if self.world > 1 else None
+        PUSHED = object()                  # the partial sums sit in the communicator's receive slots
+
+        def row_parallel(name, inp):
+            if comm is None:
+                return self.lin[name](inp)                   # fp32 (all-reduced by NCCL when sharded)
+            y = comm.push_linear(self.lin[name].linear, inp)
+            return PUSHED if y is None else y
+
+        def add_norm(delta, gamma):
+            if comm is None or delta is None:
+                _lib.check(lib.bq_add_rmsnorm(x.data_ptr(), delta.data_ptr() if delta is not None else None,
+                                              gamma.data_ptr(), h.data_ptr(), B, c.hidden, c.eps, dt, st))
+            else:
+                comm.add_rmsnorm(None if delta is PUSHED else delta, x, gamma, h, c.eps)
+
         delta = None
         for l in range(c.layers):
-            _lib.check(lib.bq_add_rmsnorm(x.data_ptr(), delta.data_ptr() if delta is not None else None,
-                                          self.norms[f"l{l}.norm1"].data_ptr(), h.data_ptr(), B, c.hidden, c.eps, dt, st))
+            add_norm(delta, self.norms[f"l{l}.norm1"])
             qkv = self.lin[f"l{l}.qkv"](h)                                        # fp32 [B, (Hq + 2 Hkv) D]
             _lib.check(lib.bq_rope_kv_append(qkv.data_ptr(), pos_t.data_ptr(), q.data_ptr(), self.k_cache[l].data_ptr(),
                                              self.v_cache[l].data_ptr(), B, self.h_local, self.kv_local, c.head_dim, S,
@@ -231,14 +249,12 @@ class QuantDecoder:
             _lib.check(lib.bq_decode_attention(q.data_ptr(), self.k_cache[l].data_ptr(), self.v_cache[l].data_ptr(),
                                                pos_t.data_ptr(), att.data_ptr(), B, self.h_local, self.kv_local,
                                                c.head_dim, S, dt, st))
-            delta = self.lin[f"l{l}.o"](att.reshape(B, -1))                       # fp32 (all-reduced when sharded)
-            _lib.check(lib.bq_add_rmsnorm(x.data_ptr(), delta.data_ptr(), self.norms[f"l{l}.norm2"].data_ptr(),
-                                          h.data_ptr(), B, c.hidden, c.eps, dt, st))
+            delta = row_parallel(f"l{l}.o", att.reshape(B, -1))
+            add_norm(delta, self.norms[f"l{l}.norm2"])
             gu = self.lin[f"l{l}.gate_up"](h)
             _lib.check(lib.bq_gated_act(gu.data_ptr(), act.data_ptr(), B, self.ffn_local, 0, dt, st))
-            delta = self.lin[f"l{l}.down"](act)
-        _lib.check(lib.bq_add_rmsnorm(x.data_ptr(), delta.data_ptr(), self.norms["norm_f"].data_ptr(), h.data_ptr(), B,
-                                      c.hidden, c.eps, dt, st))
+            delta = row_parallel(f"l{l}.down", act)
+        add_norm(delta, self.norms["norm_f"])
         head = self.lin["lm_head"]
         if self.world > 1:
             ids = parallel.VocabParallelHead(head, c.vocab // self.world).greedy(h)

@@ -240,6 +240,73 @@ class QuantLinear:
         return y.reshape(*x.shape[:-1], self.pw.N)
 
 
+class PeerComm:
+    """Sums over the GPUs of one node through peer-mapped memory (one process per GPU): the fused alternative
+    to an NCCL all-reduce for decode-sized messages.  `group` is the torch.distributed process group that
+    carries the 64-byte IPC handles at set-up (any backend); it is not used afterwards.  Every rank must issue
+    the same sequence of summing calls.  `max_elems` bounds the fp32 elements of one sum."""
+
+    def __init__(self, max_elems: int, group=None, rank: int = 0, world: int = 1):
+        import ctypes as C
+        self.group, self.max_elems = group, int(max_elems)
+        if world > 1 or group is not None:
+            import torch.distributed as dist
+            rank, world = dist.get_rank(group), dist.get_world_size(group)
+        self.rank, self.world = rank, world
+        lib = _lib.lib()
+        h = C.c_uint64(0)
+        _lib.check(lib.bq_comm_create(rank, world, self.max_elems, C.byref(h)))
+        self.handle = h.value
+        if world > 1:
+            buf = C.create_string_buffer(64)
+            _lib.check(lib.bq_comm_handle(self.handle, buf))
+            handles = [None] * world
+            dist.all_gather_object(handles, buf.raw, group=group)
+            _lib.check(lib.bq_comm_connect(self.handle, b"".join(handles)))
+            dist.barrier(group)           # nobody deposits before every buffer is zeroed and mapped
+
+    def close(self):
+        if self.handle:
+            if self.world > 1:
+                import torch.distributed as dist
+                _torch().cuda.synchronize()
+                dist.barrier(self.group)  # nobody frees while a peer may still store into the buffer
+            _lib.check(_lib.lib().bq_comm_destroy(self.handle))
+            self.handle = 0
+
+    def push_linear(self, linear: "QuantLinear", x):
+        """Row-parallel partial product of `linear` on this rank's K slice.  Returns None when the GEMV deposited
+        its partial sums directly in the peers' receive slots, else the local fp32 partial y (to be passed as
+        `inp` to the summing call)."""
+        x2 = x.reshape(-1, linear.pw.K)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        rc = _lib.lib().bq_qlinear_push(linear.pw.handle, x2.data_ptr(), _dt_of_torch(x2), x2.shape[0], self.handle,
+                                        _stream_ptr())
+        if rc == _lib.ERR_UNSUPPORTED:
+            return QuantLinear(linear.pw)(x2)
+        _lib.check(rc)
+        return None
+
+    def all_reduce(self, inp, count: int = 0, out=None):
+        """Sum of `inp` (fp32, CUDA) over the ranks; inp None sums what push_linear deposited (count elements)."""
+        torch = _torch()
+        n = inp.numel() if inp is not None else int(count)
+        if out is None:
+            out = torch.empty(n, dtype=torch.float32, device="cuda") if inp is None else torch.empty_like(inp)
+        _lib.check(_lib.lib().bq_allreduce(self.handle, inp.data_ptr() if inp is not None else None, out.data_ptr(), n,
+                                           _stream_ptr()))
+        return out
+
+    def add_rmsnorm(self, inp, x, weight, normed, eps: float):
+        """x[rows, H] += sum over ranks (of `inp`, or of the deposited partial sums when inp is None);
+        normed = rmsnorm(x) * weight.  In place on x and normed."""
+        rows, H = x.shape
+        _lib.check(_lib.lib().bq_allreduce_add_rmsnorm(self.handle, inp.data_ptr() if inp is not None else None,
+                                                       x.data_ptr(), weight.data_ptr(), normed.data_ptr(), rows, H,
+                                                       float(eps), _dt_of_torch(x), _stream_ptr()))
+
+
 class LMHead(QuantLinear):
     """Vocabulary projection; `greedy` returns argmax token ids (ties -> lower id)."""
 

@@ -34,6 +34,8 @@ extern "C" {
 
 typedef uint64_t bq_weight_t;      /* opaque handle to a packed weight resident in HBM   */
 typedef uint64_t bq_moe_t;         /* opaque handle to a set of MoE expert weights        */
+typedef uint64_t bq_comm_t;        /* opaque handle to a peer-memory communicator         */
+#define BQ_COMM_HANDLE_BYTES 64
 
 enum { BQ_FMT_Q8G32 = 0, BQ_FMT_Q4G32 = 1 };
 enum { BQ_DT_F32 = 0, BQ_DT_BF16 = 1 };
@@ -168,6 +170,47 @@ int bq_moe_experts(bq_moe_t m, const void* xp_bf16, const int32_t* offsets, int6
  * no atomics).  inv as produced by bq_moe_permute.  y dtype F32 or BF16.                 */
 int bq_moe_combine(const float* out, const int32_t* inv, const float* w, int64_t T,
                    int top_k, int64_t H, void* y, int y_dtype, void* stream);
+
+/* ---- tensor-parallel shard boundary: sums over the GPUs of one node through peer memory -----
+ * The specification asks for "NCCL all-reduce ... only at those shard boundaries"; the host
+ * mirror keeps an NCCL route (torch.distributed) and these entry points are the fused
+ * alternative for decode-sized messages: one process per GPU, each owns a buffer of receive
+ * slots and flags that every other process maps through CUDA IPC; a sum is plain stores into
+ * the peers' slots, a flag, a bounded wait and an add in rank order (bit-identical on every
+ * rank).  Set-up, identical on every rank:
+ *   bq_comm_create(rank, world, max_elems, &c);  bq_comm_handle(c, h64);
+ *   -- exchange the 64-byte handles (all-gather over any host channel), rank-major --
+ *   bq_comm_connect(c, handles);  -- host barrier before the first call and before destroy --
+ * world <= 8; world == 1 needs no connect.  max_elems bounds the fp32 elements of one sum.
+ * All ranks must issue the same sequence of summing calls with the same sizes.  A wait that
+ * is not answered within the time limit (5 s unless changed) records BQ_ERR_TIMEOUT (see
+ * bq_status_poll) and the kernel returns; the results of that call are then undefined.  Calls are graph-capturable.      */
+int bq_comm_create(int rank, int world, int64_t max_elems, bq_comm_t* out);
+int bq_comm_handle(bq_comm_t c, void* out_handle /* BQ_COMM_HANDLE_BYTES */);
+int bq_comm_connect(bq_comm_t c, const void* handles /* world x BQ_COMM_HANDLE_BYTES */);
+/* Self-test aid: instead of mapping the other ranks, give each a private stand-in buffer in
+ * this process.  Nobody answers, so every summing call runs into the bounded wait: this is how
+ * the time-out path (BQ_ERR_TIMEOUT from bq_status_poll, context still usable) is exercised
+ * on one GPU.                                                                             */
+int bq_comm_connect_loopback(bq_comm_t c);
+/* Time limit of the flag wait, 1..60000 ms (synchronises the device when already connected). */
+int bq_comm_set_timeout_ms(bq_comm_t c, int ms);
+int bq_comm_destroy(bq_comm_t c);
+/* Row-parallel shard of a linear (this rank's K slice): y_partial = x . W^T, fp32, deposited
+ * directly in every rank's receive slot by the GEMV's epilogue (no local y).  Decode-sized
+ * calls only (the shapes of BQ_PATH_MMA), else BQ_ERR_UNSUPPORTED and nothing is launched:
+ * run bq_qlinear and pass its y as `in` below.  Must be followed on the same stream by
+ * exactly one of the two summing calls with in == NULL.                                   */
+int bq_qlinear_push(bq_weight_t w, const void* x, int x_dtype, int64_t M, bq_comm_t c,
+                    void* stream);
+/* out[i] = sum over ranks of in_r[i], i < count (fp32).  in == NULL: sum what the preceding
+ * bq_qlinear_push deposited (count = M * N).                                              */
+int bq_allreduce(bq_comm_t c, const float* in, float* out, int64_t count, void* stream);
+/* bq_add_rmsnorm with delta = the sum over ranks: x += sum; normed = rmsnorm(x) * weight.
+ * rows <= 1024, H <= 4096 (else BQ_ERR_UNSUPPORTED).  in as for bq_allreduce.             */
+int bq_allreduce_add_rmsnorm(bq_comm_t c, const float* in, void* x, const float* weight,
+                             void* normed, int64_t rows, int64_t H, float eps, int dtype,
+                             void* stream);
 
 #ifdef __cplusplus
 }
