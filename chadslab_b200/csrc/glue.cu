@@ -120,13 +120,20 @@ template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bflo
 template <typename T>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
-                        const int64_t* __restrict__ pos_p, T* __restrict__ out, int Hq, int Hkv, int D, int64_t S) {
+                        const int64_t* __restrict__ pos_p, T* __restrict__ out, int Hq, int Hkv, int D, int64_t S,
+                        float* __restrict__ part, unsigned* __restrict__ counters) {
   const int b = blockIdx.y, h = blockIdx.x;
+  // gridDim.z > 1: the positions are split over gridDim.z CTAs (long contexts, few heads); each leaves its
+  // (max, sum, unnormalised output) in `part` and the last one to arrive merges them in split order
+  const int nsplit = gridDim.z, z = blockIdx.z;
   const int kv = h / (Hq / Hkv);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   pdl_launch_dependents();
   pdl_wait();
-  const int64_t n_pos = *pos_p + 1;
+  const int64_t n_all = *pos_p + 1;
+  const int64_t per = ((n_all + nsplit - 1) / nsplit + ATT_PB - 1) / ATT_PB * ATT_PB;
+  const int64_t p_lo = (int64_t)z * per;
+  const int64_t n_pos = p_lo + per < n_all ? p_lo + per : n_all;        // this CTA covers [p_lo, n_pos)
   const int d0 = lane * ATT_EPL;
   const bool live = d0 < D;
   float qv[ATT_EPL], acc[ATT_EPL];
@@ -142,7 +149,7 @@ decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
   const int64_t row_stride = (int64_t)Hkv * D;
   const T* kbase = k_cache + ((int64_t)b * S * Hkv + kv) * D + d0;
   const T* vbase = v_cache + ((int64_t)b * S * Hkv + kv) * D + d0;
-  for (int64_t s0 = (int64_t)warp * ATT_PB; s0 < n_pos; s0 += ATT_WARPS * ATT_PB) {
+  for (int64_t s0 = p_lo + (int64_t)warp * ATT_PB; s0 < n_pos; s0 += ATT_WARPS * ATT_PB) {
     float kf[ATT_PB][ATT_EPL], dot[ATT_PB];
 #pragma unroll
     for (int j = 0; j < ATT_PB; ++j) {
@@ -192,11 +199,50 @@ decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
   float gs = 0.0f;
 #pragma unroll
   for (int w = 0; w < ATT_WARPS; ++w) gs += s_mx[w] == -INFINITY ? 0.0f : s_sum[w] * __expf(s_mx[w] - gm);
+  if (nsplit == 1) {
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+      float o = 0.0f;
+#pragma unroll
+      for (int w = 0; w < ATT_WARPS; ++w) o += s_mx[w] == -INFINITY ? 0.0f : s_acc[w][d] * __expf(s_mx[w] - gm);
+      out[((int64_t)b * Hq + h) * D + d] = from_float<T>(o / gs);
+    }
+    return;
+  }
+  const int64_t bh = (int64_t)b * Hq + h;
+  float* mine = part + (bh * nsplit + z) * (D + 2);
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     float o = 0.0f;
 #pragma unroll
     for (int w = 0; w < ATT_WARPS; ++w) o += s_mx[w] == -INFINITY ? 0.0f : s_acc[w][d] * __expf(s_mx[w] - gm);
-    out[((int64_t)b * Hq + h) * D + d] = from_float<T>(o / gs);
+    mine[2 + d] = o;
+  }
+  if (threadIdx.x == 0) { mine[0] = gm; mine[1] = gs; }
+  __threadfence();
+  __syncthreads();
+  __shared__ int s_last;
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicAdd(&counters[bh], 1u);
+    s_last = prev == (unsigned)nsplit - 1;
+    if (s_last) counters[bh] = 0;                       // ready for the next launch
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const float* all = part + bh * nsplit * (D + 2);
+  float tm = -INFINITY;
+  for (int i = 0; i < nsplit; ++i) tm = fmaxf(tm, __ldcg(all + (int64_t)i * (D + 2)));
+  float ts = 0.0f;
+  for (int i = 0; i < nsplit; ++i) {
+    const float m_i = __ldcg(all + (int64_t)i * (D + 2));
+    ts += m_i == -INFINITY ? 0.0f : __ldcg(all + (int64_t)i * (D + 2) + 1) * __expf(m_i - tm);
+  }
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float o = 0.0f;
+    for (int i = 0; i < nsplit; ++i) {
+      const float m_i = __ldcg(all + (int64_t)i * (D + 2));
+      o += m_i == -INFINITY ? 0.0f : __ldcg(all + (int64_t)i * (D + 2) + 2 + d) * __expf(m_i - tm);
+    }
+    out[bh * D + d] = from_float<T>(o / ts);
   }
 }
 
@@ -221,6 +267,9 @@ __global__ void __launch_bounds__(256) gated_act_kernel(const float* __restrict_
 }  // namespace bq
 
 using namespace bq;
+
+static float* g_att_part = nullptr;     // split-position attention: partial states + arrival counters
+static size_t g_att_bytes = 0;
 
 static int glue_ready(int dtype) {
   if (device_id() < 0) return fail(BQ_ERR_STATE, "bq_init() has not been called");
@@ -274,14 +323,34 @@ int bq_decode_attention(const void* q, const void* k_cache, const void* v_cache,
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || D <= 0 || D > ATT_MAXD || (D % 8) || S <= 0)
     return fail(BQ_ERR_ARG, "bad sizes (head_dim <= 256 and a multiple of 8, Hq a multiple of Hkv)");
   if (!q || !k_cache || !v_cache || !pos || !out) return fail(BQ_ERR_ARG, "null pointer");
-  dim3 grid((unsigned)Hq, (unsigned)B);
+  // few (batch, head) pairs and a long cache: split the positions so that about two CTAs per SM stream K/V
+  int64_t nsplit = (2 * (int64_t)sm_count()) / (B * Hq);
+  if (nsplit > S / 128) nsplit = S / 128;
+  if (nsplit > 32) nsplit = 32;
+  if (nsplit < 1) nsplit = 1;
+  if (nsplit > 1) {
+    const size_t need = (size_t)B * Hq * nsplit * (D + 2) * sizeof(float) + (size_t)B * Hq * sizeof(unsigned);
+    if (need > g_att_bytes) {          // grow-only scratch owned by the library (first call: before any graph capture)
+      if (g_att_part) BQ_CUDA(cudaFree(g_att_part));
+      g_att_part = nullptr; g_att_bytes = 0;
+      const size_t cap = need * 2;
+      BQ_CUDA(cudaMalloc((void**)&g_att_part, 2 * cap));
+      BQ_CUDA(cudaMemset(g_att_part, 0, 2 * cap));
+      g_att_bytes = cap;
+    }
+  }
+  // partial states first, the arrival counters (all zero between launches) in the second half of the allocation
+  float* part = g_att_part;
+  unsigned* counters = reinterpret_cast<unsigned*>(reinterpret_cast<uint8_t*>(g_att_part) + g_att_bytes);
+  dim3 grid((unsigned)Hq, (unsigned)B, (unsigned)nsplit);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == BQ_DT_F32)
     BQ_CUDA(launch_chain(decode_attention_kernel<float>, grid, dim3(ATT_WARPS * 32), 0, s, 1, (const float*)q, (const float*)k_cache,
-                         (const float*)v_cache, pos, (float*)out, Hq, Hkv, D, S));
+                         (const float*)v_cache, pos, (float*)out, Hq, Hkv, D, S, part, counters));
   else
     BQ_CUDA(launch_chain(decode_attention_kernel<__nv_bfloat16>, grid, dim3(ATT_WARPS * 32), 0, s, 1, (const __nv_bfloat16*)q,
-                         (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, pos, (__nv_bfloat16*)out, Hq, Hkv, D, S));
+                         (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, pos, (__nv_bfloat16*)out, Hq, Hkv, D, S,
+                         part, counters));
   count_launch();
   BQ_CUDA(cudaGetLastError());
   return BQ_OK;

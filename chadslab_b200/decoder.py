@@ -257,7 +257,7 @@ class QuantDecoder:
         add_norm(delta, self.norms["norm_f"])
         head = self.lin["lm_head"]
         if self.world > 1:
-            ids = parallel.VocabParallelHead(head, c.vocab // self.world).greedy(h)
+            ids = parallel.VocabParallelHead(head, c.vocab // self.world, comm=comm).greedy(h)
         else:
             ids = head.greedy(h).long()
         tokens.copy_(ids)
@@ -269,7 +269,9 @@ class QuantDecoder:
         dev = self.embed.device
         tokens = first_tokens.to(dev).long().clone()
         pos_t = torch.tensor([start_pos], device=dev, dtype=torch.int64)
-        keep = (tokens.clone(), pos_t.clone(), [k.clone() for k in self.k_cache], [v.clone() for v in self.v_cache])
+        # the two trial steps below (warm-up, capture) write cache positions start_pos and start_pos + 1 only
+        sl = (slice(0, batch), slice(start_pos, start_pos + 2))
+        keep = (tokens.clone(), pos_t.clone(), [k[sl].clone() for k in self.k_cache], [v[sl].clone() for v in self.v_cache])
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):                      # warm-up outside capture (sizes library scratch)
@@ -281,9 +283,9 @@ class QuantDecoder:
         # restore the state the two trial steps consumed
         tokens.copy_(keep[0]); pos_t.copy_(keep[1])
         for dst, src in zip(self.k_cache, keep[2]):
-            dst.copy_(src)
+            dst[sl].copy_(src)
         for dst, src in zip(self.v_cache, keep[3]):
-            dst.copy_(src)
+            dst[sl].copy_(src)
         self.pos = start_pos
 
         def step():

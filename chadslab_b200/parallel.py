@@ -55,21 +55,28 @@ class RowParallelLinear:
 class VocabParallelHead:
     """Vocabulary-sharded lm_head.  `head(x)` -> local logits [M, V/world]."""
 
-    def __init__(self, head: Callable, vocab_local: int, group=None):
-        self.head, self.vocab_local, self.group = head, vocab_local, group
+    def __init__(self, head: Callable, vocab_local: int, group=None, comm=None):
+        # comm: an ops.PeerComm; the (max, argmax) pairs then travel through peer memory instead of the process
+        # group (an all-gather written as a sum: every rank contributes zeros outside its own row)
+        self.head, self.vocab_local, self.group, self.comm = head, vocab_local, group, comm
 
     def logits(self, x):
         return ColumnParallelLinear(self.head, gather_output=True, group=self.group)(x)
 
     def greedy(self, x):
         """Global argmax ids (ties -> lower id) exchanging 2 numbers per row and rank."""
-        world, rank = _world(self.group)
+        world, rank = (self.comm.world, self.comm.rank) if self.comm is not None else _world(self.group)
         local = self.head(x).float()
         mx, am = local.max(dim=-1)
         pair = torch.stack([mx, (am + rank * self.vocab_local).to(mx.dtype)], dim=-1).contiguous()   # [M, 2]
-        pairs = [torch.empty_like(pair) for _ in range(world)]
-        dist.all_gather(pairs, pair, group=self.group)
-        allp = torch.stack(pairs, dim=0)                     # [world, M, 2]
+        if self.comm is not None:
+            mine = torch.zeros((world,) + tuple(pair.shape), dtype=torch.float32, device=pair.device)
+            mine[rank] = pair                                # ids < 2^24 are exact in fp32; v + 0 = v
+            allp = self.comm.all_reduce(mine.reshape(-1)).reshape(mine.shape)
+        else:
+            pairs = [torch.empty_like(pair) for _ in range(world)]
+            dist.all_gather(pairs, pair, group=self.group)
+            allp = torch.stack(pairs, dim=0)                 # [world, M, 2]
         vals, ids = allp[..., 0], allp[..., 1]
         best = vals.max(dim=0).values
         # lowest id among the ranks that hold the maximum
