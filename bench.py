@@ -227,63 +227,6 @@ def run_extras(torch, cb, lib, problems):
     return out
 
 
-# configs[2]: Gemma-7B-shaped decoder, 4-bit g32, tensor-parallel over all ranks of the run (column / row sharded
-# linears, vocabulary-sharded head).  The shard boundaries go through the library's peer-memory communicator.
-# Runs on every rank; returns the report on rank 0.
-def run_tp_decode(torch, cb, dist, rank, world):
-    from chadslab_b200.decoder import GEMMA_7B_SHAPE, QuantDecoder
-    ctx, steps = 2048, 16
-    out = {"model": "gemma-7b-shape q4-g32, bf16 activations, random-init", "tensor_parallel": world,
-           "context": f"{ctx} positions of synthetic (random) K/V in the cache instead of a prefill pass",
-           "exchange": "peer-memory communicator (GEMV deposits + fused sum/add/RMSNorm)" if world > 1 else "none",
-           "timing": f"{steps} CUDA-graph replays after 3, CUDA events, max over ranks", "batches": []}
-    comm = None
-    try:
-        if world > 1:
-            comm = cb.PeerComm(max_elems=64 * GEMMA_7B_SHAPE.hidden, group=dist.group.WORLD)
-        dec = QuantDecoder.random(GEMMA_7B_SHAPE, seed=0, act_dtype=torch.bfloat16, rank=rank, world=world,
-                                  max_seq=ctx + 64, max_batch=64, comm=comm)
-        for kc, vc in zip(dec.k_cache, dec.v_cache):
-            kc.normal_()
-            vc.normal_()
-        bpt = dec.linear_bytes_per_token()
-        for B in (1, 16, 64):
-            g = torch.Generator(device="cuda").manual_seed(B)
-            first = torch.randint(0, GEMMA_7B_SHAPE.vocab, (B,), device="cuda", generator=g)
-            dec.pos = ctx
-            step, tokens = dec.make_graph_stepper(B, first, start_pos=ctx)
-            for _ in range(3):
-                step()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            torch.cuda.synchronize()
-            if world > 1:
-                dist.barrier()
-            a.record()
-            for _ in range(steps):
-                step()
-            b.record()
-            torch.cuda.synchronize()
-            t = torch.tensor([a.elapsed_time(b) / steps], device="cuda")
-            if world > 1:
-                dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t[0])
-            out["batches"].append({"batch": B, "ms_per_step": round(ms, 4), "tokens_per_s": round(B * 1e3 / ms, 1),
-                                   "linear_stream_gbs_per_gpu": round(bpt / ms / 1e6, 1)})
-            del step
-        out["linear_GB_per_step_per_gpu"] = round(bpt / 1e9, 3)
-        out["status"] = int(cb._lib.lib().bq_status_poll())
-        del dec
-    except Exception as e:  # never breaks the headline line
-        out["error"] = repr(e)[:300]
-    if comm is not None:
-        try:
-            comm.close()
-        except Exception as e:
-            out["close_error"] = repr(e)[:200]
-    torch.cuda.empty_cache()
-    return out
-
-
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -427,7 +370,10 @@ def run_gpu(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_total, e2e_ms = float(t[0]), float(t[1])
 
-    tp_decode = run_tp_decode(torch, cb, dist, rank, world) if args.extras else None
+    tp_decode = None
+    if args.extras:      # configs[2]: Gemma-7B-shaped decoder, 4-bit g32, tensor-parallel over all ranks of the run
+        from chadslab_b200 import decode_bench
+        tp_decode = decode_bench.run(torch, dist, rank, world, "gemma7b", (1, 16, 64), 2048, 16)
     if rank == 0:
         peak, peak_src = load_peaks()
         value = world * step_bytes * args.steps / (ms_total * 1e-3) / 1e9

@@ -117,6 +117,33 @@ template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bflo
     f[2 * i + 1] = __uint_as_float(wds[i] & 0xFFFF0000u);
   }
 }
+// a row's 8 elements as loaded (converted to fp32 only where they are used, so that the K and V rows of a whole
+// trip can be in flight together without a register per element)
+template <typename T> struct RawRow;
+template <> struct RawRow<float> { float4 a, b; };
+template <> struct RawRow<__nv_bfloat16> { uint4 r; };
+__device__ __forceinline__ RawRow<float> load_raw(const float* p) {
+  RawRow<float> v;
+  v.a = *reinterpret_cast<const float4*>(p);
+  v.b = *reinterpret_cast<const float4*>(p + 4);
+  return v;
+}
+__device__ __forceinline__ RawRow<__nv_bfloat16> load_raw(const __nv_bfloat16* p) {
+  RawRow<__nv_bfloat16> v;
+  v.r = *reinterpret_cast<const uint4*>(p);
+  return v;
+}
+__device__ __forceinline__ void unpack_raw(const RawRow<float>& v, float* f) {
+  f[0] = v.a.x; f[1] = v.a.y; f[2] = v.a.z; f[3] = v.a.w; f[4] = v.b.x; f[5] = v.b.y; f[6] = v.b.z; f[7] = v.b.w;
+}
+__device__ __forceinline__ void unpack_raw(const RawRow<__nv_bfloat16>& v, float* f) {
+  const uint32_t wds[4] = {v.r.x, v.r.y, v.r.z, v.r.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(wds[i] << 16);
+    f[2 * i + 1] = __uint_as_float(wds[i] & 0xFFFF0000u);
+  }
+}
 template <typename T>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
@@ -150,18 +177,29 @@ decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
   const T* kbase = k_cache + ((int64_t)b * S * Hkv + kv) * D + d0;
   const T* vbase = v_cache + ((int64_t)b * S * Hkv + kv) * D + d0;
   for (int64_t s0 = p_lo + (int64_t)warp * ATT_PB; s0 < n_pos; s0 += ATT_WARPS * ATT_PB) {
-    float kf[ATT_PB][ATT_EPL], dot[ATT_PB];
+    // all K and V rows of the trip are requested before anything is computed
+    RawRow<T> kr[ATT_PB], vr[ATT_PB];
+    float dot[ATT_PB];
+    if (live) {
 #pragma unroll
-    for (int j = 0; j < ATT_PB; ++j) {
-      const int64_t sidx = s0 + j < n_pos ? s0 + j : n_pos - 1;       // clamp: masked below
-      if (live) load8<T>(kbase + sidx * row_stride, kf[j]);
+      for (int j = 0; j < ATT_PB; ++j) {
+        const int64_t sidx = s0 + j < n_pos ? s0 + j : n_pos - 1;       // clamp: masked below
+        kr[j] = load_raw(kbase + sidx * row_stride);
+      }
+#pragma unroll
+      for (int j = 0; j < ATT_PB; ++j) {
+        const int64_t sidx = s0 + j < n_pos ? s0 + j : n_pos - 1;
+        vr[j] = load_raw(vbase + sidx * row_stride);
+      }
     }
 #pragma unroll
     for (int j = 0; j < ATT_PB; ++j) {
       float dsum = 0.0f;
       if (live) {
+        float kf[ATT_EPL];
+        unpack_raw(kr[j], kf);
 #pragma unroll
-        for (int i = 0; i < ATT_EPL; ++i) dsum += qv[i] * kf[j][i];
+        for (int i = 0; i < ATT_EPL; ++i) dsum += qv[i] * kf[i];
       }
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) dsum += __shfl_xor_sync(0xffffffffu, dsum, off);
@@ -176,12 +214,11 @@ decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
     for (int i = 0; i < ATT_EPL; ++i) acc[i] *= corr;
 #pragma unroll
     for (int j = 0; j < ATT_PB; ++j) {
-      const int64_t sidx = s0 + j < n_pos ? s0 + j : n_pos - 1;
       const float p = __expf(dot[j] - nm);                                   // 0 for masked positions
       sum += p;
       if (live) {
         float vf[ATT_EPL];
-        load8<T>(vbase + sidx * row_stride, vf);
+        unpack_raw(vr[j], vf);
 #pragma unroll
         for (int i = 0; i < ATT_EPL; ++i) acc[i] += p * vf[i];
       }
@@ -323,9 +360,9 @@ int bq_decode_attention(const void* q, const void* k_cache, const void* v_cache,
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || D <= 0 || D > ATT_MAXD || (D % 8) || S <= 0)
     return fail(BQ_ERR_ARG, "bad sizes (head_dim <= 256 and a multiple of 8, Hq a multiple of Hkv)");
   if (!q || !k_cache || !v_cache || !pos || !out) return fail(BQ_ERR_ARG, "null pointer");
-  // few (batch, head) pairs and a long cache: split the positions so that about two CTAs per SM stream K/V
-  int64_t nsplit = (2 * (int64_t)sm_count()) / (B * Hq);
-  if (nsplit > S / 128) nsplit = S / 128;
+  // few (batch, head) pairs and a long cache: split the positions so that several CTAs per SM stream K/V
+  int64_t nsplit = (4 * (int64_t)sm_count() + B * Hq - 1) / (B * Hq);
+  if (nsplit > S / 64) nsplit = S / 64;          // a CTA takes 32 positions per trip: at least two trips each
   if (nsplit > 32) nsplit = 32;
   if (nsplit < 1) nsplit = 1;
   if (nsplit > 1) {

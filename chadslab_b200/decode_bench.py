@@ -1,0 +1,115 @@
+"""Decode-step throughput of a Gemma-shaped decoder with random-init packed weights.
+
+    python -m chadslab_b200.decode_bench --shape gemma7b --batch 1,16,64 --ctx 2048 --steps 16
+    torchrun --nproc-per-node N ... -m chadslab_b200.decode_bench ...     (tensor parallel over the N ranks)
+
+The context is synthetic: `ctx` positions of random K/V are placed in the cache instead of running a prefill.
+Each batch size is captured as one CUDA graph per step and replayed; `--eager 1` launches the kernels directly
+(what a profiler wants).  Prints one JSON object on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+
+def run(torch, dist, rank: int, world: int, shape: str = "gemma7b", batches=(1, 16, 64), ctx: int = 2048, steps: int = 16,
+        eager: bool = False):
+    """Runs on every rank; returns the report (complete on rank 0)."""
+    import chadslab_b200 as cb
+    from chadslab_b200 import _lib
+    from chadslab_b200.decoder import GEMMA_2B_SHAPE, GEMMA_7B_SHAPE, QuantDecoder
+    cfg = {"gemma2b": GEMMA_2B_SHAPE, "gemma7b": GEMMA_7B_SHAPE}[shape]
+    fmt = "int8-g32" if cfg.fmt == 0 else "q4-g32"
+    out = {"model": f"{shape}-shape {fmt}, bf16 activations, random-init", "tensor_parallel": world,
+           "context": f"{ctx} positions of synthetic (random) K/V in the cache instead of a prefill pass",
+           "exchange": "peer-memory communicator (GEMV deposits + fused sum/add/RMSNorm)" if world > 1 else "none",
+           "timing": (f"{steps} eager steps" if eager else f"{steps} CUDA-graph replays") + " after 3, CUDA events, max over ranks",
+           "batches": []}
+    comm = None
+    try:
+        max_b = max(batches)
+        if world > 1:
+            comm = cb.PeerComm(max_elems=max(max_b * cfg.hidden, 4096), group=dist.group.WORLD)
+        dec = QuantDecoder.random(cfg, seed=0, act_dtype=torch.bfloat16, rank=rank, world=world, max_seq=ctx + 64,
+                                  max_batch=max_b, comm=comm)
+        for kc, vc in zip(dec.k_cache, dec.v_cache):
+            kc.normal_()
+            vc.normal_()
+        bpt = dec.linear_bytes_per_token()
+        kv_bytes = sum(k[:1, :ctx].numel() * k.element_size() for k in dec.k_cache) * 2      # K + V, per sequence
+        for B in batches:
+            g = torch.Generator(device="cuda").manual_seed(B)
+            first = torch.randint(0, cfg.vocab, (B,), device="cuda", generator=g)
+            dec.pos = ctx
+            if eager:
+                tokens = first.clone()
+                pos_t = torch.tensor([ctx], device="cuda", dtype=torch.int64)
+
+                def step():
+                    dec._step_static(tokens, pos_t)
+                    pos_t.fill_(ctx)                     # stay at the same position: the cache has 64 spare slots
+            else:
+                step, tokens = dec.make_graph_stepper(B, first, start_pos=ctx)
+            for _ in range(3):
+                step()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            a.record()
+            for _ in range(steps):
+                step()
+            b.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([a.elapsed_time(b) / steps], device="cuda")
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t[0])
+            out["batches"].append({"batch": B, "ms_per_step": round(ms, 4), "tokens_per_s": round(B * 1e3 / ms, 1),
+                                   "stream_gbs_per_gpu": round((bpt + B * kv_bytes) / ms / 1e6, 1)})
+            del step
+        out["linear_GB_per_step_per_gpu"] = round(bpt / 1e9, 3)
+        out["kv_GB_per_sequence_per_gpu"] = round(kv_bytes / 1e9, 3)
+        out["status"] = int(_lib.lib().bq_status_poll())
+        del dec
+    except Exception as e:  # the caller decides what a failure means
+        out["error"] = repr(e)[:300]
+    if comm is not None:
+        try:
+            comm.close()
+        except Exception as e:
+            out["close_error"] = repr(e)[:200]
+    torch.cuda.empty_cache()
+    return out
+
+
+def main():
+    import torch
+    import torch.distributed as dist
+    from chadslab_b200 import _lib
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--shape", default="gemma7b", choices=["gemma2b", "gemma7b"])
+    ap.add_argument("--batch", default="1,16,64")
+    ap.add_argument("--ctx", type=int, default=2048)
+    ap.add_argument("--steps", type=int, default=16)
+    ap.add_argument("--eager", type=int, default=0)
+    args = ap.parse_args()
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    _lib.init(local)
+    rep = run(torch, dist, rank, world, args.shape, tuple(int(b) for b in args.batch.split(",")), args.ctx, args.steps,
+              bool(args.eager))
+    if rank == 0:
+        print(json.dumps(rep))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
