@@ -1,18 +1,22 @@
 // Peer-memory communicator for the tensor-parallel shard boundary: a one-shot all-reduce over NVLink written as
-// plain stores into the other ranks' HBM plus flags, fused with what precedes it (the row-parallel GEMV deposits
-// its partial sums directly in the peers' receive slots, gemv_push.cu) and with what follows it (residual add +
-// RMSNorm of the reduced row).  One process per GPU; the buffers are exchanged as CUDA IPC handles by the host
-// code (which carries the 64-byte handles over its own process group).
+// plain stores into the other ranks' HBM, fused with what precedes it (the row-parallel GEMV deposits its partial
+// sums directly in the peers' receive slots, gemv_push.cu) and with what follows it (residual add + RMSNorm of the
+// reduced row).  One process per GPU; the buffers are exchanged as CUDA IPC handles by the host code (which
+// carries the 64-byte handles over its own process group).
 //
 // Protocol, per call (epoch e, parity p = e & 1), identical on every rank:
-//   1. deposit: rank s stores its contribution into slot [p][s] of EVERY rank's buffer (its own included);
-//   2. signal:  after a system-scope fence, rank s stores e into flag [s][chunk] of every rank (release);
-//   3. wait:    a rank polls its own flags [r][chunk] for all r until they reach e (acquire) -- bounded: after
-//               the communicator's time limit (5 s unless changed) the kernel records BQ_ERR_TIMEOUT in the library's status word and carries on;
-//   4. sum:     slots [p][0..world) are added in rank order, so every rank gets bit-identical results;
-//   5. the last CTA to finish advances the epoch (device-side, so a replayed CUDA graph keeps working).
-// Two parities suffice: a rank can only be one call ahead of the slowest (it needs everybody's flag of call e to
-// finish call e), and it deposits call e+1 in the other parity.  Flags only grow; "reached e" is (int)(flag - e) >= 0.
+//   1. deposit: rank s stores its contribution into slot [p][s] of EVERY rank's buffer (its own included), one
+//               4-byte system-scope store per element;
+//   2. collect: a slot element reads COMM_EMPTY (the bits of -0.0f; deposits never carry them) until its value has
+//               arrived, so the receiver simply re-reads an element until it is there -- no flags and no fences.
+//               The wait is bounded: after the communicator's time limit (5 s unless changed) the kernel records
+//               BQ_ERR_TIMEOUT in the library's status word and carries on;
+//   3. sum:     slots [p][0..world) are added in rank order, so every rank gets bit-identical results, and the
+//               thread that read an element puts COMM_EMPTY back;
+//   4. the last CTA to finish advances the epoch (device-side, so a replayed CUDA graph keeps working).
+// Two parities suffice: a rank can only be one call ahead of the slowest (it needs everybody's values of call e to
+// finish call e) and deposits call e+1 in the other parity; it reaches call e+2 -- the same parity again -- only
+// after the slowest rank has finished call e, i.e. has read and emptied those elements.
 // Nothing here uses multicast or multimem: plain ld / st on peer-mapped memory only.
 #include <cstring>
 #include <mutex>
@@ -54,19 +58,18 @@ static Comm* get_comm(bq_comm_t h) {
   return static_cast<Comm*>(p);
 }
 
-static size_t comm_flag_bytes() { return (size_t)COMM_MAX_WORLD * COMM_MAX_CHUNKS * sizeof(uint32_t); }
 static size_t comm_total_bytes(int world, int64_t slot_elems) {
-  return COMM_HEADER_BYTES + comm_flag_bytes() + (size_t)2 * world * slot_elems * sizeof(float);
+  return COMM_HEADER_BYTES + (size_t)2 * world * slot_elems * sizeof(float);
 }
 
 // ---- device side ---------------------------------------------------------------------------------------
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+__device__ __forceinline__ uint32_t ld_sys_u32(const float* p) {
   uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
+}
+__device__ __forceinline__ void st_empty(float* p) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(COMM_EMPTY) : "memory");
 }
 __device__ __forceinline__ uint64_t comm_now_ns() {
   uint64_t t;
@@ -74,27 +77,48 @@ __device__ __forceinline__ uint64_t comm_now_ns() {
   return t;
 }
 
-// Steps 2 and 3 for one chunk.  Called by every thread of the CTA after its deposits were issued.
-__device__ __forceinline__ void comm_signal_wait(const CommDev* d, uint32_t e, int chunk, int* status) {
-  __syncthreads();
-  if ((int)threadIdx.x < d->world) {
-    const int r = threadIdx.x;
-    __threadfence_system();
-    st_release_sys(d->flags[r] + (int64_t)d->rank * COMM_MAX_CHUNKS + chunk, e);
-    const uint32_t* mine = d->flags[d->rank] + (int64_t)r * COMM_MAX_CHUNKS + chunk;
-    const uint64_t t0 = comm_now_ns();
-    uint32_t spins = 0;
-    while ((int32_t)(ld_acquire_sys(mine) - e) < 0) {
-      if ((++spins & 255u) == 0 && comm_now_ns() - t0 > d->wait_ns) {
-        atomicExch(status, (int)BQ_ERR_TIMEOUT);
-        break;
+// Step 2 for one element whose first read found it empty: re-read until the value is there or the time is up.
+// `deadline` (0 = not started) is shared by all waits of a thread, so a kernel gives up after one time limit in
+// total, not one per element.
+__device__ __noinline__ uint32_t comm_wait_value(const float* p, uint64_t wait_ns, uint64_t* deadline, int* status) {
+  if (*deadline == 0) *deadline = comm_now_ns() + wait_ns;
+  uint32_t spins = 0;
+  for (;;) {
+    const uint32_t v = ld_sys_u32(p);
+    if (v != COMM_EMPTY) return v;
+    if ((++spins & 63u) == 0 && comm_now_ns() > *deadline) {
+      atomicExch(status, (int)BQ_ERR_TIMEOUT);
+      return 0u;
+    }
+  }
+}
+
+// Steps 2 and 3 for NE elements (index idx[j], skipped when < 0) of this rank's slots: sum over the ranks in rank
+// order, slots emptied.  All first reads of a rank's slot are issued together.
+template <int NE>
+__device__ __forceinline__ void comm_collect(const CommDev* d, int64_t par, const int64_t* idx, float* sum, uint64_t* deadline,
+                                             int* status) {
+  float* mine = d->data[d->rank];
+  const int world = d->world;
+#pragma unroll
+  for (int j = 0; j < NE; ++j) sum[j] = 0.0f;
+  for (int r = 0; r < world; ++r) {
+    float* slot = mine + (par + r) * d->slot_elems;
+    uint32_t v[NE];
+#pragma unroll
+    for (int j = 0; j < NE; ++j) v[j] = idx[j] >= 0 ? ld_sys_u32(slot + idx[j]) : 0u;
+#pragma unroll
+    for (int j = 0; j < NE; ++j) {
+      if (idx[j] >= 0) {
+        if (v[j] == COMM_EMPTY) v[j] = comm_wait_value(slot + idx[j], d->wait_ns, deadline, status);
+        st_empty(slot + idx[j]);
+        sum[j] = r == 0 ? __uint_as_float(v[j]) : sum[j] + __uint_as_float(v[j]);
       }
     }
   }
-  __syncthreads();
 }
 
-// Step 5.  Called by every thread of the CTA when its reads of the slots are done.
+// Step 4.  Called by every thread of the CTA when its reads of the slots are done.
 __device__ __forceinline__ void comm_finish(const CommDev* d, uint32_t e) {
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -108,10 +132,12 @@ __device__ __forceinline__ void comm_finish(const CommDev* d, uint32_t e) {
   }
 }
 
-__device__ __forceinline__ float ld_slot(const float* p) { return __ldcg(p); }   // L2 only: the line was written remotely
+__global__ void comm_fill_empty_kernel(uint32_t* p, int64_t n) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) p[i] = COMM_EMPTY;
+}
 
 // out[i] = sum over ranks of in_r[i].  `in` == nullptr: the contributions were already deposited by the kernel
-// before this one (the PUSH GEMV).  One chunk of `chunk` elements per CTA.
+// before this one (the PUSH GEMV).  A CTA owns `chunk` consecutive elements.
 __global__ void __launch_bounds__(AR_THREADS) allreduce_sum_kernel(const CommDev* __restrict__ d, const float* __restrict__ in,
                                                                    float* __restrict__ out, int64_t count, int64_t chunk,
                                                                    int* status) {
@@ -126,15 +152,19 @@ __global__ void __launch_bounds__(AR_THREADS) allreduce_sum_kernel(const CommDev
     const int64_t off = (par + d->rank) * d->slot_elems;
     for (int64_t i = lo + threadIdx.x; i < hi; i += AR_THREADS) {
       const float v = in[i];
-      for (int r = 0; r < world; ++r) d->data[r][off + i] = v;
+      for (int r = 0; r < world; ++r) comm_deposit(d->data[r] + off + i, v);
     }
   }
-  comm_signal_wait(d, e, blockIdx.x, status);
-  const float* mine = d->data[d->rank];
-  for (int64_t i = lo + threadIdx.x; i < hi; i += AR_THREADS) {
-    float s = ld_slot(mine + par * d->slot_elems + i);
-    for (int r = 1; r < world; ++r) s += ld_slot(mine + (par + r) * d->slot_elems + i);
-    out[i] = s;
+  uint64_t deadline = 0;
+  for (int64_t i0 = lo + threadIdx.x; i0 < hi; i0 += 4 * AR_THREADS) {
+    int64_t idx[4];
+    float s[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) idx[j] = i0 + (int64_t)j * AR_THREADS < hi ? i0 + (int64_t)j * AR_THREADS : -1;
+    comm_collect<4>(d, par, idx, s, &deadline, status);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (idx[j] >= 0) out[idx[j]] = s[j];
   }
   comm_finish(d, e);
 }
@@ -158,27 +188,35 @@ __global__ void __launch_bounds__(AR_THREADS) allreduce_add_rmsnorm_kernel(const
     const int64_t off = (par + d->rank) * d->slot_elems + row0;
     for (int64_t i = threadIdx.x; i < H; i += AR_THREADS) {
       const float v = in[row0 + i];
-      for (int r = 0; r < world; ++r) d->data[r][off + i] = v;
+      for (int r = 0; r < world; ++r) comm_deposit(d->data[r] + off + i, v);
     }
   }
-  comm_signal_wait(d, e, blockIdx.x, status);
-  const float* mine = d->data[d->rank] + row0;
   T* xr = x + row0;
   T* orow = normed + row0;
   float cache[AR_CACHE];
   float ss = 0.0f;
+  uint64_t deadline = 0;
 #pragma unroll
-  for (int j = 0; j < AR_CACHE; ++j) {
-    const int64_t i = threadIdx.x + (int64_t)j * AR_THREADS;
-    float v = 0.0f;
-    if (i < H) {
-      float s = ld_slot(mine + par * d->slot_elems + i);
-      for (int r = 1; r < world; ++r) s += ld_slot(mine + (par + r) * d->slot_elems + i);
-      v = to_float<T>(from_float<T>(to_float<T>(xr[i]) + s));
-      xr[i] = from_float<T>(v);
+  for (int j0 = 0; j0 < AR_CACHE; j0 += 4) {
+    int64_t idx[4];
+    float s[4], xv[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int64_t i = threadIdx.x + (int64_t)(j0 + j) * AR_THREADS;
+      idx[j] = i < H ? row0 + i : -1;
+      xv[j] = i < H ? to_float<T>(xr[i]) : 0.0f;
     }
-    cache[j] = v;
-    ss += v * v;
+    comm_collect<4>(d, par, idx, s, &deadline, status);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float v = 0.0f;
+      if (idx[j] >= 0) {
+        v = to_float<T>(from_float<T>(xv[j] + s[j]));
+        xr[idx[j] - row0] = from_float<T>(v);
+      }
+      cache[j0 + j] = v;
+      ss += v * v;
+    }
   }
   __shared__ float red[AR_THREADS / 32];
 #pragma unroll
@@ -207,8 +245,7 @@ static int upload_desc(Comm* c) {
   for (int r = 0; r < c->world; ++r) {
     uint8_t* base = r == c->rank ? c->local : static_cast<uint8_t*>(c->peer[r]);
     if (!base) return fail(BQ_ERR_STATE, "communicator is not connected to every rank");
-    h.flags[r] = reinterpret_cast<uint32_t*>(base + COMM_HEADER_BYTES);
-    h.data[r] = reinterpret_cast<float*>(base + COMM_HEADER_BYTES + comm_flag_bytes());
+    h.data[r] = reinterpret_cast<float*>(base + COMM_HEADER_BYTES);
   }
   h.state = reinterpret_cast<uint32_t*>(c->local);
   h.slot_elems = c->slot_elems;
@@ -240,7 +277,12 @@ int bq_comm_create(int rank, int world, int64_t max_elems, bq_comm_t* out) {
   for (int r = 0; r < COMM_MAX_WORLD; ++r) c->peer[r] = nullptr;
   cudaError_t e = cudaMalloc((void**)&c->local, c->bytes);
   if (e == cudaSuccess) e = cudaMalloc((void**)&c->dev, sizeof(CommDev));
-  if (e == cudaSuccess) e = cudaMemset(c->local, 0, c->bytes);
+  if (e == cudaSuccess) e = cudaMemset(c->local, 0, COMM_HEADER_BYTES);
+  if (e == cudaSuccess) {
+    comm_fill_empty_kernel<<<256, 256>>>(reinterpret_cast<uint32_t*>(c->local + COMM_HEADER_BYTES),
+                                         (int64_t)((c->bytes - COMM_HEADER_BYTES) / 4));
+    e = cudaGetLastError();
+  }
   const uint32_t one = 1;
   if (e == cudaSuccess) e = cudaMemcpy(c->local, &one, sizeof(one), cudaMemcpyHostToDevice);   // epoch starts at 1
   if (e == cudaSuccess) e = cudaDeviceSynchronize();
@@ -298,7 +340,7 @@ int bq_comm_connect_loopback(bq_comm_t comm) {
   for (int r = 0; r < c->world; ++r) {
     if (r == c->rank) continue;
     BQ_CUDA(cudaMalloc(&c->peer[r], c->bytes));
-    BQ_CUDA(cudaMemset(c->peer[r], 0, c->bytes));
+    BQ_CUDA(cudaMemset(c->peer[r], 0, c->bytes));      // stand-in for a rank that never deposits
   }
   c->loopback = true;
   int rc = upload_desc(c);
@@ -346,8 +388,8 @@ int bq_allreduce(bq_comm_t comm, const float* in, float* out, int64_t count, voi
   if (count < 0 || count > c->slot_elems) return fail(BQ_ERR_ARG, "count exceeds the communicator's max_elems");
   if (count == 0) return BQ_OK;
   if (!out) return fail(BQ_ERR_ARG, "null pointer");
-  int64_t chunk = (count + COMM_MAX_CHUNKS - 1) / COMM_MAX_CHUNKS;
-  if (chunk < 2048) chunk = 2048;
+  int64_t chunk = (count + 4 * sm_count() - 1) / (4 * sm_count());
+  if (chunk < 1024) chunk = 1024;
   const int64_t grid = (count + chunk - 1) / chunk;
   BQ_CUDA(launch_chain(allreduce_sum_kernel, dim3((unsigned)grid), dim3(AR_THREADS), 0, (cudaStream_t)stream, 1,
                        (const CommDev*)c->dev, in, out, count, chunk, status_word()));
@@ -364,7 +406,7 @@ int bq_allreduce_add_rmsnorm(bq_comm_t comm, const float* in, void* x, const flo
   if (dtype != BQ_DT_F32 && dtype != BQ_DT_BF16) return fail(BQ_ERR_ARG, "dtype must be BQ_DT_F32 or BQ_DT_BF16");
   if (rows < 0 || H <= 0) return fail(BQ_ERR_ARG, "bad sizes");
   if (H > (int64_t)AR_THREADS * AR_CACHE) return fail(BQ_ERR_UNSUPPORTED, "rows longer than 4096 elements");
-  if (rows > COMM_MAX_CHUNKS || rows * H > c->slot_elems) return fail(BQ_ERR_ARG, "rows * H exceeds the communicator's max_elems");
+  if (rows * H > c->slot_elems) return fail(BQ_ERR_ARG, "rows * H exceeds the communicator's max_elems");
   if (rows == 0) return BQ_OK;
   if (!x || !gamma || !normed) return fail(BQ_ERR_ARG, "null pointer");
   cudaStream_t s = (cudaStream_t)stream;

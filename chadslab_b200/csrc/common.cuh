@@ -41,18 +41,19 @@ struct Moe {
 };
 constexpr uint32_t MOE_MAGIC = 0xB2003E00u;
 
-// Peer-memory communicator (comm.cu): what the kernels read.  Every rank owns one buffer (flags + receive slots)
-// that all ranks of the node map through CUDA IPC.  Rank s deposits its contribution to a sum in slot
-// [parity][s] of EVERY rank's buffer and then raises flag [s][chunk] there; the receiver adds the slots in rank
-// order.  `state[0]` is the call counter (epoch, starts at 1; parity = epoch & 1), `state[1]` counts finished CTAs.
+// Peer-memory communicator (comm.cu): what the kernels read.  Every rank owns one buffer of receive slots that all
+// ranks of the node map through CUDA IPC.  Rank s deposits its contribution to a sum in slot [parity][s] of EVERY
+// rank's buffer; a slot element holds COMM_EMPTY (the bit pattern of -0.0f, which no deposit ever carries) until
+// the value arrives, so the data announces itself: no flags, no fences.  The receiver adds the slots in rank order
+// and puts COMM_EMPTY back.  `state[0]` is the call counter (epoch, starts at 1; parity = epoch & 1), `state[1]`
+// counts finished CTAs.
 constexpr int COMM_MAX_WORLD = 8;
-constexpr int COMM_MAX_CHUNKS = 1024;
+constexpr uint32_t COMM_EMPTY = 0x80000000u;
 struct CommDev {
   float* data[COMM_MAX_WORLD];        // rank r's receive slots: [2][world][slot_elems] floats
-  uint32_t* flags[COMM_MAX_WORLD];    // rank r's flags: [world][COMM_MAX_CHUNKS]
   uint32_t* state;                    // this rank's {epoch, finished-CTA counter}
   int64_t slot_elems;
-  uint64_t wait_ns;                   // bound of the flag wait
+  uint64_t wait_ns;                   // bound of the wait for a value
   int rank, world;
 };
 
@@ -133,13 +134,19 @@ inline cudaError_t launch_chain(void (*kern)(KArgs...), dim3 grid, dim3 block, s
 
 // ---- device helpers --------------------------------------------------------------------------
 #ifdef __CUDACC__
-// Deposit one partial sum (element `idx` of this call's vector) in every rank's receive slot for this rank.
-__device__ __forceinline__ void comm_push_store(const void* desc, int64_t idx, float v) {
+// Where this rank's contribution to the current call goes in rank r's buffer (element 0 of its receive slot).
+__device__ __forceinline__ float* comm_push_base(const void* desc, int r) {
   const CommDev* d = reinterpret_cast<const CommDev*>(desc);
   const uint32_t e = *reinterpret_cast<const volatile uint32_t*>(d->state);
-  const int64_t off = ((int64_t)(e & 1u) * d->world + d->rank) * d->slot_elems + idx;
-  for (int r = 0; r < d->world; ++r) d->data[r][off] = v;
-  __threadfence_system();             // the deposits are on their way before this kernel can be seen as finished
+  return d->data[r] + ((int64_t)(e & 1u) * d->world + d->rank) * d->slot_elems;
+}
+__device__ __forceinline__ int comm_world(const void* desc) { return reinterpret_cast<const CommDev*>(desc)->world; }
+// One deposit: a system-scope 4-byte store (atomic by size); -0.0f is stored as +0.0f so that it cannot be taken
+// for an empty slot.
+__device__ __forceinline__ void comm_deposit(float* p, float v) {
+  uint32_t b = __float_as_uint(v);
+  if (b == COMM_EMPTY) b = 0u;
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(b) : "memory");
 }
 // Programmatic dependent launch: a kernel lets its successor start launching right away and itself waits for its
 // predecessor (completion + memory visibility) before it touches anything the predecessor may have written.

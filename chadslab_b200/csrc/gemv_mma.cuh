@@ -94,8 +94,8 @@ __device__ __forceinline__ void q4_word_to_h2(uint32_t v, uint32_t* o) {
 //            instantiation carries no cluster code at all)
 // PUSH       row-parallel shard of a tensor-parallel linear: `y` is not an output array but the device descriptor
 //            of a peer-memory communicator (CommDev, comm.cu); every partial sum is stored into the receive slot
-//            of every rank (plain stores over NVLink), and the kernel that follows on the stream signals, waits and
-//            sums the slots.  YT must be float.
+//            of every rank (plain stores over NVLink), and the kernel that follows on the stream waits for the
+//            values and sums the slots.  YT must be float.
 template <int FMT, int NV, int KSPLIT, typename XT, typename YT, bool CL, bool PUSH>
 __global__ void __launch_bounds__(GM_THREADS)
 qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ scales, const XT* __restrict__ x,
@@ -124,6 +124,9 @@ qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ s
   // still runs, so wait before touching x / y.  It never triggers its own successor early: CTAs of a following GEMV
   // parked on the SMs cost this one bandwidth (measured).
   pdl_wait();
+  // PUSH: the receive-slot addresses of this call, one per rank, parked behind the reduction buffers
+  float** push_dst = reinterpret_cast<float**>(cred + GM_WARPS * 16 * NV);
+  if (PUSH && threadIdx.x < comm_world(y)) push_dst[threadIdx.x] = comm_push_base(y, threadIdx.x);
 
   // ---- activations -> scaled fp16 vectors in shared memory ------------------------------------------
   {
@@ -385,8 +388,11 @@ qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ s
         if (active && writer && v < NV && m < m_rows) {
           const int64_t ra = rb * 16 + g, rbb = ra + 8;
           if (PUSH) {       // y is a CommDev: the partial sums go straight into every rank's receive slot
-            if (ra < N) comm_push_store(y, (int64_t)m * ldy + ra, a0);
-            if (rbb < N) comm_push_store(y, (int64_t)m * ldy + rbb, a1);
+            const int world = comm_world(y);
+            for (int r = 0; r < world; ++r) {
+              if (ra < N) comm_deposit(push_dst[r] + (int64_t)m * ldy + ra, a0);
+              if (rbb < N) comm_deposit(push_dst[r] + (int64_t)m * ldy + rbb, a1);
+            }
           } else {
             if (ra < N) y[(int64_t)m * ldy + ra] = from_float<YT>(a0);
             if (rbb < N) y[(int64_t)m * ldy + rbb] = from_float<YT>(a1);
@@ -405,7 +411,7 @@ static int gm_launch(const uint8_t* codes, const __half* scales, const XT* x, YT
                      int64_t ldy, cudaStream_t s) {
   auto kern = qgemv_mma_kernel<FMT, NV, KSPLIT, XT, YT, false, PUSH>;
   auto kern_cl = qgemv_mma_kernel<FMT, NV, KSPLIT, XT, YT, true, PUSH>;
-  const size_t smem = (size_t)NV * K * 2 + 32 + 2 * (size_t)GM_WARPS * 16 * NV * sizeof(float);
+  const size_t smem = (size_t)NV * K * 2 + 32 + 2 * (size_t)GM_WARPS * 16 * NV * sizeof(float) + (PUSH ? 128 : 0);
   static size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
     BQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));

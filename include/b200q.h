@@ -175,16 +175,19 @@ int bq_moe_combine(const float* out, const int32_t* inv, const float* w, int64_t
  * The specification asks for "NCCL all-reduce ... only at those shard boundaries"; the host
  * mirror keeps an NCCL route (torch.distributed) and these entry points are the fused
  * alternative for decode-sized messages: one process per GPU, each owns a buffer of receive
- * slots and flags that every other process maps through CUDA IPC; a sum is plain stores into
- * the peers' slots, a flag, a bounded wait and an add in rank order (bit-identical on every
- * rank).  Set-up, identical on every rank:
+ * slots that every other process maps through CUDA IPC; a sum is plain 4-byte stores into the
+ * peers' slots (an empty slot element holds the bits of -0.0f, so a value announces itself: no
+ * flags, no fences), a bounded wait for the values and an add in rank order (bit-identical on
+ * every rank).  Set-up, identical on every rank:
  *   bq_comm_create(rank, world, max_elems, &c);  bq_comm_handle(c, h64);
  *   -- exchange the 64-byte handles (all-gather over any host channel), rank-major --
  *   bq_comm_connect(c, handles);  -- host barrier before the first call and before destroy --
  * world <= 8; world == 1 needs no connect.  max_elems bounds the fp32 elements of one sum.
- * All ranks must issue the same sequence of summing calls with the same sizes.  A wait that
- * is not answered within the time limit (5 s unless changed) records BQ_ERR_TIMEOUT (see
- * bq_status_poll) and the kernel returns; the results of that call are then undefined.  Calls are graph-capturable.      */
+ * All ranks must issue the same sequence of summing calls with the same sizes.  A value that
+ * does not arrive within the time limit (5 s unless changed) records BQ_ERR_TIMEOUT (see
+ * bq_status_poll) and the kernel returns; the results of that call are then undefined and the
+ * communicator must be destroyed.  Calls are graph-capturable.  A contribution of -0.0f counts
+ * as +0.0f.                                                                               */
 int bq_comm_create(int rank, int world, int64_t max_elems, bq_comm_t* out);
 int bq_comm_handle(bq_comm_t c, void* out_handle /* BQ_COMM_HANDLE_BYTES */);
 int bq_comm_connect(bq_comm_t c, const void* handles /* world x BQ_COMM_HANDLE_BYTES */);
@@ -207,7 +210,7 @@ int bq_qlinear_push(bq_weight_t w, const void* x, int x_dtype, int64_t M, bq_com
  * bq_qlinear_push deposited (count = M * N).                                              */
 int bq_allreduce(bq_comm_t c, const float* in, float* out, int64_t count, void* stream);
 /* bq_add_rmsnorm with delta = the sum over ranks: x += sum; normed = rmsnorm(x) * weight.
- * rows <= 1024, H <= 4096 (else BQ_ERR_UNSUPPORTED).  in as for bq_allreduce.             */
+ * H <= 4096 (else BQ_ERR_UNSUPPORTED).  in as for bq_allreduce.                           */
 int bq_allreduce_add_rmsnorm(bq_comm_t c, const float* in, void* x, const float* weight,
                              void* normed, int64_t rows, int64_t H, float eps, int dtype,
                              void* stream);
