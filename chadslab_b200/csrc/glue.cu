@@ -362,9 +362,17 @@ int bq_decode_attention(const void* q, const void* k_cache, const void* v_cache,
   if (!q || !k_cache || !v_cache || !pos || !out) return fail(BQ_ERR_ARG, "null pointer");
   // few (batch, head) pairs and a long cache: split the positions so that several CTAs per SM stream K/V
   int64_t nsplit = (4 * (int64_t)sm_count() + B * Hq - 1) / (B * Hq);
-  if (nsplit > S / 64) nsplit = S / 64;          // a CTA takes 32 positions per trip: at least two trips each
+  if (nsplit > S / 128) nsplit = S / 128;        // at least 128 cache positions per split (measured: finer is slower)
   if (nsplit > 32) nsplit = 32;
   if (nsplit < 1) nsplit = 1;
+  {
+    static int forced = -1;            // BQ_ATT_SPLIT: tuning override of the number of position splits
+    if (forced < 0) {
+      const char* e = getenv("BQ_ATT_SPLIT");
+      forced = e ? atoi(e) : 0;
+    }
+    if (forced > 0) nsplit = forced > 64 ? 64 : forced;
+  }
   if (nsplit > 1) {
     const size_t need = (size_t)B * Hq * nsplit * (D + 2) * sizeof(float) + (size_t)B * Hq * sizeof(unsigned);
     if (need > g_att_bytes) {          // grow-only scratch owned by the library (first call: before any graph capture)
