@@ -45,12 +45,14 @@ PROTOTYPES = {
     "bq_qlinear": (_i32, [_h, _vp, _i32, _i64, _vp, _i32, _vp]),
     "bq_qlinear_ex": (_i32, [_h, _vp, _i32, _i64, _vp, _i32, _i32, _vp]),
     "bq_qlinear_host": (_i32, [_h, _vp, _i32, _i64, _vp, _i32]),
+    "bq_qlinear_gated": (_i32, [_h, _vp, _i32, _i64, _vp, _i32, _vp]),
     "bq_lm_head": (_i32, [_h, _vp, _i32, _i64, _vp, _i32, _vp, _vp]),
     "bq_last_path": (_i32, []),
     "bq_launch_count": (_i64, []),
     "bq_add_rmsnorm": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, C.c_float, _i32, _vp]),
     "bq_rope_kv_append": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i64, C.c_float, _i32, _vp]),
     "bq_decode_attention": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i64, _i32, _vp]),
+    "bq_decode_attention_rope": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i64, C.c_float, _i32, _vp]),
     "bq_gated_act": (_i32, [_vp, _vp, _i64, _i64, _i32, _i32, _vp]),
     "bq_moe_route": (_i32, [_vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp]),
     "bq_moe_permute_scratch_bytes": (_i64, [_i64, _i32, _i32]),

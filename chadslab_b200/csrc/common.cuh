@@ -94,6 +94,10 @@ bool gemv_mma_supported(int fmt, int64_t N, int64_t K, int x_dtype, int64_t M);
 // same GEMV, fp32 partial sums pushed into every rank's receive slot of a peer-memory communicator (gemv_push.cu)
 int launch_qlinear_mma_push(const uint8_t* codes, const __half* scales, int fmt, int64_t N, int64_t K,
                             const void* x, int x_dtype, int64_t M, const CommDev* comm_dev, cudaStream_t s);
+// same GEMV on a fused gate|up weight (16-row blocks = 8 gate rows + 8 up rows): out[M, N/2] = act(gate) * up in the
+// activations' dtype; act 0 = gelu (tanh), 1 = silu (gemv_gated.cu)
+int launch_qlinear_mma_gated(const uint8_t* codes, const __half* scales, int fmt, int64_t N, int64_t K,
+                             const void* x, int x_dtype, int64_t M, void* out, int act, cudaStream_t s);
 bool moe_tc_supported(const Moe* m);
 int moe_tc_prepare(Moe* m, const std::vector<const uint8_t*>* codes, const std::vector<const __half*>* scales);
 void moe_tc_release(Moe* m);

@@ -13,7 +13,7 @@ int launch_qlinear_mma(const uint8_t* codes, const __half* scales, int fmt, int6
                        int x_dtype, int64_t M, void* y, int y_dtype, int64_t ldy, cudaStream_t s) {
   if (!gemv_mma_supported(fmt, N, K, x_dtype, M)) return fail(BQ_ERR_UNSUPPORTED, "shape not supported by the MMA GEMV");
   const int m = (int)M;
-#define BQ_GM_CASE(F, XT, YT) return gm_pick_nv<F, XT, YT, false>(codes, scales, (const XT*)x, (YT*)y, N, K, m, ldy, s)
+#define BQ_GM_CASE(F, XT, YT) return gm_pick_nv<F, XT, YT, GM_OUT_PLAIN>(codes, scales, (const XT*)x, (YT*)y, N, K, m, ldy, s)
   if (fmt == BQ_FMT_Q8G32) {
     if (x_dtype == BQ_DT_BF16 && y_dtype == BQ_DT_F32) BQ_GM_CASE(BQ_FMT_Q8G32, __nv_bfloat16, float);
     if (x_dtype == BQ_DT_BF16 && y_dtype == BQ_DT_BF16) BQ_GM_CASE(BQ_FMT_Q8G32, __nv_bfloat16, __nv_bfloat16);

@@ -26,6 +26,7 @@
 
 namespace bq {
 
+constexpr int GM_OUT_PLAIN = 0, GM_OUT_PUSH = 1, GM_OUT_GELU = 2, GM_OUT_SILU = 3;
 constexpr int GM_WARPS = 8;
 constexpr int GM_THREADS = GM_WARPS * 32;
 
@@ -96,11 +97,15 @@ __device__ __forceinline__ void q4_word_to_h2(uint32_t v, uint32_t* o) {
 //            of a peer-memory communicator (CommDev, comm.cu); every partial sum is stored into the receive slot
 //            of every rank (plain stores over NVLink), and the kernel that follows on the stream waits for the
 //            values and sums the slots.  YT must be float.
-template <int FMT, int NV, int KSPLIT, typename XT, typename YT, bool CL, bool PUSH>
+// OUT        GM_OUT_PLAIN: y[m, row]; GM_OUT_PUSH: as above; GM_OUT_GELU / GM_OUT_SILU: the weight is a fused
+//            gate|up projection whose 16-row blocks hold 8 gate rows followed by the 8 up rows of the same output
+//            columns, so a lane owns both halves of a column: y[m, block*8 + g] = act(gate) * up, ldy = N / 2.
+template <int FMT, int NV, int KSPLIT, typename XT, typename YT, bool CL, int OUT>
 __global__ void __launch_bounds__(GM_THREADS)
 qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ scales, const XT* __restrict__ x,
                  YT* __restrict__ y, int64_t N, int64_t K, int m_rows, int64_t ldy, int kc_arg) {
   const int kc = CL ? kc_arg : 1;
+  constexpr bool PUSH = OUT == GM_OUT_PUSH;
   constexpr bool Q8 = FMT == BQ_FMT_Q8G32;
   constexpr bool XF32 = sizeof(XT) == 4;
   constexpr int GROUPS_PER_STEP = Q8 ? 2 : 4;          // groups covered by a quad per step
@@ -237,7 +242,9 @@ qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ s
 #pragma unroll
     for (int b = 0; b < NB; ++b) acc0[b][0] = acc1[b][0] = 0.0f;
 
-#pragma unroll 2
+    // KSPLIT == 8 is the small-N / long-K case: a warp has only a dozen steps, so more of them are kept in flight
+    constexpr int UNR = KSPLIT == 8 ? 4 : 2;
+#pragma unroll UNR
     for (int64_t s = active ? s_begin : s_end; s < s_end; ++s) {
       const uint4 w0 = ldg_stream16(p0 + s * 64);
       const uint4 w1 = ldg_stream16(p1 + s * 64);
@@ -393,6 +400,13 @@ qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ s
               if (ra < N) comm_deposit(push_dst[r] + (int64_t)m * ldy + ra, a0);
               if (rbb < N) comm_deposit(push_dst[r] + (int64_t)m * ldy + rbb, a1);
             }
+          } else if (OUT == GM_OUT_GELU || OUT == GM_OUT_SILU) {
+            if (rbb < N) {   // a0 = gate, a1 = up of output column rb*8 + g (same formulas as gated_act_kernel)
+              float a;
+              if (OUT == GM_OUT_GELU) a = 0.5f * a0 * (1.0f + tanhf(0.7978845608028654f * (a0 + 0.044715f * a0 * a0 * a0)));
+              else a = a0 / (1.0f + __expf(-a0));
+              y[(int64_t)m * ldy + rb * 8 + g] = from_float<YT>(a * a1);
+            }
           } else {
             if (ra < N) y[(int64_t)m * ldy + ra] = from_float<YT>(a0);
             if (rbb < N) y[(int64_t)m * ldy + rbb] = from_float<YT>(a1);
@@ -406,12 +420,12 @@ qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ s
 }
 
 // ---- host side ------------------------------------------------------------------------------------------
-template <int FMT, int NV, int KSPLIT, typename XT, typename YT, bool PUSH>
+template <int FMT, int NV, int KSPLIT, typename XT, typename YT, int OUT>
 static int gm_launch(const uint8_t* codes, const __half* scales, const XT* x, YT* y, int64_t N, int64_t K, int m_rows,
                      int64_t ldy, cudaStream_t s) {
-  auto kern = qgemv_mma_kernel<FMT, NV, KSPLIT, XT, YT, false, PUSH>;
-  auto kern_cl = qgemv_mma_kernel<FMT, NV, KSPLIT, XT, YT, true, PUSH>;
-  const size_t smem = (size_t)NV * K * 2 + 32 + 2 * (size_t)GM_WARPS * 16 * NV * sizeof(float) + (PUSH ? 128 : 0);
+  auto kern = qgemv_mma_kernel<FMT, NV, KSPLIT, XT, YT, false, OUT>;
+  auto kern_cl = qgemv_mma_kernel<FMT, NV, KSPLIT, XT, YT, true, OUT>;
+  const size_t smem = (size_t)NV * K * 2 + 32 + 2 * (size_t)GM_WARPS * 16 * NV * sizeof(float) + (OUT == GM_OUT_PUSH ? 128 : 0);
   static size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
     BQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
@@ -442,29 +456,29 @@ static int gm_launch(const uint8_t* codes, const __half* scales, const XT* x, YT
   return BQ_OK;
 }
 
-template <int FMT, int NV, typename XT, typename YT, bool PUSH>
+template <int FMT, int NV, typename XT, typename YT, int OUT>
 static int gm_pick_split(const uint8_t* codes, const __half* scales, const XT* x, YT* y, int64_t N, int64_t K,
                          int m_rows, int64_t ldy, cudaStream_t s) {
   // enough 16-row blocks for every SM to hold several warps -> no K split; otherwise split K in the CTA
   const int64_t rb = (N + 15) / 16;
   const int64_t want = (int64_t)sm_count() * 16;      // warps that keep the memory system busy
-  if (rb >= want || K < 1024) return gm_launch<FMT, NV, 1, XT, YT, PUSH>(codes, scales, x, y, N, K, m_rows, ldy, s);
-  if (rb * 2 >= want || K < 2048) return gm_launch<FMT, NV, 2, XT, YT, PUSH>(codes, scales, x, y, N, K, m_rows, ldy, s);
-  if (rb * 4 >= want || K < 4096) return gm_launch<FMT, NV, 4, XT, YT, PUSH>(codes, scales, x, y, N, K, m_rows, ldy, s);
-  return gm_launch<FMT, NV, 8, XT, YT, PUSH>(codes, scales, x, y, N, K, m_rows, ldy, s);
+  if (rb >= want || K < 1024) return gm_launch<FMT, NV, 1, XT, YT, OUT>(codes, scales, x, y, N, K, m_rows, ldy, s);
+  if (rb * 2 >= want || K < 2048) return gm_launch<FMT, NV, 2, XT, YT, OUT>(codes, scales, x, y, N, K, m_rows, ldy, s);
+  if (rb * 4 >= want || K < 4096) return gm_launch<FMT, NV, 4, XT, YT, OUT>(codes, scales, x, y, N, K, m_rows, ldy, s);
+  return gm_launch<FMT, NV, 8, XT, YT, OUT>(codes, scales, x, y, N, K, m_rows, ldy, s);
 }
 
-template <int FMT, typename XT, typename YT, bool PUSH>
+template <int FMT, typename XT, typename YT, int OUT>
 static int gm_pick_nv(const uint8_t* codes, const __half* scales, const XT* x, YT* y, int64_t N, int64_t K, int m_rows,
                       int64_t ldy, cudaStream_t s) {
   const int nv = m_rows * (sizeof(XT) == 4 ? 2 : 1);
   if (sizeof(XT) == 4) {
-    if (nv <= 2) return gm_pick_split<FMT, 2, XT, YT, PUSH>(codes, scales, x, y, N, K, m_rows, ldy, s);
-    return gm_pick_split<FMT, 4, XT, YT, PUSH>(codes, scales, x, y, N, K, m_rows, ldy, s);
+    if (nv <= 2) return gm_pick_split<FMT, 2, XT, YT, OUT>(codes, scales, x, y, N, K, m_rows, ldy, s);
+    return gm_pick_split<FMT, 4, XT, YT, OUT>(codes, scales, x, y, N, K, m_rows, ldy, s);
   }
-  if (nv == 1) return gm_pick_split<FMT, 1, XT, YT, PUSH>(codes, scales, x, y, N, K, m_rows, ldy, s);
-  if (nv == 2) return gm_pick_split<FMT, 2, XT, YT, PUSH>(codes, scales, x, y, N, K, m_rows, ldy, s);
-  return gm_pick_split<FMT, 4, XT, YT, PUSH>(codes, scales, x, y, N, K, m_rows, ldy, s);
+  if (nv == 1) return gm_pick_split<FMT, 1, XT, YT, OUT>(codes, scales, x, y, N, K, m_rows, ldy, s);
+  if (nv == 2) return gm_pick_split<FMT, 2, XT, YT, OUT>(codes, scales, x, y, N, K, m_rows, ldy, s);
+  return gm_pick_split<FMT, 4, XT, YT, OUT>(codes, scales, x, y, N, K, m_rows, ldy, s);
 }
 
 }  // namespace bq

@@ -144,11 +144,52 @@ __device__ __forceinline__ void unpack_raw(const RawRow<__nv_bfloat16>& v, float
     f[2 * i + 1] = __uint_as_float(wds[i] & 0xFFFF0000u);
   }
 }
+// Elements d0 .. d0+7 of one head taken from the fp32 projection output, RoPE-rotated (rotate-half pairs d, d + D/2)
+// with the roundings of rope_kv_append_kernel: through T before the rotation and T after it.
 template <typename T>
+__device__ __forceinline__ void rope8(const float* __restrict__ src, int d0, int D, int64_t pos, float base, bool rotate,
+                                      float* o) {
+  const int half = D / 2;
+#pragma unroll
+  for (int i = 0; i < ATT_EPL; ++i) {
+    const int d = d0 + i;
+    if (!rotate) {
+      o[i] = to_float<T>(from_float<T>(src[d]));
+    } else {
+      const int j = d < half ? d : d - half;
+      const float x1 = to_float<T>(from_float<T>(src[j])), x2 = to_float<T>(from_float<T>(src[j + half]));
+      const float inv = 1.0f / powf(base, (float)(2 * j) / (float)D);
+      float sn, cs;
+      sincosf((float)pos * inv, &sn, &cs);
+      o[i] = to_float<T>(from_float<T>(d < half ? x1 * cs - x2 * sn : x2 * cs + x1 * sn));
+    }
+  }
+}
+template <typename T> __device__ __forceinline__ void store8(T* p, const float* f);
+template <> __device__ __forceinline__ void store8<float>(float* p, const float* f) {
+  *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
+}
+template <> __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const float* f) {
+  uint4 r;
+  uint32_t* w = &r.x;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    w[i] = *reinterpret_cast<const uint32_t*>(&v);
+  }
+  *reinterpret_cast<uint4*>(p) = r;
+}
+
+// FUSED: `q` is unused; the query, and the K / V rows of the current position, come straight from `qkv` (fp32
+// [B, (Hq + 2 Hkv) D], the fused projection's output), rotated here; the cache supplies positions < pos only and
+// the CTA of the first query head of each KV group appends the new rows to it.  One launch instead of
+// rope_kv_append_kernel + this kernel.
+template <typename T, bool FUSED>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
-decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
-                        const int64_t* __restrict__ pos_p, T* __restrict__ out, int Hq, int Hkv, int D, int64_t S,
-                        float* __restrict__ part, unsigned* __restrict__ counters) {
+decode_attention_kernel(const T* __restrict__ q, const float* __restrict__ qkv, T* __restrict__ k_cache,
+                        T* __restrict__ v_cache, const int64_t* __restrict__ pos_p, T* __restrict__ out, int Hq, int Hkv,
+                        int D, int64_t S, float rope_base, float* __restrict__ part, unsigned* __restrict__ counters) {
   const int b = blockIdx.y, h = blockIdx.x;
   // gridDim.z > 1: the positions are split over gridDim.z CTAs (long contexts, few heads); each leaves its
   // (max, sum, unnormalised output) in `part` and the last one to arrive merges them in split order
@@ -160,7 +201,9 @@ decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
   const int64_t n_all = *pos_p + 1;
   const int64_t per = ((n_all + nsplit - 1) / nsplit + ATT_PB - 1) / ATT_PB * ATT_PB;
   const int64_t p_lo = (int64_t)z * per;
-  const int64_t n_pos = p_lo + per < n_all ? p_lo + per : n_all;        // this CTA covers [p_lo, n_pos)
+  const int64_t n_own = p_lo + per < n_all ? p_lo + per : n_all;        // this CTA covers [p_lo, n_own)
+  // FUSED: the current position (n_all - 1) is not in the cache yet; the CTA that owns it adds it after the loop
+  const int64_t n_pos = FUSED && n_own == n_all ? n_all - 1 : n_own;
   const int d0 = lane * ATT_EPL;
   const bool live = d0 < D;
   float qv[ATT_EPL], acc[ATT_EPL];
@@ -168,7 +211,8 @@ decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
 #pragma unroll
   for (int i = 0; i < ATT_EPL; ++i) { qv[i] = 0.0f; acc[i] = 0.0f; }
   if (live) {
-    load8<T>(q + ((int64_t)b * Hq + h) * D + d0, qv);
+    if (FUSED) rope8<T>(qkv + ((int64_t)b * (Hq + 2 * Hkv) + h) * D, d0, D, n_all - 1, rope_base, true, qv);
+    else load8<T>(q + ((int64_t)b * Hq + h) * D + d0, qv);
 #pragma unroll
     for (int i = 0; i < ATT_EPL; ++i) qv[i] *= scale;
   }
@@ -222,6 +266,32 @@ decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
 #pragma unroll
         for (int i = 0; i < ATT_EPL; ++i) acc[i] += p * vf[i];
       }
+    }
+    mx = nm;
+  }
+  if (FUSED && warp == 0 && p_lo < n_all && n_own == n_all) {
+    // the current position: K (rotated) and V from the projection output, one more online-softmax step
+    const int64_t pos = n_all - 1;
+    float kn[ATT_EPL], vn[ATT_EPL];
+    float dsum = 0.0f;
+    if (live) {
+      rope8<T>(qkv + ((int64_t)b * (Hq + 2 * Hkv) + Hq + kv) * D, d0, D, pos, rope_base, true, kn);
+      rope8<T>(qkv + ((int64_t)b * (Hq + 2 * Hkv) + Hq + Hkv + kv) * D, d0, D, pos, rope_base, false, vn);
+#pragma unroll
+      for (int i = 0; i < ATT_EPL; ++i) dsum += qv[i] * kn[i];
+      if (h % (Hq / Hkv) == 0) {                      // first query head of the group appends to the cache
+        store8<T>(k_cache + (((int64_t)b * S + pos) * Hkv + kv) * D + d0, kn);
+        store8<T>(v_cache + (((int64_t)b * S + pos) * Hkv + kv) * D + d0, vn);
+      }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) dsum += __shfl_xor_sync(0xffffffffu, dsum, off);
+    const float nm = fmaxf(mx, dsum);
+    const float corr = __expf(mx - nm), p = __expf(dsum - nm);
+    sum = sum * corr + p;
+    if (live) {
+#pragma unroll
+      for (int i = 0; i < ATT_EPL; ++i) acc[i] = acc[i] * corr + p * vn[i];
     }
     mx = nm;
   }
@@ -287,13 +357,15 @@ decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
 // act: 0 = gelu (tanh approximation), 1 = silu
 template <typename T>
 __global__ void __launch_bounds__(256) gated_act_kernel(const float* __restrict__ gu, T* __restrict__ out, int64_t rows,
-                                                        int64_t F, int act) {
+                                                        int64_t F, int act, int blocked) {
   pdl_launch_dependents();
   pdl_wait();
   const int64_t total = rows * F;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t r = i / F, f = i - r * F;
-    const float g = gu[r * 2 * F + f], u = gu[r * 2 * F + F + f];
+    // blocked: 16-column blocks of gu hold 8 gate values followed by the 8 up values of the same outputs
+    const int64_t gi = blocked ? (f >> 3) * 16 + (f & 7) : f, ui = blocked ? gi + 8 : F + f;
+    const float g = gu[r * 2 * F + gi], u = gu[r * 2 * F + ui];
     float a;
     if (act == 0) a = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
     else a = g / (1.0f + __expf(-g));
@@ -305,6 +377,8 @@ __global__ void __launch_bounds__(256) gated_act_kernel(const float* __restrict_
 
 using namespace bq;
 
+static float* g_gu = nullptr;           // bq_qlinear_gated, large batches: the gate|up product before the activation
+static size_t g_gu_bytes = 0;
 static float* g_att_part = nullptr;     // split-position attention: partial states + arrival counters
 static size_t g_att_bytes = 0;
 
@@ -313,6 +387,57 @@ static int glue_ready(int dtype) {
   if (dtype != BQ_DT_F32 && dtype != BQ_DT_BF16) return fail(BQ_ERR_ARG, "dtype must be BQ_DT_F32 or BQ_DT_BF16");
   return BQ_OK;
 }
+
+static int launch_attention(const void* q, const float* qkv, void* k_cache, void* v_cache, const int64_t* pos, void* out,
+                            int64_t B, int Hq, int Hkv, int D, int64_t S, float rope_base, int dtype, void* stream) {
+  int rc = glue_ready(dtype);
+  if (rc) return rc;
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || D <= 0 || D > ATT_MAXD || (D % 8) || S <= 0)
+    return fail(BQ_ERR_ARG, "bad sizes (head_dim <= 256 and a multiple of 8, Hq a multiple of Hkv)");
+  if (!k_cache || !v_cache || !pos || !out) return fail(BQ_ERR_ARG, "null pointer");
+  // few (batch, head) pairs and a long cache: split the positions so that several CTAs per SM stream K/V
+  int64_t nsplit = (4 * (int64_t)sm_count() + B * Hq - 1) / (B * Hq);
+  if (nsplit > S / 128) nsplit = S / 128;        // at least 128 cache positions per split (measured: finer is slower)
+  if (nsplit > 32) nsplit = 32;
+  if (nsplit < 1) nsplit = 1;
+  {
+    static int forced = -1;            // BQ_ATT_SPLIT: tuning override of the number of position splits
+    if (forced < 0) {
+      const char* e = getenv("BQ_ATT_SPLIT");
+      forced = e ? atoi(e) : 0;
+    }
+    if (forced > 0) nsplit = forced > 64 ? 64 : forced;
+  }
+  if (nsplit > 1) {
+    const size_t need = (size_t)B * Hq * nsplit * (D + 2) * sizeof(float) + (size_t)B * Hq * sizeof(unsigned);
+    if (need > g_att_bytes) {          // grow-only scratch owned by the library (first call: before any graph capture)
+      if (g_att_part) BQ_CUDA(cudaFree(g_att_part));
+      g_att_part = nullptr; g_att_bytes = 0;
+      const size_t cap = need * 2;
+      BQ_CUDA(cudaMalloc((void**)&g_att_part, 2 * cap));
+      BQ_CUDA(cudaMemset(g_att_part, 0, 2 * cap));
+      g_att_bytes = cap;
+    }
+  }
+  // partial states first, the arrival counters (all zero between launches) in the second half of the allocation
+  float* part = g_att_part;
+  unsigned* counters = reinterpret_cast<unsigned*>(reinterpret_cast<uint8_t*>(g_att_part) + g_att_bytes);
+  dim3 grid((unsigned)Hq, (unsigned)B, (unsigned)nsplit);
+  cudaStream_t s = (cudaStream_t)stream;
+#define BQ_ATT_LAUNCH(TT, FUSED)                                                                                        \
+  BQ_CUDA(launch_chain(decode_attention_kernel<TT, FUSED>, grid, dim3(ATT_WARPS * 32), 0, s, 1, (const TT*)q, qkv, (TT*)k_cache, \
+                       (TT*)v_cache, pos, (TT*)out, Hq, Hkv, D, S, rope_base, part, counters))
+  if (dtype == BQ_DT_F32) {
+    if (qkv) BQ_ATT_LAUNCH(float, true); else BQ_ATT_LAUNCH(float, false);
+  } else {
+    if (qkv) BQ_ATT_LAUNCH(__nv_bfloat16, true); else BQ_ATT_LAUNCH(__nv_bfloat16, false);
+  }
+#undef BQ_ATT_LAUNCH
+  count_launch();
+  BQ_CUDA(cudaGetLastError());
+  return BQ_OK;
+}
+
 
 extern "C" {
 
@@ -355,47 +480,27 @@ int bq_rope_kv_append(const float* qkv, const int64_t* pos, void* q_out, void* k
 
 int bq_decode_attention(const void* q, const void* k_cache, const void* v_cache, const int64_t* pos, void* out, int64_t B,
                         int Hq, int Hkv, int D, int64_t S, int dtype, void* stream) {
-  int rc = glue_ready(dtype);
-  if (rc) return rc;
-  if (B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || D <= 0 || D > ATT_MAXD || (D % 8) || S <= 0)
-    return fail(BQ_ERR_ARG, "bad sizes (head_dim <= 256 and a multiple of 8, Hq a multiple of Hkv)");
-  if (!q || !k_cache || !v_cache || !pos || !out) return fail(BQ_ERR_ARG, "null pointer");
-  // few (batch, head) pairs and a long cache: split the positions so that several CTAs per SM stream K/V
-  int64_t nsplit = (4 * (int64_t)sm_count() + B * Hq - 1) / (B * Hq);
-  if (nsplit > S / 128) nsplit = S / 128;        // at least 128 cache positions per split (measured: finer is slower)
-  if (nsplit > 32) nsplit = 32;
-  if (nsplit < 1) nsplit = 1;
-  {
-    static int forced = -1;            // BQ_ATT_SPLIT: tuning override of the number of position splits
-    if (forced < 0) {
-      const char* e = getenv("BQ_ATT_SPLIT");
-      forced = e ? atoi(e) : 0;
-    }
-    if (forced > 0) nsplit = forced > 64 ? 64 : forced;
-  }
-  if (nsplit > 1) {
-    const size_t need = (size_t)B * Hq * nsplit * (D + 2) * sizeof(float) + (size_t)B * Hq * sizeof(unsigned);
-    if (need > g_att_bytes) {          // grow-only scratch owned by the library (first call: before any graph capture)
-      if (g_att_part) BQ_CUDA(cudaFree(g_att_part));
-      g_att_part = nullptr; g_att_bytes = 0;
-      const size_t cap = need * 2;
-      BQ_CUDA(cudaMalloc((void**)&g_att_part, 2 * cap));
-      BQ_CUDA(cudaMemset(g_att_part, 0, 2 * cap));
-      g_att_bytes = cap;
-    }
-  }
-  // partial states first, the arrival counters (all zero between launches) in the second half of the allocation
-  float* part = g_att_part;
-  unsigned* counters = reinterpret_cast<unsigned*>(reinterpret_cast<uint8_t*>(g_att_part) + g_att_bytes);
-  dim3 grid((unsigned)Hq, (unsigned)B, (unsigned)nsplit);
-  cudaStream_t s = (cudaStream_t)stream;
+  if (!q) return fail(BQ_ERR_ARG, "null pointer");
+  return launch_attention(q, nullptr, const_cast<void*>(k_cache), const_cast<void*>(v_cache), pos, out, B, Hq, Hkv, D, S, 0.0f,
+                          dtype, stream);
+}
+
+int bq_decode_attention_rope(const float* qkv, void* k_cache, void* v_cache, const int64_t* pos, void* out, int64_t B,
+                             int Hq, int Hkv, int D, int64_t S, float rope_base, int dtype, void* stream) {
+  if (!qkv) return fail(BQ_ERR_ARG, "null pointer");
+  return launch_attention(nullptr, qkv, k_cache, v_cache, pos, out, B, Hq, Hkv, D, S, rope_base, dtype, stream);
+}
+
+static int launch_gated_act(const float* gate_up, void* out, int64_t rows, int64_t F, int act, int dtype, int blocked,
+                            cudaStream_t s) {
+  int64_t grid = (rows * F + 255) / 256;
+  if (grid > (int64_t)sm_count() * 8) grid = (int64_t)sm_count() * 8;
   if (dtype == BQ_DT_F32)
-    BQ_CUDA(launch_chain(decode_attention_kernel<float>, grid, dim3(ATT_WARPS * 32), 0, s, 1, (const float*)q, (const float*)k_cache,
-                         (const float*)v_cache, pos, (float*)out, Hq, Hkv, D, S, part, counters));
+    BQ_CUDA(launch_chain(gated_act_kernel<float>, dim3((unsigned)grid), dim3(256), 0, s, 1, gate_up, (float*)out, rows, F, act,
+                         blocked));
   else
-    BQ_CUDA(launch_chain(decode_attention_kernel<__nv_bfloat16>, grid, dim3(ATT_WARPS * 32), 0, s, 1, (const __nv_bfloat16*)q,
-                         (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, pos, (__nv_bfloat16*)out, Hq, Hkv, D, S,
-                         part, counters));
+    BQ_CUDA(launch_chain(gated_act_kernel<__nv_bfloat16>, dim3((unsigned)grid), dim3(256), 0, s, 1, gate_up, (__nv_bfloat16*)out,
+                         rows, F, act, blocked));
   count_launch();
   BQ_CUDA(cudaGetLastError());
   return BQ_OK;
@@ -407,17 +512,35 @@ int bq_gated_act(const float* gate_up, void* out, int64_t rows, int64_t F, int a
   if (rows < 0 || F <= 0 || (act != 0 && act != 1)) return fail(BQ_ERR_ARG, "bad arguments");
   if (rows == 0) return BQ_OK;
   if (!gate_up || !out) return fail(BQ_ERR_ARG, "null pointer");
-  int64_t grid = (rows * F + 255) / 256;
-  if (grid > (int64_t)sm_count() * 8) grid = (int64_t)sm_count() * 8;
+  return launch_gated_act(gate_up, out, rows, F, act, dtype, 0, (cudaStream_t)stream);
+}
+
+int bq_qlinear_gated(bq_weight_t weight, const void* x, int x_dtype, int64_t M, void* out, int act, void* stream) {
+  int rc = glue_ready(x_dtype);
+  if (rc) return rc;
+  Weight* w = get_weight(weight);
+  if (!w) return BQ_ERR_HANDLE;
+  if (M < 0 || (act != 0 && act != 1)) return fail(BQ_ERR_ARG, "bad arguments");
+  if (w->N % 16) return fail(BQ_ERR_ARG, "a fused gate|up weight has a multiple of 16 rows");
+  if (M == 0) return BQ_OK;
+  if (!x || !out) return fail(BQ_ERR_ARG, "null pointer");
   cudaStream_t s = (cudaStream_t)stream;
-  if (dtype == BQ_DT_F32)
-    BQ_CUDA(launch_chain(gated_act_kernel<float>, dim3((unsigned)grid), dim3(256), 0, s, 1, gate_up, (float*)out, rows, F, act));
-  else
-    BQ_CUDA(launch_chain(gated_act_kernel<__nv_bfloat16>, dim3((unsigned)grid), dim3(256), 0, s, 1, gate_up, (__nv_bfloat16*)out,
-                         rows, F, act));
-  count_launch();
-  BQ_CUDA(cudaGetLastError());
-  return BQ_OK;
+  if (gemv_mma_supported(w->fmt, w->N, w->K, x_dtype, M)) {      // decode-sized: activation in the GEMV's epilogue
+    set_last_path(BQ_PATH_MMA);
+    return launch_qlinear_mma_gated(w->codes, w->scales, w->fmt, w->N, w->K, x, x_dtype, M, out, act, s);
+  }
+  // larger batches: plain product into a scratch owned by the library (sized on the first call: before any graph
+  // capture), then the activation kernel reading the blocked layout
+  const size_t need = (size_t)M * w->N * sizeof(float);
+  if (need > g_gu_bytes) {
+    if (g_gu) BQ_CUDA(cudaFree(g_gu));
+    g_gu = nullptr; g_gu_bytes = 0;
+    BQ_CUDA(cudaMalloc((void**)&g_gu, need + need / 4));
+    g_gu_bytes = need + need / 4;
+  }
+  rc = bq_qlinear(weight, x, x_dtype, M, g_gu, BQ_DT_F32, stream);
+  if (rc) return rc;
+  return launch_gated_act(g_gu, out, M, w->N / 2, act, x_dtype, 1, s);
 }
 
 }  // extern "C"

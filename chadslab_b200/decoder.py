@@ -18,7 +18,7 @@ import torch
 import torch.nn.functional as F
 
 from . import parallel
-from .ops import LMHead, PackedWeight, QuantLinear, shard
+from .ops import LMHead, PackedWeight, QuantLinear, interleave_gate_up, shard, split_gate_up
 from .synth import make_device_weight
 
 
@@ -87,7 +87,9 @@ class QuantDecoder:
         for l in range(cfg.layers):
             # q|k|v and gate|up are each one packed weight (rows concatenated): one launch instead of three / two
             lin[f"l{l}.qkv"] = QuantLinear(get([f"l{l}.q", f"l{l}.k", f"l{l}.v"], ["n", kv_axis, kv_axis]))
-            lin[f"l{l}.gate_up"] = QuantLinear(get([f"l{l}.gate", f"l{l}.up"], ["n", "n"]))
+            # gate|up rows interleaved in blocks of 8 (ops.interleave_gate_up): the decode GEMV applies the gated
+            # activation in its epilogue
+            lin[f"l{l}.gate_up"] = QuantLinear(get([f"l{l}.gate", f"l{l}.up"], ["n", "n"], True))
             o, d = QuantLinear(get(f"l{l}.o", "k")), QuantLinear(get(f"l{l}.down", "k"))
             lin[f"l{l}.o"] = parallel.RowParallelLinear(o) if world > 1 else o
             lin[f"l{l}.down"] = parallel.RowParallelLinear(d) if world > 1 else d
@@ -102,10 +104,12 @@ class QuantDecoder:
             pw = PackedWeight(w[name][0], w[name][1], cfg.fmt, upload=upload and (world == 1 or axis is None))
             return pw if (world == 1 or axis is None) else shard(pw, axis, rank, world, upload=upload)
 
-        def get(name, axis):
+        def get(name, axis, blocked=False):
             if isinstance(name, str):
                 return get_one(name, axis, True)
             parts = [get_one(n_, a_, False) for n_, a_ in zip(name, axis)]
+            if blocked:
+                return interleave_gate_up(parts[0], parts[1])
             return PackedWeight(np.concatenate([p_.codes for p_ in parts], 0), np.concatenate([p_.scales for p_ in parts], 0),
                                 cfg.fmt)
         lin = cls._wrap(cfg, get, rank, world)
@@ -123,7 +127,7 @@ class QuantDecoder:
                   "gate": (cfg.ffn, cfg.hidden), "up": (cfg.ffn, cfg.hidden), "down": (cfg.hidden, cfg.ffn),
                   "lm_head": (cfg.vocab, cfg.hidden)}
 
-        def get(name, axis):
+        def get(name, axis, blocked=False):          # random rows: the interleaved layout needs no permutation
             names, axes = ([name], [axis]) if isinstance(name, str) else (name, axis)
             N, K = 0, shapes[names[0].split(".")[-1]][1]
             for n_, a_ in zip(names, axes):
@@ -172,8 +176,8 @@ class QuantDecoder:
             o = o.transpose(1, 2).reshape(B, T, self.h_local * c.head_dim)
             x = x + self.lin[f"l{l}.o"](o.contiguous()).to(self.act_dtype)
             h = _rmsnorm(x, self.norms[f"l{l}.norm2"], c.eps)
-            gu = self.lin[f"l{l}.gate_up"](h)
-            a = F.gelu(gu[..., :self.ffn_local], approximate="tanh") * gu[..., self.ffn_local:]
+            gate, up = split_gate_up(self.lin[f"l{l}.gate_up"](h))
+            a = F.gelu(gate, approximate="tanh") * up
             x = x + self.lin[f"l{l}.down"](a.to(self.act_dtype)).to(self.act_dtype)
         self.pos = S
         return _rmsnorm(x, self.norms["norm_f"], c.eps)
@@ -209,7 +213,7 @@ class QuantDecoder:
     def _step_static(self, tokens, pos_t):
         """One greedy decode step with every shape fixed: `tokens` int64 [B] and `pos_t` int64 [1] live on the
         device and are updated in place (tokens <- next ids, pos_t += 1).  Between the quantized matmuls the step
-        runs the library's glue kernels (residual add + RMSNorm, RoPE + KV append, single-query attention, gated
+        runs the library's glue kernels (residual add + RMSNorm, RoPE + KV append + single-query attention, gated
         activation), all of which read the position from device memory, so the step is graph-capturable."""
         from . import _lib
         from .ops import _dt_of_torch, _stream_ptr
@@ -220,8 +224,7 @@ class QuantDecoder:
         x = self.embed[tokens].to(self.act_dtype).contiguous()                    # residual stream [B, hidden]
         h = torch.empty_like(x)
         S = self.k_cache[0].shape[1]
-        q = torch.empty((B, self.h_local, c.head_dim), dtype=self.act_dtype, device=dev)
-        att = torch.empty_like(q)
+        att = torch.empty((B, self.h_local, c.head_dim), dtype=self.act_dtype, device=dev)
         act = torch.empty((B, self.ffn_local), dtype=self.act_dtype, device=dev)
         comm = self.comm if self.world > 1 else None
         PUSHED = object()                  # the partial sums sit in the communicator's receive slots
@@ -243,16 +246,13 @@ class QuantDecoder:
         for l in range(c.layers):
             add_norm(delta, self.norms[f"l{l}.norm1"])
             qkv = self.lin[f"l{l}.qkv"](h)                                        # fp32 [B, (Hq + 2 Hkv) D]
-            _lib.check(lib.bq_rope_kv_append(qkv.data_ptr(), pos_t.data_ptr(), q.data_ptr(), self.k_cache[l].data_ptr(),
-                                             self.v_cache[l].data_ptr(), B, self.h_local, self.kv_local, c.head_dim, S,
-                                             c.rope_base, dt, st))
-            _lib.check(lib.bq_decode_attention(q.data_ptr(), self.k_cache[l].data_ptr(), self.v_cache[l].data_ptr(),
-                                               pos_t.data_ptr(), att.data_ptr(), B, self.h_local, self.kv_local,
-                                               c.head_dim, S, dt, st))
+            # RoPE, KV append and single-query attention in one launch
+            _lib.check(lib.bq_decode_attention_rope(qkv.data_ptr(), self.k_cache[l].data_ptr(), self.v_cache[l].data_ptr(),
+                                                    pos_t.data_ptr(), att.data_ptr(), B, self.h_local, self.kv_local,
+                                                    c.head_dim, S, c.rope_base, dt, st))
             delta = row_parallel(f"l{l}.o", att.reshape(B, -1))
             add_norm(delta, self.norms[f"l{l}.norm2"])
-            gu = self.lin[f"l{l}.gate_up"](h)
-            _lib.check(lib.bq_gated_act(gu.data_ptr(), act.data_ptr(), B, self.ffn_local, 0, dt, st))
+            self.lin[f"l{l}.gate_up"].gated(h, 0, out=act)                         # GeGLU in the GEMV's epilogue
             delta = row_parallel(f"l{l}.down", act)
         add_norm(delta, self.norms["norm_f"])
         head = self.lin["lm_head"]

@@ -196,6 +196,27 @@ def shard(pw: PackedWeight, axis: str, rank: int, world: int, **kw) -> PackedWei
     raise ValueError("axis must be 'n' or 'k'")
 
 
+def interleave_gate_up(gate: PackedWeight, up: PackedWeight, **kw) -> PackedWeight:
+    """Fused gate|up weight for `QuantLinear.gated`: 2F rows in 16-row blocks, 8 gate rows followed by the 8 up
+    rows of the same output columns (a row permutation of the concatenated weights)."""
+    if gate.codes is None or up.codes is None:
+        raise ValueError("interleave_gate_up() needs the host arrays of both weights")
+    if (gate.N, gate.K, gate.fmt) != (up.N, up.K, up.fmt) or gate.N % 8:
+        raise ValueError("gate and up must have the same shape and format, with a multiple of 8 rows")
+    F = gate.N
+
+    def mix(a, b):
+        return np.stack([a.reshape(F // 8, 8, -1), b.reshape(F // 8, 8, -1)], axis=1).reshape(2 * F, -1)
+    return PackedWeight(mix(gate.codes, up.codes), mix(gate.scales, up.scales), gate.fmt, **kw)
+
+
+def split_gate_up(gu):
+    """[..., 2F] output of a plain product with an interleaved gate|up weight -> (gate [..., F], up [..., F])."""
+    F = gu.shape[-1] // 2
+    g4 = gu.reshape(*gu.shape[:-1], F // 8, 2, 8)
+    return g4[..., 0, :].reshape(*gu.shape[:-1], F), g4[..., 1, :].reshape(*gu.shape[:-1], F)
+
+
 class QuantLinear:
     """y = x . dequant(W)^T for a packed weight; fp32 accumulate."""
 
@@ -231,6 +252,20 @@ class QuantLinear:
         _lib.check(_lib.lib().bq_qlinear_ex(self.pw.handle, x2.data_ptr(), _dt_of_torch(x2), M, out.data_ptr(),
                                             _dt_of_torch(out), self.path, _stream_ptr()))
         return out.reshape(*lead, self.pw.N)
+
+    def gated(self, x, act: int = 0, out=None):
+        """For a weight built by `interleave_gate_up`: act(x . gate^T) * (x . up^T) in the dtype of x
+        (act 0 = gelu-tanh, 1 = silu); decode-sized calls are one launch."""
+        torch = _torch()
+        x2 = x.reshape(-1, self.pw.K)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        M = x2.shape[0]
+        if out is None:
+            out = torch.empty((M, self.pw.N // 2), dtype=x2.dtype, device=x.device)
+        _lib.check(_lib.lib().bq_qlinear_gated(self.pw.handle, x2.data_ptr(), _dt_of_torch(x2), M, out.data_ptr(), int(act),
+                                               _stream_ptr()))
+        return out.reshape(*x.shape[:-1], self.pw.N // 2)
 
     def _host(self, x: np.ndarray) -> np.ndarray:
         x2 = np.ascontiguousarray(x).reshape(-1, self.pw.K)

@@ -91,6 +91,14 @@ int bq_qlinear_ex(bq_weight_t w, const void* x, int x_dtype, int64_t M, void* y,
 /* Same with HOST buffers: copies x in, runs, copies y out, synchronises.                 */
 int bq_qlinear_host(bq_weight_t w, const void* x_host, int x_dtype, int64_t M,
                     void* y_host, int y_dtype);
+/* Fused gate|up projection with the gated activation applied on the way out.  `w` has 2F rows in
+ * 16-row blocks: 8 gate rows followed by the 8 up rows of the same output columns (block b holds
+ * columns 8b .. 8b+7; chadslab_b200.ops.interleave_gate_up builds it from the two weights).
+ * out[M, F] = act(x . gate^T) * (x . up^T) in the dtype of x; act 0 = gelu (tanh), 1 = silu.
+ * Decode-sized calls apply the activation in the GEMV's epilogue (one launch); larger batches run the
+ * product into a scratch owned by the library (first call outside stream capture) plus a second kernel. */
+int bq_qlinear_gated(bq_weight_t w, const void* x, int x_dtype, int64_t M, void* out, int act,
+                     void* stream);
 /* lm_head + greedy argmax: logits may be NULL (then only argmax is produced).
  * argmax_out: device int32[M]; ties resolve to the lower vocabulary index.               */
 int bq_lm_head(bq_weight_t w, const void* x, int x_dtype, int64_t M, void* logits,
@@ -115,6 +123,13 @@ int bq_rope_kv_append(const float* qkv, const int64_t* pos, void* q_out, void* k
 /* out[B,Hq,D] = softmax(q . K[0..*pos] / sqrt(D)) . V[0..*pos], grouped-query (Hq % Hkv == 0), D <= 256 */
 int bq_decode_attention(const void* q, const void* k_cache, const void* v_cache, const int64_t* pos,
                         void* out, int64_t B, int Hq, int Hkv, int D, int64_t S, int dtype, void* stream);
+/* bq_rope_kv_append + bq_decode_attention in one launch: q and the current position's K / V are taken from
+ * qkv and rotated inside the attention kernel (same roundings), the caches supply positions < *pos and
+ * receive the new rows.  When the positions are split over several CTAs the first call sizes a scratch
+ * buffer owned by the library: make it outside stream capture.                                            */
+int bq_decode_attention_rope(const float* qkv, void* k_cache, void* v_cache, const int64_t* pos, void* out,
+                             int64_t B, int Hq, int Hkv, int D, int64_t S, float rope_base, int dtype,
+                             void* stream);
 /* gate_up: fp32 [rows, 2F] (gate | up); out[rows,F] = act(gate) * up; act 0 = gelu(tanh), 1 = silu    */
 int bq_gated_act(const float* gate_up, void* out, int64_t rows, int64_t F, int act, int dtype,
                  void* stream);

@@ -123,3 +123,68 @@ def test_gated_activation(cuda_lib, adt, act):
     else:
         a = gt / (1.0 + torch.exp(-gt))
     assert _rel(out.double().cpu().numpy(), (a * up).cpu().numpy()) <= _tol(dt)
+
+
+@pytest.mark.parametrize("adt", ["float32", "bfloat16"])
+@pytest.mark.parametrize("shape", [(2, 4, 2, 64, 64, 0), (1, 8, 1, 256, 1024, 700), (2, 4, 4, 128, 512, 511),
+                                   (1, 16, 16, 256, 2112, 2048), (3, 2, 1, 64, 4096, 128)])
+def test_fused_rope_append_attention_equals_the_two_kernels(cuda_lib, adt, shape):
+    """bq_decode_attention_rope against bq_rope_kv_append + bq_decode_attention: the appended cache rows are
+    bit-identical, the attention output agrees to rounding (the current position joins the softmax last)."""
+    import torch
+    from chadslab_b200 import _lib
+    from chadslab_b200.ops import _dt_of_torch, _stream_ptr
+    B, Hq, Hkv, D, S, pos = shape
+    dt = getattr(torch, adt)
+    g = torch.Generator(device="cuda").manual_seed(pos + 7)
+    qkv = torch.randn((B, (Hq + 2 * Hkv) * D), device="cuda", generator=g)
+    k0 = torch.randn((B, S, Hkv, D), device="cuda", generator=g).to(dt)
+    v0 = torch.randn((B, S, Hkv, D), device="cuda", generator=g).to(dt)
+    pos_t = torch.tensor([pos], device="cuda", dtype=torch.int64)
+    ka, va = k0.clone(), v0.clone()
+    qa = torch.empty((B, Hq, D), device="cuda", dtype=dt)
+    oa = torch.empty_like(qa)
+    d, st = _dt_of_torch(ka), _stream_ptr()
+    _lib.check(cuda_lib.bq_rope_kv_append(qkv.data_ptr(), pos_t.data_ptr(), qa.data_ptr(), ka.data_ptr(), va.data_ptr(), B, Hq,
+                                          Hkv, D, S, 10000.0, d, st))
+    _lib.check(cuda_lib.bq_decode_attention(qa.data_ptr(), ka.data_ptr(), va.data_ptr(), pos_t.data_ptr(), oa.data_ptr(), B, Hq,
+                                            Hkv, D, S, d, st))
+    kb, vb = k0.clone(), v0.clone()
+    ob = torch.empty_like(oa)
+    for _ in range(2):
+        ob.zero_()
+        _lib.check(cuda_lib.bq_decode_attention_rope(qkv.data_ptr(), kb.data_ptr(), vb.data_ptr(), pos_t.data_ptr(), ob.data_ptr(),
+                                                     B, Hq, Hkv, D, S, 10000.0, d, st))
+        assert torch.equal(ka, kb) and torch.equal(va, vb)
+        assert _rel(ob.double().cpu().numpy(), oa.double().cpu().numpy()) <= _tol(dt)
+    assert cuda_lib.bq_status_poll() == 0
+
+
+@pytest.mark.parametrize("fmt", [0, 1])
+@pytest.mark.parametrize("adt", ["float32", "bfloat16"])
+@pytest.mark.parametrize("act", [0, 1])
+@pytest.mark.parametrize("M", [1, 2, 16])
+def test_gated_linear_equals_product_then_activation(cuda_lib, fmt, adt, act, M):
+    """bq_qlinear_gated on an interleaved gate|up weight against the plain products of the two weights followed by
+    the activation: M <= 2 runs the GEMV with the activation in its epilogue, M = 16 the two-kernel route."""
+    import torch
+    import chadslab_b200 as cb
+    dt = getattr(torch, adt)
+    F, K = 1024, 512
+    rng = np.random.default_rng(3)
+    gate = cb.PackedWeight.from_float(rng.normal(0, 0.05, (F, K)).astype(np.float32), fmt)
+    up = cb.PackedWeight.from_float(rng.normal(0, 0.05, (F, K)).astype(np.float32), fmt)
+    fused = cb.QuantLinear(cb.interleave_gate_up(gate, up))
+    x = torch.randn((M, K), device="cuda").to(dt)
+    got = fused.gated(x, act)
+    assert got.dtype == dt and tuple(got.shape) == (M, F)
+    g, u = cb.QuantLinear(gate)(x).double(), cb.QuantLinear(up)(x).double()
+    if act == 0:
+        a = 0.5 * g * (1.0 + torch.tanh(0.7978845608028654 * (g + 0.044715 * g ** 3)))
+    else:
+        a = g / (1.0 + torch.exp(-g))
+    assert _rel(got.double().cpu().numpy(), (a * u).cpu().numpy()) <= _tol(dt)
+    # the plain product of the fused weight is the interleaved pair
+    from chadslab_b200.ops import split_gate_up
+    g2, u2 = split_gate_up(fused(x))
+    assert torch.equal(g2, cb.QuantLinear(gate)(x)) and torch.equal(u2, cb.QuantLinear(up)(x))

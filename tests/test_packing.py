@@ -83,3 +83,19 @@ def test_container_round_trip(tmp_path):
     assert np.array_equal(tensors["embed"], extra["embed"])
     with pytest.raises(ValueError):
         container.save_packed(path, ws, {"x.codes": extra["embed"]})
+
+
+def test_interleave_gate_up_is_a_row_permutation():
+    from chadslab_b200.ops import PackedWeight, interleave_gate_up, split_gate_up
+    from oracle import spec
+    rng = np.random.default_rng(4)
+    for fmt in (0, 1):
+        Wg, Wu = (rng.normal(0, 0.02, (24, 64)).astype(np.float32) for _ in range(2))
+        g = PackedWeight(*spec.quantize(Wg, fmt), fmt, upload=False)
+        u = PackedWeight(*spec.quantize(Wu, fmt), fmt, upload=False)
+        f = interleave_gate_up(g, u, upload=False)
+        assert f.N == 48 and f.K == 64
+        d = spec.dequantize(f.codes, f.scales, fmt)                      # [48, 64]
+        gg, uu = split_gate_up(d.T)                                      # split along the last axis
+        assert np.array_equal(gg.T, spec.dequantize(g.codes, g.scales, fmt))
+        assert np.array_equal(uu.T, spec.dequantize(u.codes, u.scales, fmt))
