@@ -40,6 +40,7 @@ PROTOTYPES = {
     "bq_weight_destroy": (_i32, [_h]),
     "bq_weight_info": (_i32, [_h, C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_i32)]),
     "bq_weight_export": (_i32, [_h, _vp, _vp]),
+    "bq_quantize": (_i32, [_vp, _i32, _i64, _i64, _i32, _vp, _vp, _vp]),
     "bq_dequant": (_i32, [_h, _vp, _i32, _vp]),
     "bq_unpack_codes": (_i32, [_h, _vp, _vp]),
     "bq_qlinear": (_i32, [_h, _vp, _i32, _i64, _vp, _i32, _vp]),

@@ -5,7 +5,8 @@
 
 The context is synthetic: `ctx` positions of random K/V are placed in the cache instead of running a prefill.
 Each batch size is captured as one CUDA graph per step and replayed; `--eager 1` launches the kernels directly
-(what a profiler wants).  Prints one JSON object on rank 0.
+(what a profiler wants).  `--prefill 8x4096 --fmt int8` times a prefill pass of 8 sequences of 4096 tokens instead
+(tcgen05 dequant-GEMM path).  Prints one JSON object on rank 0.
 """
 from __future__ import annotations
 
@@ -85,6 +86,50 @@ def run(torch, dist, rank: int, world: int, shape: str = "gemma7b", batches=(1, 
     return out
 
 
+def run_prefill(torch, dist, rank: int, world: int, shape: str = "gemma7b", fmt: int = 0, B: int = 8, T: int = 4096,
+                reps: int = 2):
+    """Prefill of B sequences of T random token ids through the eager path (tcgen05 dequant-GEMM for every linear,
+    PyTorch attention and glue, NCCL all-reduce after the row-parallel linears).  Runs on every rank."""
+    import dataclasses
+    from chadslab_b200 import _lib
+    from chadslab_b200.decoder import GEMMA_2B_SHAPE, GEMMA_7B_SHAPE, QuantDecoder
+    cfg = dataclasses.replace({"gemma2b": GEMMA_2B_SHAPE, "gemma7b": GEMMA_7B_SHAPE}[shape], fmt=fmt)
+    out = {"model": f"{shape}-shape {'int8' if fmt == 0 else 'q4'}-g32, bf16 activations, random-init",
+           "tensor_parallel": world, "batch": B, "seq_len": T,
+           "timing": f"{reps} passes after 1, CUDA events, max over ranks; last position projected by the head"}
+    try:
+        dec = QuantDecoder.random(cfg, seed=0, act_dtype=torch.bfloat16, rank=rank, world=world, max_seq=T, max_batch=B)
+        g = torch.Generator(device="cuda").manual_seed(0)
+        tokens = torch.randint(0, cfg.vocab, (B, T), device="cuda", generator=g)
+        lin_weights = sum((l.linear if hasattr(l, "linear") else l).pw.N * (l.linear if hasattr(l, "linear") else l).pw.K
+                          for n, l in dec.lin.items() if n != "lm_head")
+        times = []
+        for i in range(reps + 1):
+            dec.reset()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            a.record()
+            dec.next_tokens(tokens)
+            b.record()
+            torch.cuda.synchronize()
+            if i:
+                times.append(a.elapsed_time(b))
+        t = torch.tensor([sum(times) / len(times)], device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+        out.update({"ms": round(ms, 2), "tokens_per_s": round(B * T / ms * 1e3, 1),
+                    "linear_tflops_per_gpu": round(2.0 * B * T * lin_weights / ms / 1e9, 1),
+                    "status": int(_lib.lib().bq_status_poll())})
+        del dec
+    except Exception as e:
+        out["error"] = repr(e)[:300]
+    torch.cuda.empty_cache()
+    return out
+
+
 def main():
     import torch
     import torch.distributed as dist
@@ -95,6 +140,8 @@ def main():
     ap.add_argument("--ctx", type=int, default=2048)
     ap.add_argument("--steps", type=int, default=16)
     ap.add_argument("--eager", type=int, default=0)
+    ap.add_argument("--prefill", default="", help="BxT: time a prefill pass instead (e.g. 8x4096)")
+    ap.add_argument("--fmt", default="", choices=["", "int8", "q4"], help="prefill: weight format (default: the shape's)")
     args = ap.parse_args()
     world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -102,8 +149,13 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     _lib.init(local)
-    rep = run(torch, dist, rank, world, args.shape, tuple(int(b) for b in args.batch.split(",")), args.ctx, args.steps,
-              bool(args.eager))
+    if args.prefill:
+        B, T = (int(v) for v in args.prefill.lower().split("x"))
+        fmt = {"": 0 if args.shape == "gemma2b" else 1, "int8": 0, "q4": 1}[args.fmt]
+        rep = run_prefill(torch, dist, rank, world, args.shape, fmt, B, T)
+    else:
+        rep = run(torch, dist, rank, world, args.shape, tuple(int(b) for b in args.batch.split(",")), args.ctx, args.steps,
+                  bool(args.eager))
     if rank == 0:
         print(json.dumps(rep))
     if world > 1:

@@ -171,8 +171,11 @@ class QuantDecoder:
             rep = self.h_local // self.kv_local
             if rep > 1:
                 kk, vv = kk.repeat_interleave(rep, dim=2), vv.repeat_interleave(rep, dim=2)
-            mask = (torch.arange(S, device=x.device)[None, :] <= pos[:, None])      # [T, S]
-            o = F.scaled_dot_product_attention(q.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2), attn_mask=mask)
+            if self.pos == 0 and T > 1:      # no earlier context: plain causal attention (lets PyTorch pick a fused kernel)
+                o = F.scaled_dot_product_attention(q.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2), is_causal=True)
+            else:
+                mask = (torch.arange(S, device=x.device)[None, :] <= pos[:, None])      # [T, S]
+                o = F.scaled_dot_product_attention(q.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2), attn_mask=mask)
             o = o.transpose(1, 2).reshape(B, T, self.h_local * c.head_dim)
             x = x + self.lin[f"l{l}.o"](o.contiguous()).to(self.act_dtype)
             h = _rmsnorm(x, self.norms[f"l{l}.norm2"], c.eps)

@@ -91,6 +91,24 @@ class PackedWeight:
         return cls(codes, scales, fmt, **kw)
 
     @classmethod
+    def from_float_device(cls, W, fmt: int) -> "PackedWeight":
+        """Quantize a CUDA tensor (fp32 or bf16 [N, K]) on the device: same codes and scales, bit for bit, as
+        `from_float` computes on the host; nothing leaves the GPU."""
+        torch = _torch()
+        if not W.is_cuda or W.dim() != 2:
+            raise BqError(_lib.ERR_ARG, "from_float_device needs a 2-D CUDA tensor")
+        W = W.contiguous()
+        N, K = W.shape
+        if K % GROUP:
+            raise ValueError(f"K={K} must be a multiple of {GROUP}")
+        codes = torch.empty((N, K if fmt == FMT_Q8 else K // 2), dtype=torch.int8 if fmt == FMT_Q8 else torch.uint8,
+                            device=W.device)
+        scales = torch.empty((N, K // GROUP), dtype=torch.float16, device=W.device)
+        _lib.check(_lib.lib().bq_quantize(W.data_ptr(), _dt_of_torch(W), N, K, fmt, codes.data_ptr(), scales.data_ptr(),
+                                          _stream_ptr()))
+        return cls.from_device(codes, scales, fmt)
+
+    @classmethod
     def from_arrays(cls, codes, scales, fmt: int, **kw) -> "PackedWeight":
         return cls(codes, scales, fmt, **kw)
 

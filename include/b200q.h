@@ -81,6 +81,14 @@ int bq_dequant(bq_weight_t w, void* out, int out_dtype, void* stream);
 /* out: device int8[N,K] — the unpacked integer codes.                                    */
 int bq_unpack_codes(bq_weight_t w, void* out_i8, void* stream);
 
+/* Quantize on the device (spec: "weight packer/loader layout on device"): w is fp32 or bf16 [N,K] in
+ * device memory; codes_out / scales_out receive the INTERFACE layout (int8[N,K] or uint8[N,K/2], and
+ * fp16[N,K/32]), bit for bit what the host packer computes: scale = fp16(absmax/qmax) (qmax 127 / 7),
+ * code = clip(rint(w / f32(scale)), +-qmax), zero-scale groups -> codes 0.  Feed the result to
+ * bq_weight_create_device.                                                                          */
+int bq_quantize(const void* w, int w_dtype, int64_t N, int64_t K, int fmt, void* codes_out,
+                void* scales_out, void* stream);
+
 /* ---- quantized linear / lm_head (spec: "multiplied against bf16/fp32 activations for
  *      every linear, MoE-expert and lm_head projection", fp32 accumulate) --------------- */
 /* y[M,N] = x[M,K] . W^T.  x, y: device pointers. x_dtype/y_dtype in {F32,BF16}.          */

@@ -215,3 +215,37 @@ def test_edge_cases_and_errors(cuda_lib):
         cb.QuantLinear(pw)(torch.zeros((1, 64), device="cuda", dtype=torch.float16))
     assert lib.bq_status_poll() == 0
     assert lib.bq_launch_count() > 0
+
+
+@pytest.mark.parametrize("fmt", [0, 1])
+@pytest.mark.parametrize("wdt", ["float32", "bfloat16"])
+def test_device_quantizer_is_bit_identical_to_the_oracle(cuda_lib, fmt, wdt):
+    """bq_quantize against oracle.spec.quantize: codes and scales bit for bit, including the edge groups (all zero,
+    exact ties x.5, values at +-absmax, an absmax that underflows fp16, a scale clamped to the fp16 maximum)."""
+    import torch
+    import chadslab_b200 as cb
+    rng = np.random.default_rng(17)
+    N, K = 96, 256
+    W = rng.normal(0, 0.02, (N, K)).astype(np.float32)
+    W[0, :32] = 0.0                                           # all-zero group
+    if fmt == 0:
+        W[1, :32] = (np.arange(-16, 16, dtype=np.float32) + 0.5) * 0.5       # w / 0.5 = -15.5 .. 15.5: every element a tie
+        W[1, 0] = -63.5                                                       # absmax chosen so that scale = 0.5
+    else:
+        W[1, :32] = (np.arange(32, dtype=np.float32) % 14 - 7 + 0.5) * 0.5   # w / 0.5 = -6.5 .. 6.5: ties
+        W[1, 0] = -3.5
+    W[2, :32] = 1e-9                                          # absmax / qmax underflows fp16 -> scale 0 -> codes 0
+    W[3, :32] = 3.0e7                                         # scale clamps to 65504
+    W[4, 32:64] = -W[4, 32:64].max()                          # every element at -absmax
+    dt = getattr(torch, wdt)
+    Wt = torch.from_numpy(W).cuda().to(dt)
+    Wref = Wt.float().cpu().numpy()                           # what the device sees (bf16-rounded when wdt is bf16)
+    pw = cb.PackedWeight.from_float_device(Wt, fmt)
+    codes, scales = pw.export()
+    rc, rs = spec.quantize(Wref, fmt)
+    assert np.array_equal(scales.view(np.uint16), rs.view(np.uint16))
+    assert np.array_equal(codes, rc)
+    # and it multiplies like a host-packed weight
+    x = torch.randn((1, K), device="cuda").to(torch.bfloat16)
+    host = cb.PackedWeight.from_arrays(rc, rs, fmt)
+    assert torch.equal(cb.QuantLinear(pw)(x), cb.QuantLinear(host)(x))
