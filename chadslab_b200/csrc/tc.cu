@@ -470,8 +470,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
 // stage, converts them in registers and writes them with tcgen05.st into one of two A buffers in TMEM;
 // the issuer uses the tensor-memory form of tcgen05.mma (A from TMEM, B from shared memory).  Shared
 // memory then only holds packed codes, activations and scales, so two CTAs fit on an SM.
-// TMEM columns: [0, BN) accumulator, then two A buffers of 64 columns (= 128 k) at 128 / 192 (BN <= 128,
-// 256 columns allocated, two CTAs per SM) or at 256 / 320 (BN = 256, 512 columns allocated).
+// TMEM columns: [0, NW*BN) accumulators, then NW x 2 A buffers of 64 columns (= 128 k) from column 128 (NW*BN <= 128)
+// or 256; 256 columns are allocated (two CTAs per SM) when that fits below 256, else all 512.
 // =================================================================================================
 constexpr int T2_BK = 128;
 constexpr int T2_ACOLS = 64;
@@ -487,12 +487,16 @@ template <int FMT, int BN, int MODE> struct T2Plan {
   static constexpr int SCT = TC_ROWS * 16;                                // 8 fp16 scales per row = 256 k = 2 steps
   static constexpr int STAGE = ((NW * RAW + XT + 1023) / 1024) * 1024;
   static constexpr int FIXED = TC_SC_SLOTS * NW * SCT + 1024 + 1024;
-  static constexpr int BUDGET = (NW * BN <= 128 ? 100 : 200) * 1024;      // two CTAs per SM up to BN = 128
+  // tensor memory: NW accumulators of BN columns from column 0, then NW x 2 A buffers of 64 columns from ACOL0.
+  // 256 columns (two CTAs per SM) only when everything fits below 256; two weight tiles always need 512.
+  static constexpr int ACOL0 = NW * BN <= 128 ? 128 : 256;                // first A-buffer column
+  static constexpr int TMEM_NEED = ACOL0 + NW * 2 * T2_ACOLS;
+  static constexpr int TMEM_COLS = TMEM_NEED <= 256 ? 256 : 512;
+  static constexpr int BUDGET = (TMEM_COLS == 256 ? 100 : 200) * 1024;    // shared memory follows: two CTAs per SM or one
   static constexpr int S_RAW = (BUDGET - FIXED) / STAGE;
   static constexpr int S = S_RAW > 4 ? 4 : (S_RAW < 2 ? 2 : S_RAW);       // S <= 2*SC_SLOTS - 1 = 5
   static constexpr int SMEM = FIXED + S * STAGE;
-  static constexpr int ACOL0 = NW * BN <= 128 ? 128 : 256;                // first A-buffer column
-  static constexpr int TMEM_COLS = NW * BN <= 128 ? 256 : 512;
+  static_assert(TMEM_NEED <= 512, "tensor memory plan too large");
   static_assert(NW * BN <= 256 && BN % 16 == 0, "accumulators must fit below the A buffers");
   static_assert(SMEM <= 227 * 1024, "shared memory plan too large");
 };
@@ -1101,9 +1105,11 @@ int launch_moe_experts_tc(const Moe* m, const void* xp, const int32_t* offsets, 
   if (!st) return fail(BQ_ERR_UNSUPPORTED, "tensor path unavailable for this expert shape");
   if ((reinterpret_cast<uintptr_t>(xp) & 15) != 0 || (reinterpret_cast<uintptr_t>(hbuf) & 15) != 0)
     return fail(BQ_ERR_ARG, "activation buffers must be 16-byte aligned");
-  // rows per expert ~ P / E: pick the batch tile for the average segment
+  // rows per expert ~ P / E: pick the batch tile for the average segment.  A tcgen05.mma costs the same to issue
+  // for 16 or 64 columns, so the 16-row tile is kept for segments that are mostly below 16 rows (at an average of
+  // 16 half the experts would need a second tile that streams the same weights again).
   const int64_t avg = (P + m->E - 1) / m->E;
-  const int bn = avg <= 16 ? 16 : avg <= 64 ? 64 : 128;
+  const int bn = avg <= 8 ? 16 : avg <= 64 ? 64 : 128;
   const int64_t max_tiles = (P + bn - 1) / bn + m->E;
   if (max_tiles > st->tiles_cap) {
     if (st->tiles) BQ_CUDA(cudaFree(st->tiles));

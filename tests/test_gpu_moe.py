@@ -142,3 +142,48 @@ def test_moe_layer_random(cuda_lib, fmt, T):
         layer = cb.MoEExperts(pw(router), [pw(g) for g in gate], [pw(u) for u in up], [pw(d) for d in down], top_k=k,
                               path=path)
         _check_layer(cb, torch, layer, x, E, k, gate, up, down, fmt, golden_y=(ref, ridx))
+
+
+@pytest.mark.parametrize("fmt", [0, 1])
+@pytest.mark.parametrize("T", [128, 400, 4096])
+def test_grouped_experts_at_scale_against_simt_path(cuda_lib, fmt, T):
+    """64 experts, hidden 2048, ffn 768 (six 128-row tiles), top-8: hundreds of tiles are resident at once and the
+    three token-tile sizes (16 / 64 / 128 rows per expert on average) are all taken.  The tensor-core grouped kernel
+    must agree with the exact CUDA-core path on the same permuted rows (hidden h within one bf16 step, outputs
+    <= 1e-3 against an fp32 product of the tensor path's own h with the bit-exact dequantized weights)."""
+    import torch
+    import chadslab_b200 as cb
+    from chadslab_b200.synth import make_device_weight
+    E, H, F, k = 64, 2048, 768, 8
+    gen = torch.Generator(device="cuda").manual_seed(7 + T)
+
+    def mk(n, kk):
+        c, s = make_device_weight(torch, n, kk, fmt, gen)
+        return cb.PackedWeight.from_device(c, s, fmt)
+    gate, up, down = [mk(F, H) for _ in range(E)], [mk(F, H) for _ in range(E)], [mk(H, F) for _ in range(E)]
+    router = mk(E, H)
+    tens = cb.MoEExperts(router, gate, up, down, top_k=k, path=cb.PATH_TENSOR)
+    simt = cb.MoEExperts(router, gate, up, down, top_k=k, path=cb.PATH_SIMT)
+    x = torch.randn((T, H), device="cuda", generator=gen).to(torch.bfloat16)
+    idx, w = cb.moe_route(tens.router(x), k)
+    perm, inv, offsets = cb.moe_permute(idx, E)
+    xp = cb.moe_gather(x, perm, k)
+    out_t, h_t = tens.experts(xp, offsets, return_h=True)
+    out_s, h_s = simt.experts(xp, offsets, return_h=True)
+    torch.cuda.synchronize()
+    assert cuda_lib.bq_status_poll() == 0
+    ht, hs = h_t.float(), h_s.float()
+    # one bf16 step (2^-7 of the value's binade) where the two paths round an element differently
+    assert float((ht - hs).abs().max()) <= (2.0 ** -7 + TOL) * float(hs.abs().max())
+    # down projection of the tensor path's own h through the exact path
+    ref = torch.zeros_like(out_s)
+    Wd = [d.dequantize() for d in down]                 # bit-exact fp32 weights
+    off = offsets.cpu().numpy()
+    for e in range(E):
+        a, b = int(off[e]), int(off[e + 1])
+        if a < b:
+            ref[a:b] = ht[a:b] @ Wd[e].t()
+    err = float((out_t - ref).abs().max() / ref.abs().max())
+    assert err <= TOL, err
+    y = cb.moe_combine(out_t, inv, w)
+    assert bool(torch.isfinite(y).all())
