@@ -145,10 +145,11 @@ __device__ __forceinline__ void unpack_raw(const RawRow<__nv_bfloat16>& v, float
   }
 }
 // Elements d0 .. d0+7 of one head taken from the fp32 projection output, RoPE-rotated (rotate-half pairs d, d + D/2)
-// with the roundings of rope_kv_append_kernel: through T before the rotation and T after it.
+// with the roundings of rope_kv_append_kernel: through T before the rotation and T after it.  cs / sn: the cosines
+// and sines of the D/2 rotation angles of this position (same expressions as rope_kv_append_kernel).
 template <typename T>
-__device__ __forceinline__ void rope8(const float* __restrict__ src, int d0, int D, int64_t pos, float base, bool rotate,
-                                      float* o) {
+__device__ __forceinline__ void rope8(const float* __restrict__ src, int d0, int D, const float* cs, const float* sn,
+                                      bool rotate, float* o) {
   const int half = D / 2;
 #pragma unroll
   for (int i = 0; i < ATT_EPL; ++i) {
@@ -158,10 +159,7 @@ __device__ __forceinline__ void rope8(const float* __restrict__ src, int d0, int
     } else {
       const int j = d < half ? d : d - half;
       const float x1 = to_float<T>(from_float<T>(src[j])), x2 = to_float<T>(from_float<T>(src[j + half]));
-      const float inv = 1.0f / powf(base, (float)(2 * j) / (float)D);
-      float sn, cs;
-      sincosf((float)pos * inv, &sn, &cs);
-      o[i] = to_float<T>(from_float<T>(d < half ? x1 * cs - x2 * sn : x2 * cs + x1 * sn));
+      o[i] = to_float<T>(from_float<T>(d < half ? x1 * cs[j] - x2 * sn[j] : x2 * cs[j] + x1 * sn[j]));
     }
   }
 }
@@ -199,6 +197,14 @@ decode_attention_kernel(const T* __restrict__ q, const float* __restrict__ qkv, 
   pdl_launch_dependents();
   pdl_wait();
   const int64_t n_all = *pos_p + 1;
+  __shared__ float s_cos[ATT_MAXD / 2], s_sin[ATT_MAXD / 2];
+  if (FUSED) {                         // the rotation angles of the current position, once per CTA
+    for (int j = threadIdx.x; j < D / 2; j += blockDim.x) {
+      const float inv = 1.0f / powf(rope_base, (float)(2 * j) / (float)D);
+      sincosf((float)(n_all - 1) * inv, &s_sin[j], &s_cos[j]);
+    }
+    __syncthreads();
+  }
   const int64_t per = ((n_all + nsplit - 1) / nsplit + ATT_PB - 1) / ATT_PB * ATT_PB;
   const int64_t p_lo = (int64_t)z * per;
   const int64_t n_own = p_lo + per < n_all ? p_lo + per : n_all;        // this CTA covers [p_lo, n_own)
@@ -211,7 +217,7 @@ decode_attention_kernel(const T* __restrict__ q, const float* __restrict__ qkv, 
 #pragma unroll
   for (int i = 0; i < ATT_EPL; ++i) { qv[i] = 0.0f; acc[i] = 0.0f; }
   if (live) {
-    if (FUSED) rope8<T>(qkv + ((int64_t)b * (Hq + 2 * Hkv) + h) * D, d0, D, n_all - 1, rope_base, true, qv);
+    if (FUSED) rope8<T>(qkv + ((int64_t)b * (Hq + 2 * Hkv) + h) * D, d0, D, s_cos, s_sin, true, qv);
     else load8<T>(q + ((int64_t)b * Hq + h) * D + d0, qv);
 #pragma unroll
     for (int i = 0; i < ATT_EPL; ++i) qv[i] *= scale;
@@ -275,8 +281,8 @@ decode_attention_kernel(const T* __restrict__ q, const float* __restrict__ qkv, 
     float kn[ATT_EPL], vn[ATT_EPL];
     float dsum = 0.0f;
     if (live) {
-      rope8<T>(qkv + ((int64_t)b * (Hq + 2 * Hkv) + Hq + kv) * D, d0, D, pos, rope_base, true, kn);
-      rope8<T>(qkv + ((int64_t)b * (Hq + 2 * Hkv) + Hq + Hkv + kv) * D, d0, D, pos, rope_base, false, vn);
+      rope8<T>(qkv + ((int64_t)b * (Hq + 2 * Hkv) + Hq + kv) * D, d0, D, s_cos, s_sin, true, kn);
+      rope8<T>(qkv + ((int64_t)b * (Hq + 2 * Hkv) + Hq + Hkv + kv) * D, d0, D, s_cos, s_sin, false, vn);
 #pragma unroll
       for (int i = 0; i < ATT_EPL; ++i) dsum += qv[i] * kn[i];
       if (h % (Hq / Hkv) == 0) {                      // first query head of the group appends to the cache
