@@ -30,7 +30,6 @@ constexpr int COMM_WAIT_MS_DEFAULT = 5000;
 constexpr int COMM_HEADER_BYTES = 256;
 constexpr uint32_t COMM_MAGIC = 0xB200C033u;
 constexpr int AR_THREADS = 256;
-constexpr int AR_CACHE = 16;                        // row elements a thread keeps in registers (rows <= 4096)
 
 struct Comm {
   uint32_t magic;
@@ -169,9 +168,11 @@ __global__ void __launch_bounds__(AR_THREADS) allreduce_sum_kernel(const CommDev
   comm_finish(d, e);
 }
 
-// One CTA per row of H elements: delta = sum over ranks of the deposited rows; x <- T(x + delta) (the residual
-// stream, stored in T); normed = T(x * rsqrt(mean(x^2) + eps) * gamma).  Same arithmetic and rounding as the
-// single-GPU add + RMSNorm kernel.  `in` as above.
+// One CTA per row of H elements (H a multiple of 8, at most AR_VCHUNKS * AR_THREADS * 8): delta = sum over ranks of
+// the deposited rows; x <- T(x + delta) (the residual stream, stored in T); normed = T(x * rsqrt(mean(x^2) + eps) *
+// gamma).  Element ownership (chunks of 8 consecutive elements per thread), arithmetic, rounding and the order of
+// the sum of squares are those of add_rmsnorm_vec_kernel (glue.cu), so the two agree bit for bit.  `in` as above.
+constexpr int AR_VCHUNKS = 2;
 template <typename T>
 __global__ void __launch_bounds__(AR_THREADS) allreduce_add_rmsnorm_kernel(const CommDev* __restrict__ d,
                                                                            const float* __restrict__ in, T* __restrict__ x,
@@ -193,29 +194,26 @@ __global__ void __launch_bounds__(AR_THREADS) allreduce_add_rmsnorm_kernel(const
   }
   T* xr = x + row0;
   T* orow = normed + row0;
-  float cache[AR_CACHE];
+  float v[AR_VCHUNKS][8], g[AR_VCHUNKS][8];
   float ss = 0.0f;
   uint64_t deadline = 0;
 #pragma unroll
-  for (int j0 = 0; j0 < AR_CACHE; j0 += 4) {
-    int64_t idx[4];
-    float s[4], xv[4];
+  for (int c = 0; c < AR_VCHUNKS; ++c) {
+    const int64_t i0 = ((int64_t)threadIdx.x + c * AR_THREADS) * 8;
+    if (i0 < H) {
+      int64_t idx[8];
+      float s[8];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int64_t i = threadIdx.x + (int64_t)(j0 + j) * AR_THREADS;
-      idx[j] = i < H ? row0 + i : -1;
-      xv[j] = i < H ? to_float<T>(xr[i]) : 0.0f;
-    }
-    comm_collect<4>(d, par, idx, s, &deadline, status);
+      for (int i = 0; i < 8; ++i) idx[i] = row0 + i0 + i;
+      load8<T>(xr + i0, v[c]);
+      load8<float>(gamma + i0, g[c]);
+      comm_collect<8>(d, par, idx, s, &deadline, status);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float v = 0.0f;
-      if (idx[j] >= 0) {
-        v = to_float<T>(from_float<T>(xv[j] + s[j]));
-        xr[idx[j] - row0] = from_float<T>(v);
+      for (int i = 0; i < 8; ++i) {
+        v[c][i] = to_float<T>(from_float<T>(v[c][i] + s[i]));
+        ss += v[c][i] * v[c][i];
       }
-      cache[j0 + j] = v;
-      ss += v * v;
+      store8<T>(xr + i0, v[c]);
     }
   }
   __shared__ float red[AR_THREADS / 32];
@@ -228,9 +226,14 @@ __global__ void __launch_bounds__(AR_THREADS) allreduce_add_rmsnorm_kernel(const
   for (int i = 0; i < AR_THREADS / 32; ++i) tot += red[i];
   const float inv = rsqrtf(tot / (float)H + eps);
 #pragma unroll
-  for (int j = 0; j < AR_CACHE; ++j) {
-    const int64_t i = threadIdx.x + (int64_t)j * AR_THREADS;
-    if (i < H) orow[i] = from_float<T>(cache[j] * inv * gamma[i]);
+  for (int c = 0; c < AR_VCHUNKS; ++c) {
+    const int64_t i0 = ((int64_t)threadIdx.x + c * AR_THREADS) * 8;
+    if (i0 < H) {
+      float o[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = v[c][i] * inv * g[c][i];
+      store8<T>(orow + i0, o);
+    }
   }
   comm_finish(d, e);
 }
@@ -405,7 +408,9 @@ int bq_allreduce_add_rmsnorm(bq_comm_t comm, const float* in, void* x, const flo
   if (!c->connected) return fail(BQ_ERR_STATE, "communicator is not connected");
   if (dtype != BQ_DT_F32 && dtype != BQ_DT_BF16) return fail(BQ_ERR_ARG, "dtype must be BQ_DT_F32 or BQ_DT_BF16");
   if (rows < 0 || H <= 0) return fail(BQ_ERR_ARG, "bad sizes");
-  if (H > (int64_t)AR_THREADS * AR_CACHE) return fail(BQ_ERR_UNSUPPORTED, "rows longer than 4096 elements");
+  if (H > (int64_t)AR_VCHUNKS * AR_THREADS * 8 || H % 8 != 0 ||
+      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(gamma) | reinterpret_cast<uintptr_t>(normed)) & 15) != 0)
+    return fail(BQ_ERR_UNSUPPORTED, "rows must be a multiple of 8 and at most 4096 elements, pointers 16-byte aligned");
   if (rows * H > c->slot_elems) return fail(BQ_ERR_ARG, "rows * H exceeds the communicator's max_elems");
   if (rows == 0) return BQ_OK;
   if (!x || !gamma || !normed) return fail(BQ_ERR_ARG, "null pointer");

@@ -61,6 +61,60 @@ __global__ void __launch_bounds__(RN_THREADS) add_rmsnorm_kernel(T* __restrict__
     orow[i] = from_float<T>(to_float<T>(xr[i]) * inv * w[i]);
 }
 
+// Same operation for rows of up to RN_VEC_MAX elements whose length is a multiple of 8 and whose pointers are
+// 16-byte aligned (every decoder shape): a thread owns chunks of 8 consecutive elements, so x, delta and the norm
+// weights arrive as a few 16-byte loads issued together before the reduction.  The per-thread order of the
+// sum of squares (chunk by chunk, element by element) is shared with allreduce_add_rmsnorm_kernel (comm.cu).
+constexpr int RN_VCHUNKS = 2;
+constexpr int RN_VEC_MAX = RN_VCHUNKS * RN_THREADS * 8;
+template <typename T>
+__global__ void __launch_bounds__(RN_THREADS) add_rmsnorm_vec_kernel(T* __restrict__ x, const float* __restrict__ delta,
+                                                                     const float* __restrict__ w, T* __restrict__ out,
+                                                                     int64_t H, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  T* xr = x + (int64_t)blockIdx.x * H;
+  const float* dr = delta ? delta + (int64_t)blockIdx.x * H : nullptr;
+  T* orow = out + (int64_t)blockIdx.x * H;
+  float v[RN_VCHUNKS][8], g[RN_VCHUNKS][8];
+  float ss = 0.0f;
+#pragma unroll
+  for (int c = 0; c < RN_VCHUNKS; ++c) {
+    const int64_t i0 = ((int64_t)threadIdx.x + c * RN_THREADS) * 8;
+    if (i0 < H) {
+      float d[8];
+      load8<T>(xr + i0, v[c]);
+      load8<float>(w + i0, g[c]);
+      if (dr) load8<float>(dr + i0, d);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (dr) v[c][i] = to_float<T>(from_float<T>(v[c][i] + d[i]));   // the residual stream is stored in T
+        ss += v[c][i] * v[c][i];
+      }
+      if (dr) store8<T>(xr + i0, v[c]);
+    }
+  }
+  __shared__ float red[RN_THREADS / 32];
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.0f;
+#pragma unroll
+  for (int i = 0; i < RN_THREADS / 32; ++i) tot += red[i];
+  const float inv = rsqrtf(tot / (float)H + eps);
+#pragma unroll
+  for (int c = 0; c < RN_VCHUNKS; ++c) {
+    const int64_t i0 = ((int64_t)threadIdx.x + c * RN_THREADS) * 8;
+    if (i0 < H) {
+      float o[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = v[c][i] * inv * g[c][i];
+      store8<T>(orow + i0, o);
+    }
+  }
+}
+
 // qkv: fp32 [B, (Hq + 2*Hkv) * D] (output of the fused q|k|v projection).  Writes q (rotated) as T [B, Hq, D],
 // and k (rotated), v into the caches [B, S, Hkv, D] at position *pos.  One block per (b, head).
 template <typename T>
@@ -103,20 +157,6 @@ constexpr int ATT_WARPS = 8;
 constexpr int ATT_MAXD = 256;
 constexpr int ATT_EPL = 8;
 constexpr int ATT_PB = 4;
-template <typename T> __device__ __forceinline__ void load8(const T* p, float* f);
-template <> __device__ __forceinline__ void load8<float>(const float* p, float* f) {
-  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
-  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
-}
-template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float* f) {
-  const uint4 r = *reinterpret_cast<const uint4*>(p);
-  const uint32_t wds[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    f[2 * i] = __uint_as_float(wds[i] << 16);
-    f[2 * i + 1] = __uint_as_float(wds[i] & 0xFFFF0000u);
-  }
-}
 // a row's 8 elements as loaded (converted to fp32 only where they are used, so that the K and V rows of a whole
 // trip can be in flight together without a register per element)
 template <typename T> struct RawRow;
@@ -163,22 +203,6 @@ __device__ __forceinline__ void rope8(const float* __restrict__ src, int d0, int
     }
   }
 }
-template <typename T> __device__ __forceinline__ void store8(T* p, const float* f);
-template <> __device__ __forceinline__ void store8<float>(float* p, const float* f) {
-  *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
-  *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
-}
-template <> __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const float* f) {
-  uint4 r;
-  uint32_t* w = &r.x;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const __nv_bfloat162 v = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
-    w[i] = *reinterpret_cast<const uint32_t*>(&v);
-  }
-  *reinterpret_cast<uint4*>(p) = r;
-}
-
 // FUSED: `q` is unused; the query, and the K / V rows of the current position, come straight from `qkv` (fp32
 // [B, (Hq + 2 Hkv) D], the fused projection's output), rotated here; the cache supplies positions < pos only and
 // the CTA of the first query head of each KV group appends the new rows to it.  One launch instead of
@@ -455,11 +479,15 @@ int bq_add_rmsnorm(void* x, const float* delta, const float* weight, void* out, 
   if (rows == 0) return BQ_OK;
   if (!x || !weight || !out) return fail(BQ_ERR_ARG, "null pointer");
   cudaStream_t s = (cudaStream_t)stream;
+  const uintptr_t align = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(delta) | reinterpret_cast<uintptr_t>(weight) |
+                          reinterpret_cast<uintptr_t>(out);
+  const bool vec = H % 8 == 0 && H <= RN_VEC_MAX && (align & 15) == 0;
   if (dtype == BQ_DT_F32)
-    BQ_CUDA(launch_chain(add_rmsnorm_kernel<float>, dim3((unsigned)rows), dim3(RN_THREADS), 0, s, 1, (float*)x, delta, weight, (float*)out, H, eps));
+    BQ_CUDA(launch_chain(vec ? add_rmsnorm_vec_kernel<float> : add_rmsnorm_kernel<float>, dim3((unsigned)rows), dim3(RN_THREADS), 0, s,
+                         1, (float*)x, delta, weight, (float*)out, H, eps));
   else
-    BQ_CUDA(launch_chain(add_rmsnorm_kernel<__nv_bfloat16>, dim3((unsigned)rows), dim3(RN_THREADS), 0, s, 1, (__nv_bfloat16*)x, delta, weight,
-                         (__nv_bfloat16*)out, H, eps));
+    BQ_CUDA(launch_chain(vec ? add_rmsnorm_vec_kernel<__nv_bfloat16> : add_rmsnorm_kernel<__nv_bfloat16>, dim3((unsigned)rows),
+                         dim3(RN_THREADS), 0, s, 1, (__nv_bfloat16*)x, delta, weight, (__nv_bfloat16*)out, H, eps));
   count_launch();
   BQ_CUDA(cudaGetLastError());
   return BQ_OK;

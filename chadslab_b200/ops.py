@@ -355,9 +355,15 @@ class PeerComm:
         """x[rows, H] += sum over ranks (of `inp`, or of the deposited partial sums when inp is None);
         normed = rmsnorm(x) * weight.  In place on x and normed."""
         rows, H = x.shape
-        _lib.check(_lib.lib().bq_allreduce_add_rmsnorm(self.handle, inp.data_ptr() if inp is not None else None,
-                                                       x.data_ptr(), weight.data_ptr(), normed.data_ptr(), rows, H,
-                                                       float(eps), _dt_of_torch(x), _stream_ptr()))
+        lib = _lib.lib()
+        rc = lib.bq_allreduce_add_rmsnorm(self.handle, inp.data_ptr() if inp is not None else None, x.data_ptr(),
+                                          weight.data_ptr(), normed.data_ptr(), rows, H, float(eps), _dt_of_torch(x),
+                                          _stream_ptr())
+        if rc == _lib.ERR_UNSUPPORTED:         # long or unaligned rows: the sum, then the single-GPU kernel
+            delta = self.all_reduce(inp, count=rows * H)
+            rc = lib.bq_add_rmsnorm(x.data_ptr(), delta.data_ptr(), weight.data_ptr(), normed.data_ptr(), rows, H,
+                                    float(eps), _dt_of_torch(x), _stream_ptr())
+        _lib.check(rc)
 
 
 class LMHead(QuantLinear):

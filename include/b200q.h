@@ -233,7 +233,8 @@ int bq_qlinear_push(bq_weight_t w, const void* x, int x_dtype, int64_t M, bq_com
  * bq_qlinear_push deposited (count = M * N).                                              */
 int bq_allreduce(bq_comm_t c, const float* in, float* out, int64_t count, void* stream);
 /* bq_add_rmsnorm with delta = the sum over ranks: x += sum; normed = rmsnorm(x) * weight.
- * H <= 4096 (else BQ_ERR_UNSUPPORTED).  in as for bq_allreduce.                           */
+ * H <= 4096 and a multiple of 8, 16-byte aligned pointers (else BQ_ERR_UNSUPPORTED: use
+ * bq_allreduce + bq_add_rmsnorm).  in as for bq_allreduce.                                */
 int bq_allreduce_add_rmsnorm(bq_comm_t c, const float* in, void* x, const float* weight,
                              void* normed, int64_t rows, int64_t H, float eps, int dtype,
                              void* stream);
