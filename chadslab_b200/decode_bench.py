@@ -33,6 +33,7 @@ def run(torch, dist, rank: int, world: int, shape: str = "gemma7b", batches=(1, 
         max_b = max(batches)
         if world > 1:
             comm = cb.PeerComm(max_elems=max(max_b * cfg.hidden, 4096), group=dist.group.WORLD)
+            _lib.check(_lib.lib().bq_comm_set_timeout_ms(comm.handle, 1000))   # a benchmark should fail fast
         dec = QuantDecoder.random(cfg, seed=0, act_dtype=torch.bfloat16, rank=rank, world=world, max_seq=ctx + 64,
                                   max_batch=max_b, comm=comm)
         for kc, vc in zip(dec.k_cache, dec.v_cache):
@@ -53,7 +54,12 @@ def run(torch, dist, rank: int, world: int, shape: str = "gemma7b", batches=(1, 
                     pos_t.fill_(ctx)                     # stay at the same position: the cache has 64 spare slots
             else:
                 step, tokens = dec.make_graph_stepper(B, first, start_pos=ctx)
-            for _ in range(3):
+            step()
+            torch.cuda.synchronize()
+            st = int(_lib.lib().bq_status_poll())
+            if st != 0:                      # e.g. a peer that never delivered: do not time the remaining steps
+                raise RuntimeError(f"device status {st} after the first step at batch {B}")
+            for _ in range(2):
                 step()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
