@@ -113,6 +113,21 @@ def _tp_case(rank):
         ref_logits, ref_ids = spec.lm_head(xq, *qv, fmt)
         assert ids[0] == 100 and np.array_equal(ids, ref_ids)
         assert np.allclose(_np(head.logits(torch.from_numpy(xq))), ref_logits, atol=1e-5)
+        # same exchange written as a sum of one-hot rows (the route the peer-memory communicator takes on GPUs);
+        # the stand-in communicator sums through the process group
+        class SumComm:
+            world, rank_ = WORLD, rank
+
+            def __init__(self):
+                self.rank = rank
+
+            def all_reduce(self, t):
+                t = t.clone()
+                torch.distributed.all_reduce(t)
+                return t
+        head2 = parallel.VocabParallelHead(_oracle_linear(*spec.shard(*qv, fmt, "n", rank, WORLD), fmt), V // WORLD,
+                                           comm=SumComm())
+        assert np.array_equal(head2.greedy(torch.from_numpy(xq)).numpy(), ref_ids)
 
 
 def _ep_case(rank):
