@@ -515,6 +515,11 @@ struct T2Args {
   const int32_t* offsets;
   const int32_t* tiles;
   int moe;
+  // dense split-K (few output tiles, long K): blockIdx.z takes `kper` 128-k steps from kper * blockIdx.z and leaves
+  // its fp32 partial tile in part[blockIdx.z][M][N]; splitk_reduce_kernel adds the slices in order.  kper is even
+  // (a scale tile covers two steps).  0 = no split.
+  int kper;
+  float* part;
 };
 
 __device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
@@ -569,7 +574,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tmem_kernel(const __grid_
     const CUtensorMap* l = args.tm_list + (int64_t)e * 4;
     tmw[0] = l; tms[0] = l + 1; tmw[1] = GATED ? l + 2 : l; tms[1] = GATED ? l + 3 : l + 1;
   }
-  const int ksteps = (int)(args.K / T2_BK);
+  const int ksteps_all = (int)(args.K / T2_BK);
+  const int k0 = args.kper ? (int)blockIdx.z * args.kper : 0;                 // first 128-k step of this CTA
+  const int ksteps = args.kper ? (ksteps_all - k0 < args.kper ? ksteps_all - k0 : args.kper) : ksteps_all;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S; ++i) { mbar_init(smem_u32(&full[i]), 1); mbar_init(smem_u32(&empty[i]), TC_CONV_WARPS + 1); }
@@ -600,14 +607,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tmem_kernel(const __grid_
         const uint32_t fb = smem_u32(&full[s]);
         mbar_expect_tx(fb, NW * P::RAW + P::XT + (with_scales ? NW * P::SCT : 0));
         uint8_t* st = stages + s * P::STAGE;
-        tma_load_2d(smem_u32(st), &args.tm_x, ks * T2_BK, (int)m0, fb);
-        tma_load_2d(smem_u32(st + BN * 128), &args.tm_x, ks * T2_BK + 64, (int)m0, fb);
+        const int kg = k0 + ks;                       // step index in the whole K (k0 is even)
+        tma_load_2d(smem_u32(st), &args.tm_x, kg * T2_BK, (int)m0, fb);
+        tma_load_2d(smem_u32(st + BN * 128), &args.tm_x, kg * T2_BK + 64, (int)m0, fb);
 #pragma unroll
         for (int w = 0; w < NW; ++w) {
           const int nrow = (int)n0 + (DUAL ? w * TC_ROWS : 0);
-          tma_load_2d(smem_u32(st + P::XT + w * P::RAW), tmw[w], ks * P::RAW_ROW, nrow, fb);
+          tma_load_2d(smem_u32(st + P::XT + w * P::RAW), tmw[w], kg * P::RAW_ROW, nrow, fb);
           if (with_scales)
-            tma_load_2d(smem_u32(sc_tiles + (((ks >> 1) % TC_SC_SLOTS) * NW + w) * P::SCT), tms[w], (ks >> 1) * 8, nrow, fb);
+            tma_load_2d(smem_u32(sc_tiles + (((ks >> 1) % TC_SC_SLOTS) * NW + w) * P::SCT), tms[w], (kg >> 1) * 8, nrow, fb);
         }
       }
       if (*abort_flag) {
@@ -741,7 +749,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tmem_kernel(const __grid_
               const int64_t m = m0 + c0 + j;
               if (m < m_end) {
                 const float f = __uint_as_float(v[j]) * args.xscale[m];
-                if (args.out_dtype == BQ_DT_F32) reinterpret_cast<float*>(args.out)[m * args.ldy + nn] = f;
+                if (args.kper) args.part[((int64_t)blockIdx.z * args.M + m) * args.N + nn] = f;
+                else if (args.out_dtype == BQ_DT_F32) reinterpret_cast<float*>(args.out)[m * args.ldy + nn] = f;
                 else reinterpret_cast<__nv_bfloat16*>(args.out)[m * args.ldy + nn] = __float2bfloat16_rn(f);
               }
             }
@@ -784,6 +793,20 @@ __global__ void __launch_bounds__(256) x_prep_kernel(const XT* __restrict__ x, i
   for (int64_t k = threadIdx.x; k < K; k += blockDim.x) orow[k] = __float2half_rn(to_float<XT>(row[k]) * down);
   if (threadIdx.x == 0) scale_back[blockIdx.x] = __uint_as_float((uint32_t)(127 + e) << 23);
 }
+
+// out[m, n] = sum over z of part[z][m][n], slices added in order (deterministic), stored in the output type
+template <typename YT>
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ part, int nz, int64_t M, int64_t N,
+                                                            YT* __restrict__ out, int64_t ldy) {
+  const int64_t total = M * N;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    float s = part[i];
+    for (int z = 1; z < nz; ++z) s += part[(int64_t)z * total + i];
+    const int64_t m = i / N, n = i - m * N;
+    out[m * ldy + n] = from_float<YT>(s);
+  }
+}
+static float* g_part = nullptr; static size_t g_part_elems = 0;      // split-K partial tiles (grow-only)
 
 // library-owned scratch for the pre-scaled activations (grow-only; calls are serialised per process)
 static __half* g_x16 = nullptr; static size_t g_x16_elems = 0;
@@ -999,7 +1022,40 @@ int launch_qlinear_tc(const uint8_t* codes, const __half* scales, int fmt, int64
     const int rows_cta = two ? 2 * TC_ROWS : TC_ROWS;
     dim3 grid2((unsigned)((M + bx - 1) / bx), (unsigned)((N + rows_cta - 1) / rows_cta));
     const int sel = two ? 512 : bn;
-    return fmt == BQ_FMT_Q8G32 ? t2_dispatch<BQ_FMT_Q8G32>(t, sel, grid2, s) : t2_dispatch<BQ_FMT_Q4G32>(t, sel, grid2, s);
+    // Few output tiles and a long K (e.g. 2048 x 16384, or a down projection at decode batch sizes): split K over
+    // grid.z so that about two CTAs per SM stream weights, each with at least 4 steps; partial tiles are summed in order.
+    const int64_t ctas = (int64_t)grid2.x * grid2.y, ksteps_all = K / T2_BK;
+    int nz = 1;
+    if (!two && ctas * 2 <= sm_count() && ksteps_all >= 8) {
+      int64_t want = (2 * (int64_t)sm_count() + ctas - 1) / ctas;
+      if (want > ksteps_all / 4) want = ksteps_all / 4;
+      while (want > 1 && (size_t)want * M * N > ((size_t)64 << 20) / sizeof(float)) --want;     // partials <= 64 MB
+      if (want > 1) {
+        int64_t kper = ((ksteps_all + want - 1) / want + 1) & ~(int64_t)1;
+        nz = (int)((ksteps_all + kper - 1) / kper);
+        if (nz > 1) {
+          const size_t need = (size_t)nz * M * N;
+          if (need > g_part_elems) {        // first call of this size: before any graph capture
+            if (g_part) BQ_CUDA(cudaFree(g_part));
+            g_part = nullptr; g_part_elems = 0;
+            BQ_CUDA(cudaMalloc((void**)&g_part, (need + need / 4) * sizeof(float)));
+            g_part_elems = need + need / 4;
+          }
+          t.kper = (int)kper; t.part = g_part; grid2.z = (unsigned)nz;
+        }
+      }
+    }
+    rc = fmt == BQ_FMT_Q8G32 ? t2_dispatch<BQ_FMT_Q8G32>(t, sel, grid2, s) : t2_dispatch<BQ_FMT_Q4G32>(t, sel, grid2, s);
+    if (rc || nz <= 1) return rc;
+    int64_t rg = (M * N + 255) / 256;
+    if (rg > (int64_t)sm_count() * 8) rg = (int64_t)sm_count() * 8;
+    if (y_dtype == BQ_DT_F32)
+      splitk_reduce_kernel<float><<<(unsigned)rg, 256, 0, s>>>(g_part, nz, M, N, (float*)y, ldy);
+    else
+      splitk_reduce_kernel<__nv_bfloat16><<<(unsigned)rg, 256, 0, s>>>(g_part, nz, M, N, (__nv_bfloat16*)y, ldy);
+    count_launch();
+    BQ_CUDA(cudaGetLastError());
+    return BQ_OK;
   }
   if ((rc = x_map(&a.tm_x, g_x16, M, K, bn))) return rc;
   a.xscale = g_xs;

@@ -249,3 +249,27 @@ def test_device_quantizer_is_bit_identical_to_the_oracle(cuda_lib, fmt, wdt):
     x = torch.randn((1, K), device="cuda").to(torch.bfloat16)
     host = cb.PackedWeight.from_arrays(rc, rs, fmt)
     assert torch.equal(cb.QuantLinear(pw)(x), cb.QuantLinear(host)(x))
+
+
+@pytest.mark.parametrize("fmt", [0, 1])
+@pytest.mark.parametrize("odt", ["float32", "bfloat16"])
+def test_tensor_path_split_k_for_few_output_tiles(cuda_lib, fmt, odt):
+    """Few 128-row output tiles and a long K: the tensor-core kernel splits K over the grid and a second kernel adds
+    the partial tiles in order.  Same tolerance as every other matmul; repeated calls give identical bits."""
+    import torch
+    import chadslab_b200 as cb
+    rng = np.random.default_rng(77 + fmt)
+    for N, K in ((200, 8192), (512, 16384), (130, 1024)):
+        codes, scales = spec.quantize(rng.normal(0, 0.02, (N, K)).astype(np.float32), fmt)
+        pw = cb.PackedWeight.from_arrays(codes, scales, fmt)
+        lin = cb.QuantLinear(pw, out_dtype=getattr(torch, odt), path=cb.PATH_TENSOR)
+        for M in (8, 64, 300):
+            x = spec.bf16_round(rng.normal(0, 1, (M, K)).astype(np.float32))
+            xt = torch.from_numpy(x).cuda().to(torch.bfloat16)
+            y1 = lin(xt)
+            y2 = lin(xt)
+            assert torch.equal(y1, y2)
+            ref = spec.qlinear(x, codes, scales, fmt, f64=True)
+            tol = TOL if odt == "float32" else TOL + 2.0 ** -8
+            assert spec.rel_err(y1.float().cpu().numpy(), ref) <= tol, (N, K, M)
+    assert cuda_lib.bq_status_poll() == 0
