@@ -10,7 +10,7 @@ all 8 (shape, format) problems.  Metric: quantized GEMV HBM GB/s = algorithmic b
 fp16 scales + activations + fp32 outputs) / device time.  Small shapes rotate over enough distinct
 weight copies that the bytes touched between two uses of a copy exceed the 126 MB L2.
 
-Lines printed: one JSON object on rank 0 (see README / DESIGN.md for the keys).
+Lines printed: one JSON object on rank 0.
 Multi-GPU (torchrun): every rank runs the same sweep on its own GPU with its own weights (the
 sweep has no cross-GPU dependency: weak scaling, no collective on the data path); value is the
 sum of bytes over ranks / max time over ranks.
