@@ -371,9 +371,15 @@ def run_gpu(args):
     ms_total, e2e_ms = float(t[0]), float(t[1])
 
     tp_decode = None
+    moe_layer = None
     if args.extras:      # configs[2]: Gemma-7B-shaped decoder, 4-bit g32, tensor-parallel over all ranks of the run
         from chadslab_b200 import decode_bench
         tp_decode = decode_bench.run(torch, dist, rank, world, "gemma7b", (1, 16, 64), 2048, 16)
+        try:             # configs[3]: one sparse-MoE layer (128 experts, top-8, q4), expert-parallel over the ranks
+            from chadslab_b200 import moe_bench
+            moe_layer = moe_bench.run(torch, dist, rank, world, tokens=(256, 4096), reps=5)
+        except Exception as e:  # extras never break the headline line
+            moe_layer = {"error": repr(e)[:300]}
     if rank == 0:
         peak, peak_src = load_peaks()
         value = world * step_bytes * args.steps / (ms_total * 1e-3) / 1e9
@@ -420,6 +426,8 @@ def run_gpu(args):
             line["extras"] = extras
         if tp_decode:
             line.setdefault("extras", {})["tp_decode"] = tp_decode
+        if moe_layer:
+            line.setdefault("extras", {})["moe_layer"] = moe_layer
         print(json.dumps(line))
     if world > 1:
         dist.barrier()
