@@ -1141,6 +1141,7 @@ template <int FMT, int MODE>
 static int t2_moe_dispatch(const T2Args& a, int bn, dim3 grid, cudaStream_t s) {
   switch (bn) {
     case 16:  return t2_launch<FMT, 16, MODE>(a, grid, s);
+    case 32:  return t2_launch<FMT, 32, MODE>(a, grid, s);
     case 64:  return t2_launch<FMT, 64, MODE>(a, grid, s);
     default:  return t2_launch<FMT, 128, MODE>(a, grid, s);
   }
@@ -1163,9 +1164,10 @@ int launch_moe_experts_tc(const Moe* m, const void* xp, const int32_t* offsets, 
     return fail(BQ_ERR_ARG, "activation buffers must be 16-byte aligned");
   // rows per expert ~ P / E: pick the batch tile for the average segment.  A tcgen05.mma costs the same to issue
   // for 16 or 64 columns, so the 16-row tile is kept for segments that are mostly below 16 rows (at an average of
-  // 16 half the experts would need a second tile that streams the same weights again).
+  // 16 half the experts would need a second tile that streams the same weights again); up to an average of 20 rows a
+  // 32-row tile covers nearly every expert in one piece and stages half the activation bytes of the 64-row one.
   const int64_t avg = (P + m->E - 1) / m->E;
-  const int bn = avg <= 8 ? 16 : avg <= 64 ? 64 : 128;
+  const int bn = avg <= 8 ? 16 : (avg <= 20 && tmem_variant_enabled()) ? 32 : avg <= 64 ? 64 : 128;
   const int64_t max_tiles = (P + bn - 1) / bn + m->E;
   if (max_tiles > st->tiles_cap) {
     if (st->tiles) BQ_CUDA(cudaFree(st->tiles));

@@ -145,7 +145,7 @@ def test_moe_layer_random(cuda_lib, fmt, T):
 
 
 @pytest.mark.parametrize("fmt", [0, 1])
-@pytest.mark.parametrize("T", [64, 400, 4096])
+@pytest.mark.parametrize("T", [64, 128, 400, 4096])
 def test_grouped_experts_at_scale_against_simt_path(cuda_lib, fmt, T):
     """64 experts, hidden 2048, ffn 768 (six 128-row tiles), top-8: hundreds of tiles are resident at once and the
     three token-tile sizes (16 / 64 / 128 rows per expert on average) are all taken.  The tensor-core grouped kernel
