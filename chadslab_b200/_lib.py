@@ -9,7 +9,7 @@ import os
 import threading
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.environ.get("B200Q_LIB") or os.path.join(HERE, "libb200q.so")   # B200Q_LIB: load another build (A/B tuning)
+LIB_PATH = os.path.join(HERE, "libb200q.so")
 
 FMT_Q8, FMT_Q4 = 0, 1
 DT_F32, DT_BF16 = 0, 1
@@ -35,9 +35,11 @@ PROTOTYPES = {
     "bq_last_error": (C.c_char_p, []),
     "bq_version": (_i32, []),
     "bq_status_poll": (_i32, []),
+    "bq_reserve": (_i32, [_i64, _i64, _i64]),
     "bq_weight_create": (_i32, [_vp, _vp, _i64, _i64, _i32, C.POINTER(_h)]),
     "bq_weight_create_device": (_i32, [_vp, _vp, _i64, _i64, _i32, _vp, C.POINTER(_h)]),
     "bq_weight_destroy": (_i32, [_h]),
+    "bq_weight_slice_rows": (_i32, [_h, _i64, _i64, C.POINTER(_h)]),
     "bq_weight_info": (_i32, [_h, C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_i32)]),
     "bq_weight_export": (_i32, [_h, _vp, _vp]),
     "bq_quantize": (_i32, [_vp, _i32, _i64, _i64, _i32, _vp, _vp, _vp]),
@@ -64,6 +66,7 @@ PROTOTYPES = {
     "bq_moe_create": (_i32, [C.POINTER(_h), C.POINTER(_h), C.POINTER(_h), _i32, C.POINTER(_h)]),
     "bq_moe_destroy": (_i32, [_h]),
     "bq_moe_experts": (_i32, [_h, _vp, _vp, _i64, _vp, _vp, _i32, _vp]),
+    "bq_moe_experts_ex": (_i32, [_h, _vp, _vp, _i64, _i64, _vp, _vp, _i32, _vp]),
     "bq_moe_combine": (_i32, [_vp, _vp, _vp, _i64, _i32, _i64, _vp, _i32, _vp]),
     "bq_comm_create": (_i32, [_i32, _i32, _i64, C.POINTER(_h)]),
     "bq_comm_handle": (_i32, [_h, _vp]),
@@ -71,6 +74,17 @@ PROTOTYPES = {
     "bq_comm_connect_loopback": (_i32, [_h]),
     "bq_comm_set_timeout_ms": (_i32, [_h, _i32]),
     "bq_comm_destroy": (_i32, [_h]),
+    "bq_comm_reset": (_i32, [_h]),
+    "bq_lm_head_sharded": (_i32, [_h, _vp, _i32, _i64, _i64, _h, _vp, _vp, _vp]),
+    "bq_ep_create": (_i32, [_i32, _i32, _i32, _i64, _i64, _i64, C.POINTER(_h)]),
+    "bq_ep_handle": (_i32, [_h, _vp]),
+    "bq_ep_connect": (_i32, [_h, _vp]),
+    "bq_ep_set_timeout_ms": (_i32, [_h, _i32]),
+    "bq_ep_destroy": (_i32, [_h]),
+    "bq_ep_dispatch": (_i32, [_h, _vp, _vp, _vp, _vp, _i64, _i32, _vp]),
+    "bq_ep_layout_selftest": (_i32, [_vp, _i32, _i32, _i32, _vp, _vp]),
+    "bq_ep_recv_view": (_i32, [_h, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_i64)]),
+    "bq_ep_combine": (_i32, [_h, _vp, _vp, _vp, _i64, _i32, _vp, _i32, _vp]),
     "bq_qlinear_push": (_i32, [_h, _vp, _i32, _i64, _h, _vp]),
     "bq_allreduce": (_i32, [_h, _vp, _vp, _i64, _vp]),
     "bq_allreduce_add_rmsnorm": (_i32, [_h, _vp, _vp, _vp, _vp, _i64, _i64, C.c_float, _i32, _vp]),

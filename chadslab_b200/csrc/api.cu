@@ -17,9 +17,10 @@ static std::unordered_set<void*> g_weights, g_moes;
 static int g_device = -1;
 static int g_sms = 0;
 static int* g_status = nullptr;
-// grow-only device staging for the host-buffer entry point
-static void* g_stage_x = nullptr; static size_t g_stage_x_bytes = 0;
-static void* g_stage_y = nullptr; static size_t g_stage_y_bytes = 0;
+// device staging for the host-buffer entry point and for argmax-only lm_head calls
+static Scratch g_stage_x, g_stage_y;
+static Scratch g_logits;                  // bq_lm_head without a logits buffer (argmax only)
+static std::vector<void*> g_retired;      // scratch buffers that were outgrown: kept, a captured graph may still use them
 
 int fail(int code, const std::string& msg) { t_err = msg; return code; }
 int fail_cuda(cudaError_t e, const char* what) {
@@ -39,6 +40,30 @@ bool pdl_enabled() {
 int device_id() { return g_device; }
 int sm_count() { return g_sms > 0 ? g_sms : SM_COUNT_B200; }
 int* status_word() { return g_status; }
+
+int scratch_ensure(Scratch* sc, size_t need, cudaStream_t stream, const char* what, bool zero_new) {
+  if (need <= sc->bytes) return BQ_OK;
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+    cudaGetLastError();
+    return fail(BQ_ERR_STATE, std::string(what) + ": the library's scratch would have to grow to " + std::to_string(need) +
+                                  " bytes during stream capture; make one call of this size, or bq_reserve(), before capturing");
+  }
+  const size_t cap_bytes = need + need / 4 + 4096;
+  void* p = nullptr;
+  BQ_CUDA(cudaMalloc(&p, cap_bytes));
+  if (zero_new) {
+    cudaError_t e = cudaMemset(p, 0, cap_bytes);
+    if (e != cudaSuccess) { cudaFree(p); return fail_cuda(e, "cudaMemset(scratch)"); }
+  }
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (sc->ptr) g_retired.push_back(sc->ptr);
+  }
+  sc->ptr = p;
+  sc->bytes = cap_bytes;
+  return BQ_OK;
+}
 
 Weight* get_weight(bq_weight_t h) {
   void* p = reinterpret_cast<void*>(static_cast<uintptr_t>(h));
@@ -81,7 +106,7 @@ static int alloc_weight(int64_t N, int64_t K, int fmt, Weight** out) {
   w->fmt = fmt; w->N = N; w->K = K;
   w->codes_bytes = (size_t)(N * (fmt == BQ_FMT_Q8G32 ? K : K / 2));
   w->scales_bytes = (size_t)(N * (K / GROUP)) * sizeof(__half);
-  w->codes = nullptr; w->scales = nullptr;
+  w->codes = nullptr; w->scales = nullptr; w->view = false;
   // +256 bytes of slack so whole-16-byte vector reads past a ragged tail stay in bounds
   cudaError_t e = cudaMalloc((void**)&w->codes, w->codes_bytes + 256);
   if (e == cudaSuccess) e = cudaMalloc((void**)&w->scales, w->scales_bytes + 256);
@@ -103,15 +128,6 @@ static bq_weight_t publish(Weight* w) {
   return static_cast<bq_weight_t>(reinterpret_cast<uintptr_t>(w));
 }
 
-static int ensure_stage(void** buf, size_t* have, size_t need) {
-  if (need <= *have) return BQ_OK;
-  if (*buf) BQ_CUDA(cudaFree(*buf));
-  *buf = nullptr; *have = 0;
-  size_t cap = need + need / 4 + 4096;
-  BQ_CUDA(cudaMalloc(buf, cap));
-  *have = cap;
-  return BQ_OK;
-}
 
 static size_t dt_size(int dt) { return dt == BQ_DT_F32 ? 4 : 2; }
 static bool dt_ok(int dt) { return dt == BQ_DT_F32 || dt == BQ_DT_BF16; }
@@ -146,13 +162,24 @@ static int qlinear_impl(Weight* w, const void* x, int x_dtype, int64_t M, void* 
   return launch_qlinear_simt(w->codes, w->scales, w->fmt, w->N, w->K, x, x_dtype, M, y, y_dtype, w->N, s);
 }
 
+int lm_head_local(bq_weight_t h, const void* x, int x_dtype, int64_t M, int32_t* imax, float* vmax, cudaStream_t s) {
+  int rc = check_ready();
+  if (rc) return rc;
+  Weight* w = get_weight(h);
+  if (!w) return BQ_ERR_HANDLE;
+  if (w->N == 0) return fail(BQ_ERR_ARG, "lm_head needs a non-empty vocabulary");
+  if ((rc = scratch_ensure(&g_logits, (size_t)M * w->N * 4, s, "bq_lm_head_sharded"))) return rc;
+  if ((rc = qlinear_impl(w, x, x_dtype, M, g_logits.ptr, BQ_DT_F32, BQ_PATH_AUTO, s))) return rc;
+  return launch_argmax(g_logits.ptr, BQ_DT_F32, M, w->N, imax, s, vmax);
+}
+
 }  // namespace bq
 
 using namespace bq;
 
 extern "C" {
 
-int bq_version(void) { return 100; }
+int bq_version(void) { return 200; }
 
 const char* bq_last_error(void) { return t_err.c_str(); }
 
@@ -184,6 +211,7 @@ int bq_status_poll(void) {
   BQ_CUDA(cudaMemcpy(&v, g_status, sizeof(int), cudaMemcpyDeviceToHost));
   if (v != 0) {
     BQ_CUDA(cudaMemset(g_status, 0, sizeof(int)));
+    if (v == BQ_ERR_TIMEOUT) { comm_mark_all_failed(); ep_mark_all_failed(); }
     return fail(v, "a kernel recorded a device-side anomaly (bounded wait expired)");
   }
   return BQ_OK;
@@ -246,9 +274,27 @@ int bq_weight_destroy(bq_weight_t h) {
     g_weights.erase(w);
   }
   w->magic = 0;
-  cudaFree(w->codes);
-  cudaFree(w->scales);
+  if (!w->view) {
+    cudaFree(w->codes);
+    cudaFree(w->scales);
+  }
   delete w;
+  return BQ_OK;
+}
+
+int bq_weight_slice_rows(bq_weight_t h, int64_t row0, int64_t nrows, bq_weight_t* out) {
+  Weight* p = get_weight(h);
+  if (!p) return BQ_ERR_HANDLE;
+  if (!out) return fail(BQ_ERR_ARG, "out must not be null");
+  if (row0 < 0 || nrows <= 0 || row0 + nrows > p->N) return fail(BQ_ERR_ARG, "row range outside the weight");
+  Weight* w = new Weight();
+  w->magic = WEIGHT_MAGIC;
+  w->fmt = p->fmt; w->N = nrows; w->K = p->K; w->view = true;
+  w->codes = p->codes + row0 * p->row_bytes();
+  w->scales = p->scales + row0 * (p->K / GROUP);
+  w->codes_bytes = (size_t)(nrows * p->row_bytes());
+  w->scales_bytes = (size_t)(nrows * (p->K / GROUP)) * sizeof(__half);
+  *out = publish(w);
   return BQ_OK;
 }
 
@@ -326,12 +372,12 @@ int bq_qlinear_host(bq_weight_t h, const void* x_host, int x_dtype, int64_t M, v
   if (M == 0 || w->N == 0) return BQ_OK;
   if (!x_host || !y_host) return fail(BQ_ERR_ARG, "x and y must not be null");
   const size_t xb = (size_t)M * w->K * dt_size(x_dtype), yb = (size_t)M * w->N * dt_size(y_dtype);
-  if ((rc = ensure_stage(&g_stage_x, &g_stage_x_bytes, xb))) return rc;
-  if ((rc = ensure_stage(&g_stage_y, &g_stage_y_bytes, yb))) return rc;
   cudaStream_t s = cudaStreamPerThread;
-  BQ_CUDA(cudaMemcpyAsync(g_stage_x, x_host, xb, cudaMemcpyHostToDevice, s));
-  if ((rc = qlinear_impl(w, g_stage_x, x_dtype, M, g_stage_y, y_dtype, BQ_PATH_AUTO, s))) return rc;
-  BQ_CUDA(cudaMemcpyAsync(y_host, g_stage_y, yb, cudaMemcpyDeviceToHost, s));
+  if ((rc = scratch_ensure(&g_stage_x, xb, s, "bq_qlinear_host"))) return rc;
+  if ((rc = scratch_ensure(&g_stage_y, yb, s, "bq_qlinear_host"))) return rc;
+  BQ_CUDA(cudaMemcpyAsync(g_stage_x.ptr, x_host, xb, cudaMemcpyHostToDevice, s));
+  if ((rc = qlinear_impl(w, g_stage_x.ptr, x_dtype, M, g_stage_y.ptr, y_dtype, BQ_PATH_AUTO, s))) return rc;
+  BQ_CUDA(cudaMemcpyAsync(y_host, g_stage_y.ptr, yb, cudaMemcpyDeviceToHost, s));
   BQ_CUDA(cudaStreamSynchronize(s));
   return BQ_OK;
 }
@@ -351,12 +397,21 @@ int bq_lm_head(bq_weight_t h, const void* x, int x_dtype, int64_t M, void* logit
   int ldt = logits_dtype;
   if (!lg) {  // argmax only: logits live in the library's staging buffer
     ldt = BQ_DT_F32;
-    if ((rc = ensure_stage(&g_stage_y, &g_stage_y_bytes, (size_t)M * w->N * 4))) return rc;
-    lg = g_stage_y;
+    if ((rc = scratch_ensure(&g_logits, (size_t)M * w->N * 4, s, "bq_lm_head"))) return rc;
+    lg = g_logits.ptr;
   }
   if ((rc = qlinear_impl(w, x, x_dtype, M, lg, ldt, BQ_PATH_AUTO, s))) return rc;
   if (argmax_out) return launch_argmax(lg, ldt, M, w->N, argmax_out, s);
   return BQ_OK;
+}
+
+int bq_reserve(int64_t max_rows, int64_t max_K, int64_t max_N) {
+  int rc = check_ready();
+  if (rc) return rc;
+  if (max_rows <= 0 || max_K <= 0 || max_N <= 0) return fail(BQ_ERR_ARG, "sizes must be positive");
+  if ((rc = tc_reserve(max_rows, max_K, max_N))) return rc;
+  if ((rc = glue_reserve(max_rows, max_N))) return rc;
+  return scratch_ensure(&g_logits, (size_t)max_rows * max_N * 4, 0, "bq_reserve");
 }
 
 int bq_last_path(void) { return t_last_path; }

@@ -24,6 +24,7 @@ struct Weight {
   uint8_t* codes;        // Q8: N*K bytes, Q4: N*K/2 bytes
   __half* scales;        // N*K/32 fp16
   size_t codes_bytes, scales_bytes;
+  bool view;             // rows of another weight (bq_weight_slice_rows): the memory is not owned
   int64_t row_bytes() const { return fmt == BQ_FMT_Q8G32 ? K : K / 2; }
 };
 constexpr uint32_t WEIGHT_MAGIC = 0xB200C0DEu;
@@ -46,12 +47,12 @@ constexpr uint32_t MOE_MAGIC = 0xB2003E00u;
 // rank's buffer; a slot element holds COMM_EMPTY (the bit pattern of -0.0f, which no deposit ever carries) until
 // the value arrives, so the data announces itself: no flags, no fences.  The receiver adds the slots in rank order
 // and puts COMM_EMPTY back.  `state[0]` is the call counter (epoch, starts at 1; parity = epoch & 1), `state[1]`
-// counts finished CTAs.
+// counts finished CTAs, `state[2]` != 0 marks a communicator on which a wait timed out.
 constexpr int COMM_MAX_WORLD = 8;
 constexpr uint32_t COMM_EMPTY = 0x80000000u;
 struct CommDev {
   float* data[COMM_MAX_WORLD];        // rank r's receive slots: [2][world][slot_elems] floats
-  uint32_t* state;                    // this rank's {epoch, finished-CTA counter}
+  uint32_t* state;                    // this rank's {epoch, finished-CTA counter, failed}
   int64_t slot_elems;
   uint64_t wait_ns;                   // bound of the wait for a value
   int rank, world;
@@ -67,6 +68,24 @@ Moe* get_moe(bq_moe_t h);
 int device_id();
 int sm_count();
 int* status_word();                    // device int, 0 = fine
+void comm_mark_all_failed();           // comm.cu: a bounded wait expired somewhere; communicators need bq_comm_reset
+void ep_mark_all_failed();             // ep.cu: same for the expert-parallel objects
+// api.cu: logits of this weight into library scratch, then per row the argmax id and the maximum itself
+int lm_head_local(bq_weight_t w, const void* x, int x_dtype, int64_t M, int32_t* imax, float* vmax, cudaStream_t s);
+
+// Library-owned scratch (activation pre-pass output, split-K partial tiles, attention partial states, ...).
+// Grow-only, and a buffer that was ever handed out is never freed while the library is loaded: a CUDA graph
+// captured earlier keeps its address (tensor maps included), so growth allocates a larger buffer and retires the old
+// one instead of freeing it.  Growth is refused (BQ_ERR_STATE) while `stream` is being captured: make one call of
+// the largest size, or bq_reserve(), before capturing.  All calls that use library scratch must be ordered on the
+// device (one stream, or events between streams): the buffers are shared.
+struct Scratch {
+  void* ptr = nullptr;
+  size_t bytes = 0;
+};
+int scratch_ensure(Scratch* s, size_t need, cudaStream_t stream, const char* what, bool zero_new = false);
+int tc_reserve(int64_t rows, int64_t K, int64_t N);      // tc.cu: activation pre-pass output, split-K partial tiles
+int glue_reserve(int64_t rows, int64_t N);               // glue.cu: gate|up product of bq_qlinear_gated
 
 #define BQ_CUDA(call)                                          \
   do {                                                         \
@@ -101,14 +120,15 @@ int launch_qlinear_mma_gated(const uint8_t* codes, const __half* scales, int fmt
 bool moe_tc_supported(const Moe* m);
 int moe_tc_prepare(Moe* m, const std::vector<const uint8_t*>* codes, const std::vector<const __half*>* scales);
 void moe_tc_release(Moe* m);
-int launch_moe_experts_tc(const Moe* m, const void* xp, const int32_t* offsets, int64_t P, void* hbuf, float* out,
-                          cudaStream_t s);
+int launch_moe_experts_tc(const Moe* m, const void* xp, const int32_t* offsets, int64_t P, int64_t rows_hint, void* hbuf,
+                          float* out, cudaStream_t s);
 // Device encoding of the codes (a bijection of the interface bytes, undone by bq_weight_export):
 //   Q4: within every 32-bit word the 8 nibbles are stored in the order e0,e2,e4,e6,e1,e3,e5,e7 (element
 //       e_i of the interface layout), so that masking with 0x000F000F / 0x00F000F0 yields adjacent pairs;
 //   Q8: every byte holds code + 128 (sign bit flipped), so mantissa insertion needs no sign fix-up.
 int launch_device_encode(uint8_t* codes, size_t bytes, int fmt, bool to_device_layout, cudaStream_t s);
-int launch_argmax(const void* logits, int dtype, int64_t M, int64_t N, int32_t* out, cudaStream_t s);
+// out[m] = argmax of row m (ties -> lower index); vout (optional): the maximum itself
+int launch_argmax(const void* logits, int dtype, int64_t M, int64_t N, int32_t* out, cudaStream_t s, float* vout = nullptr);
 bool pdl_enabled();     // BQ_PDL environment switch (default on)
 
 #ifdef __CUDACC__
@@ -151,6 +171,14 @@ __device__ __forceinline__ void comm_deposit(float* p, float v) {
   uint32_t b = __float_as_uint(v);
   if (b == COMM_EMPTY) b = 0u;
   asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(b) : "memory");
+}
+__device__ __forceinline__ void comm_deposit4(float* p, float4 v) {      // p 16-byte aligned
+  uint32_t a = __float_as_uint(v.x), b = __float_as_uint(v.y), c = __float_as_uint(v.z), d = __float_as_uint(v.w);
+  if (a == COMM_EMPTY) a = 0u;
+  if (b == COMM_EMPTY) b = 0u;
+  if (c == COMM_EMPTY) c = 0u;
+  if (d == COMM_EMPTY) d = 0u;
+  asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 // Programmatic dependent launch: a kernel lets its successor start launching right away and itself waits for its
 // predecessor (completion + memory visibility) before it touches anything the predecessor may have written.

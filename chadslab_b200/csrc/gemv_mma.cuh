@@ -132,6 +132,7 @@ qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ s
   // PUSH: the receive-slot addresses of this call, one per rank, parked behind the reduction buffers
   float** push_dst = reinterpret_cast<float**>(cred + GM_WARPS * 16 * NV);
   if (PUSH && threadIdx.x < comm_world(y)) push_dst[threadIdx.x] = comm_push_base(y, threadIdx.x);
+  float* push_stage = reinterpret_cast<float*>(push_dst + 16);      // PUSH: [row block of the CTA][activation row][16 outputs]
 
   // ---- activations -> scaled fp16 vectors in shared memory ------------------------------------------
   {
@@ -232,6 +233,7 @@ qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ s
     int64_t r0 = rb * 16 + g, r1 = r0 + 8;
     if (r0 >= N) r0 = N - 1;
     if (r1 >= N) r1 = N - 1;
+    const bool push_vec = PUSH && rb * 16 + 16 <= N && (ldy & 3) == 0;      // warp-uniform
     const uint8_t* p0 = codes + r0 * row_bytes + t * 16;
     const uint8_t* p1 = codes + r1 * row_bytes + t * 16;
     const __half* sc0 = scales + r0 * groups;
@@ -395,10 +397,15 @@ qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ s
         if (active && writer && v < NV && m < m_rows) {
           const int64_t ra = rb * 16 + g, rbb = ra + 8;
           if (PUSH) {       // y is a CommDev: the partial sums go straight into every rank's receive slot
-            const int world = comm_world(y);
-            for (int r = 0; r < world; ++r) {
-              if (ra < N) comm_deposit(push_dst[r] + (int64_t)m * ldy + ra, a0);
-              if (rbb < N) comm_deposit(push_dst[r] + (int64_t)m * ldy + rbb, a1);
+            if (push_vec) {   // whole 16-row block: staged, then stored as 16-byte vectors (below)
+              push_stage[(rb_in_cta * 4 + m) * 16 + g] = a0;
+              push_stage[(rb_in_cta * 4 + m) * 16 + g + 8] = a1;
+            } else {
+              const int world = comm_world(y);
+              for (int r = 0; r < world; ++r) {
+                if (ra < N) comm_deposit(push_dst[r] + (int64_t)m * ldy + ra, a0);
+                if (rbb < N) comm_deposit(push_dst[r] + (int64_t)m * ldy + rbb, a1);
+              }
             }
           } else if (OUT == GM_OUT_GELU || OUT == GM_OUT_SILU) {
             if (rbb < N) {   // a0 = gate, a1 = up of output column rb*8 + g (same formulas as gated_act_kernel)
@@ -414,6 +421,20 @@ qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ s
         }
       }
     }
+    if (PUSH && (KSPLIT == 1 || ksp == 0) && cy == 0 && active && push_vec) {
+      // lane = (rank, 16-byte piece of the block's 16 outputs): one vector store per lane and activation row covers
+      // every rank (world <= 8)
+      __syncwarp();
+      const int world = comm_world(y);
+      const int r = lane >> 2, piece = lane & 3;
+      if (r < world) {
+        for (int m = 0; m < m_rows; ++m) {
+          const float4 v = *reinterpret_cast<const float4*>(&push_stage[(rb_in_cta * 4 + m) * 16 + piece * 4]);
+          comm_deposit4(push_dst[r] + (int64_t)m * ldy + rb * 16 + piece * 4, v);
+        }
+      }
+      __syncwarp();
+    }
     if (KSPLIT > 1) __syncthreads();
     if (CL) cluster_sync_all();             // rank 0 is done reading before anybody overwrites or exits
   }
@@ -425,7 +446,7 @@ static int gm_launch(const uint8_t* codes, const __half* scales, const XT* x, YT
                      int64_t ldy, cudaStream_t s) {
   auto kern = qgemv_mma_kernel<FMT, NV, KSPLIT, XT, YT, false, OUT>;
   auto kern_cl = qgemv_mma_kernel<FMT, NV, KSPLIT, XT, YT, true, OUT>;
-  const size_t smem = (size_t)NV * K * 2 + 32 + 2 * (size_t)GM_WARPS * 16 * NV * sizeof(float) + (OUT == GM_OUT_PUSH ? 128 : 0);
+  const size_t smem = (size_t)NV * K * 2 + 32 + 2 * (size_t)GM_WARPS * 16 * NV * sizeof(float) + (OUT == GM_OUT_PUSH ? 128 + GM_WARPS * 4 * 16 * sizeof(float) : 0);
   static size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
     BQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));

@@ -121,11 +121,15 @@ template <typename T>
 __global__ void __launch_bounds__(128) rope_kv_append_kernel(const float* __restrict__ qkv, const int64_t* __restrict__ pos_p,
                                                              T* __restrict__ q_out, T* __restrict__ k_cache,
                                                              T* __restrict__ v_cache, int Hq, int Hkv, int D, int64_t S,
-                                                             float base) {
+                                                             float base, int* __restrict__ status) {
   const int b = blockIdx.y, h = blockIdx.x;            // h in [0, Hq + 2*Hkv)
   pdl_launch_dependents();
   pdl_wait();
   const int64_t pos = *pos_p;
+  if (pos < 0 || pos >= S) {                           // the cache has no row for this position: record it, write nothing
+    if (threadIdx.x == 0) atomicExch(status, (int)BQ_ERR_ARG);
+    return;
+  }
   const float* src = qkv + ((int64_t)b * (Hq + 2 * Hkv) + h) * D;
   const int half = D / 2;
   T* dst;
@@ -211,7 +215,8 @@ template <typename T, bool FUSED>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 decode_attention_kernel(const T* __restrict__ q, const float* __restrict__ qkv, T* __restrict__ k_cache,
                         T* __restrict__ v_cache, const int64_t* __restrict__ pos_p, T* __restrict__ out, int Hq, int Hkv,
-                        int D, int64_t S, float rope_base, float* __restrict__ part, unsigned* __restrict__ counters) {
+                        int D, int64_t S, float rope_base, float* __restrict__ part, unsigned* __restrict__ counters,
+                        int* __restrict__ status) {
   const int b = blockIdx.y, h = blockIdx.x;
   // gridDim.z > 1: the positions are split over gridDim.z CTAs (long contexts, few heads); each leaves its
   // (max, sum, unnormalised output) in `part` and the last one to arrive merges them in split order
@@ -221,6 +226,10 @@ decode_attention_kernel(const T* __restrict__ q, const float* __restrict__ qkv, 
   pdl_launch_dependents();
   pdl_wait();
   const int64_t n_all = *pos_p + 1;
+  if (n_all < 1 || n_all > S) {        // position outside the cache (same for every CTA of the launch): record it and
+    if (threadIdx.x == 0) atomicExch(status, (int)BQ_ERR_ARG);      // leave the cache, `out` and the counters untouched
+    return;
+  }
   __shared__ float s_cos[ATT_MAXD / 2], s_sin[ATT_MAXD / 2];
   if (FUSED) {                         // the rotation angles of the current position, once per CTA
     for (int j = threadIdx.x; j < D / 2; j += blockDim.x) {
@@ -407,10 +416,14 @@ __global__ void __launch_bounds__(256) gated_act_kernel(const float* __restrict_
 
 using namespace bq;
 
-static float* g_gu = nullptr;           // bq_qlinear_gated, large batches: the gate|up product before the activation
-static size_t g_gu_bytes = 0;
-static float* g_att_part = nullptr;     // split-position attention: partial states + arrival counters
-static size_t g_att_bytes = 0;
+// library-owned scratch (see Scratch in common.cuh: never freed, growth refused during stream capture)
+static Scratch g_gu;            // bq_qlinear_gated, large batches: the gate|up product before the activation
+static Scratch g_att_part;      // split-position attention: partial (max, sum, output) states
+static Scratch g_att_count;     // its arrival counters, one per (batch, head): all zero between launches
+
+namespace bq {
+int glue_reserve(int64_t rows, int64_t N) { return scratch_ensure(&g_gu, (size_t)rows * N * sizeof(float), 0, "bq_reserve"); }
+}  // namespace bq
 
 static int glue_ready(int dtype) {
   if (device_id() < 0) return fail(BQ_ERR_STATE, "bq_init() has not been called");
@@ -430,33 +443,18 @@ static int launch_attention(const void* q, const float* qkv, void* k_cache, void
   if (nsplit > S / 128) nsplit = S / 128;        // at least 128 cache positions per split (measured: finer is slower)
   if (nsplit > 32) nsplit = 32;
   if (nsplit < 1) nsplit = 1;
-  {
-    static int forced = -1;            // BQ_ATT_SPLIT: tuning override of the number of position splits
-    if (forced < 0) {
-      const char* e = getenv("BQ_ATT_SPLIT");
-      forced = e ? atoi(e) : 0;
-    }
-    if (forced > 0) nsplit = forced > 64 ? 64 : forced;
-  }
-  if (nsplit > 1) {
-    const size_t need = (size_t)B * Hq * nsplit * (D + 2) * sizeof(float) + (size_t)B * Hq * sizeof(unsigned);
-    if (need > g_att_bytes) {          // grow-only scratch owned by the library (first call: before any graph capture)
-      if (g_att_part) BQ_CUDA(cudaFree(g_att_part));
-      g_att_part = nullptr; g_att_bytes = 0;
-      const size_t cap = need * 2;
-      BQ_CUDA(cudaMalloc((void**)&g_att_part, 2 * cap));
-      BQ_CUDA(cudaMemset(g_att_part, 0, 2 * cap));
-      g_att_bytes = cap;
-    }
-  }
-  // partial states first, the arrival counters (all zero between launches) in the second half of the allocation
-  float* part = g_att_part;
-  unsigned* counters = reinterpret_cast<unsigned*>(reinterpret_cast<uint8_t*>(g_att_part) + g_att_bytes);
-  dim3 grid((unsigned)Hq, (unsigned)B, (unsigned)nsplit);
   cudaStream_t s = (cudaStream_t)stream;
+  if (nsplit > 1) {
+    if ((rc = scratch_ensure(&g_att_part, (size_t)B * Hq * nsplit * (D + 2) * sizeof(float), s, "split-position attention")))
+      return rc;
+    if ((rc = scratch_ensure(&g_att_count, (size_t)B * Hq * sizeof(unsigned), s, "split-position attention", true))) return rc;
+  }
+  float* part = (float*)g_att_part.ptr;
+  unsigned* counters = (unsigned*)g_att_count.ptr;
+  dim3 grid((unsigned)Hq, (unsigned)B, (unsigned)nsplit);
 #define BQ_ATT_LAUNCH(TT, FUSED)                                                                                        \
   BQ_CUDA(launch_chain(decode_attention_kernel<TT, FUSED>, grid, dim3(ATT_WARPS * 32), 0, s, 1, (const TT*)q, qkv, (TT*)k_cache, \
-                       (TT*)v_cache, pos, (TT*)out, Hq, Hkv, D, S, rope_base, part, counters))
+                       (TT*)v_cache, pos, (TT*)out, Hq, Hkv, D, S, rope_base, part, counters, status_word()))
   if (dtype == BQ_DT_F32) {
     if (qkv) BQ_ATT_LAUNCH(float, true); else BQ_ATT_LAUNCH(float, false);
   } else {
@@ -503,10 +501,10 @@ int bq_rope_kv_append(const float* qkv, const int64_t* pos, void* q_out, void* k
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == BQ_DT_F32)
     BQ_CUDA(launch_chain(rope_kv_append_kernel<float>, grid, dim3(128), 0, s, 1, qkv, pos, (float*)q_out, (float*)k_cache,
-                         (float*)v_cache, Hq, Hkv, D, S, rope_base));
+                         (float*)v_cache, Hq, Hkv, D, S, rope_base, status_word()));
   else
     BQ_CUDA(launch_chain(rope_kv_append_kernel<__nv_bfloat16>, grid, dim3(128), 0, s, 1, qkv, pos, (__nv_bfloat16*)q_out,
-                         (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, Hq, Hkv, D, S, rope_base));
+                         (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, Hq, Hkv, D, S, rope_base, status_word()));
   count_launch();
   BQ_CUDA(cudaGetLastError());
   return BQ_OK;
@@ -565,16 +563,10 @@ int bq_qlinear_gated(bq_weight_t weight, const void* x, int x_dtype, int64_t M, 
   }
   // larger batches: plain product into a scratch owned by the library (sized on the first call: before any graph
   // capture), then the activation kernel reading the blocked layout
-  const size_t need = (size_t)M * w->N * sizeof(float);
-  if (need > g_gu_bytes) {
-    if (g_gu) BQ_CUDA(cudaFree(g_gu));
-    g_gu = nullptr; g_gu_bytes = 0;
-    BQ_CUDA(cudaMalloc((void**)&g_gu, need + need / 4));
-    g_gu_bytes = need + need / 4;
-  }
-  rc = bq_qlinear(weight, x, x_dtype, M, g_gu, BQ_DT_F32, stream);
+  if ((rc = scratch_ensure(&g_gu, (size_t)M * w->N * sizeof(float), s, "bq_qlinear_gated"))) return rc;
+  rc = bq_qlinear(weight, x, x_dtype, M, g_gu.ptr, BQ_DT_F32, stream);
   if (rc) return rc;
-  return launch_gated_act(g_gu, out, M, w->N / 2, act, x_dtype, 1, s);
+  return launch_gated_act((const float*)g_gu.ptr, out, M, w->N / 2, act, x_dtype, 1, s);
 }
 
 }  // extern "C"

@@ -1,6 +1,8 @@
 // MoE bookkeeping kernels: router softmax/top-k, stable counting-sort permute, row gather,
 // deterministic weighted combine, and the CUDA-core grouped SwiGLU expert FFN (exact fp32
 // arithmetic; the tensor-core grouped kernel lives in tc.cu).
+#include <mutex>
+
 #include "common.cuh"
 
 namespace bq {
@@ -97,7 +99,8 @@ moe_hist_kernel(const int32_t* __restrict__ idx, int64_t A, int E, int nchunks, 
 
 // one block, E <= 1024 threads: per-expert exclusive scan over chunks, then over experts
 __global__ void __launch_bounds__(1024)
-moe_scan_kernel(int32_t* __restrict__ counts, int E, int nchunks, int32_t* __restrict__ offsets) {
+moe_scan_kernel(int32_t* __restrict__ counts, int E, int nchunks, int32_t* __restrict__ offsets, int32_t* __restrict__ perm,
+                int64_t A) {
   __shared__ int32_t tot[1024];
   const int e = threadIdx.x;
   int32_t run = 0;
@@ -127,6 +130,8 @@ moe_scan_kernel(int32_t* __restrict__ counts, int E, int nchunks, int32_t* __res
   }
   if (e < E) offsets[e + 1] = tot[e];
   if (e == 0) offsets[0] = 0;
+  // assignments with an expert id outside [0, E) are dropped: the sorted positions behind the last segment hold -1
+  for (int64_t p = (int64_t)tot[E - 1] + e; p < A; p += 1024) perm[p] = -1;
 }
 
 __global__ void __launch_bounds__(PERM_WARPS * 32)
@@ -172,8 +177,8 @@ __global__ void __launch_bounds__(256) moe_gather_kernel(const uint4* __restrict
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
        i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t p = i / row_vec, c = i - p * row_vec;
-    const int64_t t = perm[p] / top_k;
-    xp[i] = x[t * row_vec + c];
+    const int32_t a = perm[p];                       // -1: a dropped assignment (expert id out of range) -> zero row
+    xp[i] = a >= 0 ? x[(int64_t)(a / top_k) * row_vec + c] : make_uint4(0u, 0u, 0u, 0u);
   }
 }
 
@@ -394,7 +399,7 @@ int bq_moe_permute(const int32_t* idx, int64_t T, int top_k, int E, int32_t* per
   const size_t smem = (size_t)PERM_WARPS * E * sizeof(int32_t);
   int32_t* counts = (int32_t*)scratch;
   moe_hist_kernel<<<blocks, PERM_WARPS * 32, smem, s>>>(idx, A, E, nchunks, chunk, counts);
-  moe_scan_kernel<<<1, 1024, 0, s>>>(counts, E, nchunks, offsets);
+  moe_scan_kernel<<<1, 1024, 0, s>>>(counts, E, nchunks, offsets, perm, A);
   moe_scatter_kernel<<<blocks, PERM_WARPS * 32, smem, s>>>(idx, A, E, nchunks, chunk, counts, offsets, perm, inv);
   count_launch(3);
   BQ_CUDA(cudaGetLastError());
@@ -411,6 +416,7 @@ constexpr int64_t PERMUTE_STATIC_INTS = 131072;   // 512 KiB: chunks * experts m
 static __device__ __align__(256) int32_t g_permute_scratch[PERMUTE_STATIC_INTS];
 // The array's name is only a host-side handle; kernels need its device address, fetched once per device.
 static int32_t* g_permute_scratch_addr[64] = {nullptr};
+static std::mutex g_permute_scratch_mu;
 
 int64_t bq_moe_permute_noalloc_max_bytes(void) { return PERMUTE_STATIC_INTS * (int64_t)sizeof(int32_t); }
 
@@ -428,16 +434,23 @@ int bq_moe_permute_noalloc(const int32_t* idx, int64_t T, int top_k, int E, int3
                                 "; use bq_moe_permute with caller-provided scratch");
   const int dev = device_id();
   if (dev < 0 || dev >= 64) return fail(BQ_ERR_STATE, "device index out of range for the built-in scratch table");
-  if (!g_permute_scratch_addr[dev]) {     // first call on this device: resolve the symbol's device address
-    int cur = -1;
-    BQ_CUDA(cudaGetDevice(&cur));
-    if (cur != dev) BQ_CUDA(cudaSetDevice(dev));
-    void* p = nullptr;
-    BQ_CUDA(cudaGetSymbolAddress(&p, g_permute_scratch));
-    g_permute_scratch_addr[dev] = static_cast<int32_t*>(p);
+  int32_t* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_permute_scratch_mu);
+    if (!g_permute_scratch_addr[dev]) {     // first call on this device: resolve the symbol's device address
+      int cur = -1;
+      BQ_CUDA(cudaGetDevice(&cur));
+      if (cur != dev) BQ_CUDA(cudaSetDevice(dev));       // the look-up answers for the current device
+      void* p = nullptr;
+      const cudaError_t e = cudaGetSymbolAddress(&p, g_permute_scratch);
+      if (cur != dev && cur >= 0) cudaSetDevice(cur);    // leave the caller's device selection as it was
+      if (e != cudaSuccess) return fail_cuda(e, "cudaGetSymbolAddress(built-in permute scratch)");
+      g_permute_scratch_addr[dev] = static_cast<int32_t*>(p);
+    }
+    scratch = g_permute_scratch_addr[dev];
   }
   // Nothing in the array has to start at zero: the histogram kernel writes every cell the later kernels read.
-  return bq_moe_permute(idx, T, top_k, E, perm, inv, offsets, g_permute_scratch_addr[dev], stream);
+  return bq_moe_permute(idx, T, top_k, E, perm, inv, offsets, scratch, stream);
 }
 
 int bq_moe_gather(const void* x, int dtype, int64_t H, const int32_t* perm, int64_t P, int top_k, void* xp,
@@ -461,11 +474,16 @@ int bq_moe_gather(const void* x, int dtype, int64_t H, const int32_t* perm, int6
 
 int bq_moe_experts(bq_moe_t h, const void* xp_bf16, const int32_t* offsets, int64_t P, void* hbuf_bf16,
                    float* out, int path, void* stream) {
+  return bq_moe_experts_ex(h, xp_bf16, offsets, P, P, hbuf_bf16, out, path, stream);
+}
+
+int bq_moe_experts_ex(bq_moe_t h, const void* xp_bf16, const int32_t* offsets, int64_t P, int64_t rows_hint,
+                      void* hbuf_bf16, float* out, int path, void* stream) {
   int rc = ready();
   if (rc) return rc;
   Moe* m = get_moe(h);
   if (!m) return BQ_ERR_HANDLE;
-  if (P < 0) return fail(BQ_ERR_ARG, "P must be >= 0");
+  if (P < 0 || rows_hint < 0 || rows_hint > P) return fail(BQ_ERR_ARG, "need 0 <= rows_hint <= P");
   if (P == 0) return BQ_OK;
   if (!xp_bf16 || !offsets || !hbuf_bf16 || !out) return fail(BQ_ERR_ARG, "null pointer");
   cudaStream_t s = (cudaStream_t)stream;
@@ -473,7 +491,7 @@ int bq_moe_experts(bq_moe_t h, const void* xp_bf16, const int32_t* offsets, int6
   if (path == BQ_PATH_TENSOR && !tc_ok) return fail(BQ_ERR_UNSUPPORTED, "tensor path unavailable for this expert shape");
   if ((path == BQ_PATH_AUTO && tc_ok) || path == BQ_PATH_TENSOR) {
     set_last_path(BQ_PATH_TENSOR);
-    return launch_moe_experts_tc(m, xp_bf16, offsets, P, hbuf_bf16, out, s);
+    return launch_moe_experts_tc(m, xp_bf16, offsets, P, rows_hint, hbuf_bf16, out, s);
   }
   set_last_path(BQ_PATH_SIMT);
   if ((rc = moe_ffn_simt(m, true, xp_bf16, offsets, hbuf_bf16, s))) return rc;

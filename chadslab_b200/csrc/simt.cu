@@ -344,7 +344,7 @@ int launch_qlinear_simt(const uint8_t* codes, const __half* scales, int fmt, int
 // -------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(1024) argmax_kernel(const T* __restrict__ logits, int64_t N,
-                                                      int32_t* __restrict__ out) {
+                                                      int32_t* __restrict__ out, float* __restrict__ vout) {
   const T* row = logits + (int64_t)blockIdx.x * N;
   float best = -INFINITY;
   int32_t bi = 0x7fffffff;
@@ -372,7 +372,10 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const T* __restrict__ logi
       const int32_t oi = __shfl_xor_sync(0xffffffffu, bi, off);
       if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
     }
-    if (threadIdx.x == 0) out[blockIdx.x] = (bi == 0x7fffffff) ? 0 : bi;
+    if (threadIdx.x == 0) {
+      out[blockIdx.x] = (bi == 0x7fffffff) ? 0 : bi;
+      if (vout) vout[blockIdx.x] = best;
+    }
   }
 }
 
@@ -410,7 +413,7 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(const T* __restrict
   }
 }
 __global__ void __launch_bounds__(ARG_CHUNKS) argmax_final_kernel(const float* __restrict__ pv, const int32_t* __restrict__ pi,
-                                                                  int32_t* __restrict__ out) {
+                                                                  int32_t* __restrict__ out, float* __restrict__ vout) {
   pdl_launch_dependents();
   pdl_wait();
   float best = pv[(int64_t)blockIdx.x * ARG_CHUNKS + threadIdx.x];
@@ -429,25 +432,20 @@ __global__ void __launch_bounds__(ARG_CHUNKS) argmax_final_kernel(const float* _
     for (int w = 1; w < ARG_CHUNKS / 32; ++w)
       if (sv[w] > best || (sv[w] == best && si[w] < bi)) { best = sv[w]; bi = si[w]; }
     out[blockIdx.x] = (bi == 0x7fffffff) ? 0 : bi;
+    if (vout) vout[blockIdx.x] = best;
   }
 }
 
-static float* g_arg_pv = nullptr;          // grow-only scratch for the stage-1 pairs
-static int32_t* g_arg_pi = nullptr;
-static int64_t g_arg_rows = 0;
+static Scratch g_arg_sv, g_arg_si;         // stage-1 (value, index) pairs (library scratch: see common.cuh)
 
-int launch_argmax(const void* logits, int dtype, int64_t M, int64_t N, int32_t* out, cudaStream_t s) {
+int launch_argmax(const void* logits, int dtype, int64_t M, int64_t N, int32_t* out, cudaStream_t s, float* vout) {
   if (M == 0) return BQ_OK;
   if (N >= 32768 && M <= 65535) {
-    if (M > g_arg_rows) {
-      if (g_arg_pv) BQ_CUDA(cudaFree(g_arg_pv));
-      if (g_arg_pi) BQ_CUDA(cudaFree(g_arg_pi));
-      g_arg_pv = nullptr; g_arg_pi = nullptr; g_arg_rows = 0;
-      const int64_t rows = M + 64;
-      BQ_CUDA(cudaMalloc((void**)&g_arg_pv, sizeof(float) * rows * ARG_CHUNKS));
-      BQ_CUDA(cudaMalloc((void**)&g_arg_pi, sizeof(int32_t) * rows * ARG_CHUNKS));
-      g_arg_rows = rows;
-    }
+    int rc = scratch_ensure(&g_arg_sv, sizeof(float) * (size_t)M * ARG_CHUNKS, s, "argmax");
+    if (!rc) rc = scratch_ensure(&g_arg_si, sizeof(int32_t) * (size_t)M * ARG_CHUNKS, s, "argmax");
+    if (rc) return rc;
+    float* g_arg_pv = (float*)g_arg_sv.ptr;
+    int32_t* g_arg_pi = (int32_t*)g_arg_si.ptr;
     dim3 grid(ARG_CHUNKS, (unsigned)M);
     if (dtype == BQ_DT_F32)
       BQ_CUDA(launch_chain(argmax_partial_kernel<float>, grid, dim3(256), 0, s, 1, (const float*)logits, N, g_arg_pv, g_arg_pi));
@@ -455,15 +453,15 @@ int launch_argmax(const void* logits, int dtype, int64_t M, int64_t N, int32_t* 
       BQ_CUDA(launch_chain(argmax_partial_kernel<__nv_bfloat16>, grid, dim3(256), 0, s, 1, (const __nv_bfloat16*)logits, N, g_arg_pv,
                            g_arg_pi));
     BQ_CUDA(launch_chain(argmax_final_kernel, dim3((unsigned)M), dim3(ARG_CHUNKS), 0, s, 1, (const float*)g_arg_pv,
-                         (const int32_t*)g_arg_pi, out));
+                         (const int32_t*)g_arg_pi, out, vout));
     count_launch(2);
     BQ_CUDA(cudaGetLastError());
     return BQ_OK;
   }
   if (dtype == BQ_DT_F32)
-    argmax_kernel<float><<<(int)M, 1024, 0, s>>>((const float*)logits, N, out);
+    argmax_kernel<float><<<(int)M, 1024, 0, s>>>((const float*)logits, N, out, vout);
   else
-    argmax_kernel<__nv_bfloat16><<<(int)M, 1024, 0, s>>>((const __nv_bfloat16*)logits, N, out);
+    argmax_kernel<__nv_bfloat16><<<(int)M, 1024, 0, s>>>((const __nv_bfloat16*)logits, N, out, vout);
   count_launch();
   BQ_CUDA(cudaGetLastError());
   return BQ_OK;

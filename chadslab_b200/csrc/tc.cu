@@ -1,28 +1,31 @@
-// Tensor-core path (sm_100a): dequantize-to-fp16 shared-memory tiles feeding tcgen05.mma with the
+// Tensor-core path (sm_100a): tcgen05.mma with the dequantized weights as the A operand in tensor memory and the
 // accumulator in tensor memory.
 //
-// Formulation ("swap-AB"): D[n, m] = sum_k W[n, k] * x[m, k].  The 128 weight rows of a tile are the
-// MMA M dimension, the batch (activation rows) is the MMA N dimension (BN = 16..256), so decode-sized
-// batches waste no tensor work on padding weight rows and the accumulator lane == output column n.
+// Formulation ("swap-AB"): D[n, m] = sum_k W[n, k] * x[m, k].  The 128 weight rows of a tile are the MMA M
+// dimension, the batch (activation rows) is the MMA N dimension (BN = 16..256), so decode-sized batches waste no
+// tensor work on padding weight rows and the accumulator lane == output column n.
 //
-// Per CTA (one 128 x BN output tile, 320 threads):
-//   warp 0      producer : TMA (cp.async.bulk.tensor.2d) of packed codes [128 x 64k], activations
-//                          [BN x 64k, 128-byte swizzle = the UMMA K-major layout] and, every 4th
-//                          k-step, the fp16 scales [128 x 8 groups] into a ring of stages
-//   warps 2..9  converter: packed codes + scale -> fp16 = code * scale (exact product rounded once to
-//                          fp16), written into a 128-byte-swizzled K-major A tile; later the epilogue
-//   warp 1      issuer   : one thread issues 4 x tcgen05.mma (K = 16 each, kind::f16, A = B = fp16,
-//                          D = fp32 in TMEM) per k-step and commits to the "free" barriers
-//   epilogue             : tcgen05.ld of the 128 x BN fp32 tile, coalesced stores of y[m, n]
+// Per CTA (one 128 x BN output tile, or two weight tiles sharing one activation tile; 320 threads), one pipeline
+// step = 128 k:
+//   warp 0      producer : TMA (cp.async.bulk.tensor.2d, no multicast) of the packed codes [128 rows x 128 k]
+//                          (swizzled so that "one thread reads one row" is free of bank conflicts), two activation
+//                          atoms [BN x 64 k, 128-byte swizzle = the UMMA K-major layout] and, every second step, the
+//                          fp16 scales [128 x 8 groups] into a ring of stages with mbarrier transaction counts
+//   warps 2..9  converter: every thread owns one weight row (= its TMEM lane): packed codes + scale -> fp16 =
+//                          code * scale (exact product rounded once to fp16) in registers, written with tcgen05.st
+//                          into one of two A buffers in tensor memory; later the epilogue
+//   warp 1      issuer   : one thread issues 8 x tcgen05.mma (K = 16 each, kind::f16, A from TMEM, B = fp16
+//                          activations from shared memory, D = fp32 in TMEM) per step and commits to the barriers
+//                          that free the A buffer and the stage
+//   epilogue             : tcgen05.ld of the 128 x BN fp32 tile, row back-scale, stores of y[m, n]
 // Every mbarrier wait is bounded; on expiry a status word is set and all roles drain and exit.
 //
-// Activations reach the tensor core as fp16: a pre-pass kernel scales every activation row by a power
-// of two that puts its largest magnitude in [2^14, 2^15) and rounds to fp16 (exact for bf16 inputs
-// down to 2^-29 of the row maximum); the epilogue multiplies the row back.  Both MMA operands then
-// have the same type.
+// Activations reach the tensor core as fp16: a pre-pass kernel scales every activation row by a power of two that
+// puts its largest magnitude in [2^14, 2^15) and rounds to fp16 (exact for bf16 inputs down to 2^-29 of the row
+// maximum); the epilogue multiplies the row back.  Both MMA operands then have the same type.
 //
-// GATED variant (MoE experts / SwiGLU): two weight matrices share the activation tile, two
-// accumulators, epilogue writes silu(g) * u as bf16.
+// MODE 1 (GATED; MoE experts / SwiGLU): the gate and up matrices share the activation tile, two accumulators, the
+// epilogue writes silu(g) * u as bf16.  MODE 2 (DUAL): rows n0.. and n0+128.. of one matrix share the activation tile.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -30,10 +33,10 @@
 namespace bq {
 
 constexpr int TC_ROWS = 128;        // weight rows per tile (UMMA M)
-constexpr int TC_BK = 64;           // k per pipeline step (one 128-byte swizzle row of 16-bit data)
 constexpr int TC_CONV_THREADS = 256;   // 8 converter warps
 constexpr int TC_THREADS = 64 + TC_CONV_THREADS;
-constexpr int TC_SC_SLOTS = 3;      // scale tiles in flight (each covers 4 k-steps)
+constexpr int TC_SC_SLOTS = 3;      // scale tiles in flight (each covers 2 k-steps)
+constexpr size_t TC_PART_BYTES = (size_t)64 << 20;   // split-K partial tiles never exceed this
 constexpr uint64_t TC_WAIT_NS = 2000000000ull;   // every device-side wait gives up after 2 s
 constexpr int TC_CONV_WARPS = TC_CONV_THREADS / 32;
 
@@ -136,44 +139,6 @@ __host__ __device__ constexpr uint32_t umma_idesc(int bn) {
   return (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(TC_ROWS >> 4) << 24);
 }
 
-// ---- shared-memory plan -------------------------------------------------------------------------
-// MODE: 0 = one weight tile; 1 = GATED (gate and up matrices, SwiGLU epilogue); 2 = DUAL (rows n0..n0+127 and
-// n0+128..n0+255 of the same matrix share the activation tile: halves the activation traffic per MAC)
-template <int FMT, int BN, int MODE> struct TcPlan {
-  static constexpr int NW = MODE ? 2 : 1;
-  static constexpr int RAW_ROW = (FMT == BQ_FMT_Q8G32) ? 64 : 32;       // code bytes per row per k-step
-  static constexpr int RAW = TC_ROWS * RAW_ROW;                           // per weight
-  static constexpr int XT = BN * 128;                                     // activation tile bytes
-  static constexpr int AT = TC_ROWS * 128;                                // fp16 A tile bytes (16 KB)
-  static constexpr int SCT = TC_ROWS * 16;                                // scale tile: 8 fp16 per row
-  static constexpr int STAGE = ((NW * RAW + XT + 1023) / 1024) * 1024;
-  static constexpr int NA = (BN >= 128) ? 3 : 2;                          // A-tile ring
-  static constexpr int BUDGET = (BN >= 128 ? 200 : 100) * 1024;           // 1 or 2 CTAs per SM
-  static constexpr int FIXED = NA * NW * AT + TC_SC_SLOTS * NW * SCT + 1024 /*barriers*/ + 1024 /*align*/;
-  static constexpr int S_RAW = (BUDGET - FIXED) / STAGE;
-  static constexpr int S = S_RAW > 8 ? 8 : (S_RAW < 2 ? 2 : S_RAW);       // S <= 4*SC_SLOTS - 3 = 9
-  static constexpr int SMEM = FIXED + S * STAGE;
-  static constexpr int TMEM_COLS = (NW * BN <= 32) ? 32 : (NW * BN <= 64) ? 64 : (NW * BN <= 128) ? 128
-                                   : (NW * BN <= 256) ? 256 : 512;
-  static_assert(NW * BN <= 512, "accumulators exceed tensor memory");
-  static_assert(SMEM <= 227 * 1024, "shared memory plan too large");
-};
-
-struct TcArgs {
-  CUtensorMap tm_x;                  // pre-scaled activations [M or P, K] fp16, box 64 x BN, 128B swizzle
-  const float* xscale;               // per activation row: the power of two to multiply the result by
-  CUtensorMap tm_w[2];               // dense: codes of weight 0 / 1 (GATED), box RAW_ROW x 128
-  CUtensorMap tm_s[2];               // dense: scales fp16 [N, K/32], box 8 x 128
-  const CUtensorMap* tm_list;        // MoE: per expert {codes0, scales0, codes1, scales1}
-  const int32_t* offsets;            // MoE: expert row ranges
-  const int32_t* tiles;              // MoE: tiles[0] = count, then (expert, m0) pairs
-  void* out;                         // dense: y [M, ldy];  GATED: bf16 h [P, N];  MoE plain: f32 [P, N]
-  int64_t ldy;
-  int64_t N, K, M;
-  int out_dtype;
-  int moe;
-  int* status;
-};
 
 // ---- converters: 16 bytes of codes -> fp16 (code * scale) -------------------------------------------
 // Q8: 16 codes -> two 16-byte pieces of the A row.
@@ -214,262 +179,9 @@ __device__ __forceinline__ uint4 cvt_q4_word(const uint32_t v, const __half2 s2)
                     *reinterpret_cast<uint32_t*>(&h45), *reinterpret_cast<uint32_t*>(&h67));
 }
 
-// Optional timeline of CTA (0,0) for tuning builds (-DBQ_TC_TRACE): role x k-step x point -> SM clock.
-#ifdef BQ_TC_TRACE
-__device__ long long g_tc_trace[3][64][6];
-#define TC_TRACE(role, ks, pt)                                                                     \
-  do {                                                                                             \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && (ks) < 64) g_tc_trace[role][ks][pt] = clock64();     \
-  } while (0)
-#else
-#define TC_TRACE(role, ks, pt) do {} while (0)
-#endif
-
-// ---- the kernel ----------------------------------------------------------------------------------------
-template <int FMT, int BN, int MODE>
-__global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_constant__ TcArgs args) {
-  using P = TcPlan<FMT, BN, MODE>;
-  constexpr bool GATED = MODE == 1, DUAL = MODE == 2, TWO = MODE != 0;
-  constexpr int NW = P::NW, S = P::S, NA = P::NA;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  // layout: [A tiles NA*NW*16K][stages S*STAGE][scale tiles][barriers]
-  uint8_t* a_tiles = smem;
-  uint8_t* stages = a_tiles + NA * NW * P::AT;
-  uint8_t* sc_tiles = stages + S * P::STAGE;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sc_tiles + TC_SC_SLOTS * NW * P::SCT);
-  // barrier indices
-  uint64_t* full = bars;               // [S]   TMA landed (tx)
-  uint64_t* empty = bars + S;          // [S]   converter warps (8) + MMA commit (1)
-  uint64_t* a_full = bars + 2 * S;     // [NA]  converter warps (8)
-  uint64_t* a_empty = a_full + NA;     // [NA]  MMA commit (1)
-  uint64_t* acc_full = a_empty + NA;   // [1]
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(acc_full + 1);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 2);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-  // ---- which tile ------------------------------------------------------------------------------------
-  int64_t n0 = (int64_t)blockIdx.y * TC_ROWS * (DUAL ? 2 : 1);
-  const int n1_off = DUAL ? TC_ROWS : 0;      // row offset of the second weight tile
-  int64_t m0, m_end;
-  const CUtensorMap *tmw0, *tms0, *tmw1, *tms1;
-  if (args.moe) {
-    const int ntiles = args.tiles[0];
-    if ((int)blockIdx.x >= ntiles) return;           // uniform across the CTA, before any barrier
-    const int e = args.tiles[1 + 2 * blockIdx.x];
-    m0 = args.tiles[2 + 2 * blockIdx.x];
-    m_end = args.offsets[e + 1];
-    const CUtensorMap* l = args.tm_list + (int64_t)e * 4;
-    tmw0 = l; tms0 = l + 1; tmw1 = l + 2; tms1 = l + 3;
-  } else {
-    m0 = (int64_t)blockIdx.x * BN;
-    m_end = args.M;
-    tmw0 = &args.tm_w[0]; tms0 = &args.tm_s[0]; tmw1 = &args.tm_w[1]; tms1 = &args.tm_s[1];
-  }
-  const int ksteps = (int)((args.K + TC_BK - 1) / TC_BK);
-
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < S; ++i) { mbar_init(smem_u32(&full[i]), 1); mbar_init(smem_u32(&empty[i]), TC_CONV_WARPS + 1); }
-    for (int i = 0; i < NA; ++i) { mbar_init(smem_u32(&a_full[i]), TC_CONV_WARPS); mbar_init(smem_u32(&a_empty[i]), 1); }
-    mbar_init(smem_u32(acc_full), 1);
-    *abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 1) {   // TMEM allocation by one full warp
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                 "r"((uint32_t)P::TMEM_COLS)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-
-  if (warp == 0) {
-    // ================= producer =================
-    if (lane == 0) {
-      for (int ks = 0; ks < ksteps; ++ks) {
-        const int s = ks % S;
-        const uint32_t ph = (uint32_t)(ks / S) & 1u;
-        if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1u, abort_flag)) break;
-        TC_TRACE(0, ks, 0);
-        const bool with_scales = (ks & 3) == 0;
-        const uint32_t bytes = NW * P::RAW + P::XT + (with_scales ? NW * P::SCT : 0);
-        const uint32_t fb = smem_u32(&full[s]);
-        mbar_expect_tx(fb, bytes);
-        uint8_t* st = stages + s * P::STAGE;
-        tma_load_2d(smem_u32(st), &args.tm_x, ks * TC_BK, (int)m0, fb);
-        tma_load_2d(smem_u32(st + P::XT), tmw0, ks * P::RAW_ROW, (int)n0, fb);
-        if (TWO) tma_load_2d(smem_u32(st + P::XT + P::RAW), tmw1, ks * P::RAW_ROW, (int)n0 + n1_off, fb);
-        if (with_scales) {
-          uint8_t* sc = sc_tiles + ((ks >> 2) % TC_SC_SLOTS) * NW * P::SCT;
-          tma_load_2d(smem_u32(sc), tms0, (ks >> 2) * 8, (int)n0, fb);
-          if (TWO) tma_load_2d(smem_u32(sc + P::SCT), tms1, (ks >> 2) * 8, (int)n0 + n1_off, fb);
-        }
-        TC_TRACE(0, ks, 1);
-      }
-      if (*abort_flag) {   // give copies already in flight time to land before the CTA exits
-        for (int i = 0; i < 64; ++i) __nanosleep(1000);
-      }
-    }
-  } else if (warp == 1) {
-    // ================= MMA issuer =================
-    if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc(BN);
-      bool ok = true;
-      for (int ks = 0; ks < ksteps && ok; ++ks) {
-        const int s = ks % S, a = ks % NA;
-        const uint32_t ph = (uint32_t)(ks / S) & 1u, aph = (uint32_t)(ks / NA) & 1u;
-        ok = mbar_wait(smem_u32(&a_full[a]), aph, abort_flag);
-        TC_TRACE(1, ks, 0);
-        ok = ok && mbar_wait(smem_u32(&full[s]), ph, abort_flag);   // activation tile (completed before a_full)
-        if (!ok) break;
-        TC_TRACE(1, ks, 1);
-        tc_fence_after();
-        const uint64_t bdesc = umma_desc_sw128(smem_u32(stages + s * P::STAGE));
-#pragma unroll
-        for (int w = 0; w < NW; ++w) {
-          const uint64_t adesc = umma_desc_sw128(smem_u32(a_tiles + (a * NW + w) * P::AT));
-#pragma unroll
-          for (int kk = 0; kk < TC_BK / 16; ++kk)
-            tc_mma_f16(tmem_base + (uint32_t)(w * BN), adesc + (uint64_t)(2 * kk), bdesc + (uint64_t)(2 * kk), idesc,
-                       (ks > 0 || kk > 0) ? 1u : 0u);
-        }
-        TC_TRACE(1, ks, 2);
-        tc_commit(smem_u32(&a_empty[a]));
-        tc_commit(smem_u32(&empty[s]));
-        TC_TRACE(1, ks, 3);
-      }
-      if (ok) tc_commit(smem_u32(acc_full));
-    }
-  } else {
-    // ================= converters, then epilogue =================
-    const int t = threadIdx.x - 64;   // 0..TC_CONV_THREADS-1
-    bool ok = true;
-    for (int ks = 0; ks < ksteps && ok; ++ks) {
-      const int s = ks % S, a = ks % NA;
-      const uint32_t ph = (uint32_t)(ks / S) & 1u, aph = (uint32_t)(ks / NA) & 1u;
-      ok = mbar_wait_warp(smem_u32(&full[s]), ph, abort_flag, lane);
-      if (t == 0) TC_TRACE(2, ks, 0);
-      ok = ok && mbar_wait_warp(smem_u32(&a_empty[a]), aph ^ 1u, abort_flag, lane);
-      if (!ok) break;
-      if (t == 0) TC_TRACE(2, ks, 1);
-      const uint8_t* st = stages + s * P::STAGE + P::XT;
-      const uint8_t* sc = sc_tiles + ((ks >> 2) % TC_SC_SLOTS) * NW * P::SCT;
-#pragma unroll
-      for (int w = 0; w < NW; ++w) {
-        const uint8_t* raw = st + w * P::RAW;
-        const __half* scw = reinterpret_cast<const __half*>(sc + w * P::SCT);
-        uint8_t* at = a_tiles + (a * NW + w) * P::AT;
-        if (FMT == BQ_FMT_Q8G32) {
-          // 512 pieces of 16 bytes: piece j -> row j>>2, 16-code column c = j&3 (group c>>1)
-#pragma unroll
-          for (int i = 0; i < 512 / TC_CONV_THREADS; ++i) {
-            const int j = t + TC_CONV_THREADS * i;
-            const int row = j >> 2, c = j & 3;
-            const uint4 wv = *reinterpret_cast<const uint4*>(raw + j * 16);
-            const __half sh = scw[row * 8 + (ks & 3) * 2 + (c >> 1)];
-            uint4 lo, hi;
-            cvt_q8_chunk(wv, __half2half2(sh), lo, hi);
-            uint8_t* rowp = at + row * 128;
-            *reinterpret_cast<uint4*>(rowp + (((2 * c) ^ (row & 7)) << 4)) = lo;
-            *reinterpret_cast<uint4*>(rowp + (((2 * c + 1) ^ (row & 7)) << 4)) = hi;
-          }
-        } else {
-          // 256 pieces of 16 bytes: piece j -> row j>>1, group c = j&1 (32 codes)
-#pragma unroll
-          for (int i = 0; i < 256 / TC_CONV_THREADS; ++i) {
-            const int j = t + TC_CONV_THREADS * i;
-            const int row = j >> 1, c = j & 1;
-            const uint4 wv = *reinterpret_cast<const uint4*>(raw + j * 16);
-            const __half2 s2 = __half2half2(scw[row * 8 + (ks & 3) * 2 + c]);
-            uint8_t* rowp = at + row * 128;
-            *reinterpret_cast<uint4*>(rowp + (((4 * c + 0) ^ (row & 7)) << 4)) = cvt_q4_word(wv.x, s2);
-            *reinterpret_cast<uint4*>(rowp + (((4 * c + 1) ^ (row & 7)) << 4)) = cvt_q4_word(wv.y, s2);
-            *reinterpret_cast<uint4*>(rowp + (((4 * c + 2) ^ (row & 7)) << 4)) = cvt_q4_word(wv.z, s2);
-            *reinterpret_cast<uint4*>(rowp + (((4 * c + 3) ^ (row & 7)) << 4)) = cvt_q4_word(wv.w, s2);
-          }
-        }
-      }
-      if (t == 0) TC_TRACE(2, ks, 2);
-      fence_async_smem();                       // generic-proxy writes -> visible to the tensor core
-      if (t == 0) TC_TRACE(2, ks, 3);
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(smem_u32(&a_full[a]));
-        mbar_arrive(smem_u32(&empty[s]));
-      }
-      if (t == 0) TC_TRACE(2, ks, 4);
-    }
-    // ---- epilogue: warp w reads TMEM lanes 32*(w%4) .. +31 = weight rows -------------------------------
-    if (ok) ok = mbar_wait_warp(smem_u32(acc_full), 0u, abort_flag, lane);
-    if (ok) {
-      tc_fence_after();
-      const int lg = warp & 3;                 // two warps share a lane group and alternate column chunks
-      const int half = (warp - 2) >> 2;
-      const int64_t n = n0 + lg * 32 + lane;
-      const uint32_t tbase = tmem_base + ((uint32_t)(lg * 32) << 16);
-#pragma unroll 1
-      for (int c0 = 16 * half; c0 < BN; c0 += 32) {
-        if (m0 + c0 >= m_end) break;             // warp-uniform
-        uint32_t v[16], u[16];
-        tc_ld16(tbase + (uint32_t)c0, v);
-        if (TWO) tc_ld16(tbase + (uint32_t)(BN + c0), u);
-        tc_ld_wait();
-        if (DUAL && n + TC_ROWS < args.N) {       // second tile: output rows n + 128
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int64_t m = m0 + c0 + j;
-            if (m < m_end) {
-              const float f2 = __uint_as_float(u[j]) * args.xscale[m];
-              if (args.out_dtype == BQ_DT_F32) reinterpret_cast<float*>(args.out)[m * args.ldy + n + TC_ROWS] = f2;
-              else reinterpret_cast<__nv_bfloat16*>(args.out)[m * args.ldy + n + TC_ROWS] = __float2bfloat16_rn(f2);
-            }
-          }
-        }
-        if (n < args.N) {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int64_t m = m0 + c0 + j;
-            if (m < m_end) {
-              const float rs = args.xscale[m];
-              const float f = __uint_as_float(v[j]) * rs;
-              if (GATED) {
-                const float h = f / (1.0f + __expf(-f)) * (__uint_as_float(u[j]) * rs);
-                reinterpret_cast<__nv_bfloat16*>(args.out)[m * args.ldy + n] = __float2bfloat16_rn(h);
-              } else if (args.out_dtype == BQ_DT_F32) {
-                reinterpret_cast<float*>(args.out)[m * args.ldy + n] = f;
-              } else {
-                reinterpret_cast<__nv_bfloat16*>(args.out)[m * args.ldy + n] = __float2bfloat16_rn(f);
-              }
-            }
-          }
-        }
-      }
-    }
-  }
-
-  // ---- teardown ------------------------------------------------------------------------------------------
-  tc_fence_before();
-  __syncthreads();
-  if (threadIdx.x == 0 && *abort_flag) atomicExch(args.status, BQ_ERR_TIMEOUT);
-  if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)P::TMEM_COLS)
-                 : "memory");
-  }
-}
-
 // =================================================================================================
-// Variant with the A operand in tensor memory (decode / mid-size batches, BN <= 128).
-//
-// Differences from qgemm_tc_kernel: a pipeline step covers 128 k (half as many barrier round trips per
-// byte); the converted fp16 weights never touch shared memory — every converter thread owns one weight
-// row (its TMEM lane), reads that row's 64 bytes of codes from the (TMA-swizzled, so bank-conflict-free)
-// stage, converts them in registers and writes them with tcgen05.st into one of two A buffers in TMEM;
-// the issuer uses the tensor-memory form of tcgen05.mma (A from TMEM, B from shared memory).  Shared
-// memory then only holds packed codes, activations and scales, so two CTAs fit on an SM.
+// The converted fp16 weights never touch shared memory: shared memory only holds packed codes, activations and
+// scales, so two CTAs fit on an SM up to BN = 128.
 // TMEM columns: [0, NW*BN) accumulators, then NW x 2 A buffers of 64 columns (= 128 k) from column 128 (NW*BN <= 128)
 // or 256; 256 columns are allocated (two CTAs per SM) when that fits below 256, else all 512.
 // =================================================================================================
@@ -633,7 +345,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tmem_kernel(const __grid_
         const uint32_t aph = (uint32_t)(ks >> 1) & 1u;
         ok = mbar_wait(smem_u32(&a_full[a]), aph, abort_flag);   // implies the stage (and its activations) landed
         if (!ok) break;
-        TC_TRACE(1, ks, 1);
         tc_fence_after();
         const uint64_t bdesc0 = bdesc_stage0 + (uint64_t)((uint32_t)(s * P::STAGE) >> 4);   // stage offsets are < 256 KB
 #pragma unroll
@@ -646,10 +357,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tmem_kernel(const __grid_
             tc_mma_f16_ts(d_tmem, a_tmem + (uint32_t)(8 * kk),
                           bdesc0 + (uint64_t)((((kk >> 2) * BN * 128) >> 4) + 2 * (kk & 3)), idesc, 1u);
         }
-        TC_TRACE(1, ks, 2);
         tc_commit(smem_u32(&a_empty[a]));
         tc_commit(smem_u32(&empty[s]));
-        TC_TRACE(1, ks, 3);
       }
       if (ok) tc_commit(smem_u32(acc_full));
     }
@@ -663,10 +372,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tmem_kernel(const __grid_
       const int s = ks % S, a = ks & 1;
       const uint32_t ph = (uint32_t)(ks / S) & 1u, aph = (uint32_t)(ks >> 1) & 1u;
       ok = mbar_wait_warp(smem_u32(&full[s]), ph, abort_flag, lane);
-      if (threadIdx.x == 64) TC_TRACE(2, ks, 0);
       ok = ok && mbar_wait_warp(smem_u32(&a_empty[a]), aph ^ 1u, abort_flag, lane);
       if (!ok) break;
-      if (threadIdx.x == 64) TC_TRACE(2, ks, 1);
 #pragma unroll
       for (int w = 0; w < NW; ++w) {
       const uint8_t* raw = stages + s * P::STAGE + P::XT + w * P::RAW + row * P::RAW_ROW;
@@ -697,18 +404,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tmem_kernel(const __grid_
           r[8] = q2.x; r[9] = q2.y; r[10] = q2.z; r[11] = q2.w; r[12] = q3.x; r[13] = q3.y; r[14] = q3.z; r[15] = q3.w;
         }
       }
-      if (threadIdx.x == 64) TC_TRACE(2, ks, 2);
       tc_st32(tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)(P::ACOL0 + (w * NA + a) * T2_ACOLS + 32 * half), regs);
       }
       tc_st_wait();
       tc_fence_before();
-      if (threadIdx.x == 64) TC_TRACE(2, ks, 3);
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(smem_u32(&a_full[a]));
         mbar_arrive(smem_u32(&empty[s]));
       }
-      if (threadIdx.x == 64) TC_TRACE(2, ks, 4);
     }
     if (ok) ok = mbar_wait_warp(smem_u32(acc_full), 0u, abort_flag, lane);
     if (ok) {
@@ -806,34 +510,30 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
     out[m * ldy + n] = from_float<YT>(s);
   }
 }
-static float* g_part = nullptr; static size_t g_part_elems = 0;      // split-K partial tiles (grow-only)
 
-// library-owned scratch for the pre-scaled activations (grow-only; calls are serialised per process)
-static __half* g_x16 = nullptr; static size_t g_x16_elems = 0;
-static float* g_xs = nullptr;   static size_t g_xs_elems = 0;
-static int ensure_x_scratch(int64_t rows, int64_t K) {
-  const size_t need = (size_t)rows * K + 64;
-  if (need > g_x16_elems) {
-    if (g_x16) BQ_CUDA(cudaFree(g_x16));
-    g_x16 = nullptr; g_x16_elems = 0;
-    BQ_CUDA(cudaMalloc((void**)&g_x16, (need + need / 8) * sizeof(__half)));
-    g_x16_elems = need + need / 8;
-  }
-  if ((size_t)rows + 64 > g_xs_elems) {
-    if (g_xs) BQ_CUDA(cudaFree(g_xs));
-    g_xs = nullptr; g_xs_elems = 0;
-    BQ_CUDA(cudaMalloc((void**)&g_xs, ((size_t)rows * 2 + 64) * sizeof(float)));
-    g_xs_elems = (size_t)rows * 2 + 64;
-  }
-  return BQ_OK;
+// ---- library-owned scratch (see Scratch in common.cuh: never freed, growth refused during capture) -------------
+static Scratch g_x16;      // pre-scaled fp16 activations [rows, K]
+static Scratch g_xs;       // per-row power-of-two back-scales
+static Scratch g_part;     // split-K partial tiles
+
+static int ensure_x_scratch(int64_t rows, int64_t K, cudaStream_t s) {
+  int rc = scratch_ensure(&g_x16, ((size_t)rows * K + 64) * sizeof(__half), s, "tcgen05 path (activation pre-pass)");
+  if (rc) return rc;
+  return scratch_ensure(&g_xs, ((size_t)rows + 64) * sizeof(float), s, "tcgen05 path (activation scales)");
+}
+int tc_reserve(int64_t rows, int64_t K, int64_t N) {
+  int rc = ensure_x_scratch(rows, K, 0);
+  if (rc) return rc;
+  // split-K partial tiles are bounded by TC_PART_BYTES whatever the shape
+  size_t part = (size_t)rows * N * 4 * sizeof(float);
+  if (part > TC_PART_BYTES) part = TC_PART_BYTES;
+  return scratch_ensure(&g_part, part, 0, "tcgen05 path (split-K partial tiles)");
 }
 static int launch_x_prep(const void* x, int x_dtype, int64_t rows, int64_t K, cudaStream_t s) {
-  int rc = ensure_x_scratch(rows, K);
+  int rc = ensure_x_scratch(rows, K, s);
   if (rc) return rc;
-  if (x_dtype == BQ_DT_BF16)
-    x_prep_kernel<__nv_bfloat16><<<(unsigned)rows, 256, 0, s>>>((const __nv_bfloat16*)x, K, g_x16, g_xs);
-  else
-    return fail(BQ_ERR_UNSUPPORTED, "tensor path takes bf16 activations");
+  if (x_dtype != BQ_DT_BF16) return fail(BQ_ERR_UNSUPPORTED, "tensor path takes bf16 activations");
+  x_prep_kernel<__nv_bfloat16><<<(unsigned)rows, 256, 0, s>>>((const __nv_bfloat16*)x, K, (__half*)g_x16.ptr, (float*)g_xs.ptr);
   count_launch();
   BQ_CUDA(cudaGetLastError());
   return BQ_OK;
@@ -865,6 +565,7 @@ __global__ void __launch_bounds__(1024) moe_tile_list_kernel(const int32_t* __re
   if (e == E - 1) tiles[0] = pre[e];
 }
 
+
 // ---- host side --------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -881,34 +582,36 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-static int make_map_2d(CUtensorMap* tm, CUtensorMapDataType dt, int elem_bytes, const void* base, uint64_t inner,
-                       uint64_t outer, uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer,
-                       CUtensorMapSwizzle sw) {
+static int make_map_2d(CUtensorMap* tm, CUtensorMapDataType dt, const void* base, uint64_t inner, uint64_t outer,
+                       uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle sw) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fail(BQ_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
   cuuint64_t dims[2] = {inner, outer};
   cuuint64_t strides[1] = {row_stride_bytes};
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
-  (void)elem_bytes;
   CUresult r = fn(tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(BQ_ERR_CUDA, "cuTensorMapEncodeTiled failed (code " + std::to_string((int)r) + ")");
   return BQ_OK;
 }
 
-int tc_weight_maps(const uint8_t* codes, const __half* scales, int fmt, int64_t N, int64_t K, CUtensorMap* tm_codes,
-                   CUtensorMap* tm_scales) {
+// Descriptors of one weight: codes box = one 128-k step of 128 rows (int8: 128-byte rows, 128-byte swizzle; 4-bit:
+// 64-byte rows, 64-byte swizzle -- either way "one thread reads one row" is free of bank conflicts); scales box =
+// 8 groups (256 k) of 128 rows.
+static int weight_maps(const uint8_t* codes, const __half* scales, int fmt, int64_t N, int64_t K, CUtensorMap* tm_codes,
+                       CUtensorMap* tm_scales) {
   const uint64_t rb = fmt == BQ_FMT_Q8G32 ? K : K / 2;
-  int rc = make_map_2d(tm_codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, codes, rb, (uint64_t)N, rb,
-                       fmt == BQ_FMT_Q8G32 ? 64 : 32, TC_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
+  int rc = make_map_2d(tm_codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, codes, rb, (uint64_t)N, rb,
+                       fmt == BQ_FMT_Q8G32 ? 128 : 64, TC_ROWS,
+                       fmt == BQ_FMT_Q8G32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
   if (rc) return rc;
-  return make_map_2d(tm_scales, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, scales, (uint64_t)(K / GROUP), (uint64_t)N,
+  return make_map_2d(tm_scales, CU_TENSOR_MAP_DATA_TYPE_UINT16, scales, (uint64_t)(K / GROUP), (uint64_t)N,
                      (uint64_t)(K / GROUP) * 2, 8, TC_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
 }
 
 static int x_map(CUtensorMap* tm, const void* x, int64_t rows, int64_t K, int bn) {
-  return make_map_2d(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x, (uint64_t)K, (uint64_t)rows, (uint64_t)K * 2, 64,
+  return make_map_2d(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x, (uint64_t)K, (uint64_t)rows, (uint64_t)K * 2, 64,
                      (uint32_t)bn, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
@@ -920,33 +623,6 @@ bool tc_shape_ok(int64_t N, int64_t K) {
 bool tc_supported(int fmt, int64_t N, int64_t K, int x_dtype, int64_t M) {
   (void)fmt;
   return x_dtype == BQ_DT_BF16 && M >= 1 && M < ((int64_t)1 << 31) && tc_shape_ok(N, K);
-}
-
-template <int FMT, int BN, int MODE>
-static int tc_launch(const TcArgs& a, dim3 grid, cudaStream_t s) {
-  using P = TcPlan<FMT, BN, MODE>;
-  auto kern = qgemm_tc_kernel<FMT, BN, MODE>;
-  static bool configured = false;
-  if (!configured) {
-    BQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P::SMEM));
-    configured = true;
-  }
-  kern<<<grid, TC_THREADS, P::SMEM, s>>>(a);
-  count_launch();
-  BQ_CUDA(cudaGetLastError());
-  return BQ_OK;
-}
-
-template <int FMT>
-static int tc_dense_dispatch(const TcArgs& a, int bn, dim3 grid, cudaStream_t s) {
-  switch (bn) {
-    case 16:  return tc_launch<FMT, 16, 0>(a, grid, s);
-    case 32:  return tc_launch<FMT, 32, 0>(a, grid, s);
-    case 64:  return tc_launch<FMT, 64, 0>(a, grid, s);
-    case 128: return tc_launch<FMT, 128, 0>(a, grid, s);
-    case 256: return tc_launch<FMT, 256, 0>(a, grid, s);
-    default:  return tc_launch<FMT, 256, 2>(a, grid, s);      // 512: DUAL, 256 weight rows x 256 batch rows
-  }
 }
 
 static int pick_bn(int64_t M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
@@ -976,123 +652,64 @@ static int t2_dispatch(const T2Args& a, int bn, dim3 grid, cudaStream_t s) {
     default:  return t2_launch<FMT, 128, 2>(a, grid, s);      // 512: two weight tiles x 128 batch rows
   }
 }
-static int dual_enabled() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("BQ_TC_DUAL");
-    v = e ? (atoi(e) != 0) : 1;
-  }
-  return v;
-}
-// BQ_TC_TMEM (tuning switch): 0 = shared-memory A tiles for every batch size, 1 = tensor-memory A for batches up
-// to 128, 2 (default) = tensor-memory A everywhere, 3 = same but never two weight tiles per CTA
-static int tmem_variant_enabled() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("BQ_TC_TMEM");
-    v = e ? atoi(e) : 2;
-  }
-  return v;
-}
 
 int launch_qlinear_tc(const uint8_t* codes, const __half* scales, int fmt, int64_t N, int64_t K, const void* x,
                       int x_dtype, int64_t M, void* y, int y_dtype, int64_t ldy, cudaStream_t s) {
   if (x_dtype != BQ_DT_BF16) return fail(BQ_ERR_UNSUPPORTED, "tensor path takes bf16 activations");
   if ((reinterpret_cast<uintptr_t>(x) & 15) != 0) return fail(BQ_ERR_ARG, "activations must be 16-byte aligned");
-  TcArgs a;
-  memset(&a, 0, sizeof(a));
   const int bn = pick_bn(M);
   int rc = launch_x_prep(x, x_dtype, M, K, s);
   if (rc) return rc;
-  if (tmem_variant_enabled() >= (bn <= 128 ? 1 : 2)) {     // BQ_TC_TMEM: 1 = batches <= 128, 2 = all
-    T2Args t;
-    memset(&t, 0, sizeof(t));
-    // large batches are bound by the L2 -> SM traffic of codes + activations per multiply-add: 4-bit weights do
-    // better with 256 weight rows x 128 batch rows per CTA, int8 with 128 x 256 (measured)
-    const bool two = bn == 256 && fmt == BQ_FMT_Q4G32 && N >= 2 * TC_ROWS && tmem_variant_enabled() != 3;
-    const int bx = two ? 128 : bn;
-    if ((rc = x_map(&t.tm_x, g_x16, M, K, bx))) return rc;
-    const uint64_t rb = fmt == BQ_FMT_Q8G32 ? K : K / 2;
-    if ((rc = make_map_2d(&t.tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, codes, rb, (uint64_t)N, rb,
-                          fmt == BQ_FMT_Q8G32 ? 128 : 64, TC_ROWS,
-                          fmt == BQ_FMT_Q8G32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B))) return rc;
-    if ((rc = make_map_2d(&t.tm_s, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, scales, (uint64_t)(K / GROUP), (uint64_t)N,
-                          (uint64_t)(K / GROUP) * 2, 8, TC_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
-    t.xscale = g_xs; t.out = y; t.ldy = ldy; t.N = N; t.K = K; t.M = M; t.out_dtype = y_dtype; t.status = status_word();
-    const int rows_cta = two ? 2 * TC_ROWS : TC_ROWS;
-    dim3 grid2((unsigned)((M + bx - 1) / bx), (unsigned)((N + rows_cta - 1) / rows_cta));
-    const int sel = two ? 512 : bn;
-    // Few output tiles and a long K (e.g. 2048 x 16384, or a down projection at decode batch sizes): split K over
-    // grid.z so that about two CTAs per SM stream weights, each with at least 4 steps; partial tiles are summed in order.
-    const int64_t ctas = (int64_t)grid2.x * grid2.y, ksteps_all = K / T2_BK;
-    int nz = 1;
-    if (!two && ctas * 2 <= sm_count() && ksteps_all >= 8) {
-      int64_t want = (2 * (int64_t)sm_count() + ctas - 1) / ctas;
-      if (want > ksteps_all / 4) want = ksteps_all / 4;
-      while (want > 1 && (size_t)want * M * N > ((size_t)64 << 20) / sizeof(float)) --want;     // partials <= 64 MB
-      if (want > 1) {
-        int64_t kper = ((ksteps_all + want - 1) / want + 1) & ~(int64_t)1;
-        nz = (int)((ksteps_all + kper - 1) / kper);
-        if (nz > 1) {
-          const size_t need = (size_t)nz * M * N;
-          if (need > g_part_elems) {        // first call of this size: before any graph capture
-            if (g_part) BQ_CUDA(cudaFree(g_part));
-            g_part = nullptr; g_part_elems = 0;
-            BQ_CUDA(cudaMalloc((void**)&g_part, (need + need / 4) * sizeof(float)));
-            g_part_elems = need + need / 4;
-          }
-          t.kper = (int)kper; t.part = g_part; grid2.z = (unsigned)nz;
-        }
+  T2Args t;
+  memset(&t, 0, sizeof(t));
+  // large batches are bound by the L2 -> SM traffic of codes + activations per multiply-add: 4-bit weights do
+  // better with 256 weight rows x 128 batch rows per CTA, int8 with 128 x 256 (measured)
+  const bool two = bn == 256 && fmt == BQ_FMT_Q4G32 && N >= 2 * TC_ROWS;
+  const int bx = two ? 128 : bn;
+  if ((rc = x_map(&t.tm_x, g_x16.ptr, M, K, bx))) return rc;
+  if ((rc = weight_maps(codes, scales, fmt, N, K, &t.tm_w, &t.tm_s))) return rc;
+  t.xscale = (const float*)g_xs.ptr; t.out = y; t.ldy = ldy; t.N = N; t.K = K; t.M = M; t.out_dtype = y_dtype;
+  t.status = status_word();
+  const int rows_cta = two ? 2 * TC_ROWS : TC_ROWS;
+  dim3 grid2((unsigned)((M + bx - 1) / bx), (unsigned)((N + rows_cta - 1) / rows_cta));
+  const int sel = two ? 512 : bn;
+  // Few output tiles and a long K (e.g. 2048 x 16384, or a down projection at decode batch sizes): split K over
+  // grid.z so that about two CTAs per SM stream weights, each with at least 4 steps; partial tiles are summed in order.
+  const int64_t ctas = (int64_t)grid2.x * grid2.y, ksteps_all = K / T2_BK;
+  int nz = 1;
+  if (!two && ctas * 2 <= sm_count() && ksteps_all >= 8) {
+    int64_t want = (2 * (int64_t)sm_count() + ctas - 1) / ctas;
+    if (want > ksteps_all / 4) want = ksteps_all / 4;
+    while (want > 1 && (size_t)want * M * N * sizeof(float) > TC_PART_BYTES) --want;
+    if (want > 1) {
+      int64_t kper = ((ksteps_all + want - 1) / want + 1) & ~(int64_t)1;
+      nz = (int)((ksteps_all + kper - 1) / kper);
+      if (nz > 1) {
+        if ((rc = scratch_ensure(&g_part, (size_t)nz * M * N * sizeof(float), s, "tcgen05 path (split-K partial tiles)")))
+          return rc;
+        t.kper = (int)kper; t.part = (float*)g_part.ptr; grid2.z = (unsigned)nz;
       }
     }
-    rc = fmt == BQ_FMT_Q8G32 ? t2_dispatch<BQ_FMT_Q8G32>(t, sel, grid2, s) : t2_dispatch<BQ_FMT_Q4G32>(t, sel, grid2, s);
-    if (rc || nz <= 1) return rc;
-    int64_t rg = (M * N + 255) / 256;
-    if (rg > (int64_t)sm_count() * 8) rg = (int64_t)sm_count() * 8;
-    if (y_dtype == BQ_DT_F32)
-      splitk_reduce_kernel<float><<<(unsigned)rg, 256, 0, s>>>(g_part, nz, M, N, (float*)y, ldy);
-    else
-      splitk_reduce_kernel<__nv_bfloat16><<<(unsigned)rg, 256, 0, s>>>(g_part, nz, M, N, (__nv_bfloat16*)y, ldy);
-    count_launch();
-    BQ_CUDA(cudaGetLastError());
-    return BQ_OK;
   }
-  if ((rc = x_map(&a.tm_x, g_x16, M, K, bn))) return rc;
-  a.xscale = g_xs;
-  if ((rc = tc_weight_maps(codes, scales, fmt, N, K, &a.tm_w[0], &a.tm_s[0]))) return rc;
-  a.tm_w[1] = a.tm_w[0];
-  a.tm_s[1] = a.tm_s[0];
-  a.out = y; a.ldy = ldy; a.N = N; a.K = K; a.M = M; a.out_dtype = y_dtype; a.moe = 0; a.status = status_word();
-  // batches of 256 rows and more: each CTA converts 256 weight rows for one activation tile (DUAL)
-  const bool dual = bn == 256 && N >= 2 * TC_ROWS && dual_enabled();
-  const int rows_per_cta = dual ? 2 * TC_ROWS : TC_ROWS;
-  dim3 grid((unsigned)((M + bn - 1) / bn), (unsigned)((N + rows_per_cta - 1) / rows_per_cta));
-  const int sel = dual ? 512 : bn;
-  return fmt == BQ_FMT_Q8G32 ? tc_dense_dispatch<BQ_FMT_Q8G32>(a, sel, grid, s)
-                             : tc_dense_dispatch<BQ_FMT_Q4G32>(a, sel, grid, s);
+  rc = fmt == BQ_FMT_Q8G32 ? t2_dispatch<BQ_FMT_Q8G32>(t, sel, grid2, s) : t2_dispatch<BQ_FMT_Q4G32>(t, sel, grid2, s);
+  if (rc || nz <= 1) return rc;
+  int64_t rg = (M * N + 255) / 256;
+  if (rg > (int64_t)sm_count() * 8) rg = (int64_t)sm_count() * 8;
+  if (y_dtype == BQ_DT_F32)
+    splitk_reduce_kernel<float><<<(unsigned)rg, 256, 0, s>>>((const float*)g_part.ptr, nz, M, N, (float*)y, ldy);
+  else
+    splitk_reduce_kernel<__nv_bfloat16><<<(unsigned)rg, 256, 0, s>>>((const float*)g_part.ptr, nz, M, N, (__nv_bfloat16*)y, ldy);
+  count_launch();
+  BQ_CUDA(cudaGetLastError());
+  return BQ_OK;
 }
 
 // ---- MoE grouped experts ---------------------------------------------------------------------------------
-struct MoeTcState {           // device-side per-expert tensor maps + tile list, owned by the library
+struct MoeTcState {           // device-side per-expert tensor maps + tile list, owned by the expert set
   CUtensorMap* gate_up;       // [E][4] = {gate codes, gate scales, up codes, up scales}
-  CUtensorMap* down;          // [E][4] = {down codes, down scales, (unused) x2}
-  CUtensorMap* gate_up2;      // same for the tensor-memory kernel (128-k boxes, swizzled codes)
-  CUtensorMap* down2;
-  int32_t* tiles; int64_t tiles_cap;
+  CUtensorMap* down;          // [E][4] = {down codes, down scales, (same again)}
+  Scratch tiles;              // tile list of the current call (grows with the row count)
 };
-
-// descriptors of one weight for qgemm_tmem_kernel: codes box = one 128-k step of 128 rows (swizzled), scales as before
-static int t2_weight_maps(const uint8_t* codes, const __half* scales, int fmt, int64_t N, int64_t K, CUtensorMap* tm_codes,
-                          CUtensorMap* tm_scales) {
-  const uint64_t rb = fmt == BQ_FMT_Q8G32 ? K : K / 2;
-  int rc = make_map_2d(tm_codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, codes, rb, (uint64_t)N, rb,
-                       fmt == BQ_FMT_Q8G32 ? 128 : 64, TC_ROWS,
-                       fmt == BQ_FMT_Q8G32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
-  if (rc) return rc;
-  return make_map_2d(tm_scales, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, scales, (uint64_t)(K / GROUP), (uint64_t)N,
-                     (uint64_t)(K / GROUP) * 2, 8, TC_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
-}
-static std::string g_dummy;
 
 bool moe_tc_supported(const Moe* m) { return tc_shape_ok(m->F, m->H) && tc_shape_ok(m->H, m->F); }
 
@@ -1100,18 +717,12 @@ int moe_tc_prepare(Moe* m, const std::vector<const uint8_t*>* codes, const std::
   // codes/scales: [0]=gate, [1]=up, [2]=down host-side pointer lists (device addresses)
   if (!moe_tc_supported(m)) { m->tc_state = nullptr; return BQ_OK; }
   MoeTcState* st = new MoeTcState();
-  memset(st, 0, sizeof(*st));
-  std::vector<CUtensorMap> gu((size_t)m->E * 4), dn((size_t)m->E * 4), gu2((size_t)m->E * 4), dn2((size_t)m->E * 4);
+  st->gate_up = st->down = nullptr;
+  std::vector<CUtensorMap> gu((size_t)m->E * 4), dn((size_t)m->E * 4);
   for (int e = 0; e < m->E; ++e) {
-    int rc = t2_weight_maps(codes[0][e], scales[0][e], m->fmt, m->F, m->H, &gu2[e * 4 + 0], &gu2[e * 4 + 1]);
-    if (!rc) rc = t2_weight_maps(codes[1][e], scales[1][e], m->fmt, m->F, m->H, &gu2[e * 4 + 2], &gu2[e * 4 + 3]);
-    if (!rc) rc = t2_weight_maps(codes[2][e], scales[2][e], m->fmt, m->H, m->F, &dn2[e * 4 + 0], &dn2[e * 4 + 1]);
-    if (rc) { delete st; return rc; }
-    dn2[e * 4 + 2] = dn2[e * 4 + 0];
-    dn2[e * 4 + 3] = dn2[e * 4 + 1];
-    rc = tc_weight_maps(codes[0][e], scales[0][e], m->fmt, m->F, m->H, &gu[e * 4 + 0], &gu[e * 4 + 1]);
-    if (!rc) rc = tc_weight_maps(codes[1][e], scales[1][e], m->fmt, m->F, m->H, &gu[e * 4 + 2], &gu[e * 4 + 3]);
-    if (!rc) rc = tc_weight_maps(codes[2][e], scales[2][e], m->fmt, m->H, m->F, &dn[e * 4 + 0], &dn[e * 4 + 1]);
+    int rc = weight_maps(codes[0][e], scales[0][e], m->fmt, m->F, m->H, &gu[e * 4 + 0], &gu[e * 4 + 1]);
+    if (!rc) rc = weight_maps(codes[1][e], scales[1][e], m->fmt, m->F, m->H, &gu[e * 4 + 2], &gu[e * 4 + 3]);
+    if (!rc) rc = weight_maps(codes[2][e], scales[2][e], m->fmt, m->H, m->F, &dn[e * 4 + 0], &dn[e * 4 + 1]);
     if (rc) { delete st; return rc; }
     dn[e * 4 + 2] = dn[e * 4 + 0];
     dn[e * 4 + 3] = dn[e * 4 + 1];
@@ -1121,10 +732,6 @@ int moe_tc_prepare(Moe* m, const std::vector<const uint8_t*>* codes, const std::
   BQ_CUDA(cudaMalloc((void**)&st->down, bytes));
   BQ_CUDA(cudaMemcpy(st->gate_up, gu.data(), bytes, cudaMemcpyHostToDevice));
   BQ_CUDA(cudaMemcpy(st->down, dn.data(), bytes, cudaMemcpyHostToDevice));
-  BQ_CUDA(cudaMalloc((void**)&st->gate_up2, bytes));
-  BQ_CUDA(cudaMalloc((void**)&st->down2, bytes));
-  BQ_CUDA(cudaMemcpy(st->gate_up2, gu2.data(), bytes, cudaMemcpyHostToDevice));
-  BQ_CUDA(cudaMemcpy(st->down2, dn2.data(), bytes, cudaMemcpyHostToDevice));
   m->tc_state = st;
   return BQ_OK;
 }
@@ -1132,7 +739,8 @@ int moe_tc_prepare(Moe* m, const std::vector<const uint8_t*>* codes, const std::
 void moe_tc_release(Moe* m) {
   MoeTcState* st = static_cast<MoeTcState*>(m->tc_state);
   if (!st) return;
-  cudaFree(st->gate_up); cudaFree(st->down); cudaFree(st->gate_up2); cudaFree(st->down2); cudaFree(st->tiles);
+  cudaFree(st->gate_up); cudaFree(st->down);
+  if (st->tiles.ptr) cudaFree(st->tiles.ptr);     // outgrown lists stay in the library's retire list
   delete st;
   m->tc_state = nullptr;
 }
@@ -1147,17 +755,8 @@ static int t2_moe_dispatch(const T2Args& a, int bn, dim3 grid, cudaStream_t s) {
   }
 }
 
-template <int FMT, int GATED>
-static int tc_moe_dispatch(const TcArgs& a, int bn, dim3 grid, cudaStream_t s) {
-  switch (bn) {
-    case 16:  return tc_launch<FMT, 16, GATED>(a, grid, s);
-    case 64:  return tc_launch<FMT, 64, GATED>(a, grid, s);
-    default:  return tc_launch<FMT, 128, GATED>(a, grid, s);
-  }
-}
-
-int launch_moe_experts_tc(const Moe* m, const void* xp, const int32_t* offsets, int64_t P, void* hbuf, float* out,
-                          cudaStream_t s) {
+int launch_moe_experts_tc(const Moe* m, const void* xp, const int32_t* offsets, int64_t P, int64_t rows_hint, void* hbuf,
+                          float* out, cudaStream_t s) {
   MoeTcState* st = static_cast<MoeTcState*>(m->tc_state);
   if (!st) return fail(BQ_ERR_UNSUPPORTED, "tensor path unavailable for this expert shape");
   if ((reinterpret_cast<uintptr_t>(xp) & 15) != 0 || (reinterpret_cast<uintptr_t>(hbuf) & 15) != 0)
@@ -1166,68 +765,33 @@ int launch_moe_experts_tc(const Moe* m, const void* xp, const int32_t* offsets, 
   // for 16 or 64 columns, so the 16-row tile is kept for segments that are mostly below 16 rows (at an average of
   // 16 half the experts would need a second tile that streams the same weights again); up to an average of 20 rows a
   // 32-row tile covers nearly every expert in one piece and stages half the activation bytes of the 64-row one.
-  const int64_t avg = (P + m->E - 1) / m->E;
-  const int bn = avg <= 8 ? 16 : (avg <= 20 && tmem_variant_enabled()) ? 32 : avg <= 64 ? 64 : 128;
+  const int64_t avg = (rows_hint + m->E - 1) / m->E;
+  const int bn = avg <= 8 ? 16 : avg <= 20 ? 32 : avg <= 64 ? 64 : 128;
   const int64_t max_tiles = (P + bn - 1) / bn + m->E;
-  if (max_tiles > st->tiles_cap) {
-    if (st->tiles) BQ_CUDA(cudaFree(st->tiles));
-    st->tiles = nullptr; st->tiles_cap = 0;
-    BQ_CUDA(cudaMalloc((void**)&st->tiles, sizeof(int32_t) * (size_t)(2 * max_tiles + 1 + 64)));
-    st->tiles_cap = max_tiles;
-  }
-  moe_tile_list_kernel<<<1, 1024, 0, s>>>(offsets, m->E, bn, st->tiles);
+  int rc = scratch_ensure(&st->tiles, sizeof(int32_t) * (size_t)(2 * max_tiles + 1 + 64), s, "bq_moe_experts (tile list)");
+  if (rc) return rc;
+  int32_t* tiles = (int32_t*)st->tiles.ptr;
+  moe_tile_list_kernel<<<1, 1024, 0, s>>>(offsets, m->E, bn, tiles);
   count_launch();
   BQ_CUDA(cudaGetLastError());
-  if (tmem_variant_enabled()) {     // tensor-memory kernel: gate|up -> h (bf16), then down -> out (f32)
-    T2Args a;
-    memset(&a, 0, sizeof(a));
-    int rc = launch_x_prep(xp, BQ_DT_BF16, P, m->H, s);
-    if (rc) return rc;
-    if ((rc = x_map(&a.tm_x, g_x16, P, m->H, bn))) return rc;
-    a.xscale = g_xs; a.tm_list = st->gate_up2; a.offsets = offsets; a.tiles = st->tiles; a.out = hbuf; a.ldy = m->F;
-    a.N = m->F; a.K = m->H; a.M = P; a.out_dtype = BQ_DT_BF16; a.moe = 1; a.status = status_word();
-    dim3 g1((unsigned)max_tiles, (unsigned)((m->F + TC_ROWS - 1) / TC_ROWS));
-    rc = m->fmt == BQ_FMT_Q8G32 ? t2_moe_dispatch<BQ_FMT_Q8G32, 1>(a, bn, g1, s) : t2_moe_dispatch<BQ_FMT_Q4G32, 1>(a, bn, g1, s);
-    if (rc) return rc;
-    T2Args b;
-    memset(&b, 0, sizeof(b));
-    if ((rc = launch_x_prep(hbuf, BQ_DT_BF16, P, m->F, s))) return rc;   // stream order: the first GEMM is done with the scratch
-    if ((rc = x_map(&b.tm_x, g_x16, P, m->F, bn))) return rc;
-    b.xscale = g_xs; b.tm_list = st->down2; b.offsets = offsets; b.tiles = st->tiles; b.out = out; b.ldy = m->H;
-    b.N = m->H; b.K = m->F; b.M = P; b.out_dtype = BQ_DT_F32; b.moe = 1; b.status = status_word();
-    dim3 g2((unsigned)max_tiles, (unsigned)((m->H + TC_ROWS - 1) / TC_ROWS));
-    return m->fmt == BQ_FMT_Q8G32 ? t2_moe_dispatch<BQ_FMT_Q8G32, 0>(b, bn, g2, s) : t2_moe_dispatch<BQ_FMT_Q4G32, 0>(b, bn, g2, s);
-  }
-  // gate|up -> h (bf16)
-  TcArgs a;
+  // gate|up -> h (bf16), then down -> out (f32)
+  T2Args a;
   memset(&a, 0, sizeof(a));
-  int rc = launch_x_prep(xp, BQ_DT_BF16, P, m->H, s);
-  if (rc) return rc;
-  if ((rc = x_map(&a.tm_x, g_x16, P, m->H, bn))) return rc;
-  a.xscale = g_xs;
-  a.tm_list = st->gate_up; a.offsets = offsets; a.tiles = st->tiles; a.out = hbuf; a.ldy = m->F; a.N = m->F;
-  a.K = m->H; a.M = P; a.out_dtype = BQ_DT_BF16; a.moe = 1; a.status = status_word();
+  if ((rc = launch_x_prep(xp, BQ_DT_BF16, P, m->H, s))) return rc;
+  if ((rc = x_map(&a.tm_x, g_x16.ptr, P, m->H, bn))) return rc;
+  a.xscale = (const float*)g_xs.ptr; a.tm_list = st->gate_up; a.offsets = offsets; a.tiles = tiles; a.out = hbuf; a.ldy = m->F;
+  a.N = m->F; a.K = m->H; a.M = P; a.out_dtype = BQ_DT_BF16; a.moe = 1; a.status = status_word();
   dim3 g1((unsigned)max_tiles, (unsigned)((m->F + TC_ROWS - 1) / TC_ROWS));
-  rc = m->fmt == BQ_FMT_Q8G32 ? tc_moe_dispatch<BQ_FMT_Q8G32, 1>(a, bn, g1, s)
-                              : tc_moe_dispatch<BQ_FMT_Q4G32, 1>(a, bn, g1, s);
+  rc = m->fmt == BQ_FMT_Q8G32 ? t2_moe_dispatch<BQ_FMT_Q8G32, 1>(a, bn, g1, s) : t2_moe_dispatch<BQ_FMT_Q4G32, 1>(a, bn, g1, s);
   if (rc) return rc;
-  // down -> out (f32)
-  TcArgs b;
+  T2Args b;
   memset(&b, 0, sizeof(b));
-  if ((rc = launch_x_prep(hbuf, BQ_DT_BF16, P, m->F, s))) return rc;   // stream order: gate|up GEMM is done with the scratch
-  if ((rc = x_map(&b.tm_x, g_x16, P, m->F, bn))) return rc;
-  b.xscale = g_xs;
-  b.tm_list = st->down; b.offsets = offsets; b.tiles = st->tiles; b.out = out; b.ldy = m->H; b.N = m->H;
-  b.K = m->F; b.M = P; b.out_dtype = BQ_DT_F32; b.moe = 1; b.status = status_word();
+  if ((rc = launch_x_prep(hbuf, BQ_DT_BF16, P, m->F, s))) return rc;   // stream order: the first GEMM is done with the scratch
+  if ((rc = x_map(&b.tm_x, g_x16.ptr, P, m->F, bn))) return rc;
+  b.xscale = (const float*)g_xs.ptr; b.tm_list = st->down; b.offsets = offsets; b.tiles = tiles; b.out = out; b.ldy = m->H;
+  b.N = m->H; b.K = m->F; b.M = P; b.out_dtype = BQ_DT_F32; b.moe = 1; b.status = status_word();
   dim3 g2((unsigned)max_tiles, (unsigned)((m->H + TC_ROWS - 1) / TC_ROWS));
-  return m->fmt == BQ_FMT_Q8G32 ? tc_moe_dispatch<BQ_FMT_Q8G32, 0>(b, bn, g2, s)
-                                : tc_moe_dispatch<BQ_FMT_Q4G32, 0>(b, bn, g2, s);
+  return m->fmt == BQ_FMT_Q8G32 ? t2_moe_dispatch<BQ_FMT_Q8G32, 0>(b, bn, g2, s) : t2_moe_dispatch<BQ_FMT_Q4G32, 0>(b, bn, g2, s);
 }
 
 }  // namespace bq
-
-#ifdef BQ_TC_TRACE
-extern "C" int bq_debug_tc_trace(long long* out) {
-  return cudaMemcpyFromSymbol(out, bq::g_tc_trace, sizeof(bq::g_tc_trace)) == cudaSuccess ? 0 : -3;
-}
-#endif

@@ -131,6 +131,17 @@ class PackedWeight:
         self._device = d_codes.device.index or 0
         return self
 
+    def slice_rows(self, row0: int, nrows: int) -> "PackedWeight":
+        """Rows row0 .. row0+nrows-1 as a weight of their own (a view: no copy; keeps this weight alive)."""
+        view = PackedWeight.__new__(PackedWeight)
+        view.codes = None if self.codes is None else self.codes[row0:row0 + nrows]
+        view.scales = None if self.scales is None else self.scales[row0:row0 + nrows]
+        view.fmt, view.N, view.K = self.fmt, int(nrows), self.K
+        h = C.c_uint64(0)
+        _lib.check(_lib.lib().bq_weight_slice_rows(self.handle, int(row0), int(nrows), C.byref(h)))
+        view._handle, view._device, view._parent = h.value, self._device, self
+        return view
+
     def upload(self, device: Optional[int] = None) -> "PackedWeight":
         if self._handle is not None:
             return self
@@ -327,6 +338,31 @@ class PeerComm:
             _lib.check(_lib.lib().bq_comm_destroy(self.handle))
             self.handle = 0
 
+    def reset(self):
+        """After a time-out: empty the receive slots and restart the call counter, on every rank together."""
+        if self.world > 1:
+            import torch.distributed as dist
+            _torch().cuda.synchronize()
+            dist.barrier(self.group)      # no rank is still inside a call
+        _lib.check(_lib.lib().bq_comm_reset(self.handle))
+        if self.world > 1:
+            dist.barrier(self.group)      # nobody deposits into a buffer that is still being refilled
+
+    def greedy_head(self, head: "QuantLinear", x, vocab_offset: int, out=None):
+        """Vocabulary-sharded lm_head + greedy arg-max: `head` holds this rank's vocabulary slice starting at token
+        id `vocab_offset`; returns the global ids (int64 [M], ties -> lower id, identical on every rank).  The
+        per-rank (maximum, id) pairs travel through the receive slots inside one kernel."""
+        torch = _torch()
+        x2 = x.reshape(-1, head.pw.K)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        M = x2.shape[0]
+        if out is None:
+            out = torch.empty((M,), dtype=torch.int64, device=x.device)
+        _lib.check(_lib.lib().bq_lm_head_sharded(head.pw.handle, x2.data_ptr(), _dt_of_torch(x2), M, int(vocab_offset),
+                                                 self.handle, None, out.data_ptr(), _stream_ptr()))
+        return out
+
     def push_linear(self, linear: "QuantLinear", x):
         """Row-parallel partial product of `linear` on this rank's K slice.  Returns None when the GEMV deposited
         its partial sums directly in the peers' receive slots, else the local fp32 partial y (to be passed as
@@ -364,6 +400,62 @@ class PeerComm:
             rc = lib.bq_add_rmsnorm(x.data_ptr(), delta.data_ptr(), weight.data_ptr(), normed.data_ptr(), rows, H,
                                     float(eps), _dt_of_torch(x), _stream_ptr())
         _lib.check(rc)
+
+
+class PeerEP:
+    """Expert-parallel exchange through peer-mapped memory (one process per GPU): routed rows are stored straight
+    into the owning rank's receive buffer and the expert outputs straight back, with no host involvement per layer.
+    `group` carries the 64-byte IPC handles at set-up only.  max_send_rows bounds T * top_k of one call on this rank,
+    max_recv_rows the rows this rank's experts may receive (default: world * max_send_rows, which always fits)."""
+
+    def __init__(self, n_experts: int, hidden: int, max_send_rows: int, max_recv_rows: int = 0, group=None, rank: int = 0,
+                 world: int = 1):
+        torch = _torch()
+        if world > 1 or group is not None:
+            import torch.distributed as dist
+            rank, world = dist.get_rank(group), dist.get_world_size(group)
+        self.group, self.rank, self.world = group, rank, world
+        self.E, self.H = int(n_experts), int(hidden)
+        self.max_send, self.max_recv = int(max_send_rows), int(max_recv_rows or world * max_send_rows)
+        lib = _lib.lib()
+        h = C.c_uint64(0)
+        _lib.check(lib.bq_ep_create(rank, world, self.E, self.H, self.max_send, self.max_recv, C.byref(h)))
+        self.handle = h.value
+        if world > 1:
+            buf = C.create_string_buffer(64)
+            _lib.check(lib.bq_ep_handle(self.handle, buf))
+            handles = [None] * world
+            dist.all_gather_object(handles, buf.raw, group=group)
+            _lib.check(lib.bq_ep_connect(self.handle, b"".join(handles)))
+            dist.barrier(group)
+        xr, lo, cap = C.c_void_p(0), C.c_void_p(0), C.c_int64(0)
+        _lib.check(lib.bq_ep_recv_view(self.handle, C.byref(xr), C.byref(lo), C.byref(cap)))
+        self.xrecv_ptr, self.loffsets_ptr = xr.value, lo.value
+        dev = torch.device("cuda", torch.cuda.current_device())
+        # expert outputs in receive order (fp32) live here between the grouped experts and the way back
+        self.out_rows = torch.empty((self.max_recv, self.H), dtype=torch.float32, device=dev)
+
+    def close(self):
+        if getattr(self, "handle", 0):
+            if self.world > 1:
+                import torch.distributed as dist
+                _torch().cuda.synchronize()
+                dist.barrier(self.group)
+            _lib.check(_lib.lib().bq_ep_destroy(self.handle))
+            self.handle = 0
+
+    def dispatch(self, xb, idx, perm, offsets):
+        T, k = idx.shape
+        _lib.check(_lib.lib().bq_ep_dispatch(self.handle, xb.data_ptr(), idx.data_ptr(), perm.data_ptr(), offsets.data_ptr(),
+                                             T, k, _stream_ptr()))
+
+    def combine(self, inv, w, out_dtype=None):
+        torch = _torch()
+        T, k = w.shape
+        y = torch.empty((T, self.H), dtype=out_dtype or torch.float32, device=w.device)
+        _lib.check(_lib.lib().bq_ep_combine(self.handle, self.out_rows.data_ptr(), inv.data_ptr(), w.data_ptr(), T, k,
+                                            y.data_ptr(), _dt_of_torch(y), _stream_ptr()))
+        return y
 
 
 class LMHead(QuantLinear):
@@ -432,14 +524,15 @@ class MoEExperts:
     """Sparse MoE layer: router linear -> softmax/top-k -> permute -> grouped SwiGLU experts ->
     weighted combine.  Activations are bf16 between the matmuls, accumulation is fp32."""
 
-    def __init__(self, router_pw: PackedWeight, gate_pws: Sequence[PackedWeight], up_pws: Sequence[PackedWeight],
+    def __init__(self, router_pw: Optional[PackedWeight], gate_pws: Sequence[PackedWeight], up_pws: Sequence[PackedWeight],
                  down_pws: Sequence[PackedWeight], top_k: int, renormalise: bool = True, path: int = PATH_AUTO):
         E = len(gate_pws)
         if not (len(up_pws) == len(down_pws) == E) or E == 0:
             raise ValueError("gate/up/down must hold one weight per expert")
-        if router_pw.N != E:
+        # router_pw None: only this rank's experts (expert parallel: routing happens over all ranks' experts elsewhere)
+        if router_pw is not None and router_pw.N != E:
             raise ValueError("router must have one output row per expert")
-        self.router = QuantLinear(router_pw)
+        self.router = QuantLinear(router_pw) if router_pw is not None else None
         self.gate, self.up, self.down = list(gate_pws), list(up_pws), list(down_pws)
         self.E, self.top_k, self.renormalise, self.path = E, top_k, renormalise, path
         self.H, self.F = gate_pws[0].K, gate_pws[0].N
@@ -468,6 +561,17 @@ class MoEExperts:
         _lib.check(_lib.lib().bq_moe_experts(self._handle, xp.data_ptr(), offsets.data_ptr(), P, hbuf.data_ptr(),
                                              out.data_ptr(), self.path, _stream_ptr()))
         return (out, hbuf) if return_h else out
+
+    def experts_received(self, ep: "PeerEP", rows_hint: int):
+        """Grouped SwiGLU FFN of this rank's experts on the rows `ep.dispatch` delivered: reads the receive buffer and
+        the device-side row ranges of the exchange object, writes `ep.out_rows`.  `rows_hint`: rows to expect (picks
+        the token tile; the actual count is only known on the device)."""
+        torch = _torch()
+        if getattr(self, "_hrecv", None) is None or self._hrecv.shape[0] < ep.max_recv:
+            self._hrecv = torch.empty((ep.max_recv, self.F), dtype=torch.bfloat16, device=ep.out_rows.device)
+        _lib.check(_lib.lib().bq_moe_experts_ex(self._handle, ep.xrecv_ptr, ep.loffsets_ptr, ep.max_recv,
+                                                min(int(rows_hint), ep.max_recv), self._hrecv.data_ptr(),
+                                                ep.out_rows.data_ptr(), self.path, _stream_ptr()))
 
     def __call__(self, x, return_aux: bool = False):
         torch = _torch()

@@ -35,6 +35,7 @@ extern "C" {
 typedef uint64_t bq_weight_t;      /* opaque handle to a packed weight resident in HBM   */
 typedef uint64_t bq_moe_t;         /* opaque handle to a set of MoE expert weights        */
 typedef uint64_t bq_comm_t;        /* opaque handle to a peer-memory communicator         */
+typedef uint64_t bq_ep_t;          /* opaque handle to an expert-parallel exchange object */
 #define BQ_COMM_HANDLE_BYTES 64
 
 enum { BQ_FMT_Q8G32 = 0, BQ_FMT_Q4G32 = 1 };
@@ -60,6 +61,19 @@ int bq_version(void);
 /* Reads and clears the device status word (0 = no anomaly; else a BQ_ERR_* code that a
  * kernel recorded, e.g. BQ_ERR_TIMEOUT from a bounded mbarrier wait).  Synchronises.     */
 int bq_status_poll(void);
+/* Scratch owned by the library.  Several entry points keep intermediate results in buffers the library
+ * allocates on demand (the fp16 copy of the activations and split-K partial tiles of the tensor-core
+ * GEMM, the gate|up product of bq_qlinear_gated at large batches, logits of an argmax-only bq_lm_head,
+ * partial states of split-position attention, staging of bq_qlinear_host).  Rules:
+ *   - a buffer grows when a larger call arrives and the outgrown one is kept, never freed, while the
+ *     library is loaded: a CUDA graph captured earlier stays valid;
+ *   - a call that would have to grow a buffer while its stream is being captured returns
+ *     BQ_ERR_STATE and launches nothing: run one call of the largest size, or bq_reserve, first;
+ *   - the buffers are shared by all calls: order calls that use them on the device (one stream, or
+ *     events between streams).
+ * bq_reserve sizes the matmul scratch once for batches of up to max_rows rows on weights of up to
+ * [max_N, max_K]; it must not be called during stream capture.                                      */
+int bq_reserve(int64_t max_rows, int64_t max_K, int64_t max_N);
 
 /* ---- packed weights (spec: "packed quantized weights ... int8 or 4-bit codes in groups
  *      of 32 with an fp16 scale per group"; "weight packer/loader layout on device") ---- */
@@ -70,6 +84,9 @@ int bq_weight_create(const void* codes, const void* scales_f16, int64_t N, int64
 int bq_weight_create_device(const void* d_codes, const void* d_scales_f16, int64_t N,
                             int64_t K, int fmt, void* stream, bq_weight_t* out);
 int bq_weight_destroy(bq_weight_t w);
+/* A handle to rows row0 .. row0+nrows-1 of w (e.g. one expert of a stacked [E*F, H] tensor): no copy, the
+ * view shares w's memory, which must outlive it.  Every entry point takes a view like any weight.     */
+int bq_weight_slice_rows(bq_weight_t w, int64_t row0, int64_t nrows, bq_weight_t* out);
 int bq_weight_info(bq_weight_t w, int64_t* N, int64_t* K, int* fmt);
 /* Copies the weight back to HOST memory in the interface layout (undoes any device-side
  * re-tiling; used to show the device layout is a pure permutation).                      */
@@ -144,6 +161,9 @@ int bq_gated_act(const float* gate_up, void* out, int64_t rows, int64_t F, int a
 
 /* ---- MoE (spec: "router top-k, a token permute/gather, a grouped quantized expert GEMM
  *      and a weighted scatter-combine") ------------------------------------------------- */
+/* (MoE) Expert ids outside [0, E) are legal input to bq_moe_permute: such assignments are dropped --
+ * inv holds -1 for them, the sorted positions behind offsets[E] hold perm = -1, bq_moe_gather writes
+ * zero rows there and bq_moe_combine skips them.                                                    */
 /* softmax over E router logits (device f32[T,E]) -> top-k ids (int32[T,k], descending
  * probability, ties to the lower expert id) and weights f32[T,k]: the softmax probabilities,
  * rescaled to sum to 1 over the k selected experts when renormalise != 0.
@@ -189,6 +209,10 @@ int bq_moe_destroy(bq_moe_t m);
  * offsets: DEVICE int32[E+1] (read by the kernel; no host sync).                          */
 int bq_moe_experts(bq_moe_t m, const void* xp_bf16, const int32_t* offsets, int64_t P,
                    void* hbuf_bf16, float* out, int path, void* stream);
+/* Same with P only a capacity (rows the buffers hold; offsets[E] rows are in use) and rows_hint the
+ * number of rows to expect, which picks the token tile; bq_moe_experts uses rows_hint = P.          */
+int bq_moe_experts_ex(bq_moe_t m, const void* xp_bf16, const int32_t* offsets, int64_t P,
+                      int64_t rows_hint, void* hbuf_bf16, float* out, int path, void* stream);
 /* y[t,:] = sum_{slot=0..k-1} w[t,slot] * out[inv[t*k+slot], :] in slot order (deterministic,
  * no atomics).  inv as produced by bq_moe_permute.  y dtype F32 or BF16.                 */
 int bq_moe_combine(const float* out, const int32_t* inv, const float* w, int64_t T,
@@ -222,6 +246,13 @@ int bq_comm_connect_loopback(bq_comm_t c);
 /* Time limit of the flag wait, 1..60000 ms (synchronises the device when already connected). */
 int bq_comm_set_timeout_ms(bq_comm_t c, int ms);
 int bq_comm_destroy(bq_comm_t c);
+/* After a time-out (bq_status_poll returned BQ_ERR_TIMEOUT) every summing call on the communicators of
+ * this process returns BQ_ERR_STATE, and kernels already captured in a graph record BQ_ERR_TIMEOUT
+ * again without touching the slots: a late value of the abandoned call could otherwise be taken for a
+ * later one.  bq_comm_reset empties the slots and restarts the call counter; call it on EVERY rank,
+ * with a host barrier before (no rank still inside a call) and after (nobody deposits into a buffer
+ * that is about to be refilled).  Synchronises the device.                                          */
+int bq_comm_reset(bq_comm_t c);
 /* Row-parallel shard of a linear (this rank's K slice): y_partial = x . W^T, fp32, deposited
  * directly in every rank's receive slot by the GEMV's epilogue (no local y).  Decode-sized
  * calls only (the shapes of BQ_PATH_MMA), else BQ_ERR_UNSUPPORTED and nothing is launched:
@@ -238,6 +269,56 @@ int bq_allreduce(bq_comm_t c, const float* in, float* out, int64_t count, void* 
 int bq_allreduce_add_rmsnorm(bq_comm_t c, const float* in, void* x, const float* weight,
                              void* normed, int64_t rows, int64_t H, float eps, int dtype,
                              void* stream);
+
+/* Vocabulary-sharded greedy head (spec: "lm_head" column-sharded over the GPUs): w holds this rank's
+ * vocabulary slice, whose first row is token id vocab_offset.  One call computes the local logits
+ * (library scratch), the local (maximum, id) per row, exchanges the pairs through the communicator's
+ * receive slots and leaves the global arg-max id (ties -> lower id, identical on every rank) in ids_out
+ * (device int32[M], may be NULL) and/or ids64_out (device int64[M], may be NULL).  2*M <= max_elems.
+ * Counts as one summing call of the communicator; graph-capturable.                                 */
+int bq_lm_head_sharded(bq_weight_t w, const void* x, int x_dtype, int64_t M, int64_t vocab_offset,
+                       bq_comm_t c, int32_t* ids_out, int64_t* ids64_out, void* stream);
+
+/* ---- expert-parallel shard boundary (spec: "experts shard expert-parallel across the 8 GPUs ...
+ *      all-to-all over NVLink only at those shard boundaries"): the two all-to-alls around the grouped
+ *      experts as plain stores into the owning rank's memory.  The reference has no counterpart.
+ * Ranks r = 0..world-1 each own experts r*E/world .. (r+1)*E/world - 1; tokens stay on the rank that
+ * holds them.  Set-up mirrors the communicator above (create, exchange 64-byte handles, connect, host
+ * barrier; world == 1 needs no connect).  max_send_rows bounds T*top_k of one call on this rank,
+ * max_recv_rows the rows this rank's experts may receive in one call (safe value: the sum of T*top_k
+ * over all ranks); a row that would not fit records BQ_ERR_ARG in the status word and is skipped.
+ * Per MoE layer, on every rank, in this order on one stream (all ranks must make the same calls):
+ *   bq_moe_route, bq_moe_permute (by GLOBAL expert id, E experts)            -- local
+ *   bq_ep_dispatch    rows travel to their owners; returns once the wait for every source is queued
+ *   bq_ep_recv_view   -> receive buffer (bf16 [max_recv_rows, H], rows grouped by local expert, sources
+ *                        in rank order) and the DEVICE int32[E/world + 1] row ranges of the local experts
+ *   bq_moe_experts_ex(local expert set, receive buffer, those row ranges, P = max_recv_rows, ...)
+ *   bq_ep_combine     output rows travel back (fp32), y[t] = sum_slot w * row in slot order: bit-identical
+ *                     to bq_moe_combine on one GPU given the same expert outputs.
+ * Waits are bounded (5 s unless changed): on expiry BQ_ERR_TIMEOUT is recorded, the object stays failed
+ * and must be destroyed.  All calls are graph-capturable; the call counter advances on the device.     */
+int bq_ep_create(int rank, int world, int n_experts, int64_t hidden, int64_t max_send_rows,
+                 int64_t max_recv_rows, bq_ep_t* out);
+int bq_ep_handle(bq_ep_t ep, void* out_handle /* BQ_COMM_HANDLE_BYTES */);
+int bq_ep_connect(bq_ep_t ep, const void* handles /* world x BQ_COMM_HANDLE_BYTES */);
+int bq_ep_set_timeout_ms(bq_ep_t ep, int ms);
+int bq_ep_destroy(bq_ep_t ep);
+/* x: device bf16 [T, H]; idx: device int32 [T, top_k] (global expert ids); perm, offsets: from
+ * bq_moe_permute(idx, T, top_k, E).                                                                 */
+int bq_ep_dispatch(bq_ep_t ep, const void* x_bf16, const int32_t* idx, const int32_t* perm,
+                   const int32_t* offsets, int64_t T, int top_k, void* stream);
+/* Self-test aid: the row bookkeeping every rank derives from the exchanged counts, run for a GIVEN count matrix
+ * (device int32 [world][E]: rows source s routes to expert x) as rank `rank` of `world`, nothing exchanged.
+ * tables_out (device int32, E + (E/world + 1) + (E/world*world + 1) + E/world*world entries): dest_base[E],
+ * local row ranges [E/world + 1], first received row of every (local expert, source) block [+1 = rows
+ * received], position of each block's first row in its source's sorted order.  Synchronises the stream. */
+int bq_ep_layout_selftest(const int32_t* counts, int rank, int world, int n_experts, int32_t* tables_out,
+                          void* stream);
+int bq_ep_recv_view(bq_ep_t ep, void** xrecv_bf16, const int32_t** local_offsets, int64_t* max_rows);
+/* out_rows: device f32 [max_recv_rows, H], the expert outputs in receive order; inv, w: as for
+ * bq_moe_combine (inv from this rank's bq_moe_permute).                                             */
+int bq_ep_combine(bq_ep_t ep, const float* out_rows, const int32_t* inv, const float* w, int64_t T,
+                  int top_k, void* y, int y_dtype, void* stream);
 
 #ifdef __cplusplus
 }

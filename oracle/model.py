@@ -2,7 +2,11 @@
 reference checkout has no LLM runtime).  Gemma-shaped block: RMSNorm -> q/k/v -> RoPE -> causal GQA attention
 with a KV cache -> o -> residual -> RMSNorm -> GeGLU FFN -> residual; final RMSNorm -> lm_head -> argmax.
 Open choices (the specification is silent): RMSNorm weight multiplies directly (initialised to 1), eps 1e-6,
-no embedding scaling, no logit soft-capping, rotate-half RoPE with base 10000, untied fp32 embedding table."""
+no embedding scaling, no logit soft-capping, rotate-half RoPE with base 10000, untied fp32 embedding table.
+A config with `n_experts` > 0 replaces the dense FFN of every layer by the sparse-MoE FFN of spec.moe_forward
+(router -> softmax -> top-k -> SwiGLU experts -> weighted combine); the MoE block sees its input rounded to bf16
+(`moe_in_bf16`, the activation type the specification names for the quantized matmuls) and rounds the hidden
+activation to bf16 between the expert matmuls, as spec.moe_experts does."""
 from __future__ import annotations
 
 import numpy as np
@@ -60,6 +64,15 @@ class OracleDecoder:
             o = np.einsum("hts,shd->thd", p, vv).reshape(T, H * D).astype(np.float32)
             x = x + self._lin(f"l{l}.o", o)
             h = rmsnorm(x, self.w[f"l{l}.norm2"])
+            if c.get("n_experts", 0):
+                E = c["n_experts"]
+                if c.get("moe_in_bf16", True):
+                    h = spec.bf16_round(h)
+                y, _ = spec.moe_forward(h, self.w[f"l{l}.router"], [self.w[f"l{l}.e{e}.gate"] for e in range(E)],
+                                        [self.w[f"l{l}.e{e}.up"] for e in range(E)],
+                                        [self.w[f"l{l}.e{e}.down"] for e in range(E)], c["fmt"], c["top_k"])
+                x = x + y
+                continue
             a = spec.gelu_tanh(self._lin(f"l{l}.gate", h)) * self._lin(f"l{l}.up", h)
             x = x + self._lin(f"l{l}.down", a)
         self.pos += T
@@ -90,5 +103,11 @@ def random_weights(cfg: dict, seed: int = 0):
         w[f"l{l}.norm2"] = np.ones(Hd, np.float32)
         w[f"l{l}.q"], w[f"l{l}.k"], w[f"l{l}.v"] = q(H * D, Hd), q(KV * D, Hd), q(KV * D, Hd)
         w[f"l{l}.o"] = q(Hd, H * D)
-        w[f"l{l}.gate"], w[f"l{l}.up"], w[f"l{l}.down"] = q(F, Hd), q(F, Hd), q(Hd, F)
+        if c.get("n_experts", 0):
+            Fm = c["moe_ffn"]
+            w[f"l{l}.router"] = spec.quantize(rng.normal(0, 0.3, (c["n_experts"], Hd)).astype(np.float32), c["fmt"])
+            for e in range(c["n_experts"]):
+                w[f"l{l}.e{e}.gate"], w[f"l{l}.e{e}.up"], w[f"l{l}.e{e}.down"] = q(Fm, Hd), q(Fm, Hd), q(Hd, Fm)
+        else:
+            w[f"l{l}.gate"], w[f"l{l}.up"], w[f"l{l}.down"] = q(F, Hd), q(F, Hd), q(Hd, F)
     return w

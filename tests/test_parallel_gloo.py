@@ -113,21 +113,6 @@ def _tp_case(rank):
         ref_logits, ref_ids = spec.lm_head(xq, *qv, fmt)
         assert ids[0] == 100 and np.array_equal(ids, ref_ids)
         assert np.allclose(_np(head.logits(torch.from_numpy(xq))), ref_logits, atol=1e-5)
-        # same exchange written as a sum of one-hot rows (the route the peer-memory communicator takes on GPUs);
-        # the stand-in communicator sums through the process group
-        class SumComm:
-            world, rank_ = WORLD, rank
-
-            def __init__(self):
-                self.rank = rank
-
-            def all_reduce(self, t):
-                t = t.clone()
-                torch.distributed.all_reduce(t)
-                return t
-        head2 = parallel.VocabParallelHead(_oracle_linear(*spec.shard(*qv, fmt, "n", rank, WORLD), fmt), V // WORLD,
-                                           comm=SumComm())
-        assert np.array_equal(head2.greedy(torch.from_numpy(xq)).numpy(), ref_ids)
 
 
 def _ep_case(rank):
@@ -163,9 +148,62 @@ def _ep_case(rank):
         assert tuple(y.shape) == (0, H)
 
 
+def _ep_layout_case(rank):
+    """The device-side exchange's row bookkeeping (parallel.ep_layout restates ep_layout_kernel): rows placed by
+    dest_base / returned by blk_start + blk_src must reproduce the unsharded oracle layer.  Peer memory is played
+    by all-gathering every rank's rows together with their destination indices."""
+    from chadslab_b200 import parallel
+    rng = np.random.default_rng(4)
+    E, H, F, k, fmt = 8, 64, 96, 3, 1
+    El = E // WORLD
+    q = lambda W: spec.quantize(W.astype(np.float32), fmt)
+    router = q(rng.normal(0, 0.5, (E, H)))
+    gate = [q(rng.normal(0, 0.1, (F, H))) for _ in range(E)]
+    up = [q(rng.normal(0, 0.1, (F, H))) for _ in range(E)]
+    down = [q(rng.normal(0, 0.1, (H, F))) for _ in range(E)]
+    xs = [spec.bf16_round(rng.normal(0, 1, (t, H)).astype(np.float32)) for t in (11, 6)]
+    x = xs[rank]
+    lg, lu, ld = (parallel.shard_experts(w_, rank, WORLD) for w_ in (gate, up, down))
+    idx, w = spec.moe_route(x, router[0], router[1], fmt, k)
+    perm, offsets = spec.moe_permute(idx, E)
+    inv = np.empty_like(perm)
+    inv[perm] = np.arange(len(perm), dtype=np.int32)
+    counts = [None] * WORLD
+    dist.all_gather_object(counts, np.diff(offsets).tolist())
+    dest_base, loffsets, blk_start, blk_src = parallel.ep_layout(counts, rank)
+    # dispatch: sorted position p (expert e, j-th of my rows for e) -> row dest_base[e] + j on rank e // El
+    ex = idx.reshape(-1)[perm]
+    dst_row = dest_base[ex] + (np.arange(len(perm)) - offsets[ex])
+    sent = [None] * WORLD
+    dist.all_gather_object(sent, (ex // El, dst_row, x[perm // k]))
+    n_recv = int(blk_start[-1])
+    xrecv = np.full((n_recv, H), np.nan, np.float32)
+    for owner, rows, data in sent:
+        m = owner == rank
+        xrecv[rows[m]] = data[m]
+    assert not np.isnan(xrecv).any() and n_recv == loffsets[-1]         # every row written exactly where expected
+    out = spec.moe_experts(xrecv, loffsets, lg, lu, ld, fmt)
+    # way back: received row i of block b = (local expert, source s) -> position blk_src[b] + (i - blk_start[b]) on s
+    blk = np.searchsorted(blk_start[1:], np.arange(n_recv), side="right")
+    back = [None] * WORLD
+    dist.all_gather_object(back, (blk % WORLD, blk_src[blk] + (np.arange(n_recv) - blk_start[blk]), out))
+    yback = np.full((len(perm), H), np.nan, np.float32)
+    for src, pos, data in back:
+        m = src == rank
+        yback[pos[m]] = data[m]
+    assert not np.isnan(yback).any()
+    y = spec.moe_combine(yback, perm, w)
+    ref, _ = spec.moe_forward(x, router, gate, up, down, fmt, k)
+    assert spec.rel_err(y, ref) < 1e-6
+
+
 def test_tensor_parallel_two_ranks():
     _run(_tp_case)
 
 
 def test_expert_parallel_two_ranks():
     _run(_ep_case)
+
+
+def test_expert_parallel_device_layout_two_ranks():
+    _run(_ep_layout_case)

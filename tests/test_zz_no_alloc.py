@@ -52,6 +52,37 @@ def test_noalloc_permute_matches_scratch_variant_twice(cuda_lib):
         assert np.array_equal(i1[p1], np.arange(T * k))
 
 
+def test_noalloc_permute_allocates_nothing_and_handles_edge_inputs(cuda_lib):
+    """After its first call on the device the entry point leaves the amount of free device memory unchanged (it may
+    not allocate: that is its reason to exist), an empty batch gives all-zero offsets, and expert ids outside
+    [0, E) are dropped exactly as bq_moe_permute drops them."""
+    import torch
+    lib = cuda_lib
+    E, k = 16, 2
+    g = torch.Generator(device="cuda").manual_seed(5)
+    idx = torch.randint(0, E, (500, k), dtype=torch.int32, device="cuda", generator=g)
+    idx[7, 0], idx[100, 1] = E + 3, -1
+    (p0, i0, o0), (p1, i1, o1) = _permute_both(lib, torch, idx, E)          # includes this device's first call
+    assert np.array_equal(p0, p1) and np.array_equal(i0, i1) and np.array_equal(o0, o1)
+    assert o1[-1] == 500 * k - 2 and (i1 == -1).sum() == 2 and (p1[o1[-1]:] == -1).all()
+    perm = torch.empty((500 * k,), dtype=torch.int32, device="cuda")
+    inv = torch.empty_like(perm)
+    offsets = torch.empty((E + 1,), dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    for _ in range(3):
+        assert lib.bq_moe_permute_noalloc(idx.data_ptr(), 500, k, E, perm.data_ptr(), inv.data_ptr(), offsets.data_ptr(),
+                                          torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+    assert np.array_equal(perm.cpu().numpy(), p1)
+    offsets.fill_(-7)
+    assert lib.bq_moe_permute_noalloc(idx.data_ptr(), 0, k, E, perm.data_ptr(), inv.data_ptr(), offsets.data_ptr(),
+                                      torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    assert bool((offsets == 0).all())
+
+
 def test_noalloc_permute_rejects_sizes_beyond_the_array(cuda_lib):
     import torch
     from chadslab_b200 import _lib

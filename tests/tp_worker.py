@@ -110,6 +110,50 @@ def main():
     ref, _ = spec.moe_forward(x, router, gate, up, down, fmt, k)
     err = spec.rel_err(y, ref)
     assert err <= 4e-3, err      # layer-level bound (bf16 hidden activation between the expert matmuls)
+    # the same layer with both exchanges on the device (peer-memory stores, no collective call, no host step):
+    # bit-identical to the route through the process group, eagerly and from a replayed CUDA graph
+    ep = cb.PeerEP(E, H, max_send_rows=64)
+    local2 = cb.MoEExperts(None, [mk(g) for g in lg_], [mk(u) for u in lu_], [mk(d) for d in ld_], top_k=k)
+    layer2 = parallel.ExpertParallelMoE(cb.QuantLinear(mk(router)), None, E, k, ep=ep, local_moe=local2)
+    xt = torch.from_numpy(x).cuda().to(torch.bfloat16)
+    for _ in range(3):
+        y2 = layer2(xt)
+        assert np.array_equal(y2.cpu().numpy(), y)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        yg = layer2(xt)
+    for _ in range(3):
+        yg.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert np.array_equal(yg.cpu().numpy(), y)
+    assert cb._lib.lib().bq_status_poll() == 0
+    # ---- sparse-MoE decoder, expert parallel: every rank decodes its own sequences ----
+    from chadslab_b200.decoder import MoEDecoder
+    cfg = dict(layers=2, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=0, vocab=1024, fmt=1, n_experts=8, top_k=2,
+               moe_ffn=256)
+    w = omodel.random_weights(cfg, seed=12)
+    prompts = np.random.default_rng(9).integers(0, cfg["vocab"], (world, 6))
+    ref_tokens, ref_logits = omodel.OracleDecoder(cfg, w).generate(list(prompts[rank]), 3)
+    ep2 = cb.PeerEP(cfg["n_experts"], cfg["hidden"], max_send_rows=6 * cfg["top_k"])
+    dec = MoEDecoder.from_numpy(DecoderConfig(**cfg), w, act_dtype=torch.float32, rank=rank, world=world, max_seq=32, ep=ep2)
+    pt = torch.from_numpy(prompts[rank])[None].cuda()
+    lg = dec.logits(pt)[0, -1].cpu().numpy()
+    assert spec.rel_err(lg, ref_logits[0]) <= 2e-3, spec.rel_err(lg, ref_logits[0])
+    dec.reset()
+    first = dec.next_tokens(pt)
+    step, tokens = dec.make_graph_stepper(1, first, start_pos=dec.pos)
+    got = [int(first[0])]
+    for _ in range(2):
+        step()
+        got.append(int(tokens[0]))
+    assert got == ref_tokens, (got, ref_tokens)
+    assert cb._lib.lib().bq_status_poll() == 0
+    del step
+    ep2.close()
+    ep.close()
     dist.barrier()
     if rank == 0:
         print("tp_worker ok")
