@@ -1,19 +1,27 @@
 #!/usr/bin/env python
-"""Benchmark of the block-quantized matmul hot path.
+"""Benchmark of the block-quantized matmul hot path, end to end.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--extras 0|1]
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...      (N > 1)
 
-Workload (configs[1] of BASELINE.json, decode-shaped part): the standalone quantized matmul sweep
-at M = 1 — W[N,K] ~ N(0, 0.02) quantized to int8-g32 and 4-bit-g32, x[1,K] ~ N(0,1) in bf16, for
-(N,K) in {(2048,2048), (16384,2048), (2048,16384), (256000,2048)}.  One "step" is one pass over
-all 8 (shape, format) problems.  Metric: quantized GEMV HBM GB/s = algorithmic bytes (codes +
-fp16 scales + activations + fp32 outputs) / device time.  Small shapes rotate over enough distinct
-weight copies that the bytes touched between two uses of a copy exceed the 126 MB L2.
+Headline (every N): greedy decode tokens/s of the Gemma-7B-shaped decoder of configs[2] — 28 layers, hidden 3072,
+16 heads of 256, GeGLU 24576, vocabulary 256000, every linear 4-bit group-32, bf16 activations, a 2048-position
+context, batch HEADLINE_BATCH — tensor-parallel over the N GPUs of the run (column / row sharded linears, sums
+through the peer-memory communicator, vocabulary-sharded head).  One "step" is one decode step of the whole batch;
+the K timed steps are K replays of the captured CUDA graph between two events (device-resident inputs), `e2e` is
+the same step driven from host buffers: token ids copied in from pinned memory and the new ids copied back out
+every step.  Strong scaling: the work per step is fixed, N GPUs share it.  Weights are random-init (seeded,
+N(0, 0.02), quantized with the format's rule) and the context is synthetic (random K/V in the cache).
 
-Lines printed: one JSON object on rank 0.
-Multi-GPU (torchrun): every rank runs the same sweep on its own GPU with its own weights (the
-sweep has no cross-GPU dependency: weak scaling, no collective on the data path); value is the
-sum of bytes over ranks / max time over ranks.
+`roofline` is the largest quantized-matmul launch of the step (the lm_head GEMV / GEMM on this rank's vocabulary
+slice), timed alone with CUDA events, L2 flushed between launches.  `extras` holds what else the configs name:
+the standalone sweep of configs[1] (with per-problem and aggregate fractions of the HBM peak), the Gemma-2B-shaped
+decoder of configs[0], all three batch sizes of configs[2], one sparse-MoE layer and the whole sparse-MoE decoder of
+configs[3], the long prefill of configs[4], and `parity`: a small same-weights decoder and MoE layer sharded over
+the N ranks of this run and compared with the numpy oracle (the oracle is only ever the checker).
+
+`--impl reference`: the reference checkout has no code for this path, so the CPU arm times the self-authored numpy
+oracle on the host cores on a bounded sample of the same decode step (stated in `cpu_baseline.sample`).
 """
 from __future__ import annotations
 
@@ -31,12 +39,11 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+HEADLINE_BATCH = 64
+HEADLINE_CTX = 2048
 SHAPES = [(2048, 2048), (16384, 2048), (2048, 16384), (256000, 2048)]
 FMT_NAMES = {0: "int8_g32", 1: "q4_g32"}
 L2_BYTES = 126 * 1024 * 1024
-DOMINANT = (256000, 2048, 0)      # the launch with the most bytes: int8 lm_head-shaped GEMV
-NCU_TRAFFIC_RATIO = 146.4 / 142.7   # measured DRAM traffic / algorithmic bytes (profiles/qgemv_mma_65536x2048.md)
-
 
 from chadslab_b200.synth import algorithmic_bytes, make_device_weight  # noqa: E402
 
@@ -45,8 +52,9 @@ def load_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
         d = json.load(open(p))
-        return float(d["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -99,79 +107,160 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------------
-# synthetic data
+# CPU arm: the numpy oracle on a bounded sample of the headline decode step
 # ------------------------------------------------------------------------------------------------
-def build_problems(torch, cb, seed):
+def cpu_decode_sample(steps: int, warmup: int, batch: int = HEADLINE_BATCH, ctx: int = HEADLINE_CTX):
+    """One decoder layer of the Gemma-7B shape (q4-g32, fp32 activations, a `ctx`-position KV cache for `batch`
+    sequences) plus 32000 rows of the head, timed with the numpy oracle's own functions; a full step is 28 such
+    layers and 8 such head slices, so step time = 28 t_layer + 8 t_head (extrapolated, stated in `sample`)."""
+    from oracle import model as omodel
+    from oracle import spec
+    from threadpoolctl import threadpool_info
+    from chadslab_b200.decoder import GEMMA_7B_SHAPE as c
+    rng = np.random.default_rng(0)
+    fmt, Hd, D, Hq, Hkv, Fd = c.fmt, c.hidden, c.head_dim, c.n_heads, c.n_kv_heads, c.ffn
+
+    def q(n, k):       # N(0, 0.02) weights; one 512-row block of random values tiled over the rows keeps set-up short
+        blk = rng.normal(0, 0.02, (min(n, 512), k)).astype(np.float32)
+        return spec.quantize(np.tile(blk, ((n + 511) // 512, 1))[:n], fmt)
+    w = {"q": q(Hq * D, Hd), "k": q(Hkv * D, Hd), "v": q(Hkv * D, Hd), "o": q(Hd, Hq * D), "gate": q(Fd, Hd), "up": q(Fd, Hd),
+         "down": q(Hd, Fd), "head": q(32000, Hd)}
+    kc = np.tile(rng.normal(0, 1, (1, 64, Hkv, D)).astype(np.float32), (batch, (ctx + 1 + 63) // 64, 1, 1))[:, :ctx + 1]
+    vc = kc[:, ::-1].copy()
+    x = rng.normal(0, 1, (batch, Hd)).astype(np.float32)
+    g1 = np.ones(Hd, np.float32)
+    pos = np.full((1,), ctx)
+
+    def lin(name, a):
+        return spec.qlinear(a, w[name][0], w[name][1], fmt)
+
+    def layer(x):
+        h = omodel.rmsnorm(x, g1)
+        qh = np.stack([omodel.rope(r[None], pos)[0] for r in lin("q", h).reshape(batch, Hq, D)])
+        kh = np.stack([omodel.rope(r[None], pos)[0] for r in lin("k", h).reshape(batch, Hkv, D)])
+        kc[:, ctx], vc[:, ctx] = kh, lin("v", h).reshape(batch, Hkv, D)
+        rep = Hq // Hkv
+        att = np.einsum("bhd,bshd->bhs", qh, np.repeat(kc, rep, axis=2) if rep > 1 else kc) / np.sqrt(np.float32(D))
+        p = spec.softmax(att)
+        o = np.einsum("bhs,bshd->bhd", p, np.repeat(vc, rep, axis=2) if rep > 1 else vc).reshape(batch, Hq * D)
+        x = x + lin("o", o.astype(np.float32))
+        h = omodel.rmsnorm(x, g1)
+        return x + lin("down", spec.gelu_tanh(lin("gate", h)) * lin("up", h))
+
+    def head(x):
+        return np.argmax(lin("head", omodel.rmsnorm(x, g1)), axis=-1)
+
+    tl, th = [], []
+    for i in range(max(1, warmup) + steps):
+        t0 = time.perf_counter()
+        y = layer(x)
+        t1 = time.perf_counter()
+        head(y)
+        t2 = time.perf_counter()
+        if i >= max(1, warmup):
+            tl.append(t1 - t0); th.append(t2 - t1)
+    step_s = c.layers * statistics.mean(tl) + (c.vocab / 32000.0) * statistics.mean(th)
+    threads = max([i.get("num_threads", 1) for i in threadpool_info() if i.get("user_api") == "blas"] or [1])
+    return {"value": batch / step_s, "unit": "tokens/s", "cores": int(threads), "kind": "port",
+            "sample": "numpy oracle (dequantize to fp32 + np.matmul, fp32 activations): ONE layer of the Gemma-7B shape "
+                      f"(q4-g32, batch {batch}, {ctx}-position context) and 32000 of the 256000 head rows, timed "
+                      f"{steps}x; step = 28 x layer + 8 x head slice (extrapolated); host cores={os.cpu_count() or 0}, "
+                      f"affinity={len(os.sched_getaffinity(0))}",
+            "ms_per_step": step_s * 1e3, "layer_ms": statistics.mean(tl) * 1e3, "head_slice_ms": statistics.mean(th) * 1e3}
+
+
+def headline_config(world: int):
+    return {"workload": f"configs[2]: Gemma-7B-shaped decoder (28 layers, hidden 3072, 16 heads x 256, GeGLU 24576, vocab 256000), "
+                        f"all linears q4-g32, bf16 activations, greedy decode at batch {HEADLINE_BATCH} behind a "
+                        f"{HEADLINE_CTX}-position context (synthetic K/V)",
+            "batch": HEADLINE_BATCH, "context": HEADLINE_CTX, "parallelism": f"tp{world}" if world > 1 else "single GPU",
+            "l2": "one step streams this rank's packed weights and KV cache, several times the 126 MB L2",
+            "launch": "the K timed steps are K replays of one captured CUDA graph"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 2))
+    cb = cpu_decode_sample(steps, 1)
+    line = {"impl": "reference", "metric": "decode_tokens_per_s", "value": cb["value"], "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": steps, "warmup": 1, "ms_per_step": cb["ms_per_step"],
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": dict(headline_config(1), note="the reference checkout has no implementation of this path; this arm times "
+                                                   "the self-authored numpy oracle on the host cores on a bounded sample"),
+            "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------------
+# extras
+# ------------------------------------------------------------------------------------------------
+def _events(torch):
+    return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+
+def run_sweep(torch, cb, lib, seed, reps=20):
+    """configs[1]: the standalone quantized matmul sweep.  M = 1 for all 8 (shape, format) problems as one CUDA graph
+    (weights rotate over distinct copies so that more than 2 x L2 is touched between reuses), then M = 8 ... 4096."""
+    from chadslab_b200 import _lib
+    peaks = load_peaks()
     gen = torch.Generator(device="cuda").manual_seed(seed)
+    stream = torch.cuda.current_stream().cuda_stream
     problems = []
     for (N, K) in SHAPES:
         for fmt in (0, 1):
             wbytes = algorithmic_bytes(N, K, fmt, 0)
             copies = 1 if wbytes > 2 * L2_BYTES else int(np.ceil(2 * L2_BYTES / wbytes))
             base = make_device_weight(torch, N, K, fmt, gen)
-            pws = []
-            for c in range(copies):
-                if c:   # distinct memory, rolled rows (cheap) so contents differ as well
-                    codes, scales = base[0].roll(c, 0).contiguous(), base[1].roll(c, 0).contiguous()
-                else:
-                    codes, scales = base
-                pws.append(cb.PackedWeight.from_device(codes, scales, fmt))
+            pws = [cb.PackedWeight.from_device(base[0].roll(c, 0).contiguous() if c else base[0],
+                                               base[1].roll(c, 0).contiguous() if c else base[1], fmt) for c in range(copies)]
             x = torch.randn((1, K), device="cuda", generator=gen).to(torch.bfloat16)
             y = torch.empty((1, N), dtype=torch.float32, device="cuda")
-            problems.append({"N": N, "K": K, "fmt": fmt, "pws": pws, "x": x, "y": y, "i": 0,
-                             "bytes": algorithmic_bytes(N, K, fmt, 1)})
+            problems.append({"N": N, "K": K, "fmt": fmt, "pws": pws, "x": x, "y": y, "i": 0, "bytes": algorithmic_bytes(N, K, fmt, 1)})
             del base
-    return problems
 
-
-# ------------------------------------------------------------------------------------------------
-# CPU arm (oracle port of the path; the reference checkout has no code for it)
-# ------------------------------------------------------------------------------------------------
-def cpu_sample(steps: int, warmup: int):
-    """The numpy oracle on a bounded sample of the sweep: every shape/format at M=1, the 256000-row
-    shape cut to its first 32000 rows.  Weights are dequantized per call (as the GPU kernel does)."""
-    from oracle import spec
-    from threadpoolctl import threadpool_info
-    rng = np.random.default_rng(0)
-    probs = []
-    for (N, K) in SHAPES:
-        n = min(N, 32000)
-        W = rng.normal(0, 0.02, (n, K)).astype(np.float32)
-        for fmt in (0, 1):
-            codes, scales = spec.quantize(W, fmt)
-            x = spec.bf16_round(rng.normal(0, 1, (1, K)).astype(np.float32))
-            probs.append((codes, scales, fmt, x, algorithmic_bytes(n, K, fmt, 1)))
-    total = sum(p[4] for p in probs)
-
-    def one_pass():
-        for codes, scales, fmt, x, _ in probs:
-            spec.qlinear(x, codes, scales, fmt)
-
-    for _ in range(max(1, warmup)):
-        one_pass()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        one_pass()
-    dt = (time.perf_counter() - t0) / steps
-    threads = max([i.get("num_threads", 1) for i in threadpool_info() if i.get("user_api") == "blas"] or [1])
-    return {"value": total / dt / 1e9, "unit": "GB/s", "cores": int(threads), "kind": "port",
-            "sample": "numpy oracle (dequantize to fp32 + np.matmul), M=1, all 8 problems of the sweep with the "
-                      "256000-row shape cut to 32000 rows; host cores=%d, affinity=%d" % (
-                          os.cpu_count() or 0, len(os.sched_getaffinity(0))),
-            "ms_per_pass": dt * 1e3}
-
-
-# ------------------------------------------------------------------------------------------------
-# extras (reported beside the headline, N=1 only): the rest of configs[1] and a decode loop
-# ------------------------------------------------------------------------------------------------
-def run_extras(torch, cb, lib, problems):
-    from chadslab_b200 import _lib
-    from chadslab_b200.decoder import GEMMA_2B_SHAPE, QuantDecoder
-    stream = torch.cuda.current_stream().cuda_stream
-    out = {"batch_sweep": [], "note": "batch_sweep: same weights as the headline, bf16 activations, CUDA events, "
-                                      "3 launches each after 1 warm-up; decode: Gemma-2B-shaped decoder, int8-g32, "
-                                      "batch 1, random-init, 128-token prefill then 32 greedy tokens replayed from a "
-                                      "CUDA graph"}
+    def launch(p, s):
+        pw = p["pws"][p["i"] % len(p["pws"])]
+        p["i"] += 1
+        _lib.check(lib.bq_qlinear(pw.handle, p["x"].data_ptr(), cb.DT_BF16, 1, p["y"].data_ptr(), cb.DT_F32, s))
+    for _ in range(3):
+        for p in problems:
+            launch(p, stream)
+    torch.cuda.synchronize()
+    graph, cap = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    cap.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.graph(graph, stream=cap):
+        cs = torch.cuda.current_stream().cuda_stream
+        for _ in range(reps):
+            for p in problems:
+                launch(p, cs)
+    graph.replay()
+    torch.cuda.synchronize()
+    a, b = _events(torch)
+    a.record()
+    graph.replay()
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / reps
+    step_bytes = sum(p["bytes"] for p in problems)
+    out = {"workload": "configs[1], M = 1: 8 (shape, format) problems per pass, bf16 x, fp32 y; one CUDA-graph replay of "
+                       f"{reps} passes between two events", "ms_per_pass": round(ms, 4), "gbs": round(step_bytes / ms / 1e6, 1),
+           "aggregate_frac": round(step_bytes / ms / 1e6 / peaks["hbm_gbs"], 4), "problems": [], "batch_sweep": []}
+    for p in problems:
+        for _ in range(3):
+            launch(p, stream)
+        a, b = _events(torch)
+        a.record()
+        for _ in range(reps):
+            launch(p, stream)
+        b.record()
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) * 1e3 / reps
+        out["problems"].append({"N": p["N"], "K": p["K"], "fmt": FMT_NAMES[p["fmt"]], "M": 1, "us": round(us, 2),
+                                "gbs": round(p["bytes"] / us / 1e3, 1), "frac": round(p["bytes"] / us / 1e3 / peaks["hbm_gbs"], 3),
+                                "copies": len(p["pws"])})
     for p in problems:
         if p["N"] < 16384:
             continue
@@ -181,67 +270,157 @@ def run_extras(torch, cb, lib, problems):
             y = torch.empty((M, p["N"]), dtype=torch.float32, device="cuda")
             call = lambda: _lib.check(lib.bq_qlinear(pw.handle, x.data_ptr(), cb.DT_BF16, M, y.data_ptr(), cb.DT_F32, stream))
             call()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a, b = _events(torch)
             a.record()
             for _ in range(3):
                 call()
             b.record()
             torch.cuda.synchronize()
             us = a.elapsed_time(b) * 1e3 / 3
+            tf = 2.0 * M * p["N"] * p["K"] / us / 1e6
+            gbs = algorithmic_bytes(p["N"], p["K"], p["fmt"], M) / us / 1e3
             out["batch_sweep"].append({"N": p["N"], "K": p["K"], "fmt": FMT_NAMES[p["fmt"]], "M": M, "us": round(us, 1),
-                                       "gbs": round(algorithmic_bytes(p["N"], p["K"], p["fmt"], M) / us / 1e3, 1),
-                                       "tflops": round(2.0 * M * p["N"] * p["K"] / us / 1e6, 1)})
+                                       "gbs": round(gbs, 1), "tflops": round(tf, 1),
+                                       "frac": round(tf / peaks["bf16_tflops"], 3) if M >= 512 else round(gbs / peaks["hbm_gbs"], 3),
+                                       "of": "bf16 burst peak" if M >= 512 else "HBM peak"})
             del x, y
     for p in problems:
         for pw in p["pws"]:
             pw.close()
     torch.cuda.empty_cache()
-    try:
-        dec = QuantDecoder.random(GEMMA_2B_SHAPE, seed=0, act_dtype=torch.bfloat16, max_seq=192, max_batch=1)
-        g = torch.Generator(device="cuda").manual_seed(0)
-        prompt = torch.randint(0, GEMMA_2B_SHAPE.vocab, (1, 128), device="cuda", generator=g)
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        first = dec.next_tokens(prompt)
-        torch.cuda.synchronize()
-        prefill_s = time.perf_counter() - t0
-        step, tokens = dec.make_graph_stepper(1, first, start_pos=dec.pos)
-        for _ in range(3):
-            step()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(32):
-            step()
-        b.record()
-        torch.cuda.synchronize()
-        ms_tok = a.elapsed_time(b) / 32
-        bpt = dec.linear_bytes_per_token()
-        peak, _ = load_peaks()
-        out["decode"] = {"model": "gemma-2b-shape int8-g32, bf16 activations, batch 1", "tokens_per_s": round(1e3 / ms_tok, 1),
-                         "ms_per_token": round(ms_tok, 4), "linear_GB_per_token": round(bpt / 1e9, 3),
-                         "linear_stream_gbs": round(bpt / ms_tok / 1e6, 1),
-                         "frac_of_hbm_ceiling": round(bpt / ms_tok / 1e6 / peak, 4),
-                         "prefill_128_tokens_s": round(prefill_s, 4)}
-    except Exception as e:  # extras never break the headline line
-        out["decode"] = {"error": repr(e)[:300]}
     return out
 
 
-def run_reference(args):
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
-        return
-    steps = min(args.steps, 5)
-    cb = cpu_sample(steps, min(args.warmup, 1))
-    line = {"impl": "reference", "metric": "quantized_gemv_hbm_gbs", "value": cb["value"], "unit": "GB/s",
-            "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": cb["ms_per_pass"],
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "configs[1] quantized matmul sweep, M=1 (bounded CPU sample)",
-                       "note": "the reference checkout has no implementation of this path; this arm times the "
-                               "self-authored numpy oracle on the host cores"},
-            "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
-            "e2e": {"value": cb["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line))
+def run_gemma2b(torch, cb):
+    """configs[0] on the GPU: Gemma-2B-shaped int8-g32 decoder, 128-token prefill then 32 greedy tokens at batch 1
+    (CUDA-graph replays), fp32 activations as the config says and bf16 for comparison."""
+    from chadslab_b200.decoder import GEMMA_2B_SHAPE, QuantDecoder
+    peaks = load_peaks()
+    out = {}
+    for name, adt in (("fp32_activations", torch.float32), ("bf16_activations", torch.bfloat16)):
+        try:
+            dec = QuantDecoder.random(GEMMA_2B_SHAPE, seed=0, act_dtype=adt, max_seq=192, max_batch=1)
+            g = torch.Generator(device="cuda").manual_seed(0)
+            prompt = torch.randint(0, GEMMA_2B_SHAPE.vocab, (1, 128), device="cuda", generator=g)
+            dec.next_tokens(prompt)                       # untimed pass: sizes the library's scratch
+            dec.reset()
+            torch.cuda.synchronize()
+            a, b = _events(torch)
+            a.record()
+            first = dec.next_tokens(prompt)
+            b.record()
+            torch.cuda.synchronize()
+            prefill_ms = a.elapsed_time(b)
+            step, tokens = dec.make_graph_stepper(1, first, start_pos=dec.pos)
+            for _ in range(3):
+                step()
+            a, b = _events(torch)
+            a.record()
+            for _ in range(32):
+                step()
+            b.record()
+            torch.cuda.synchronize()
+            ms_tok = a.elapsed_time(b) / 32
+            bpt = dec.linear_bytes_per_token()
+            out[name] = {"tokens_per_s": round(1e3 / ms_tok, 1), "ms_per_token": round(ms_tok, 4),
+                         "prefill_128_tokens_ms": round(prefill_ms, 2),
+                         "frac_of_hbm_ceiling": round(bpt / ms_tok / 1e6 / peaks["hbm_gbs"], 4),
+                         "linear_GB_per_token": round(bpt / 1e9, 3)}
+            del step, dec
+        except Exception as e:
+            out[name] = {"error": repr(e)[:300]}
+        torch.cuda.empty_cache()
+    out["model"] = "configs[0]: gemma-2b-shape int8-g32, batch 1, random-init, 128-token prefill then 32 greedy tokens (graph replays)"
+    return out
+
+
+def parity_check(torch, dist, cb, rank, world):
+    """Same-weights correctness of the sharded paths of THIS run (not timed): a small decoder and a small MoE layer
+    are built from the oracle's seeded weights, sharded over the `world` ranks, run through the peer-memory
+    communicator / exchange, and compared with the numpy oracle."""
+    from oracle import model as omodel
+    from oracle import spec
+    from chadslab_b200 import _lib, parallel
+    from chadslab_b200.decoder import DecoderConfig, MoEDecoder, QuantDecoder
+    out = {"world": world}
+    try:
+        cfg = dict(layers=2, hidden=512, n_heads=16, n_kv_heads=8, head_dim=64, ffn=2048, vocab=2048, fmt=1)
+        w = omodel.random_weights(cfg, seed=21)
+        prompt = np.random.default_rng(5).integers(0, cfg["vocab"], (1, 6))
+        ref_tokens, ref_logits = omodel.OracleDecoder(cfg, w).generate(list(prompt[0]), 4)
+        comm = cb.PeerComm(max_elems=4 * 4096, group=dist.group.WORLD if world > 1 else None)
+        dec = QuantDecoder.from_numpy(DecoderConfig(**cfg), w, act_dtype=torch.float32, rank=rank, world=world, max_seq=32,
+                                      comm=comm if world > 1 else None)
+        pt = torch.from_numpy(prompt).cuda()
+        lg = dec.logits(pt)[0, -1].cpu().numpy()
+        out["tp_logits_rel_err"] = float(spec.rel_err(lg, ref_logits[0]))
+        dec.reset()
+        first = dec.next_tokens(pt)
+        step, tokens = dec.make_graph_stepper(1, first, start_pos=dec.pos)       # the captured step: peer-memory sums
+        got = [int(first[0])]
+        for _ in range(3):
+            step()
+            got.append(int(tokens[0]))
+        out["tp_tokens_equal"] = got == ref_tokens
+        out["tp_tokens"] = {"got": got, "oracle": ref_tokens}
+        del step, dec
+        comm.close()
+    except Exception as e:
+        out["tp_error"] = repr(e)[:300]
+    try:
+        rng = np.random.default_rng(2)
+        E, H, Fd, k, fmt = 16, 256, 256, 4, 1
+        q = lambda W: spec.quantize(W.astype(np.float32), fmt)
+        router = q(rng.normal(0, 0.5, (E, H)))
+        gate = [q(rng.normal(0, 0.05, (Fd, H))) for _ in range(E)]
+        up = [q(rng.normal(0, 0.05, (Fd, H))) for _ in range(E)]
+        down = [q(rng.normal(0, 0.05, (H, Fd))) for _ in range(E)]
+        xs = [spec.bf16_round(rng.normal(0, 1, (5 + 3 * r, H)).astype(np.float32)) for r in range(world)]   # ragged
+        x = xs[rank]
+        mk = lambda cs: cb.PackedWeight.from_arrays(cs[0], cs[1], fmt)
+        lg_, lu_, ld_ = (parallel.shard_experts(w_, rank, world) for w_ in (gate, up, down))
+        ep = cb.PeerEP(E, H, max_send_rows=64 * k, group=dist.group.WORLD if world > 1 else None)
+        local = cb.MoEExperts(None, [mk(g) for g in lg_], [mk(u) for u in lu_], [mk(d) for d in ld_], top_k=k)
+        layer = parallel.ExpertParallelMoE(cb.QuantLinear(mk(router)), None, E, k, ep=ep, local_moe=local)
+        y = layer(torch.from_numpy(x).cuda().to(torch.bfloat16)).cpu().numpy()
+        ref, _ = spec.moe_forward(x, router, gate, up, down, fmt, k)
+        err = torch.tensor([spec.rel_err(y, ref)], device="cuda")
+        if world > 1:
+            dist.all_reduce(err, op=dist.ReduceOp.MAX)
+        out["ep_layer_rel_err"] = float(err[0])
+        ep.close()
+        # sparse-MoE decoder, expert parallel, each rank its own sequence, graph decode vs the oracle's tokens
+        mcfg = dict(layers=2, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=0, vocab=1024, fmt=1, n_experts=16, top_k=2,
+                    moe_ffn=256)
+        mw = omodel.random_weights(mcfg, seed=12)
+        prompts = np.random.default_rng(9).integers(0, mcfg["vocab"], (world, 6))
+        ref_tokens, ref_logits = omodel.OracleDecoder(mcfg, mw).generate(list(prompts[rank]), 3)
+        ep2 = cb.PeerEP(mcfg["n_experts"], mcfg["hidden"], max_send_rows=6 * mcfg["top_k"],
+                        group=dist.group.WORLD if world > 1 else None) if world > 1 else None
+        mdec = MoEDecoder.from_numpy(DecoderConfig(**mcfg), mw, act_dtype=torch.float32, rank=rank, world=world, max_seq=32, ep=ep2)
+        pt = torch.from_numpy(prompts[rank])[None].cuda()
+        lg = mdec.logits(pt)[0, -1].cpu().numpy()
+        mdec.reset()
+        first = mdec.next_tokens(pt)
+        step, tokens = mdec.make_graph_stepper(1, first, start_pos=mdec.pos)
+        got = [int(first[0])]
+        for _ in range(2):
+            step()
+            got.append(int(tokens[0]))
+        res = torch.tensor([spec.rel_err(lg, ref_logits[0]), 0.0 if got == ref_tokens else 1.0], device="cuda")
+        if world > 1:
+            dist.all_reduce(res, op=dist.ReduceOp.MAX)
+        out["moe_decoder_logits_rel_err"] = float(res[0])
+        out["moe_decoder_tokens_equal"] = bool(res[1] == 0)
+        del step, mdec
+        if ep2 is not None:
+            ep2.close()
+    except Exception as e:
+        out["ep_error"] = repr(e)[:300]
+    out["status"] = int(_lib.lib().bq_status_poll())
+    out["tolerances"] = "logits <= 1e-3 (dense), <= 2e-3 (MoE decoder), MoE layer <= 4e-3 (bf16 hidden activation between the expert matmuls)"
+    torch.cuda.empty_cache()
+    return out
 
 
 # ------------------------------------------------------------------------------------------------
@@ -251,7 +430,7 @@ def run_gpu(args):
     import torch
     import torch.distributed as dist
     import chadslab_b200 as cb
-    from chadslab_b200 import _lib
+    from chadslab_b200 import _lib, decode_bench, moe_bench
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -262,172 +441,78 @@ def run_gpu(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     lib = _lib.init(local)
-    problems = build_problems(torch, cb, seed=rank)
-    stream = torch.cuda.current_stream().cuda_stream
-    step_bytes = sum(p["bytes"] for p in problems)
+    peaks = load_peaks()
+    steps, warmup = args.steps, max(3, args.warmup)
 
-    def launch(p):
-        pw = p["pws"][p["i"] % len(p["pws"])]
-        p["i"] += 1
-        _lib.check(lib.bq_qlinear(pw.handle, p["x"].data_ptr(), cb.DT_BF16, 1, p["y"].data_ptr(), cb.DT_F32, stream))
-
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
-
-    dom = [p for p in problems if (p["N"], p["K"], p["fmt"]) == DOMINANT][0]
-    for _ in range(max(3, args.warmup)):
-        for p in problems:
-            launch(p)
-    barrier()
-
-    # ---- the K steps as one CUDA graph (what a decode loop replays); copies rotate inside it -------
-    launches0 = lib.bq_launch_count()
-    graph = torch.cuda.CUDAGraph()
-    cap_stream = torch.cuda.Stream()
-    cap_stream.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.graph(graph, stream=cap_stream):
-        cs = torch.cuda.current_stream().cuda_stream
-        for s in range(args.steps):
-            for p in problems:
-                pw = p["pws"][p["i"] % len(p["pws"])]
-                p["i"] += 1
-                _lib.check(lib.bq_qlinear(pw.handle, p["x"].data_ptr(), cb.DT_BF16, 1, p["y"].data_ptr(), cb.DT_F32, cs))
-    launches = lib.bq_launch_count() - launches0          # kernels of ours inside one replay = the timed region
-    graph.replay()                                          # one untimed replay (graph upload)
-    barrier()
-
-    # ---- timed region: device-resident inputs, exactly K steps = one replay ---------------------------
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-        time.sleep(0.3)
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    ev0.record()
-    graph.replay()
-    ev1.record()
-    barrier()
-    ms_total = ev0.elapsed_time(ev1)
-
-    # ---- the same K steps launched eagerly, with events around the dominant kernel (roofline) ----------
-    dom_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    eg0, eg1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    eg0.record()
-    for s in range(args.steps):
-        for p in problems:
-            if p is dom:
-                dom_ev[s][0].record()
-                launch(p)
-                dom_ev[s][1].record()
-            else:
-                launch(p)
-    eg1.record()
-    barrier()
-    ms_eager = eg0.elapsed_time(eg1)
-    dom_ms = statistics.mean(a.elapsed_time(b) for a, b in dom_ev)
-
-    # ---- per-problem timings (reported in "detail"; not the headline) ----------------------------
-    detail = []
-    for p in problems:
-        reps = max(args.steps, 20)
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        for _ in range(3):
-            launch(p)
-        a.record()
-        for _ in range(reps):
-            launch(p)
-        b.record()
-        torch.cuda.synchronize()
-        us = a.elapsed_time(b) * 1e3 / reps
-        detail.append({"N": p["N"], "K": p["K"], "fmt": FMT_NAMES[p["fmt"]], "M": 1, "us": round(us, 2),
-                       "gbs": round(p["bytes"] / us / 1e3, 1), "copies": len(p["pws"])})
-
-    # ---- end to end: host buffers through the C ABI (H2D of x and D2H of y inside the timing) ----
-    hx = [torch.randn((1, p["K"])).to(torch.bfloat16).pin_memory() for p in problems]
-    hy = [torch.empty((1, p["N"]), dtype=torch.float32).pin_memory() for p in problems]
-
-    def e2e_pass():
-        for p, x, y in zip(problems, hx, hy):
-            pw = p["pws"][p["i"] % len(p["pws"])]
-            p["i"] += 1
-            _lib.check(lib.bq_qlinear_host(pw.handle, x.data_ptr(), cb.DT_BF16, 1, y.data_ptr(), cb.DT_F32))
-
-    for _ in range(3):
-        e2e_pass()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        e2e_pass()
-    torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
+    batches = (1, 16, HEADLINE_BATCH) if args.extras else (HEADLINE_BATCH,)
+    head = decode_bench.run(torch, dist, rank, world, "gemma7b", batches, HEADLINE_CTX, steps, warmup=warmup,
+                            headline_batch=HEADLINE_BATCH)
     clocks = sampler.stop() if rank == 0 else None
+    hb = head.get("headline") or {}
 
-    t = torch.tensor([ms_total, e2e_s * 1e3], device="cuda", dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total, e2e_ms = float(t[0]), float(t[1])
-
-    tp_decode = None
-    moe_layer = None
-    if args.extras:      # configs[2]: Gemma-7B-shaped decoder, 4-bit g32, tensor-parallel over all ranks of the run
-        from chadslab_b200 import decode_bench
-        tp_decode = decode_bench.run(torch, dist, rank, world, "gemma7b", (1, 16, 64), 2048, 16)
-        try:             # configs[3]: one sparse-MoE layer (128 experts, top-8, q4), expert-parallel over the ranks
-            from chadslab_b200 import moe_bench
-            moe_layer = moe_bench.run(torch, dist, rank, world, tokens=(256, 4096), reps=5)
-        except Exception as e:  # extras never break the headline line
-            moe_layer = {"error": repr(e)[:300]}
+    extras = {}
+    if args.extras:
+        extras["parity"] = parity_check(torch, dist, cb, rank, world)
+        if world > 1:
+            # the same step on ONE GPU, measured in this run by rank 0 alone (the others wait): the basis of the speed-up
+            one = None
+            if rank == 0:
+                one = decode_bench.run(torch, dist, 0, 1, "gemma7b", batches, HEADLINE_CTX, max(4, steps // 2), warmup=3)
+            dist.barrier()
+            if rank == 0:
+                extras["one_gpu_same_run"] = {"batches": one.get("batches"), "error": one.get("error")}
+                by_b = {b["batch"]: b["ms_per_step"] for b in one.get("batches", [])}
+                extras["speedup_vs_one_gpu"] = {str(b["batch"]): round(by_b[b["batch"]] / b["ms_per_step"], 3)
+                                                for b in head.get("batches", []) if b["batch"] in by_b}
+        try:
+            extras["moe_layer"] = moe_bench.run(torch, dist, rank, world, tokens=(256, 4096), reps=5)
+        except Exception as e:
+            extras["moe_layer"] = {"error": repr(e)[:300]}
+        try:
+            extras["moe_decoder"] = moe_bench.run_decoder(torch, dist, rank, world)
+        except Exception as e:
+            extras["moe_decoder"] = {"error": repr(e)[:300]}
+        try:
+            extras["prefill"] = decode_bench.run_prefill(torch, dist, rank, world, "gemma7b", 0, 8, 4096, reps=2)
+        except Exception as e:
+            extras["prefill"] = {"error": repr(e)[:300]}
+        if world == 1:
+            try:
+                extras["sweep"] = run_sweep(torch, cb, lib, seed=0, reps=max(5, steps))
+            except Exception as e:
+                extras["sweep"] = {"error": repr(e)[:300]}
+            extras["gemma2b_decode"] = run_gemma2b(torch, cb)
     if rank == 0:
-        peak, peak_src = load_peaks()
-        value = world * step_bytes * args.steps / (ms_total * 1e-3) / 1e9
-        e2e_value = world * step_bytes * args.steps / (e2e_ms * 1e-3) / 1e9
-        achieved = dom["bytes"] / (dom_ms * 1e-3) / 1e9
-        cpu = cpu_sample(2, 1) if world == 1 else None
-        extras = None
-        if world == 1 and args.extras:
-            del hx, hy
-            for p in problems:           # keep only what the extras reuse
-                for pw in p["pws"][1:]:
-                    pw.close()
-                p["pws"] = p["pws"][:1]
-            torch.cuda.empty_cache()
-            extras = run_extras(torch, cb, lib, problems)
+        ms = hb.get("ms_per_step")
+        value = HEADLINE_BATCH * 1e3 / ms if ms else None
+        e2e_ms = hb.get("e2e_ms_per_step")
         line = {
-            "metric": "quantized_gemv_hbm_gbs", "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": round(ms_total / args.steps, 4),
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "configs[1] quantized matmul sweep, decode-shaped M=1: (N,K) in "
-                                   "{(2048,2048),(16384,2048),(2048,16384),(256000,2048)} x {int8-g32, q4-g32}, "
-                                   "x bf16 N(0,1), W N(0,0.02)",
-                       "l2": "weights rotate over distinct copies so > 2x L2 (126 MB) is touched between reuses; "
-                             "the 256000-row weights exceed L2 by themselves",
-                       "launch": "the K timed steps are one CUDA-graph replay; roofline.achieved is the same kernel timed "
-                                 "with events in an eager pass of the same step sequence",
-                       "bytes_per_step_per_gpu": int(step_bytes), "parallelism": f"independent sweep per GPU x{world}"},
-            "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                         "frac": round(achieved / peak, 4), "traffic": int(NCU_TRAFFIC_RATIO * dom["bytes"]),
-                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of the same kernel on a 65536-row "
-                                           "case (146.4 MB for 142.7 MB algorithmic), scaled by rows to this launch",
-                         "peak_source": peak_src,
-                         "kernel": "qgemv int8-g32 (256000,2048) M=1", "frac_of_nominal_8TBs": round(achieved / 8000, 4),
-                         "launch_us": round(dom_ms * 1e3, 2)},
-            "e2e": {"value": round(e2e_value, 1), "unit": "GB/s",
-                    "h2d_bytes_per_step": int(sum(p["K"] * 2 for p in problems)),
-                    "d2h_bytes_per_step": int(sum(p["N"] * 4 for p in problems))},
-            "gpu_launches": int(launches), "clocks": clocks, "detail": detail,
-            "eager_ms_per_step": round(ms_eager / args.steps, 4),
+            "metric": "decode_tokens_per_s", "value": round(value, 1) if value else None, "unit": "tokens/s", "n_gpus": world,
+            "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 4) if ms else None, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": headline_config(world),
+            "roofline": hb.get("roofline"),
+            "e2e": {"value": round(HEADLINE_BATCH * 1e3 / e2e_ms, 1) if e2e_ms else None, "unit": "tokens/s",
+                    "h2d_bytes_per_step": HEADLINE_BATCH * 8, "d2h_bytes_per_step": HEADLINE_BATCH * 8,
+                    "how": "every step: token ids copied from pinned host memory, one graph replay, new ids copied back to "
+                           "pinned host memory, stream synchronised"},
+            "gpu_launches": int(hb.get("launches_per_step", 0)) * steps, "clocks": clocks,
+            "step": {"launches_per_step": hb.get("launches_per_step"), "stream_GB_per_step_per_gpu": hb.get("stream_GB_per_step_per_gpu"),
+                     "frac_of_hbm_peak": hb.get("frac_of_hbm_peak"), "peak_gbs": peaks["hbm_gbs"], "peak_source": peaks["source"]},
+            "tp_decode": {k: head.get(k) for k in ("model", "tensor_parallel", "context", "exchange", "timing", "batches", "status",
+                                                   "error") if k in head},
         }
-        if cpu:
-            line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        if world == 1 and args.cpu:
+            try:
+                cpu = cpu_decode_sample(1, 1)
+                line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+            except Exception as e:
+                line["cpu_baseline"] = {"error": repr(e)[:300]}
         if extras:
             line["extras"] = extras
-        if tp_decode:
-            line.setdefault("extras", {})["tp_decode"] = tp_decode
-        if moe_layer:
-            line.setdefault("extras", {})["moe_layer"] = moe_layer
         print(json.dumps(line))
     if world > 1:
         dist.barrier()
@@ -440,7 +525,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--extras", type=int, default=1, help="also report the batch sweep and decode tokens/s (N=1 only)")
+    ap.add_argument("--extras", type=int, default=1, help="also run the other configs, the parity check and the sweep")
+    ap.add_argument("--cpu", type=int, default=1, help="N = 1: also time the numpy oracle sample (cpu_baseline)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

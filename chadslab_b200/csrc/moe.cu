@@ -167,6 +167,79 @@ moe_scatter_kernel(const int32_t* __restrict__ idx, int64_t A, int E, int nchunk
   }
 }
 
+// Decode-sized sorts (A <= PERM_SMALL_A, E <= PERM_SMALL_E): the three kernels above as ONE single-CTA kernel --
+// totals, scan and the stable placement all happen in shared memory, so the sort costs one launch instead of three
+// latency-bound ones.  Same results bit for bit (stable: by expert, then by assignment index); needs no scratch.
+constexpr int PERM_SMALL_A = 16384;
+constexpr int PERM_SMALL_E = 256;
+__global__ void __launch_bounds__(1024)
+moe_permute_small_kernel(const int32_t* __restrict__ idx, int A, int E, int32_t* __restrict__ perm, int32_t* __restrict__ inv,
+                         int32_t* __restrict__ offsets) {
+  __shared__ int32_t base[PERM_SMALL_E];          // next free sorted position of every expert
+  __shared__ int32_t scan[1024];
+  __shared__ int32_t wcnt[32][PERM_SMALL_E];      // per warp: assignments of the current chunk that go to expert e
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  pdl_launch_dependents();
+  pdl_wait();
+  for (int e = t; e < E; e += 1024) base[e] = 0;
+  __syncthreads();
+  for (int i = t; i < A; i += 1024) {
+    const int e = idx[i];
+    if (e >= 0 && e < E) atomicAdd(&base[e], 1);
+  }
+  __syncthreads();
+  const int32_t cnt = t < E ? base[t] : 0;
+  scan[t] = cnt;
+  __syncthreads();
+  for (int off = 1; off < 1024; off <<= 1) {
+    const int32_t add = t >= off ? scan[t - off] : 0;
+    __syncthreads();
+    scan[t] += add;
+    __syncthreads();
+  }
+  if (t < E) { offsets[t + 1] = scan[t]; base[t] = scan[t] - cnt; }
+  if (t == 0) offsets[0] = 0;
+  const int32_t valid = scan[E - 1];
+  __syncthreads();
+  for (int p = valid + t; p < A; p += 1024) perm[p] = -1;      // dropped assignments (expert id outside [0, E))
+  for (int c0 = 0; c0 < A; c0 += 1024) {                       // chunks of 1024 assignments, in order
+    for (int j = lane; j < E; j += 32) wcnt[warp][j] = 0;
+    __syncwarp();
+    const int i = c0 + t;
+    const int e = i < A ? idx[i] : -1;
+    const bool ok = e >= 0 && e < E;
+    const unsigned act = __ballot_sync(0xffffffffu, ok);
+    int rank = 0;
+    if (ok) {
+      const unsigned same = __match_any_sync(act, e);
+      rank = __popc(same & ((1u << lane) - 1u));
+      if (rank == 0) wcnt[warp][e] = __popc(same);
+    }
+    __syncthreads();
+    if (t < E) {                                               // exclusive prefix over the warps, chunk total to base
+      int32_t run = 0;
+#pragma unroll 4
+      for (int w = 0; w < 32; ++w) {
+        const int32_t c = wcnt[w][t];
+        wcnt[w][t] = run;
+        run += c;
+      }
+      scan[t] = run;                                           // this chunk's count of expert t
+    }
+    __syncthreads();
+    if (ok) {
+      const int pos = base[e] + wcnt[warp][e] + rank;
+      perm[pos] = i;
+      if (inv) inv[i] = pos;
+    } else if (i < A && inv) {
+      inv[i] = -1;
+    }
+    __syncthreads();
+    if (t < E) base[t] += scan[t];
+    __syncthreads();
+  }
+}
+
 // -------------------------------------------------------------------------------------------
 // gather / combine
 // -------------------------------------------------------------------------------------------
@@ -393,6 +466,12 @@ int bq_moe_permute(const int32_t* idx, int64_t T, int top_k, int E, int32_t* per
     return BQ_OK;
   }
   if (!idx || !perm || !scratch) return fail(BQ_ERR_ARG, "null pointer");
+  if (A <= PERM_SMALL_A && E <= PERM_SMALL_E) {      // decode-sized: one single-CTA launch (the scratch is not needed)
+    BQ_CUDA(launch_chain(moe_permute_small_kernel, dim3(1), dim3(1024), 0, s, 1, idx, (int)A, E, perm, inv, offsets));
+    count_launch();
+    BQ_CUDA(cudaGetLastError());
+    return BQ_OK;
+  }
   const int nchunks = perm_chunks(A);
   const int64_t chunk = (A + nchunks - 1) / nchunks;
   const int blocks = (nchunks + PERM_WARPS - 1) / PERM_WARPS;

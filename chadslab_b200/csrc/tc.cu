@@ -199,9 +199,18 @@ template <int FMT, int BN, int MODE> struct T2Plan {
   static constexpr int SCT = TC_ROWS * 16;                                // 8 fp16 scales per row = 256 k = 2 steps
   static constexpr int STAGE = ((NW * RAW + XT + 1023) / 1024) * 1024;
   static constexpr int FIXED = TC_SC_SLOTS * NW * SCT + 1024 + 1024;
-  // tensor memory: NW accumulators of BN columns from column 0, then NW x 2 A buffers of 64 columns from ACOL0.
+  // Small batch tiles: successive tcgen05.mma into ONE accumulator serialise on that accumulator (each takes the
+  // pipeline's latency whatever N is), so the 8 MMAs of a step rotate over NACC independent accumulators (chains of
+  // every NACC-th k-slice) which the epilogue adds up.  NACC keeps all accumulators within 128 columns.
+#ifndef BQ_NACC_MAX
+#define BQ_NACC_MAX 4
+#endif
+  static constexpr int NACC_WANT = NW * BN <= 32 ? 4 : NW * BN <= 64 ? 2 : 1;
+  static constexpr int NACC = NACC_WANT < BQ_NACC_MAX ? NACC_WANT : BQ_NACC_MAX;
+  // tensor memory: NW x NACC accumulators of BN columns from column 0 (weight w, chain c at (w * NACC + c) * BN), then
+  // NW x 2 A buffers of 64 columns from ACOL0.
   // 256 columns (two CTAs per SM) only when everything fits below 256; two weight tiles always need 512.
-  static constexpr int ACOL0 = NW * BN <= 128 ? 128 : 256;                // first A-buffer column
+  static constexpr int ACOL0 = NW * BN * NACC <= 128 ? 128 : 256;         // first A-buffer column
   static constexpr int TMEM_NEED = ACOL0 + NW * 2 * T2_ACOLS;
   static constexpr int TMEM_COLS = TMEM_NEED <= 256 ? 256 : 512;
   static constexpr int BUDGET = (TMEM_COLS == 256 ? 100 : 200) * 1024;    // shared memory follows: two CTAs per SM or one
@@ -209,7 +218,7 @@ template <int FMT, int BN, int MODE> struct T2Plan {
   static constexpr int S = S_RAW > 4 ? 4 : (S_RAW < 2 ? 2 : S_RAW);       // S <= 2*SC_SLOTS - 1 = 5
   static constexpr int SMEM = FIXED + S * STAGE;
   static_assert(TMEM_NEED <= 512, "tensor memory plan too large");
-  static_assert(NW * BN <= 256 && BN % 16 == 0, "accumulators must fit below the A buffers");
+  static_assert(NW * BN * NACC <= ACOL0 && BN % 16 == 0, "accumulators must fit below the A buffers");
   static_assert(SMEM <= 227 * 1024, "shared memory plan too large");
 };
 
@@ -279,6 +288,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tmem_kernel(const __grid_
   const CUtensorMap* tmw[2] = {&args.tm_w, &args.tm_w};
   const CUtensorMap* tms[2] = {&args.tm_s, &args.tm_s};
   if (args.moe) {
+    pdl_wait();                                       // the tile list and the row ranges come from preceding kernels
     if ((int)blockIdx.x >= args.tiles[0]) return;     // uniform across the CTA, before any barrier
     const int e = args.tiles[1 + 2 * blockIdx.x];
     m0 = args.tiles[2 + 2 * blockIdx.x];
@@ -307,6 +317,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tmem_kernel(const __grid_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Programmatic dependent launch: barriers and tensor memory are set up while the preceding kernel drains; nothing
+  // it wrote (activations, tile list) has been read yet, and nothing is written before this point.
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (warp == 0) {
     // ================= producer =================
@@ -350,12 +364,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tmem_kernel(const __grid_
 #pragma unroll
         for (int w = 0; w < NW; ++w) {
           const uint32_t a_tmem = tmem_base + (uint32_t)(P::ACOL0 + (w * NA + a) * T2_ACOLS);
-          const uint32_t d_tmem = tmem_base + (uint32_t)(w * BN);
-          tc_mma_f16_ts(d_tmem, a_tmem, bdesc0, idesc, ks > 0 ? 1u : 0u);
+          const uint32_t d_tmem = tmem_base + (uint32_t)(w * P::NACC * BN);
 #pragma unroll
-          for (int kk = 1; kk < T2_BK / 16; ++kk)
-            tc_mma_f16_ts(d_tmem, a_tmem + (uint32_t)(8 * kk),
-                          bdesc0 + (uint64_t)((((kk >> 2) * BN * 128) >> 4) + 2 * (kk & 3)), idesc, 1u);
+          for (int kk = 0; kk < T2_BK / 16; ++kk)      // k-slice kk goes to chain kk % NACC; a chain's first MMA overwrites
+            tc_mma_f16_ts(d_tmem + (uint32_t)((kk % P::NACC) * BN), a_tmem + (uint32_t)(8 * kk),
+                          bdesc0 + (uint64_t)((((kk >> 2) * BN * 128) >> 4) + 2 * (kk & 3)), idesc,
+                          (ks > 0 || kk >= P::NACC) ? 1u : 0u);
         }
         tc_commit(smem_u32(&a_empty[a]));
         tc_commit(smem_u32(&empty[s]));
@@ -425,8 +439,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tmem_kernel(const __grid_
         if (GATED) {                               // h = silu(gate) * up, rounded to bf16
           uint32_t v[16], u[16];
           tc_ld16(tbase + (uint32_t)c0, v);
-          tc_ld16(tbase + (uint32_t)(BN + c0), u);
+          tc_ld16(tbase + (uint32_t)(P::NACC * BN + c0), u);
           tc_ld_wait();
+#pragma unroll
+          for (int ch = 1; ch < P::NACC; ++ch) {      // add the other accumulation chains
+            uint32_t v2[16], u2[16];
+            tc_ld16(tbase + (uint32_t)(ch * BN + c0), v2);
+            tc_ld16(tbase + (uint32_t)((P::NACC + ch) * BN + c0), u2);
+            tc_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(v2[j]));
+              u[j] = __float_as_uint(__uint_as_float(u[j]) + __uint_as_float(u2[j]));
+            }
+          }
           if (n < args.N) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
@@ -444,8 +470,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tmem_kernel(const __grid_
 #pragma unroll
         for (int w = 0; w < NW; ++w) {
           uint32_t v[16];
-          tc_ld16(tbase + (uint32_t)(w * BN + c0), v);
+          tc_ld16(tbase + (uint32_t)(w * P::NACC * BN + c0), v);
           tc_ld_wait();
+#pragma unroll
+          for (int ch = 1; ch < P::NACC; ++ch) {      // add the other accumulation chains
+            uint32_t v2[16];
+            tc_ld16(tbase + (uint32_t)((w * P::NACC + ch) * BN + c0), v2);
+            tc_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(v2[j]));
+          }
           const int64_t nn = n + w * TC_ROWS;
           if (nn < args.N) {
 #pragma unroll
@@ -477,11 +511,33 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tmem_kernel(const __grid_
 // x16[m, k] = fp16(x[m, k] * 2^-e).  Rows that are all zero (or hold inf / nan) use e = 0.
 template <typename XT>
 __global__ void __launch_bounds__(256) x_prep_kernel(const XT* __restrict__ x, int64_t K, __half* __restrict__ x16,
-                                                     float* __restrict__ scale_back) {
+                                                     float* __restrict__ scale_back, const int32_t* __restrict__ nrows_dev) {
+  pdl_launch_dependents();
+  pdl_wait();
+  if (nrows_dev && (int64_t)blockIdx.x >= (int64_t)*nrows_dev) return;     // rows in use are only known on the device
   const XT* row = x + (int64_t)blockIdx.x * K;
   __half* orow = x16 + (int64_t)blockIdx.x * K;
+  // K is a multiple of 256 and rows are 16-byte aligned: a thread owns chunks of 8 elements; the first XP_CACHE chunks
+  // stay in registers between the two passes (rows up to 8192 elements are read once)
+  constexpr int XP_CACHE = 4;
+  float v[XP_CACHE][8];
   float mx = 0.0f;
-  for (int64_t k = threadIdx.x; k < K; k += blockDim.x) mx = fmaxf(mx, fabsf(to_float<XT>(row[k])));
+  const int64_t chunks = K / 8;
+#pragma unroll
+  for (int c = 0; c < XP_CACHE; ++c) {
+    const int64_t i = (int64_t)threadIdx.x + (int64_t)c * 256;
+    if (i < chunks) {
+      load8<XT>(row + i * 8, v[c]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fabsf(v[c][j]));
+    }
+  }
+  for (int64_t i = (int64_t)threadIdx.x + (int64_t)XP_CACHE * 256; i < chunks; i += 256) {
+    float t[8];
+    load8<XT>(row + i * 8, t);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fabsf(t[j]));
+  }
   __shared__ float red[8];
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
@@ -494,7 +550,22 @@ __global__ void __launch_bounds__(256) x_prep_kernel(const XT* __restrict__ x, i
   if (mx > 0.0f && mx < INFINITY) e = (int)((__float_as_uint(mx) >> 23) & 0xFF) - 127 - 14;   // floor(log2) - 14
   if (e < -100) e = -100;                                   // denormal row maxima: keep 2^-e finite
   const float down = __uint_as_float((uint32_t)(127 - e) << 23);   // 2^-e
-  for (int64_t k = threadIdx.x; k < K; k += blockDim.x) orow[k] = __float2half_rn(to_float<XT>(row[k]) * down);
+  auto emit = [&](int64_t i, const float* f) {
+    __half h[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(f[j] * down);
+    *reinterpret_cast<uint4*>(orow + i * 8) = *reinterpret_cast<const uint4*>(h);
+  };
+#pragma unroll
+  for (int c = 0; c < XP_CACHE; ++c) {
+    const int64_t i = (int64_t)threadIdx.x + (int64_t)c * 256;
+    if (i < chunks) emit(i, v[c]);
+  }
+  for (int64_t i = (int64_t)threadIdx.x + (int64_t)XP_CACHE * 256; i < chunks; i += 256) {
+    float t[8];
+    load8<XT>(row + i * 8, t);
+    emit(i, t);
+  }
   if (threadIdx.x == 0) scale_back[blockIdx.x] = __uint_as_float((uint32_t)(127 + e) << 23);
 }
 
@@ -502,6 +573,8 @@ __global__ void __launch_bounds__(256) x_prep_kernel(const XT* __restrict__ x, i
 template <typename YT>
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ part, int nz, int64_t M, int64_t N,
                                                             YT* __restrict__ out, int64_t ldy) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t total = M * N;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     float s = part[i];
@@ -529,11 +602,13 @@ int tc_reserve(int64_t rows, int64_t K, int64_t N) {
   if (part > TC_PART_BYTES) part = TC_PART_BYTES;
   return scratch_ensure(&g_part, part, 0, "tcgen05 path (split-K partial tiles)");
 }
-static int launch_x_prep(const void* x, int x_dtype, int64_t rows, int64_t K, cudaStream_t s) {
+static int launch_x_prep(const void* x, int x_dtype, int64_t rows, int64_t K, cudaStream_t s,
+                         const int32_t* nrows_dev = nullptr) {
   int rc = ensure_x_scratch(rows, K, s);
   if (rc) return rc;
   if (x_dtype != BQ_DT_BF16) return fail(BQ_ERR_UNSUPPORTED, "tensor path takes bf16 activations");
-  x_prep_kernel<__nv_bfloat16><<<(unsigned)rows, 256, 0, s>>>((const __nv_bfloat16*)x, K, (__half*)g_x16.ptr, (float*)g_xs.ptr);
+  BQ_CUDA(launch_chain(x_prep_kernel<__nv_bfloat16>, dim3((unsigned)rows), dim3(256), 0, s, 1, (const __nv_bfloat16*)x, K,
+                       (__half*)g_x16.ptr, (float*)g_xs.ptr, nrows_dev));
   count_launch();
   BQ_CUDA(cudaGetLastError());
   return BQ_OK;
@@ -545,6 +620,8 @@ __global__ void __launch_bounds__(1024) moe_tile_list_kernel(const int32_t* __re
   __shared__ int32_t pre[1024];
   const int e = threadIdx.x;
   int32_t cnt = 0;
+  pdl_launch_dependents();
+  pdl_wait();
   if (e < E) cnt = (offsets[e + 1] - offsets[e] + bn - 1) / bn;
   pre[e] = cnt;
   __syncthreads();
@@ -636,7 +713,7 @@ static int t2_launch(const T2Args& a, dim3 grid, cudaStream_t s) {
     BQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P::SMEM));
     configured = true;
   }
-  kern<<<grid, TC_THREADS, P::SMEM, s>>>(a);
+  BQ_CUDA(launch_chain(kern, grid, dim3(TC_THREADS), (size_t)P::SMEM, s, 1, a));
   count_launch();
   BQ_CUDA(cudaGetLastError());
   return BQ_OK;
@@ -696,9 +773,11 @@ int launch_qlinear_tc(const uint8_t* codes, const __half* scales, int fmt, int64
   int64_t rg = (M * N + 255) / 256;
   if (rg > (int64_t)sm_count() * 8) rg = (int64_t)sm_count() * 8;
   if (y_dtype == BQ_DT_F32)
-    splitk_reduce_kernel<float><<<(unsigned)rg, 256, 0, s>>>((const float*)g_part.ptr, nz, M, N, (float*)y, ldy);
+    BQ_CUDA(launch_chain(splitk_reduce_kernel<float>, dim3((unsigned)rg), dim3(256), 0, s, 1, (const float*)g_part.ptr, nz, M, N,
+                         (float*)y, ldy));
   else
-    splitk_reduce_kernel<__nv_bfloat16><<<(unsigned)rg, 256, 0, s>>>((const float*)g_part.ptr, nz, M, N, (__nv_bfloat16*)y, ldy);
+    BQ_CUDA(launch_chain(splitk_reduce_kernel<__nv_bfloat16>, dim3((unsigned)rg), dim3(256), 0, s, 1, (const float*)g_part.ptr, nz, M,
+                         N, (__nv_bfloat16*)y, ldy));
   count_launch();
   BQ_CUDA(cudaGetLastError());
   return BQ_OK;
@@ -771,13 +850,13 @@ int launch_moe_experts_tc(const Moe* m, const void* xp, const int32_t* offsets, 
   int rc = scratch_ensure(&st->tiles, sizeof(int32_t) * (size_t)(2 * max_tiles + 1 + 64), s, "bq_moe_experts (tile list)");
   if (rc) return rc;
   int32_t* tiles = (int32_t*)st->tiles.ptr;
-  moe_tile_list_kernel<<<1, 1024, 0, s>>>(offsets, m->E, bn, tiles);
+  BQ_CUDA(launch_chain(moe_tile_list_kernel, dim3(1), dim3(1024), 0, s, 1, offsets, m->E, bn, tiles));
   count_launch();
   BQ_CUDA(cudaGetLastError());
   // gate|up -> h (bf16), then down -> out (f32)
   T2Args a;
   memset(&a, 0, sizeof(a));
-  if ((rc = launch_x_prep(xp, BQ_DT_BF16, P, m->H, s))) return rc;
+  if ((rc = launch_x_prep(xp, BQ_DT_BF16, P, m->H, s, offsets + m->E))) return rc;     // offsets[E] = rows in use
   if ((rc = x_map(&a.tm_x, g_x16.ptr, P, m->H, bn))) return rc;
   a.xscale = (const float*)g_xs.ptr; a.tm_list = st->gate_up; a.offsets = offsets; a.tiles = tiles; a.out = hbuf; a.ldy = m->F;
   a.N = m->F; a.K = m->H; a.M = P; a.out_dtype = BQ_DT_BF16; a.moe = 1; a.status = status_word();
@@ -786,7 +865,7 @@ int launch_moe_experts_tc(const Moe* m, const void* xp, const int32_t* offsets, 
   if (rc) return rc;
   T2Args b;
   memset(&b, 0, sizeof(b));
-  if ((rc = launch_x_prep(hbuf, BQ_DT_BF16, P, m->F, s))) return rc;   // stream order: the first GEMM is done with the scratch
+  if ((rc = launch_x_prep(hbuf, BQ_DT_BF16, P, m->F, s, offsets + m->E))) return rc;   // stream order: the first GEMM is done with the scratch
   if ((rc = x_map(&b.tm_x, g_x16.ptr, P, m->F, bn))) return rc;
   b.xscale = (const float*)g_xs.ptr; b.tm_list = st->down; b.offsets = offsets; b.tiles = tiles; b.out = out; b.ldy = m->H;
   b.N = m->H; b.K = m->F; b.M = P; b.out_dtype = BQ_DT_F32; b.moe = 1; b.status = status_word();

@@ -15,9 +15,84 @@ import json
 import os
 
 
+def _flush_l2(torch, buf):
+    buf.zero_()
+
+
+def _headline(torch, dist, rank, world, dec, cfg, B, ctx, step, tokens, steps, ms, launches, bpt, kv_bytes):
+    """For the batch the benchmark quotes: the same step driven from host buffers (token ids in from pinned memory, new
+    ids out, every step) and the largest quantized-matmul launch of the step -- the head on this rank's vocabulary
+    slice -- timed alone with events, L2 flushed between launches."""
+    import json
+    import os
+    from chadslab_b200 import _lib
+    from chadslab_b200.synth import algorithmic_bytes
+    lib = _lib.lib()
+    h_in = torch.randint(0, cfg.vocab, (B,), dtype=torch.int64).pin_memory()
+    h_out = torch.empty((B,), dtype=torch.int64).pin_memory()
+
+    def e2e_step():
+        tokens.copy_(h_in, non_blocking=True)
+        step()
+        h_out.copy_(tokens, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    for _ in range(3):
+        e2e_step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    import time
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        e2e_step()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / steps
+    t = torch.tensor([e2e_ms], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t[0])
+    # the head launch alone
+    head = dec.lin["lm_head"]
+    pw = head.pw
+    x = torch.randn((B, pw.K), device="cuda").to(torch.bfloat16)
+    y = torch.empty((B, pw.N), dtype=torch.float32, device="cuda")
+    flush = torch.empty((256 << 20,), dtype=torch.uint8, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    call = lambda: _lib.check(lib.bq_qlinear(pw.handle, x.data_ptr(), 1, B, y.data_ptr(), 0, st))
+    call()
+    n0 = lib.bq_launch_count()
+    call()
+    head_launches = lib.bq_launch_count() - n0
+    times = []
+    for _ in range(8):
+        _flush_l2(torch, flush)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        call()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    us = sorted(times)[len(times) // 2] * 1e3
+    abytes = algorithmic_bytes(pw.N, pw.K, pw.fmt, B)
+    peaks_path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    peak, src = (float(json.load(open(peaks_path))["hbm_gbs"]), "measured") if os.path.exists(peaks_path) else (6650.0, "fallback")
+    ach = abytes / us / 1e3
+    del flush, x, y
+    return {"ms_per_step": ms, "e2e_ms_per_step": e2e_ms, "launches_per_step": int(launches),
+            "stream_GB_per_step_per_gpu": round((bpt + B * kv_bytes) / 1e9, 3),
+            "frac_of_hbm_peak": round((bpt + B * kv_bytes) / ms / 1e6 / peak, 4),
+            "roofline": {"bound": "hbm", "achieved": round(ach, 1), "peak": peak, "unit": "GB/s", "frac": round(ach / peak, 4),
+                         "traffic": None, "traffic_source": "not captured in this run (ncu summaries of this kernel family: profiles/)",
+                         "peak_source": src, "kernel": f"lm_head {'int8' if pw.fmt == 0 else 'q4'}-g32 ({pw.N},{pw.K}) M={B}: "
+                                                       f"the largest quantized-matmul launch of the step ({head_launches} kernel"
+                                                       f"{'s' if head_launches != 1 else ''}: activation pre-pass + GEMM when M > 4)",
+                         "algorithmic_bytes": int(abytes), "launch_us": round(us, 2),
+                         "frac_of_nominal_8TBs": round(ach / 8000, 4)}}
+
+
 def run(torch, dist, rank: int, world: int, shape: str = "gemma7b", batches=(1, 16, 64), ctx: int = 2048, steps: int = 16,
-        eager: bool = False):
-    """Runs on every rank; returns the report (complete on rank 0)."""
+        eager: bool = False, warmup: int = 3, headline_batch=None):
+    """Runs on every rank; returns the report (complete on rank 0).  `headline_batch`: also measure that batch end to
+    end from host buffers and time its largest quantized-matmul launch alone (`headline` in the report)."""
     import chadslab_b200 as cb
     from chadslab_b200 import _lib
     from chadslab_b200.decoder import GEMMA_2B_SHAPE, GEMMA_7B_SHAPE, QuantDecoder
@@ -26,7 +101,7 @@ def run(torch, dist, rank: int, world: int, shape: str = "gemma7b", batches=(1, 
     out = {"model": f"{shape}-shape {fmt}, bf16 activations, random-init", "tensor_parallel": world,
            "context": f"{ctx} positions of synthetic (random) K/V in the cache instead of a prefill pass",
            "exchange": "peer-memory communicator (GEMV deposits + fused sum/add/RMSNorm)" if world > 1 else "none",
-           "timing": (f"{steps} eager steps" if eager else f"{steps} CUDA-graph replays") + " after 3, CUDA events, max over ranks",
+           "timing": (f"{steps} eager steps" if eager else f"{steps} CUDA-graph replays") + f" after {warmup}, CUDA events, max over ranks",
            "batches": []}
     comm = None
     try:
@@ -34,7 +109,8 @@ def run(torch, dist, rank: int, world: int, shape: str = "gemma7b", batches=(1, 
         if world > 1:
             comm = cb.PeerComm(max_elems=max(max_b * cfg.hidden, 4096), group=dist.group.WORLD)
             _lib.check(_lib.lib().bq_comm_set_timeout_ms(comm.handle, 1000))   # a benchmark should fail fast
-        dec = QuantDecoder.random(cfg, seed=0, act_dtype=torch.bfloat16, rank=rank, world=world, max_seq=ctx + 64,
+        spare = warmup + 2 * steps + 16            # cache rows behind the context: every step of a batch size writes one
+        dec = QuantDecoder.random(cfg, seed=0, act_dtype=torch.bfloat16, rank=rank, world=world, max_seq=ctx + spare,
                                   max_batch=max_b, comm=comm)
         for kc, vc in zip(dec.k_cache, dec.v_cache):
             kc.normal_()
@@ -51,15 +127,17 @@ def run(torch, dist, rank: int, world: int, shape: str = "gemma7b", batches=(1, 
 
                 def step():
                     dec._step_static(tokens, pos_t)
-                    pos_t.fill_(ctx)                     # stay at the same position: the cache has 64 spare slots
+                    pos_t.fill_(ctx)                     # stay at the same position
             else:
+                n0 = _lib.lib().bq_launch_count()
                 step, tokens = dec.make_graph_stepper(B, first, start_pos=ctx)
+                launches = (_lib.lib().bq_launch_count() - n0) // 2       # warm-up step + captured step
             step()
             torch.cuda.synchronize()
             st = int(_lib.lib().bq_status_poll())
             if st != 0:                      # e.g. a peer that never delivered: do not time the remaining steps
                 raise RuntimeError(f"device status {st} after the first step at batch {B}")
-            for _ in range(2):
+            for _ in range(max(0, warmup - 1)):
                 step()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
@@ -76,6 +154,9 @@ def run(torch, dist, rank: int, world: int, shape: str = "gemma7b", batches=(1, 
             ms = float(t[0])
             out["batches"].append({"batch": B, "ms_per_step": round(ms, 4), "tokens_per_s": round(B * 1e3 / ms, 1),
                                    "stream_gbs_per_gpu": round((bpt + B * kv_bytes) / ms / 1e6, 1)})
+            if headline_batch == B and not eager:
+                out["headline"] = _headline(torch, dist, rank, world, dec, cfg, B, ctx, step, tokens, steps, ms, launches, bpt,
+                                            kv_bytes)
             del step
         out["linear_GB_per_step_per_gpu"] = round(bpt / 1e9, 3)
         out["kv_GB_per_sequence_per_gpu"] = round(kv_bytes / 1e9, 3)

@@ -44,12 +44,15 @@ def run(torch, dist, rank, world, tokens=(256,), E=128, H=2048, F=768, top_k=8, 
     bytes_per_expert = sum(p.nbytes for p in (gate[0], up[0], down[0]))
     out = {"layer": f"{E} experts, hidden {H}, SwiGLU ffn {F}, top-{top_k}, {'int8' if fmt == 0 else 'q4'}-g32",
            "expert_parallel": world, "expert_MB": round(bytes_per_expert / 1e6, 3), "cases": []}
+    ep = None
     if world == 1:
         moe = cb.MoEExperts(router, gate, up, down, top_k)
         layer = moe
-    else:
-        local = cb.MoEExperts(mk(E_loc, H), gate, up, down, top_k=1)       # only its grouped-expert kernel is used
-        layer = parallel.ExpertParallelMoE(cb.QuantLinear(router), local.experts, E, top_k)
+    else:                      # both exchanges on the device: rows stored straight into the owning rank's memory
+        local = cb.MoEExperts(None, gate, up, down, top_k=top_k)
+        ep = cb.PeerEP(E, H, max_send_rows=max(tokens) // world * top_k, group=dist.group.WORLD)
+        layer = parallel.ExpertParallelMoE(cb.QuantLinear(router), None, E, top_k, ep=ep, local_moe=local)
+        out["exchange"] = "peer-memory stores (ops.PeerEP): counts, rows and outputs travel without a collective call or a host step"
     for T in tokens:
         T_loc = T // world
         x = torch.randn((T_loc, H), device="cuda", generator=gen).to(torch.bfloat16)
@@ -81,6 +84,85 @@ def run(torch, dist, rank, world, tokens=(256,), E=128, H=2048, F=768, top_k=8, 
         out["cases"].append(case)
         del x
     out["status"] = int(cb._lib.lib().bq_status_poll())
+    if ep is not None:
+        ep.close()
+    return out
+
+
+def run_decoder(torch, dist, rank, world, batch: int = 256, prompt_len: int = 512, steps: int = 8, chunk_seqs: int = 16,
+                cfg=None):
+    """The whole sparse-MoE decoder (48 layers, hidden 2048, 32 query / 4 KV heads of 128, 128 experts of SwiGLU 768,
+    top-8, every weight 4-bit group-32, random-init): prefill of `batch` random sequences of `prompt_len` tokens in
+    chunks of sequences, then greedy decode of the whole batch as replays of one captured CUDA graph.  With `world`
+    ranks the sequences are data-parallel (batch / world per rank), attention is replicated and the experts are
+    expert-parallel through the device-side exchange.  Times are CUDA events, max over ranks."""
+    import chadslab_b200 as cb
+    from chadslab_b200 import _lib
+    from chadslab_b200.decoder import MOE_SHAPE, MoEDecoder
+    cfg = cfg or MOE_SHAPE
+    B_loc = batch // world
+    out = {"model": f"sparse-MoE decoder: {cfg.layers} layers, hidden {cfg.hidden}, {cfg.n_heads}/{cfg.n_kv_heads} heads x "
+                    f"{cfg.head_dim}, {cfg.n_experts} experts x SwiGLU {cfg.moe_ffn}, top-{cfg.top_k}, q4-g32, vocab {cfg.vocab}",
+           "expert_parallel": world, "batch": batch, "sequences_per_rank": B_loc, "prompt_len": prompt_len}
+    ep = None
+    try:
+        chunk = min(chunk_seqs, B_loc)
+        if world > 1:
+            send = max(chunk * prompt_len, B_loc) * cfg.top_k
+            # receive capacity: twice the balanced share (random routing stays within a few percent of it); a row that
+            # would not fit is skipped and recorded in the status word, which this report prints
+            ep = cb.PeerEP(cfg.n_experts, cfg.hidden, max_send_rows=send, max_recv_rows=2 * send, group=dist.group.WORLD)
+        dec = MoEDecoder.random(cfg, seed=0, act_dtype=torch.bfloat16, rank=rank, world=world, max_seq=prompt_len + steps + 8,
+                                max_batch=B_loc, ep=ep)
+        g = torch.Generator(device="cuda").manual_seed(100 + rank)
+        tokens = torch.randint(0, cfg.vocab, (B_loc, prompt_len), device="cuda", generator=g)
+        dec.prefill(tokens[:chunk], chunk)                # untimed pass over one chunk: sizes the library's scratch
+        dec.reset()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        first = dec.prefill(tokens, chunk)
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b)], device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        pre_ms = float(t[0])
+        step, toks = dec.make_graph_stepper(B_loc, first, start_pos=dec.pos)
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            step()
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / steps], device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+        wb = dec.weight_bytes()
+        kvb = sum(k[:, :prompt_len].numel() * k.element_size() for k in dec.k_cache) * 2
+        out.update({"prefill_ms": round(pre_ms, 1), "prefill_tokens_per_s": round(batch * prompt_len / pre_ms * 1e3, 1),
+                    "prefill_chunk_sequences": chunk,
+                    "decode_ms_per_step": round(ms, 4), "decode_tokens_per_s": round(batch * 1e3 / ms, 1),
+                    "weight_GB_per_gpu": round(wb / 1e9, 3), "kv_GB_per_gpu": round(kvb / 1e9, 3),
+                    "floor_ms_weights_plus_kv_at_measured_hbm": round((wb + kvb) / 6545e6, 3),
+                    "status": int(_lib.lib().bq_status_poll())})
+        del step, dec
+    except Exception as e:
+        out["error"] = repr(e)[:300]
+    if ep is not None:
+        try:
+            ep.close()
+        except Exception as e:
+            out["close_error"] = repr(e)[:200]
+    torch.cuda.empty_cache()
     return out
 
 
@@ -96,6 +178,9 @@ def main():
     ap.add_argument("--top-k", type=int, default=8)
     ap.add_argument("--fmt", default="q4", choices=["int8", "q4"])
     ap.add_argument("--reps", type=int, default=10)
+    ap.add_argument("--decoder", type=int, default=0, help="1: time the whole sparse-MoE decoder (prefill + decode) instead")
+    ap.add_argument("--batch", type=int, default=256)
+    ap.add_argument("--prompt", type=int, default=512)
     a = ap.parse_args()
     world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -103,8 +188,11 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     _lib.init(local)
-    rep = run(torch, dist, rank, world, tuple(int(t) for t in a.tokens.split(",")), a.experts, a.hidden, a.ffn, a.top_k,
-              0 if a.fmt == "int8" else 1, a.reps)
+    if a.decoder:
+        rep = run_decoder(torch, dist, rank, world, batch=a.batch, prompt_len=a.prompt)
+    else:
+        rep = run(torch, dist, rank, world, tuple(int(t) for t in a.tokens.split(",")), a.experts, a.hidden, a.ffn, a.top_k,
+                  0 if a.fmt == "int8" else 1, a.reps)
     if rank == 0:
         print(json.dumps(rep))
     if world > 1:
