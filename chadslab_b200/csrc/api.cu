@@ -132,13 +132,15 @@ static bq_weight_t publish(Weight* w) {
 static size_t dt_size(int dt) { return dt == BQ_DT_F32 ? 4 : 2; }
 static bool dt_ok(int dt) { return dt == BQ_DT_F32 || dt == BQ_DT_BF16; }
 
-// Kernel-family choice.  MMA = tensor-core GEMV with exact group scaling (1..4 activation rows);
-// TENSOR = tcgen05 dequant-GEMM (bf16 activations, any M); SIMT = CUDA-core exact fp32 (any shape).
+// Kernel-family choice.  MMA = tensor-core GEMV: exact group scaling for 1..4 activation rows, the batched variant
+// (weights rounded to fp16 like the tcgen05 kernel) for 5..16 bf16 rows; TENSOR = tcgen05 dequant-GEMM (bf16
+// activations, any M); SIMT = CUDA-core exact fp32 (any shape).
 static int choose_path(const Weight* w, const void* x, int x_dtype, int64_t M, int requested) {
   if (requested == BQ_PATH_SIMT) return BQ_PATH_SIMT;
   const bool tc_ok = tc_supported(w->fmt, w->N, w->K, x_dtype, M) && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
   if (requested == BQ_PATH_TENSOR) return tc_ok ? BQ_PATH_TENSOR : -1;
-  const bool mma_ok = gemv_mma_supported(w->fmt, w->N, w->K, x_dtype, M);
+  const bool mma_ok = gemv_mma_supported(w->fmt, w->N, w->K, x_dtype, M) ||
+                      (gemv_batch_supported(w->fmt, w->N, w->K, x_dtype, M) && (reinterpret_cast<uintptr_t>(x) & 15) == 0);
   if (requested == BQ_PATH_MMA) return mma_ok ? BQ_PATH_MMA : -1;
   if (requested != BQ_PATH_AUTO) return -1;
   if (mma_ok) return BQ_PATH_MMA;
@@ -155,8 +157,15 @@ static int qlinear_impl(Weight* w, const void* x, int x_dtype, int64_t M, void* 
   const int p = choose_path(w, x, x_dtype, M, path);
   if (p < 0) return fail(BQ_ERR_UNSUPPORTED, "requested kernel path does not support this shape/dtype");
   set_last_path(p);
-  if (p == BQ_PATH_MMA)
-    return launch_qlinear_mma(w->codes, w->scales, w->fmt, w->N, w->K, x, x_dtype, M, y, y_dtype, w->N, s);
+  if (p == BQ_PATH_MMA) {
+    // 4-bit weights with 3 or 4 bf16 rows: the exact-scaling GEMV needs two column sets there (1.5x the one-row time,
+    // measured), the batched kernel serves up to 8 rows per set
+    const bool prefer_batch = w->fmt == BQ_FMT_Q4G32 && M >= 3 && gemv_batch_supported(w->fmt, w->N, w->K, x_dtype, M) &&
+                              (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+    if (!prefer_batch && gemv_mma_supported(w->fmt, w->N, w->K, x_dtype, M))
+      return launch_qlinear_mma(w->codes, w->scales, w->fmt, w->N, w->K, x, x_dtype, M, y, y_dtype, w->N, s);
+    return launch_qlinear_batch(w->codes, w->scales, w->fmt, w->N, w->K, x, x_dtype, M, y, y_dtype, w->N, -1, s);
+  }
   if (p == BQ_PATH_TENSOR)
     return launch_qlinear_tc(w->codes, w->scales, w->fmt, w->N, w->K, x, x_dtype, M, y, y_dtype, w->N, s);
   return launch_qlinear_simt(w->codes, w->scales, w->fmt, w->N, w->K, x, x_dtype, M, y, y_dtype, w->N, s);

@@ -117,6 +117,17 @@ int launch_qlinear_mma_push(const uint8_t* codes, const __half* scales, int fmt,
 // activations' dtype; act 0 = gelu (tanh), 1 = silu (gemv_gated.cu)
 int launch_qlinear_mma_gated(const uint8_t* codes, const __half* scales, int fmt, int64_t N, int64_t K,
                              const void* x, int x_dtype, int64_t M, void* out, int act, cudaStream_t s);
+// batched decode GEMV (gemv_batch.cu): 5..16 bf16 activation rows, code * scale rounded to fp16 like the tcgen05 kernel.
+// gated_act < 0: plain product; 0 / 1: fused gate|up weight (16-row blocks = 8 gate + 8 up rows), gelu / silu epilogue,
+// out[M, N/2] in bf16.
+bool gemv_batch_supported(int fmt, int64_t N, int64_t K, int x_dtype, int64_t M);
+int launch_qlinear_batch(const uint8_t* codes, const __half* scales, int fmt, int64_t N, int64_t K, const void* x,
+                         int x_dtype, int64_t M, void* y, int y_dtype, int64_t ldy, int gated_act, cudaStream_t s);
+// grouped experts at decode sizes on the same kernel: x holds the sorted rows (perm == nullptr) or the TOKEN rows, which
+// are then read through perm (row of sorted position p = perm[p] / top_k): no gathered copy is needed
+bool moe_batch_supported(const Moe* m);
+int launch_moe_experts_batch(const Moe* m, const void* x, const int32_t* perm, int top_k, const int32_t* offsets, int64_t P,
+                             void* hbuf, float* out, cudaStream_t s);
 bool moe_tc_supported(const Moe* m);
 int moe_tc_prepare(Moe* m, const std::vector<const uint8_t*>* codes, const std::vector<const __half*>* scales);
 void moe_tc_release(Moe* m);

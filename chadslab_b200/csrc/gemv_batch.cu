@@ -1,0 +1,432 @@
+// Batched decode GEMV: 5..16 activation rows (and the grouped MoE experts at decode sizes, where an expert sees a
+// dozen rows) on the tensor cores without the shared-memory / tensor-memory pipeline of the large-batch kernel.
+//
+// Same data path as the 1..4-row GEMV (gemv_mma.cuh): a warp owns 16 weight rows, every lane streams 16 contiguous
+// bytes of "its" row per step straight from HBM into registers (ld.global.nc, 128-bit), unpacks them with the
+// mantissa-insertion trick and feeds mma.sync.m16n8k16.  What differs is the exactness model: here the A operand holds
+// code * scale rounded once to fp16 (as in the tcgen05 kernel; max-normalised error ~2e-4 against the fp32 oracle),
+// so all 8 columns of the B operand are activation rows and one pass over the weights serves 8 rows per column set
+// (NB sets: 8 or 16 rows) with accumulators that live across the whole K loop.
+//
+// Activations: every CTA converts its (at most 16) rows to fp16 in shared memory, each row scaled by the power of two
+// that puts its maximum in [2^14, 2^15) (undone in the epilogue).  Within every k-step the row is stored so that the
+// four lanes of a quad read consecutive 16-byte pieces, and rows are padded by 64 bytes: the B-fragment loads of a
+// warp are then free of bank conflicts.
+//
+// Modes: plain y = x W^T; fused gate|up weight with the gated activation in the epilogue (16-row blocks = 8 gate rows +
+// the 8 up rows of the same outputs); MoE gate|up (two weights of one expert, rows of a 16-row tile of the expert's
+// segment, optionally gathered through the sort permutation, h = silu(g) * u as bf16); MoE down (fp32 rows out).
+#include "gemv_mma.cuh"
+
+namespace bq {
+
+constexpr int GB_WARPS = 8;
+constexpr int GB_THREADS = GB_WARPS * 32;
+constexpr int GB_DENSE = 0, GB_GATED = 1, GB_MOE_GU = 2, GB_MOE_DOWN = 3;
+
+struct GbArgs {
+  const uint8_t* codes;              // dense / gated: the weight
+  const __half* scales;
+  const uint8_t* const* codesA;      // MoE: per-expert pointers (gate or down)
+  const __half* const* scalesA;
+  const uint8_t* const* codesB;      // MoE gate|up: the up matrices
+  const __half* const* scalesB;
+  const __nv_bfloat16* x;            // activations (bf16): [m_rows, K]; MoE: rows addressed through the tile
+  const int32_t* perm;               // MoE gate|up: x holds TOKEN rows, sorted position p reads row perm[p] / top_k
+  const int32_t* offsets;            // MoE: expert row ranges
+  const int32_t* tiles;              // MoE: tiles[0] = count, then (expert, first row) pairs of 16-row tiles
+  void* y;
+  int64_t ldy, N, K;
+  int m_rows, top_k, act;
+};
+
+// 8 fp16 values of a row, k = 8c .. 8c+7, go to this offset (in halves) of the row's shared-memory image: inside a
+// k-step the pieces are ordered (piece i, lane t) instead of (lane t, piece i)
+template <bool Q8> __device__ __forceinline__ int64_t gb_xoffset(int64_t c) {
+  if (Q8) {   // step = 64 k = 8 pieces; lane t owns pieces 2t, 2t+1
+    const int64_t s = c >> 3;
+    const int r = (int)(c & 7), t = r >> 1, i = r & 1;
+    return s * 64 + i * 32 + t * 8;
+  } else {    // step = 128 k = 16 pieces; lane t owns pieces 4t .. 4t+3
+    const int64_t s = c >> 4;
+    const int r = (int)(c & 15), t = r >> 2, i = r & 3;
+    return s * 128 + i * 32 + t * 8;
+  }
+}
+
+template <int FMT, int NB, int KSPLIT, int MODE, typename YT>
+__global__ void __launch_bounds__(GB_THREADS) qgemv_batch_kernel(const __grid_constant__ GbArgs a) {
+  constexpr bool Q8 = FMT == BQ_FMT_Q8G32;
+  constexpr int KSTEP = Q8 ? 64 : 128;
+  constexpr int MMAS = Q8 ? 4 : 8;
+  constexpr int MP = 8 * NB;                       // activation rows a CTA holds (padded)
+  constexpr int RB_PER_CTA = GB_WARPS / KSPLIT;
+  constexpr bool MOE = MODE >= GB_MOE_GU;
+  constexpr bool TWO = MODE == GB_MOE_GU;          // two weight matrices share the activations
+  constexpr int NACC = TWO ? 2 : 1;
+  extern __shared__ __align__(16) uint8_t gb_smem[];
+  const int64_t K = a.K, N = a.N;
+  const int64_t xstride = K + 32;                  // halves: rows 64 bytes apart modulo 128
+  __half* xs = reinterpret_cast<__half*>(gb_smem);
+  float* xscale = reinterpret_cast<float*>(gb_smem + (size_t)MP * xstride * 2);     // [MP]
+  float* red = xscale + MP;                                                         // [NACC][GB_WARPS][16][MP]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+
+  pdl_wait();                                      // activations, tile list and row ranges come from preceding kernels
+  const uint8_t* codesA = a.codes;
+  const __half* scalesA = a.scales;
+  const uint8_t* codesB = nullptr;
+  const __half* scalesB = nullptr;
+  int64_t m0 = 0;
+  int m_rows = a.m_rows;
+  if (MOE) {
+    if ((int)blockIdx.x >= a.tiles[0]) return;     // uniform across the CTA, before any barrier
+    const int e = a.tiles[1 + 2 * blockIdx.x];
+    m0 = a.tiles[2 + 2 * blockIdx.x];
+    const int64_t m_end = a.offsets[e + 1];
+    m_rows = (int)(m_end - m0 < MP ? m_end - m0 : MP);
+    codesA = a.codesA[e]; scalesA = a.scalesA[e];
+    if (TWO) { codesB = a.codesB[e]; scalesB = a.scalesB[e]; }
+  }
+
+  // ---- activations -> scaled fp16 rows in shared memory (one warp per row, two passes over the row) ----------
+  for (int r = warp; r < MP; r += GB_WARPS) {
+    if (r >= m_rows) {                              // warp-uniform; unused columns only feed outputs nobody stores
+      if (lane == 0) xscale[r] = 0.0f;
+      continue;
+    }
+    int64_t src = MOE ? m0 + r : r;
+    if (MODE == GB_MOE_GU && a.perm) {
+      const int32_t p = a.perm[src];
+      src = p >= 0 ? p / a.top_k : 0;
+    }
+    const __nv_bfloat16* xrow = a.x + src * K;
+    float mx = 0.0f;
+    for (int64_t c = lane; c < K / 8; c += 32) {
+      float f[8];
+      load8<__nv_bfloat16>(xrow + c * 8, f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(f[i]));
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    int e = 0;
+    if (mx > 0.0f && mx < INFINITY) e = (int)((__float_as_uint(mx) >> 23) & 0xFF) - 127 - 14;
+    if (e < -100) e = -100;
+    const float down = __uint_as_float((uint32_t)(127 - e) << 23);
+    __half* xr = xs + (int64_t)r * xstride;
+    for (int64_t c = lane; c < K / 8; c += 32) {
+      float f[8];
+      load8<__nv_bfloat16>(xrow + c * 8, f);
+      __half h[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) h[i] = __float2half_rn(f[i] * down);
+      *reinterpret_cast<uint4*>(xr + gb_xoffset<Q8>(c)) = *reinterpret_cast<const uint4*>(h);
+    }
+    if (lane == 0) xscale[r] = __uint_as_float((uint32_t)(127 + e) << 23);
+  }
+  __syncthreads();
+
+  const int64_t row_bytes = Q8 ? K : K / 2;
+  const int64_t groups = K / GROUP;
+  const int rb_in_cta = warp / KSPLIT;
+  const int ksp = warp % KSPLIT;
+  const int64_t steps_total = K / KSTEP;
+  const int64_t s_begin = steps_total * ksp / KSPLIT, s_end = steps_total * (ksp + 1) / KSPLIT;
+  const int64_t cta_rb0 = (MOE ? (int64_t)blockIdx.y : (int64_t)blockIdx.x) * RB_PER_CTA;
+  const int64_t cta_rb_stride = (MOE ? (int64_t)gridDim.y : (int64_t)gridDim.x) * RB_PER_CTA;
+
+  for (int64_t rb_base = cta_rb0; rb_base * 16 < N; rb_base += cta_rb_stride) {
+    const int64_t rb = rb_base + rb_in_cta;
+    const bool active = rb * 16 < N;               // warp-uniform
+    int64_t r0 = rb * 16 + g, r1 = r0 + 8;
+    if (r0 >= N) r0 = N - 1;
+    if (r1 >= N) r1 = N - 1;
+    const uint8_t* pA0 = codesA + r0 * row_bytes + t * 16;
+    const uint8_t* pA1 = codesA + r1 * row_bytes + t * 16;
+    const __half* sA0 = scalesA + r0 * groups + (Q8 ? (t >> 1) : t);
+    const __half* sA1 = scalesA + r1 * groups + (Q8 ? (t >> 1) : t);
+    const uint8_t* pB0 = TWO ? codesB + r0 * row_bytes + t * 16 : nullptr;
+    const uint8_t* pB1 = TWO ? codesB + r1 * row_bytes + t * 16 : nullptr;
+    const __half* sB0 = TWO ? scalesB + r0 * groups + (Q8 ? (t >> 1) : t) : nullptr;
+    const __half* sB1 = TWO ? scalesB + r1 * groups + (Q8 ? (t >> 1) : t) : nullptr;
+    float d[NACC][NB][4];
+#pragma unroll
+    for (int w = 0; w < NACC; ++w)
+#pragma unroll
+      for (int b = 0; b < NB; ++b) d[w][b][0] = d[w][b][1] = d[w][b][2] = d[w][b][3] = 0.0f;
+
+#pragma unroll 2
+    for (int64_t s = active ? s_begin : s_end; s < s_end; ++s) {
+      uint4 wq[NACC][2];
+      __half2 sc[NACC][2];
+      wq[0][0] = ldg_stream16(pA0 + s * 64);
+      wq[0][1] = ldg_stream16(pA1 + s * 64);
+      sc[0][0] = __half2half2(sA0[s * (Q8 ? 2 : 4)]);
+      sc[0][1] = __half2half2(sA1[s * (Q8 ? 2 : 4)]);
+      if (TWO) {
+        wq[NACC - 1][0] = ldg_stream16(pB0 + s * 64);
+        wq[NACC - 1][1] = ldg_stream16(pB1 + s * 64);
+        sc[NACC - 1][0] = __half2half2(sB0[s * (Q8 ? 2 : 4)]);
+        sc[NACC - 1][1] = __half2half2(sB1[s * (Q8 ? 2 : 4)]);
+      }
+      // A fragments (code * scale as fp16): afr[j] = {row g slots 2t..; row g+8 slots 2t..; row g slots 2t+8..; row g+8 ..}
+      uint32_t afr[NACC][MMAS][4];
+#pragma unroll
+      for (int w = 0; w < NACC; ++w) {
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+          const uint32_t ww[4] = {wq[w][rr].x, wq[w][rr].y, wq[w][rr].z, wq[w][rr].w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            if (Q8) {
+              uint32_t lo, hi;
+              q8_word_to_h2(ww[q], lo, hi);
+              __half2 l2 = __hmul2(*reinterpret_cast<__half2*>(&lo), sc[w][rr]);
+              __half2 h2 = __hmul2(*reinterpret_cast<__half2*>(&hi), sc[w][rr]);
+              afr[w][q][rr] = *reinterpret_cast<uint32_t*>(&l2);
+              afr[w][q][2 + rr] = *reinterpret_cast<uint32_t*>(&h2);
+            } else {
+              uint32_t h[4];
+              q4_word_to_h2(ww[q], h);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                __half2 v = __hmul2(*reinterpret_cast<__half2*>(&h[i]), sc[w][rr]);
+                h[i] = *reinterpret_cast<uint32_t*>(&v);
+              }
+              afr[w][2 * q][rr] = h[0]; afr[w][2 * q][2 + rr] = h[1];
+              afr[w][2 * q + 1][rr] = h[2]; afr[w][2 * q + 1][2 + rr] = h[3];
+            }
+          }
+        }
+      }
+      // B fragments: column n = g is activation row 8 b + g; MMA j takes this lane's 4 consecutive k
+      const __half* xlane = xs + s * KSTEP + 8 * t;
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        const uint4* xp = reinterpret_cast<const uint4*>(xlane + (int64_t)(8 * b + g) * xstride);
+        uint32_t bfr[MMAS][2];
+#pragma unroll
+        for (int i = 0; i < MMAS / 2; ++i) {
+          const uint4 xv = xp[4 * i];                // pieces of a lane are 32 halves (4 x 16 bytes) apart
+          bfr[2 * i][0] = xv.x; bfr[2 * i][1] = xv.y; bfr[2 * i + 1][0] = xv.z; bfr[2 * i + 1][1] = xv.w;
+        }
+#pragma unroll
+        for (int w = 0; w < NACC; ++w)
+#pragma unroll
+          for (int j = 0; j < MMAS; ++j) mma_f16_16816(d[w][b], afr[w][j], bfr[j][0], bfr[j][1]);
+      }
+    }
+
+    // ---- K-split partials meet in shared memory (fixed order), then scale back and store -------------------------
+    // d[w][b] = {(row g, m = 8b+2t), (row g, m+1), (row g+8, m), (row g+8, m+1)}
+    if (KSPLIT > 1) {
+#pragma unroll
+      for (int w = 0; w < NACC; ++w)
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+          float* rw = red + ((size_t)(w * GB_WARPS + warp) * 16) * MP;
+          rw[g * MP + 8 * b + 2 * t] = d[w][b][0];
+          rw[g * MP + 8 * b + 2 * t + 1] = d[w][b][1];
+          rw[(g + 8) * MP + 8 * b + 2 * t] = d[w][b][2];
+          rw[(g + 8) * MP + 8 * b + 2 * t + 1] = d[w][b][3];
+        }
+      __syncthreads();
+      if (ksp == 0) {
+#pragma unroll
+        for (int w = 0; w < NACC; ++w)
+#pragma unroll
+          for (int b = 0; b < NB; ++b) {
+            float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+#pragma unroll
+            for (int i = 0; i < KSPLIT; ++i) {
+              const float* rw = red + ((size_t)(w * GB_WARPS + rb_in_cta * KSPLIT + i) * 16) * MP;
+              s0 += rw[g * MP + 8 * b + 2 * t];
+              s1 += rw[g * MP + 8 * b + 2 * t + 1];
+              s2 += rw[(g + 8) * MP + 8 * b + 2 * t];
+              s3 += rw[(g + 8) * MP + 8 * b + 2 * t + 1];
+            }
+            d[w][b][0] = s0; d[w][b][1] = s1; d[w][b][2] = s2; d[w][b][3] = s3;
+          }
+      }
+    }
+    if (active && (KSPLIT == 1 || ksp == 0)) {
+      const int64_t ra = rb * 16 + g, rbb = ra + 8;
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int m = 8 * b + 2 * t + j;
+          if (m < m_rows) {
+            const float back = xscale[m];
+            const float v0 = d[0][b][j] * back, v1 = d[0][b][2 + j] * back;        // rows g and g + 8
+            YT* yrow = reinterpret_cast<YT*>(a.y) + (m0 + m) * a.ldy;
+            if (MODE == GB_DENSE || MODE == GB_MOE_DOWN) {
+              if (ra < N) yrow[ra] = from_float<YT>(v0);
+              if (rbb < N) yrow[rbb] = from_float<YT>(v1);
+            } else if (MODE == GB_GATED) {        // v0 = gate, v1 = up of output column rb * 8 + g
+              if (rbb < N) {
+                float act;
+                if (a.act == 0) act = 0.5f * v0 * (1.0f + tanhf(0.7978845608028654f * (v0 + 0.044715f * v0 * v0 * v0)));
+                else act = v0 / (1.0f + __expf(-v0));
+                yrow[rb * 8 + g] = from_float<YT>(act * v1);
+              }
+            } else {                               // MoE gate|up: h = silu(gate) * up, same rows of both matrices
+              const float u0 = d[NACC - 1][b][j] * back, u1 = d[NACC - 1][b][2 + j] * back;
+              if (ra < N) yrow[ra] = from_float<YT>(v0 / (1.0f + __expf(-v0)) * u0);
+              if (rbb < N) yrow[rbb] = from_float<YT>(v1 / (1.0f + __expf(-v1)) * u1);
+            }
+          }
+        }
+      }
+    }
+    if (KSPLIT > 1) __syncthreads();
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------------------------------
+static size_t gb_smem_bytes(int nb, int64_t K, bool two) {
+  const int mp = 8 * nb;
+  return (size_t)mp * (K + 32) * 2 + (size_t)mp * 4 + (size_t)(two ? 2 : 1) * GB_WARPS * 16 * mp * 4;
+}
+
+bool gemv_batch_supported(int fmt, int64_t N, int64_t K, int x_dtype, int64_t M) {
+  (void)fmt;
+  if (x_dtype != BQ_DT_BF16 || M < 1 || M > 16 || N < 1 || (K % 128) != 0) return false;
+  return gb_smem_bytes(M <= 8 ? 1 : 2, K, false) <= 200 * 1024;
+}
+
+template <int FMT, int NB, int KSPLIT, int MODE, typename YT>
+static int gb_launch(const GbArgs& a, dim3 grid, bool two, cudaStream_t s) {
+  auto kern = qgemv_batch_kernel<FMT, NB, KSPLIT, MODE, YT>;
+  const size_t smem = gb_smem_bytes(NB, a.K, two);
+  static bool configured = false;
+  if (!configured) {
+    // the activation rows take tens of KB per CTA: ask for the largest shared-memory carve-out, or the default split
+    // between L1 and shared memory limits the kernel to one CTA per SM (measured: twice the run time)
+    BQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    BQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared));
+    configured = true;
+  }
+  BQ_CUDA(launch_chain(kern, grid, dim3(GB_THREADS), smem, s, 1, a));
+  count_launch();
+  BQ_CUDA(cudaGetLastError());
+  return BQ_OK;
+}
+
+// dense / gated: pick the K split like the 1..4-row GEMV does (enough warps to keep the memory system busy)
+template <int FMT, int NB, int MODE, typename YT>
+static int gb_dense(const GbArgs& a, cudaStream_t s) {
+  const int64_t rb = (a.N + 15) / 16;
+  const int64_t want = (int64_t)sm_count() * 16;
+  const size_t smem = gb_smem_bytes(NB, a.K, false);
+  int per_sm = (int)((220 * 1024) / (smem + 2048));
+  if (per_sm > 4) per_sm = 4;
+  if (per_sm < 1) per_sm = 1;
+  const int64_t cap = (int64_t)sm_count() * per_sm;
+  auto grid_for = [&](int ksplit) {
+    int64_t gx = (rb + GB_WARPS / ksplit - 1) / (GB_WARPS / ksplit);
+    return dim3((unsigned)(gx > cap ? cap : gx));
+  };
+  if (rb >= want || a.K < 1024) return gb_launch<FMT, NB, 1, MODE, YT>(a, grid_for(1), false, s);
+  if (rb * 2 >= want || a.K < 2048) return gb_launch<FMT, NB, 2, MODE, YT>(a, grid_for(2), false, s);
+  if (rb * 4 >= want || a.K < 4096) return gb_launch<FMT, NB, 4, MODE, YT>(a, grid_for(4), false, s);
+  return gb_launch<FMT, NB, 8, MODE, YT>(a, grid_for(8), false, s);
+}
+
+int launch_qlinear_batch(const uint8_t* codes, const __half* scales, int fmt, int64_t N, int64_t K, const void* x,
+                         int x_dtype, int64_t M, void* y, int y_dtype, int64_t ldy, int gated_act, cudaStream_t s) {
+  if (!gemv_batch_supported(fmt, N, K, x_dtype, M)) return fail(BQ_ERR_UNSUPPORTED, "shape not supported by the batched GEMV");
+  if ((reinterpret_cast<uintptr_t>(x) & 15) != 0) return fail(BQ_ERR_ARG, "activations must be 16-byte aligned");
+  GbArgs a;
+  memset(&a, 0, sizeof(a));
+  a.codes = codes; a.scales = scales; a.x = (const __nv_bfloat16*)x; a.y = y; a.ldy = ldy; a.N = N; a.K = K;
+  a.m_rows = (int)M; a.act = gated_act < 0 ? 0 : gated_act;
+  const bool gated = gated_act >= 0;
+#define BQ_GB_CASE(F, NBV)                                                                                      \
+  do {                                                                                                          \
+    if (gated) return gb_dense<F, NBV, GB_GATED, __nv_bfloat16>(a, s);                                          \
+    if (y_dtype == BQ_DT_F32) return gb_dense<F, NBV, GB_DENSE, float>(a, s);                                   \
+    return gb_dense<F, NBV, GB_DENSE, __nv_bfloat16>(a, s);                                                     \
+  } while (0)
+  if (fmt == BQ_FMT_Q8G32) { if (M <= 8) BQ_GB_CASE(BQ_FMT_Q8G32, 1); BQ_GB_CASE(BQ_FMT_Q8G32, 2); }
+  else                     { if (M <= 8) BQ_GB_CASE(BQ_FMT_Q4G32, 1); BQ_GB_CASE(BQ_FMT_Q4G32, 2); }
+#undef BQ_GB_CASE
+  return fail(BQ_ERR_ARG, "bad format");
+}
+
+// ---- MoE grouped experts at decode sizes: 16-row tiles of every expert's segment ----------------------------------
+__global__ void __launch_bounds__(1024) moe_tile16_kernel(const int32_t* __restrict__ offsets, int E, int32_t* __restrict__ tiles) {
+  __shared__ int32_t pre[1024];
+  const int e = threadIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
+  int32_t cnt = 0;
+  if (e < E) cnt = (offsets[e + 1] - offsets[e] + 15) / 16;
+  pre[e] = cnt;
+  __syncthreads();
+  for (int off = 1; off < 1024; off <<= 1) {
+    const int32_t add = e >= off ? pre[e - off] : 0;
+    __syncthreads();
+    pre[e] += add;
+    __syncthreads();
+  }
+  if (e < E) {
+    const int32_t base = pre[e] - cnt, first = offsets[e];
+    for (int i = 0; i < cnt; ++i) {
+      tiles[1 + 2 * (base + i)] = e;
+      tiles[2 + 2 * (base + i)] = first + i * 16;
+    }
+  }
+  if (e == E - 1) tiles[0] = pre[e];
+}
+
+bool moe_batch_supported(const Moe* m) {
+  return (m->H % 128) == 0 && (m->F % 128) == 0 && gb_smem_bytes(2, m->H, true) <= 200 * 1024 &&
+         gb_smem_bytes(2, m->F, false) <= 200 * 1024 && m->E <= 1024;
+}
+
+static Scratch g_tiles16;      // tile list of the current call (library scratch: see common.cuh)
+
+int launch_moe_experts_batch(const Moe* m, const void* x, const int32_t* perm, int top_k, const int32_t* offsets, int64_t P,
+                             void* hbuf, float* out, cudaStream_t s) {
+  if (!moe_batch_supported(m)) return fail(BQ_ERR_UNSUPPORTED, "batched-GEMV expert path unavailable for this expert shape");
+  if ((reinterpret_cast<uintptr_t>(x) & 15) != 0 || (reinterpret_cast<uintptr_t>(hbuf) & 15) != 0)
+    return fail(BQ_ERR_ARG, "activation buffers must be 16-byte aligned");
+  const int64_t max_tiles = (P + 15) / 16 + m->E;
+  int rc = scratch_ensure(&g_tiles16, sizeof(int32_t) * (size_t)(2 * max_tiles + 1 + 64), s, "bq_moe_experts (tile list)");
+  if (rc) return rc;
+  int32_t* tiles = (int32_t*)g_tiles16.ptr;
+  BQ_CUDA(launch_chain(moe_tile16_kernel, dim3(1), dim3(1024), 0, s, 1, offsets, m->E, tiles));
+  count_launch();
+  GbArgs a;
+  memset(&a, 0, sizeof(a));
+  a.codesA = m->gate_codes; a.scalesA = m->gate_scales; a.codesB = m->up_codes; a.scalesB = m->up_scales;
+  a.x = (const __nv_bfloat16*)x; a.perm = perm; a.top_k = top_k > 0 ? top_k : 1; a.offsets = offsets; a.tiles = tiles;
+  a.y = hbuf; a.ldy = m->F; a.N = m->F; a.K = m->H;
+  // gate|up: a warp streams 16 gate rows and the 16 up rows of the same outputs; 8 row blocks per CTA pass
+  {
+    const int64_t rb = (m->F + 15) / 16;
+    dim3 grid((unsigned)max_tiles, (unsigned)((rb + GB_WARPS - 1) / GB_WARPS));
+    rc = m->fmt == BQ_FMT_Q8G32 ? gb_launch<BQ_FMT_Q8G32, 2, 1, GB_MOE_GU, __nv_bfloat16>(a, grid, true, s)
+                                : gb_launch<BQ_FMT_Q4G32, 2, 1, GB_MOE_GU, __nv_bfloat16>(a, grid, true, s);
+    if (rc) return rc;
+  }
+  GbArgs b;
+  memset(&b, 0, sizeof(b));
+  b.codesA = m->down_codes; b.scalesA = m->down_scales; b.x = (const __nv_bfloat16*)hbuf; b.offsets = offsets; b.tiles = tiles;
+  b.y = out; b.ldy = m->H; b.N = m->H; b.K = m->F; b.top_k = 1;
+  {
+    // down: short K (a handful of steps per warp): every warp walks several row blocks
+    const int64_t rb = (m->H + 15) / 16;
+    int64_t gy = (rb + GB_WARPS * 4 - 1) / (GB_WARPS * 4);
+    if (gy < 1) gy = 1;
+    dim3 grid((unsigned)max_tiles, (unsigned)gy);
+    rc = m->fmt == BQ_FMT_Q8G32 ? gb_launch<BQ_FMT_Q8G32, 2, 1, GB_MOE_DOWN, float>(b, grid, false, s)
+                                : gb_launch<BQ_FMT_Q4G32, 2, 1, GB_MOE_DOWN, float>(b, grid, false, s);
+  }
+  return rc;
+}
+
+}  // namespace bq

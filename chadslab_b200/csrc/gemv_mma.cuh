@@ -448,9 +448,11 @@ static int gm_launch(const uint8_t* codes, const __half* scales, const XT* x, YT
   auto kern_cl = qgemv_mma_kernel<FMT, NV, KSPLIT, XT, YT, true, OUT>;
   const size_t smem = (size_t)NV * K * 2 + 32 + 2 * (size_t)GM_WARPS * 16 * NV * sizeof(float) + (OUT == GM_OUT_PUSH ? 128 + GM_WARPS * 4 * 16 * sizeof(float) : 0);
   static size_t configured = 0;
-  if (smem > 48 * 1024 && smem > configured) {
+  if (smem > 16 * 1024 && smem > configured) {      // long K or several vectors: room for several CTAs' activations per SM
     BQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     BQ_CUDA(cudaFuncSetAttribute(kern_cl, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    BQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared));
+    BQ_CUDA(cudaFuncSetAttribute(kern_cl, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared));
     configured = 200 * 1024;
   }
   const int64_t rb = (N + 15) / 16;

@@ -392,6 +392,220 @@ decode_attention_kernel(const T* __restrict__ q, const float* __restrict__ qkv, 
   }
 }
 
+// Grouped-query variant: one CTA serves `hpw` query heads of one KV head, so a K / V row is fetched once for all of
+// them instead of once per query head.  A warp's lanes are split as (head hl, chunk c): lane = hl * (32 / hpw) + c
+// owns EPLN = D * hpw / 32 consecutive head-dim elements of head hl; the lanes of different heads read the same K / V
+// bytes (one transaction).  Positions are walked as in the kernel above (a warp takes ATT_PB per trip, online softmax,
+// the 8 warps' states merge through shared memory, optional split over gridDim.z with a last-arrival merge).
+// grid.x = Hkv * (rep / hpw): KV head kv = blockIdx.x / (rep / hpw), query heads kv * rep + hg * hpw + hl.
+template <typename T, int N> struct RawVec { uint4 v[N * (int)sizeof(T) / 16]; };
+template <typename T, int N> __device__ __forceinline__ RawVec<T, N> load_rawvec(const T* p) {
+  RawVec<T, N> r;
+#pragma unroll
+  for (int i = 0; i < N * (int)sizeof(T) / 16; ++i) r.v[i] = reinterpret_cast<const uint4*>(p)[i];
+  return r;
+}
+template <int N> __device__ __forceinline__ void unpack_rawvec(const RawVec<float, N>& r, float* f) {
+#pragma unroll
+  for (int i = 0; i < N / 4; ++i) {
+    f[4 * i] = __uint_as_float(r.v[i].x); f[4 * i + 1] = __uint_as_float(r.v[i].y);
+    f[4 * i + 2] = __uint_as_float(r.v[i].z); f[4 * i + 3] = __uint_as_float(r.v[i].w);
+  }
+}
+template <int N> __device__ __forceinline__ void unpack_rawvec(const RawVec<__nv_bfloat16, N>& r, float* f) {
+#pragma unroll
+  for (int i = 0; i < N / 8; ++i) {
+    const uint32_t wds[4] = {r.v[i].x, r.v[i].y, r.v[i].z, r.v[i].w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      f[8 * i + 2 * j] = __uint_as_float(wds[j] << 16);
+      f[8 * i + 2 * j + 1] = __uint_as_float(wds[j] & 0xFFFF0000u);
+    }
+  }
+}
+// element d of a head taken from the fp32 projection output, rotated like rope_kv_append_kernel does
+template <typename T>
+__device__ __forceinline__ float rope_elem(const float* __restrict__ src, int d, int D, const float* cs, const float* sn, bool rotate) {
+  if (!rotate) return to_float<T>(from_float<T>(src[d]));
+  const int half = D / 2, j = d < half ? d : d - half;
+  const float x1 = to_float<T>(from_float<T>(src[j])), x2 = to_float<T>(from_float<T>(src[j + half]));
+  return to_float<T>(from_float<T>(d < half ? x1 * cs[j] - x2 * sn[j] : x2 * cs[j] + x1 * sn[j]));
+}
+constexpr int GQA_MAX_HD = 512;          // hpw * D handled by one warp (EPLN <= 16)
+template <typename T, bool FUSED, int EPLN, int PB>      // PB positions per warp and trip (K and V rows of a trip in flight)
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+decode_attention_gqa_kernel(const T* __restrict__ q, const float* __restrict__ qkv, T* __restrict__ k_cache,
+                            T* __restrict__ v_cache, const int64_t* __restrict__ pos_p, T* __restrict__ out, int Hq, int Hkv,
+                            int D, int64_t S, float rope_base, float* __restrict__ part, unsigned* __restrict__ counters,
+                            int* __restrict__ status, int hpw) {
+  const int rep = Hq / Hkv, gpk = rep / hpw;
+  const int b = blockIdx.y, kv = blockIdx.x / gpk, hg = blockIdx.x % gpk;
+  const int nsplit = gridDim.z, z = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int lph = 32 / hpw;                      // lanes per head = D / EPLN
+  const int hl = lane / lph, c = lane % lph;
+  const int h = kv * rep + hg * hpw + hl;        // this lane's query head
+  const int d0 = c * EPLN;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t n_all = *pos_p + 1;
+  if (n_all < 1 || n_all > S) {
+    if (threadIdx.x == 0) atomicExch(status, (int)BQ_ERR_ARG);
+    return;
+  }
+  __shared__ float s_cos[ATT_MAXD / 2], s_sin[ATT_MAXD / 2];
+  if (FUSED) {
+    for (int j = threadIdx.x; j < D / 2; j += blockDim.x) {
+      const float inv = 1.0f / powf(rope_base, (float)(2 * j) / (float)D);
+      sincosf((float)(n_all - 1) * inv, &s_sin[j], &s_cos[j]);
+    }
+    __syncthreads();
+  }
+  const int64_t per = ((n_all + nsplit - 1) / nsplit + PB - 1) / PB * PB;
+  const int64_t p_lo = (int64_t)z * per;
+  const int64_t n_own = p_lo + per < n_all ? p_lo + per : n_all;
+  const int64_t n_pos = FUSED && n_own == n_all ? n_all - 1 : n_own;
+  float qv[EPLN], acc[EPLN];
+  const float scale = rsqrtf((float)D);
+  if (FUSED) {
+    const float* src = qkv + ((int64_t)b * (Hq + 2 * Hkv) + h) * D;
+#pragma unroll
+    for (int i = 0; i < EPLN; ++i) qv[i] = rope_elem<T>(src, d0 + i, D, s_cos, s_sin, true) * scale;
+  } else {
+    const RawVec<T, EPLN> r = load_rawvec<T, EPLN>(q + ((int64_t)b * Hq + h) * D + d0);
+    unpack_rawvec<EPLN>(r, qv);
+#pragma unroll
+    for (int i = 0; i < EPLN; ++i) qv[i] *= scale;
+  }
+#pragma unroll
+  for (int i = 0; i < EPLN; ++i) acc[i] = 0.0f;
+  float mx = -INFINITY, sum = 0.0f;
+  const int64_t row_stride = (int64_t)Hkv * D;
+  const T* kbase = k_cache + ((int64_t)b * S * Hkv + kv) * D + d0;
+  const T* vbase = v_cache + ((int64_t)b * S * Hkv + kv) * D + d0;
+  for (int64_t s0 = p_lo + (int64_t)warp * PB; s0 < n_pos; s0 += ATT_WARPS * PB) {
+    RawVec<T, EPLN> kr[PB], vr[PB];
+    float dot[PB];
+#pragma unroll
+    for (int j = 0; j < PB; ++j) {
+      const int64_t sidx = s0 + j < n_pos ? s0 + j : n_pos - 1;       // clamp: masked below
+      kr[j] = load_rawvec<T, EPLN>(kbase + sidx * row_stride);
+    }
+#pragma unroll
+    for (int j = 0; j < PB; ++j) {
+      const int64_t sidx = s0 + j < n_pos ? s0 + j : n_pos - 1;
+      vr[j] = load_rawvec<T, EPLN>(vbase + sidx * row_stride);
+    }
+#pragma unroll
+    for (int j = 0; j < PB; ++j) {
+      float kf[EPLN], dsum = 0.0f;
+      unpack_rawvec<EPLN>(kr[j], kf);
+#pragma unroll
+      for (int i = 0; i < EPLN; ++i) dsum += qv[i] * kf[i];
+      for (int off = lph >> 1; off > 0; off >>= 1) dsum += __shfl_xor_sync(0xffffffffu, dsum, off);   // over the head's lanes
+      dot[j] = s0 + j < n_pos ? dsum : -INFINITY;
+    }
+    float nm = mx;
+#pragma unroll
+    for (int j = 0; j < PB; ++j) nm = fmaxf(nm, dot[j]);
+    const float corr = __expf(mx - nm);
+    sum *= corr;
+#pragma unroll
+    for (int i = 0; i < EPLN; ++i) acc[i] *= corr;
+#pragma unroll
+    for (int j = 0; j < PB; ++j) {
+      const float p = __expf(dot[j] - nm);
+      sum += p;
+      float vf[EPLN];
+      unpack_rawvec<EPLN>(vr[j], vf);
+#pragma unroll
+      for (int i = 0; i < EPLN; ++i) acc[i] += p * vf[i];
+    }
+    mx = nm;
+  }
+  if (FUSED && warp == 0 && p_lo < n_all && n_own == n_all) {
+    const int64_t pos = n_all - 1;
+    float kn[EPLN], vn[EPLN], dsum = 0.0f;
+    const float* ksrc = qkv + ((int64_t)b * (Hq + 2 * Hkv) + Hq + kv) * D;
+    const float* vsrc = qkv + ((int64_t)b * (Hq + 2 * Hkv) + Hq + Hkv + kv) * D;
+#pragma unroll
+    for (int i = 0; i < EPLN; ++i) {
+      kn[i] = rope_elem<T>(ksrc, d0 + i, D, s_cos, s_sin, true);
+      vn[i] = rope_elem<T>(vsrc, d0 + i, D, s_cos, s_sin, false);
+      dsum += qv[i] * kn[i];
+    }
+    if (hg == 0 && hl == 0) {                       // one head's lanes append the new rows to the cache
+      T* kd = k_cache + (((int64_t)b * S + pos) * Hkv + kv) * D + d0;
+      T* vd = v_cache + (((int64_t)b * S + pos) * Hkv + kv) * D + d0;
+#pragma unroll
+      for (int i = 0; i < EPLN; i += 8) { store8<T>(kd + i, kn + i); store8<T>(vd + i, vn + i); }
+    }
+    for (int off = lph >> 1; off > 0; off >>= 1) dsum += __shfl_xor_sync(0xffffffffu, dsum, off);
+    const float nm = fmaxf(mx, dsum);
+    const float corr = __expf(mx - nm), p = __expf(dsum - nm);
+    sum = sum * corr + p;
+#pragma unroll
+    for (int i = 0; i < EPLN; ++i) acc[i] = acc[i] * corr + p * vn[i];
+    mx = nm;
+  }
+  // ---- merge the 8 warps (per head), then the position splits ----------------------------------------------------
+  __shared__ float s_mx[ATT_WARPS][32], s_sum[ATT_WARPS][32], s_acc[ATT_WARPS][GQA_MAX_HD];
+  s_mx[warp][lane] = mx;
+  s_sum[warp][lane] = sum;
+#pragma unroll
+  for (int i = 0; i < EPLN; ++i) s_acc[warp][lane * EPLN + i] = acc[i];        // = [hl][d0 + i] since lane = hl * lph + c
+  __syncthreads();
+  const int HD = hpw * D;
+  const int64_t bh0 = (int64_t)b * Hq + kv * rep + hg * hpw;                    // first query head of this CTA
+  for (int e = threadIdx.x; e < HD; e += blockDim.x) {
+    const int eh = e / D, ed = e - eh * D, el = eh * lph;                       // a lane of head eh holds its (max, sum)
+    float gm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS; ++w) gm = fmaxf(gm, s_mx[w][el]);
+    float gs = 0.0f, o = 0.0f;
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS; ++w) {
+      const float f = s_mx[w][el] == -INFINITY ? 0.0f : __expf(s_mx[w][el] - gm);
+      gs += s_sum[w][el] * f;
+      o += s_acc[w][e] * f;
+    }
+    if (nsplit == 1) {
+      out[(bh0 + eh) * D + ed] = from_float<T>(o / gs);
+    } else {
+      float* mine = part + ((bh0 + eh) * nsplit + z) * (D + 2);
+      mine[2 + ed] = o;
+      if (ed == 0) { mine[0] = gm; mine[1] = gs; }
+    }
+  }
+  if (nsplit == 1) return;
+  __threadfence();
+  __syncthreads();
+  __shared__ int s_last;
+  const int64_t cidx = (int64_t)b * (Hkv * gpk) + blockIdx.x;                   // one arrival counter per (batch, head group)
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicAdd(&counters[cidx], 1u);
+    s_last = prev == (unsigned)nsplit - 1;
+    if (s_last) counters[cidx] = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int e = threadIdx.x; e < HD; e += blockDim.x) {
+    const int eh = e / D, ed = e - eh * D;
+    const float* all = part + (bh0 + eh) * nsplit * (D + 2);
+    float tm = -INFINITY;
+    for (int i = 0; i < nsplit; ++i) tm = fmaxf(tm, __ldcg(all + (int64_t)i * (D + 2)));
+    float ts = 0.0f, o = 0.0f;
+    for (int i = 0; i < nsplit; ++i) {
+      const float m_i = __ldcg(all + (int64_t)i * (D + 2));
+      const float f = m_i == -INFINITY ? 0.0f : __expf(m_i - tm);
+      ts += __ldcg(all + (int64_t)i * (D + 2) + 1) * f;
+      o += __ldcg(all + (int64_t)i * (D + 2) + 2 + ed) * f;
+    }
+    out[(bh0 + eh) * D + ed] = from_float<T>(o / ts);
+  }
+}
+
 // gu: fp32 [rows, 2F] = (gate | up) from the fused projection; out[r, f] = act(gate) * up, stored as T.
 // act: 0 = gelu (tanh approximation), 1 = silu
 template <typename T>
@@ -438,8 +652,17 @@ static int launch_attention(const void* q, const float* qkv, void* k_cache, void
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || D <= 0 || D > ATT_MAXD || (D % 8) || S <= 0)
     return fail(BQ_ERR_ARG, "bad sizes (head_dim <= 256 and a multiple of 8, Hq a multiple of Hkv)");
   if (!k_cache || !v_cache || !pos || !out) return fail(BQ_ERR_ARG, "null pointer");
-  // few (batch, head) pairs and a long cache: split the positions so that several CTAs per SM stream K/V
-  int64_t nsplit = (4 * (int64_t)sm_count() + B * Hq - 1) / (B * Hq);
+  // grouped-query attention: one CTA serves hpw query heads of a KV head (K / V rows fetched once for all of them)
+  const int rep = Hq / Hkv;
+  int hpw = 1;
+  while (hpw * 2 <= rep && rep % (hpw * 2) == 0 && hpw * 2 * D <= GQA_MAX_HD && hpw * 2 <= 32) hpw *= 2;
+  const int epln = D * hpw / 32;
+  const bool gqa = hpw > 1 && (D * hpw) % 32 == 0 && (epln == 8 || epln == 16) &&
+                   ((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) | reinterpret_cast<uintptr_t>(q) |
+                     reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  const int64_t ctas_xy = gqa ? B * Hkv * (rep / hpw) : B * Hq;
+  // few CTAs and a long cache: split the positions so that several CTAs per SM stream K/V
+  int64_t nsplit = (4 * (int64_t)sm_count() + ctas_xy - 1) / ctas_xy;
   if (nsplit > S / 128) nsplit = S / 128;        // at least 128 cache positions per split (measured: finer is slower)
   if (nsplit > 32) nsplit = 32;
   if (nsplit < 1) nsplit = 1;
@@ -451,6 +674,23 @@ static int launch_attention(const void* q, const float* qkv, void* k_cache, void
   }
   float* part = (float*)g_att_part.ptr;
   unsigned* counters = (unsigned*)g_att_count.ptr;
+  if (gqa) {
+    dim3 grid((unsigned)(Hkv * (rep / hpw)), (unsigned)B, (unsigned)nsplit);
+#define BQ_GQA_LAUNCH(TT, FUSED, EP)                                                                                       \
+  BQ_CUDA(launch_chain(decode_attention_gqa_kernel<TT, FUSED, EP, (sizeof(TT) * EP > 32 ? 2 : 4)>, grid, dim3(ATT_WARPS * 32), 0, s, 1, (const TT*)q, qkv,   \
+                       (TT*)k_cache, (TT*)v_cache, pos, (TT*)out, Hq, Hkv, D, S, rope_base, part, counters, status_word(), hpw))
+#define BQ_GQA_PICK(TT)                                                                            \
+  do {                                                                                             \
+    if (epln == 8) { if (qkv) BQ_GQA_LAUNCH(TT, true, 8); else BQ_GQA_LAUNCH(TT, false, 8); }      \
+    else           { if (qkv) BQ_GQA_LAUNCH(TT, true, 16); else BQ_GQA_LAUNCH(TT, false, 16); }    \
+  } while (0)
+    if (dtype == BQ_DT_F32) BQ_GQA_PICK(float); else BQ_GQA_PICK(__nv_bfloat16);
+#undef BQ_GQA_PICK
+#undef BQ_GQA_LAUNCH
+    count_launch();
+    BQ_CUDA(cudaGetLastError());
+    return BQ_OK;
+  }
   dim3 grid((unsigned)Hq, (unsigned)B, (unsigned)nsplit);
 #define BQ_ATT_LAUNCH(TT, FUSED)                                                                                        \
   BQ_CUDA(launch_chain(decode_attention_kernel<TT, FUSED>, grid, dim3(ATT_WARPS * 32), 0, s, 1, (const TT*)q, qkv, (TT*)k_cache, \
@@ -557,6 +797,12 @@ int bq_qlinear_gated(bq_weight_t weight, const void* x, int x_dtype, int64_t M, 
   if (M == 0) return BQ_OK;
   if (!x || !out) return fail(BQ_ERR_ARG, "null pointer");
   cudaStream_t s = (cudaStream_t)stream;
+  const bool batch_ok = x_dtype == BQ_DT_BF16 && gemv_batch_supported(w->fmt, w->N, w->K, x_dtype, M) &&
+                        (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+  if (batch_ok && (M > 4 || (w->fmt == BQ_FMT_Q4G32 && M >= 3))) {      // 3..16 rows: the batched GEMV, same epilogue
+    set_last_path(BQ_PATH_MMA);
+    return launch_qlinear_batch(w->codes, w->scales, w->fmt, w->N, w->K, x, x_dtype, M, out, BQ_DT_BF16, w->N / 2, act, s);
+  }
   if (gemv_mma_supported(w->fmt, w->N, w->K, x_dtype, M)) {      // decode-sized: activation in the GEMV's epilogue
     set_last_path(BQ_PATH_MMA);
     return launch_qlinear_mma_gated(w->codes, w->scales, w->fmt, w->N, w->K, x, x_dtype, M, out, act, s);

@@ -568,6 +568,14 @@ int bq_moe_experts_ex(bq_moe_t h, const void* xp_bf16, const int32_t* offsets, i
   cudaStream_t s = (cudaStream_t)stream;
   const bool tc_ok = m->tc_state != nullptr;
   if (path == BQ_PATH_TENSOR && !tc_ok) return fail(BQ_ERR_UNSUPPORTED, "tensor path unavailable for this expert shape");
+  // decode sizes (an expert sees about a dozen rows): the batched GEMV streams every expert's weights once per
+  // 16-row tile straight from HBM into registers; larger segments amortise the tcgen05 pipeline
+  const bool batch_ok = moe_batch_supported(m) && ((reinterpret_cast<uintptr_t>(xp_bf16) | reinterpret_cast<uintptr_t>(hbuf_bf16)) & 15) == 0;
+  if (path == BQ_PATH_MMA && !batch_ok) return fail(BQ_ERR_UNSUPPORTED, "batched-GEMV path unavailable for this expert shape");
+  if (path == BQ_PATH_MMA || (path == BQ_PATH_AUTO && batch_ok && rows_hint <= (int64_t)m->E * 20)) {
+    set_last_path(BQ_PATH_MMA);
+    return launch_moe_experts_batch(m, xp_bf16, nullptr, 1, offsets, P, hbuf_bf16, out, s);
+  }
   if ((path == BQ_PATH_AUTO && tc_ok) || path == BQ_PATH_TENSOR) {
     set_last_path(BQ_PATH_TENSOR);
     return launch_moe_experts_tc(m, xp_bf16, offsets, P, rows_hint, hbuf_bf16, out, s);

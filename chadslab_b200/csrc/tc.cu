@@ -199,18 +199,12 @@ template <int FMT, int BN, int MODE> struct T2Plan {
   static constexpr int SCT = TC_ROWS * 16;                                // 8 fp16 scales per row = 256 k = 2 steps
   static constexpr int STAGE = ((NW * RAW + XT + 1023) / 1024) * 1024;
   static constexpr int FIXED = TC_SC_SLOTS * NW * SCT + 1024 + 1024;
-  // Small batch tiles: successive tcgen05.mma into ONE accumulator serialise on that accumulator (each takes the
-  // pipeline's latency whatever N is), so the 8 MMAs of a step rotate over NACC independent accumulators (chains of
-  // every NACC-th k-slice) which the epilogue adds up.  NACC keeps all accumulators within 128 columns.
-#ifndef BQ_NACC_MAX
-#define BQ_NACC_MAX 4
-#endif
-  static constexpr int NACC_WANT = NW * BN <= 32 ? 4 : NW * BN <= 64 ? 2 : 1;
-  static constexpr int NACC = NACC_WANT < BQ_NACC_MAX ? NACC_WANT : BQ_NACC_MAX;
-  // tensor memory: NW x NACC accumulators of BN columns from column 0 (weight w, chain c at (w * NACC + c) * BN), then
-  // NW x 2 A buffers of 64 columns from ACOL0.
+  // tensor memory: NW accumulators of BN columns from column 0, then NW x 2 A buffers of 64 columns from ACOL0.
+  // (One accumulator per weight tile: rotating the 8 MMAs of a step over several independent accumulators was
+  // measured and gave nothing at any batch size -- small MMAs do not serialise on the accumulator -- while it made
+  // the k-summation order, hence the low bits of the result, depend on the tile size.)
   // 256 columns (two CTAs per SM) only when everything fits below 256; two weight tiles always need 512.
-  static constexpr int ACOL0 = NW * BN * NACC <= 128 ? 128 : 256;         // first A-buffer column
+  static constexpr int ACOL0 = NW * BN <= 128 ? 128 : 256;                // first A-buffer column
   static constexpr int TMEM_NEED = ACOL0 + NW * 2 * T2_ACOLS;
   static constexpr int TMEM_COLS = TMEM_NEED <= 256 ? 256 : 512;
   static constexpr int BUDGET = (TMEM_COLS == 256 ? 100 : 200) * 1024;    // shared memory follows: two CTAs per SM or one
@@ -218,7 +212,7 @@ template <int FMT, int BN, int MODE> struct T2Plan {
   static constexpr int S = S_RAW > 4 ? 4 : (S_RAW < 2 ? 2 : S_RAW);       // S <= 2*SC_SLOTS - 1 = 5
   static constexpr int SMEM = FIXED + S * STAGE;
   static_assert(TMEM_NEED <= 512, "tensor memory plan too large");
-  static_assert(NW * BN * NACC <= ACOL0 && BN % 16 == 0, "accumulators must fit below the A buffers");
+  static_assert(NW * BN <= ACOL0 && BN % 16 == 0, "accumulators must fit below the A buffers");
   static_assert(SMEM <= 227 * 1024, "shared memory plan too large");
 };
 
@@ -364,12 +358,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tmem_kernel(const __grid_
 #pragma unroll
         for (int w = 0; w < NW; ++w) {
           const uint32_t a_tmem = tmem_base + (uint32_t)(P::ACOL0 + (w * NA + a) * T2_ACOLS);
-          const uint32_t d_tmem = tmem_base + (uint32_t)(w * P::NACC * BN);
+          const uint32_t d_tmem = tmem_base + (uint32_t)(w * BN);
 #pragma unroll
-          for (int kk = 0; kk < T2_BK / 16; ++kk)      // k-slice kk goes to chain kk % NACC; a chain's first MMA overwrites
-            tc_mma_f16_ts(d_tmem + (uint32_t)((kk % P::NACC) * BN), a_tmem + (uint32_t)(8 * kk),
-                          bdesc0 + (uint64_t)((((kk >> 2) * BN * 128) >> 4) + 2 * (kk & 3)), idesc,
-                          (ks > 0 || kk >= P::NACC) ? 1u : 0u);
+          for (int kk = 0; kk < T2_BK / 16; ++kk)
+            tc_mma_f16_ts(d_tmem, a_tmem + (uint32_t)(8 * kk),
+                          bdesc0 + (uint64_t)((((kk >> 2) * BN * 128) >> 4) + 2 * (kk & 3)), idesc, (ks > 0 || kk > 0) ? 1u : 0u);
         }
         tc_commit(smem_u32(&a_empty[a]));
         tc_commit(smem_u32(&empty[s]));
@@ -439,20 +432,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tmem_kernel(const __grid_
         if (GATED) {                               // h = silu(gate) * up, rounded to bf16
           uint32_t v[16], u[16];
           tc_ld16(tbase + (uint32_t)c0, v);
-          tc_ld16(tbase + (uint32_t)(P::NACC * BN + c0), u);
+          tc_ld16(tbase + (uint32_t)(BN + c0), u);
           tc_ld_wait();
-#pragma unroll
-          for (int ch = 1; ch < P::NACC; ++ch) {      // add the other accumulation chains
-            uint32_t v2[16], u2[16];
-            tc_ld16(tbase + (uint32_t)(ch * BN + c0), v2);
-            tc_ld16(tbase + (uint32_t)((P::NACC + ch) * BN + c0), u2);
-            tc_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(v2[j]));
-              u[j] = __float_as_uint(__uint_as_float(u[j]) + __uint_as_float(u2[j]));
-            }
-          }
           if (n < args.N) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
@@ -470,16 +451,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tmem_kernel(const __grid_
 #pragma unroll
         for (int w = 0; w < NW; ++w) {
           uint32_t v[16];
-          tc_ld16(tbase + (uint32_t)(w * P::NACC * BN + c0), v);
+          tc_ld16(tbase + (uint32_t)(w * BN + c0), v);
           tc_ld_wait();
-#pragma unroll
-          for (int ch = 1; ch < P::NACC; ++ch) {      // add the other accumulation chains
-            uint32_t v2[16];
-            tc_ld16(tbase + (uint32_t)((w * P::NACC + ch) * BN + c0), v2);
-            tc_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(v2[j]));
-          }
           const int64_t nn = n + w * TC_ROWS;
           if (nn < args.N) {
 #pragma unroll

@@ -90,7 +90,7 @@ def run(torch, dist, rank, world, tokens=(256,), E=128, H=2048, F=768, top_k=8, 
 
 
 def run_decoder(torch, dist, rank, world, batch: int = 256, prompt_len: int = 512, steps: int = 8, chunk_seqs: int = 16,
-                cfg=None):
+                cfg=None, eager: bool = False):
     """The whole sparse-MoE decoder (48 layers, hidden 2048, 32 query / 4 KV heads of 128, 128 experts of SwiGLU 768,
     top-8, every weight 4-bit group-32, random-init): prefill of `batch` random sequences of `prompt_len` tokens in
     chunks of sequences, then greedy decode of the whole batch as replays of one captured CUDA graph.  With `world`
@@ -130,7 +130,16 @@ def run_decoder(torch, dist, rank, world, batch: int = 256, prompt_len: int = 51
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         pre_ms = float(t[0])
-        step, toks = dec.make_graph_stepper(B_loc, first, start_pos=dec.pos)
+        if eager:                      # launches the step's kernels directly (what a profiler wants)
+            toks = first.clone()
+            pos_t = torch.tensor([dec.pos], device="cuda", dtype=torch.int64)
+            p0 = dec.pos
+
+            def step():
+                dec._step_static(toks, pos_t)
+                pos_t.fill_(p0)
+        else:
+            step, toks = dec.make_graph_stepper(B_loc, first, start_pos=dec.pos)
         for _ in range(3):
             step()
         torch.cuda.synchronize()
@@ -181,6 +190,9 @@ def main():
     ap.add_argument("--decoder", type=int, default=0, help="1: time the whole sparse-MoE decoder (prefill + decode) instead")
     ap.add_argument("--batch", type=int, default=256)
     ap.add_argument("--prompt", type=int, default=512)
+    ap.add_argument("--layers", type=int, default=0, help="decoder: use this many layers instead of the shape's 48")
+    ap.add_argument("--eager", type=int, default=0, help="decoder: launch the decode step's kernels directly")
+    ap.add_argument("--steps", type=int, default=8)
     a = ap.parse_args()
     world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -189,7 +201,10 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     _lib.init(local)
     if a.decoder:
-        rep = run_decoder(torch, dist, rank, world, batch=a.batch, prompt_len=a.prompt)
+        import dataclasses
+        from chadslab_b200.decoder import MOE_SHAPE
+        cfg = dataclasses.replace(MOE_SHAPE, layers=a.layers) if a.layers else MOE_SHAPE
+        rep = run_decoder(torch, dist, rank, world, batch=a.batch, prompt_len=a.prompt, steps=a.steps, cfg=cfg, eager=bool(a.eager))
     else:
         rep = run(torch, dist, rank, world, tuple(int(t) for t in a.tokens.split(",")), a.experts, a.hidden, a.ffn, a.top_k,
                   0 if a.fmt == "int8" else 1, a.reps)

@@ -138,7 +138,7 @@ def test_moe_layer_random(cuda_lib, fmt, T):
     down = [q(rng.normal(0, 0.05, (H, F)).astype(np.float32)) for _ in range(E)]
     ref, (ridx, rw, rperm, roff) = spec.moe_forward(x, router, gate, up, down, fmt, k)
     pw = lambda cs: cb.PackedWeight.from_arrays(cs[0], cs[1], fmt)
-    for path in (cb.PATH_SIMT, cb.PATH_TENSOR):
+    for path in (cb.PATH_SIMT, cb.PATH_TENSOR, cb.PATH_MMA):       # exact CUDA-core, tcgen05 grouped, batched GEMV
         layer = cb.MoEExperts(pw(router), [pw(g) for g in gate], [pw(u) for u in up], [pw(d) for d in down], top_k=k,
                               path=path)
         _check_layer(cb, torch, layer, x, E, k, gate, up, down, fmt, golden_y=(ref, ridx))
@@ -162,7 +162,9 @@ def test_grouped_experts_at_scale_against_simt_path(cuda_lib, fmt, T):
         return cb.PackedWeight.from_device(c, s, fmt)
     gate, up, down = [mk(F, H) for _ in range(E)], [mk(F, H) for _ in range(E)], [mk(H, F) for _ in range(E)]
     router = mk(E, H)
-    tens = cb.MoEExperts(router, gate, up, down, top_k=k, path=cb.PATH_TENSOR)
+    # up to ~20 rows per expert the dispatcher takes the batched GEMV (16-row tiles), above it the tcgen05 kernel;
+    # T = 4096 also runs the batched GEMV explicitly (segments of ~512 rows = 32 tiles per expert)
+    tens = cb.MoEExperts(router, gate, up, down, top_k=k, path=cb.PATH_AUTO if T != 4096 else cb.PATH_MMA)
     simt = cb.MoEExperts(router, gate, up, down, top_k=k, path=cb.PATH_SIMT)
     x = torch.randn((T, H), device="cuda", generator=gen).to(torch.bfloat16)
     idx, w = cb.moe_route(tens.router(x), k)

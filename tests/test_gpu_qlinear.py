@@ -66,7 +66,7 @@ def test_qlinear_parity_sweep(cuda_lib, N, K, fmt, xdt):
     codes, scales = spec.quantize(W, fmt)
     pw = cb.PackedWeight.from_arrays(codes, scales, fmt)
     lin = cb.QuantLinear(pw)
-    for M in (1, 2, 3, 5, 8, 17, 64, 130):
+    for M in (1, 2, 3, 5, 8, 9, 16, 17, 64, 130):
         x = rng.normal(0, 1, (M, K)).astype(np.float32)
         if xdt == "bf16":
             x = spec.bf16_round(x)
