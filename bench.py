@@ -13,8 +13,9 @@ the same step driven from host buffers: token ids copied in from pinned memory a
 every step.  Strong scaling: the work per step is fixed, N GPUs share it.  Weights are random-init (seeded,
 N(0, 0.02), quantized with the format's rule) and the context is synthetic (random K/V in the cache).
 
-`roofline` is the largest quantized-matmul launch of the step (the lm_head GEMV / GEMM on this rank's vocabulary
-slice), timed alone with CUDA events, L2 flushed between launches.  `extras` holds what else the configs name:
+`roofline` is the kernel with the largest share of the step (decode attention at this batch: K and V rows are its
+algorithmic bytes), `roofline_quantized_matmul` the largest quantized-matmul launch of the step (the lm_head on this
+rank's vocabulary slice); both are timed alone with CUDA events, L2 flushed between launches.  `extras` holds what else the configs name:
 the standalone sweep of configs[1] (with per-problem and aggregate fractions of the HBM peak), the Gemma-2B-shaped
 decoder of configs[0], all three batch sizes of configs[2], one sparse-MoE layer and the whole sparse-MoE decoder of
 configs[3], the long prefill of configs[4], and `parity`: a small same-weights decoder and MoE layer sharded over
@@ -495,6 +496,7 @@ def run_gpu(args):
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": headline_config(world),
             "roofline": hb.get("roofline"),
+            "roofline_quantized_matmul": hb.get("roofline_quantized_matmul"),
             "e2e": {"value": round(HEADLINE_BATCH * 1e3 / e2e_ms, 1) if e2e_ms else None, "unit": "tokens/s",
                     "h2d_bytes_per_step": HEADLINE_BATCH * 8, "d2h_bytes_per_step": HEADLINE_BATCH * 8,
                     "how": "every step: token ids copied from pinned host memory, one graph replay, new ids copied back to "
@@ -519,6 +521,46 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
+def run_one_qlinear(args):
+    """`--only qlinear`: one weight shape, the given batch sizes and kernel path, CUDA-event timing per launch (the small,
+    single-kernel case the ncu summaries under profiles/ are captured on).  One JSON line per (format, M)."""
+    import torch
+    import chadslab_b200 as cb
+    from chadslab_b200 import _lib
+    torch.cuda.set_device(0)
+    lib = _lib.init(0)
+    paths = {"auto": 0, "simt": 1, "tensor": 2, "mma": 3}
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    stream = torch.cuda.current_stream().cuda_stream
+    for fname in args.fmt.split(","):
+        fmt = {"int8": 0, "q4": 1}[fname]
+        codes, scales = make_device_weight(torch, args.n, args.k, fmt, gen)
+        pws = [cb.PackedWeight.from_device(codes.roll(c, 0).contiguous() if c else codes,
+                                           scales.roll(c, 0).contiguous() if c else scales, fmt) for c in range(args.copies)]
+        del codes, scales
+        for M in [int(v) for v in args.m.split(",")]:
+            x = torch.randn((M, args.k), device="cuda", generator=gen).to(torch.bfloat16)
+            y = torch.empty((M, args.n), dtype=torch.float32, device="cuda")
+            call = lambda i: _lib.check(lib.bq_qlinear_ex(pws[i % len(pws)].handle, x.data_ptr(), cb.DT_BF16, M, y.data_ptr(),
+                                                          cb.DT_F32, paths[args.path], stream))
+            for i in range(3):
+                call(i)
+            a, b = _events(torch)
+            a.record()
+            for i in range(args.reps):
+                call(i)
+            b.record()
+            torch.cuda.synchronize()
+            us = a.elapsed_time(b) * 1e3 / args.reps
+            print(json.dumps({"N": args.n, "K": args.k, "fmt": fname, "M": M,
+                              "path": {0: "none", 1: "simt", 2: "tensor", 3: "mma"}[lib.bq_last_path()], "us": round(us, 2),
+                              "GBps": round(algorithmic_bytes(args.n, args.k, fmt, M) / us / 1e3, 1),
+                              "TFLOPs": round(2.0 * M * args.n * args.k / us / 1e6, 2)}), flush=True)
+        for p in pws:
+            p.close()
+    _lib.check(lib.bq_status_poll())
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -527,8 +569,18 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--extras", type=int, default=1, help="also run the other configs, the parity check and the sweep")
     ap.add_argument("--cpu", type=int, default=1, help="N = 1: also time the numpy oracle sample (cpu_baseline)")
+    ap.add_argument("--only", default="", choices=["", "qlinear"], help="qlinear: time one weight shape instead of the benchmark")
+    ap.add_argument("--n", type=int, default=65536)
+    ap.add_argument("--k", type=int, default=2048)
+    ap.add_argument("--fmt", default="int8,q4")
+    ap.add_argument("--m", default="1")
+    ap.add_argument("--path", default="auto", choices=["auto", "simt", "tensor", "mma"])
+    ap.add_argument("--reps", type=int, default=3)
+    ap.add_argument("--copies", type=int, default=1)
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.only == "qlinear":
+        run_one_qlinear(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_gpu(args)

@@ -58,6 +58,7 @@ PROTOTYPES = {
     "bq_decode_attention_rope": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i64, C.c_float, _i32, _vp]),
     "bq_gated_act": (_i32, [_vp, _vp, _i64, _i64, _i32, _i32, _vp]),
     "bq_moe_route": (_i32, [_vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp]),
+    "bq_moe_route_linear": (_i32, [_h, _vp, _i64, _i32, _i32, _vp, _vp, _vp]),
     "bq_moe_permute_scratch_bytes": (_i64, [_i64, _i32, _i32]),
     "bq_moe_permute": (_i32, [_vp, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp]),
     "bq_moe_permute_noalloc_max_bytes": (_i64, []),
@@ -67,6 +68,7 @@ PROTOTYPES = {
     "bq_moe_destroy": (_i32, [_h]),
     "bq_moe_experts": (_i32, [_h, _vp, _vp, _i64, _vp, _vp, _i32, _vp]),
     "bq_moe_experts_ex": (_i32, [_h, _vp, _vp, _i64, _i64, _vp, _vp, _i32, _vp]),
+    "bq_moe_experts_tokens": (_i32, [_h, _vp, _vp, _i32, _vp, _i64, _i64, _vp, _vp, _vp, _i32, _vp]),
     "bq_moe_combine": (_i32, [_vp, _vp, _vp, _i64, _i32, _i64, _vp, _i32, _vp]),
     "bq_comm_create": (_i32, [_i32, _i32, _i64, C.POINTER(_h)]),
     "bq_comm_handle": (_i32, [_h, _vp]),

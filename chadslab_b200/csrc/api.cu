@@ -158,9 +158,9 @@ static int qlinear_impl(Weight* w, const void* x, int x_dtype, int64_t M, void* 
   if (p < 0) return fail(BQ_ERR_UNSUPPORTED, "requested kernel path does not support this shape/dtype");
   set_last_path(p);
   if (p == BQ_PATH_MMA) {
-    // 4-bit weights with 3 or 4 bf16 rows: the exact-scaling GEMV needs two column sets there (1.5x the one-row time,
-    // measured), the batched kernel serves up to 8 rows per set
-    const bool prefer_batch = w->fmt == BQ_FMT_Q4G32 && M >= 3 && gemv_batch_supported(w->fmt, w->N, w->K, x_dtype, M) &&
+    // 3 or 4 bf16 rows: the exact-scaling GEMV needs a second column set there (4-bit: 1.5x the one-row time, int8 at 4
+    // rows the same as the batched kernel or worse, measured); the batched kernel serves up to 8 rows per set
+    const bool prefer_batch = M >= 3 && gemv_batch_supported(w->fmt, w->N, w->K, x_dtype, M) &&
                               (reinterpret_cast<uintptr_t>(x) & 15) == 0;
     if (!prefer_batch && gemv_mma_supported(w->fmt, w->N, w->K, x_dtype, M))
       return launch_qlinear_mma(w->codes, w->scales, w->fmt, w->N, w->K, x, x_dtype, M, y, y_dtype, w->N, s);

@@ -100,10 +100,11 @@ int launch_unpack(const Weight* w, int8_t* out, cudaStream_t s);
 int launch_qlinear_simt(const uint8_t* codes, const __half* scales, int fmt, int64_t N, int64_t K,
                         const void* x, int x_dtype, int64_t M, void* y, int y_dtype, int64_t ldy,
                         cudaStream_t s);
-// tensor-core (tcgen05) path: bf16 activations
+// tensor-core (tcgen05) path: bf16 activations.  gated_act >= 0: fused gate|up weight (16-row blocks = 8 gate + 8 up rows),
+// y = act(gate) * up as bf16 [M, N / 2] with ldy = N / 2 (0 = gelu-tanh, 1 = silu)
 int launch_qlinear_tc(const uint8_t* codes, const __half* scales, int fmt, int64_t N, int64_t K,
                       const void* x, int x_dtype, int64_t M, void* y, int y_dtype, int64_t ldy,
-                      cudaStream_t s);
+                      cudaStream_t s, int gated_act = -1);
 bool tc_supported(int fmt, int64_t N, int64_t K, int x_dtype, int64_t M);
 // tensor-core GEMV with exact group scaling (mma.sync), 1..4 activation rows
 int launch_qlinear_mma(const uint8_t* codes, const __half* scales, int fmt, int64_t N, int64_t K,
@@ -125,6 +126,10 @@ int launch_qlinear_batch(const uint8_t* codes, const __half* scales, int fmt, in
                          int x_dtype, int64_t M, void* y, int y_dtype, int64_t ldy, int gated_act, cudaStream_t s);
 // grouped experts at decode sizes on the same kernel: x holds the sorted rows (perm == nullptr) or the TOKEN rows, which
 // are then read through perm (row of sorted position p = perm[p] / top_k): no gathered copy is needed
+// router linear + softmax + top-k in one launch (E <= 128 experts)
+bool moe_route_linear_supported(int fmt, int64_t E, int64_t K, int top_k);
+int launch_moe_route_linear(const uint8_t* codes, const __half* scales, int fmt, int64_t E, int64_t K, const void* x, int64_t T,
+                            int top_k, int renorm, int32_t* idx_out, float* w_out, cudaStream_t s);
 bool moe_batch_supported(const Moe* m);
 int launch_moe_experts_batch(const Moe* m, const void* x, const int32_t* perm, int top_k, const int32_t* offsets, int64_t P,
                              void* hbuf, float* out, cudaStream_t s);

@@ -165,13 +165,13 @@ __device__ __forceinline__ void ep_signal_all(const EpDev* d, int counter_word, 
 }
 
 // ---- step 2: counts to everybody, layout tables ------------------------------------------------------------
-// One CTA of 1024 threads; thread x owns expert x (E <= 1024).
+// One CTA of NT = the power of two >= E threads (at least 32); thread x owns expert x (E <= 1024).
 // `matrix` != nullptr (self-test): the whole count matrix [world][E] is given, nothing is exchanged.
 __global__ void __launch_bounds__(1024) ep_layout_kernel(const EpDev* __restrict__ d, const int32_t* __restrict__ offsets,
                                                           const int32_t* __restrict__ matrix, int* status) {
   __shared__ int32_t scan[1024];
   __shared__ int32_t tot[1024];
-  const int x = threadIdx.x;
+  const int x = threadIdx.x, NT = blockDim.x;
   const int world = d->world, E = d->E, El = d->El, me = d->rank;
   if (!matrix && ep_failed(d, status)) return;
   const uint32_t e = matrix ? 0u : *reinterpret_cast<const volatile uint32_t*>(ep_hdr(d, me));
@@ -223,7 +223,7 @@ __global__ void __launch_bounds__(1024) ep_layout_kernel(const EpDev* __restrict
   tot[x] = x < E ? total : 0;
   scan[x] = tot[x];
   __syncthreads();
-  for (int off = 1; off < 1024; off <<= 1) {
+  for (int off = 1; off < NT; off <<= 1) {
     const int32_t add = x >= off ? scan[x - off] : 0;
     __syncthreads();
     scan[x] += add;
@@ -254,7 +254,7 @@ __global__ void __launch_bounds__(1024) ep_layout_kernel(const EpDev* __restrict
     for (int q = 0; q < EP_MAX_WORLD; ++q) if (q == s) cs = C[q];
     scan[x] = x < E ? cs : 0;
     __syncthreads();
-    for (int off = 1; off < 1024; off <<= 1) {
+    for (int off = 1; off < NT; off <<= 1) {
       const int32_t add = x >= off ? scan[x - off] : 0;
       __syncthreads();
       scan[x] += add;
@@ -525,7 +525,9 @@ int bq_ep_dispatch(bq_ep_t ep, const void* x_bf16, const int32_t* idx, const int
   if (!offsets || (A > 0 && (!x_bf16 || !idx || !perm))) return fail(BQ_ERR_ARG, "null pointer");
   if ((reinterpret_cast<uintptr_t>(x_bf16) & 15) != 0) return fail(BQ_ERR_ARG, "activations must be 16-byte aligned");
   cudaStream_t s = (cudaStream_t)stream;
-  ep_layout_kernel<<<1, 1024, 0, s>>>(c->dev, offsets, nullptr, status_word());
+  int nt = 32;
+  while (nt < c->E) nt <<= 1;
+  ep_layout_kernel<<<1, nt, 0, s>>>(c->dev, offsets, nullptr, status_word());
   int64_t grid = (A + 7) / 8;
   if (grid > (int64_t)sm_count() * 8) grid = (int64_t)sm_count() * 8;
   if (grid < 1) grid = 1;                      // a rank without tokens still raises its flag
@@ -548,7 +550,9 @@ int bq_ep_layout_selftest(const int32_t* counts, int rank, int world, int n_expe
   BQ_CUDA(cudaMalloc((void**)&dev, sizeof(EpDev)));
   cudaError_t e = cudaMemcpy(dev, &h, sizeof(h), cudaMemcpyHostToDevice);
   if (e == cudaSuccess) {
-    ep_layout_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(dev, nullptr, counts, status_word());
+    int nt = 32;
+    while (nt < n_experts) nt <<= 1;
+    ep_layout_kernel<<<1, nt, 0, (cudaStream_t)stream>>>(dev, nullptr, counts, status_word());
     count_launch();
     e = cudaGetLastError();
   }

@@ -13,6 +13,9 @@
 // four lanes of a quad read consecutive 16-byte pieces, and rows are padded by 64 bytes: the B-fragment loads of a
 // warp are then free of bank conflicts.
 //
+// GB_ROUTE: the MoE router in one launch -- a CTA takes 16 tokens, its 8 warps the (at most 128) expert rows of the
+// router weight, the logits meet in shared memory and a warp per token does softmax + top-k (the arithmetic of
+// moe_route_kernel).
 // Modes: plain y = x W^T; fused gate|up weight with the gated activation in the epilogue (16-row blocks = 8 gate rows +
 // the 8 up rows of the same outputs); MoE gate|up (two weights of one expert, rows of a 16-row tile of the expert's
 // segment, optionally gathered through the sort permutation, h = silu(g) * u as bf16); MoE down (fp32 rows out).
@@ -22,7 +25,7 @@ namespace bq {
 
 constexpr int GB_WARPS = 8;
 constexpr int GB_THREADS = GB_WARPS * 32;
-constexpr int GB_DENSE = 0, GB_GATED = 1, GB_MOE_GU = 2, GB_MOE_DOWN = 3;
+constexpr int GB_DENSE = 0, GB_GATED = 1, GB_MOE_GU = 2, GB_MOE_DOWN = 3, GB_ROUTE = 4;
 
 struct GbArgs {
   const uint8_t* codes;              // dense / gated: the weight
@@ -35,9 +38,10 @@ struct GbArgs {
   const int32_t* perm;               // MoE gate|up: x holds TOKEN rows, sorted position p reads row perm[p] / top_k
   const int32_t* offsets;            // MoE: expert row ranges
   const int32_t* tiles;              // MoE: tiles[0] = count, then (expert, first row) pairs of 16-row tiles
-  void* y;
+  void* y;                           // GB_ROUTE: int32 idx_out [T, top_k]
+  float* w_out;                      // GB_ROUTE: f32 routing weights [T, top_k]
   int64_t ldy, N, K;
-  int m_rows, top_k, act;
+  int m_rows, top_k, act;            // GB_ROUTE: m_rows = T (all tokens), act = renormalise
 };
 
 // 8 fp16 values of a row, k = 8c .. 8c+7, go to this offset (in halves) of the row's shared-memory image: inside a
@@ -61,7 +65,7 @@ __global__ void __launch_bounds__(GB_THREADS) qgemv_batch_kernel(const __grid_co
   constexpr int MMAS = Q8 ? 4 : 8;
   constexpr int MP = 8 * NB;                       // activation rows a CTA holds (padded)
   constexpr int RB_PER_CTA = GB_WARPS / KSPLIT;
-  constexpr bool MOE = MODE >= GB_MOE_GU;
+  constexpr bool MOE = MODE == GB_MOE_GU || MODE == GB_MOE_DOWN;
   constexpr bool TWO = MODE == GB_MOE_GU;          // two weight matrices share the activations
   constexpr int NACC = TWO ? 2 : 1;
   extern __shared__ __align__(16) uint8_t gb_smem[];
@@ -80,6 +84,10 @@ __global__ void __launch_bounds__(GB_THREADS) qgemv_batch_kernel(const __grid_co
   const __half* scalesB = nullptr;
   int64_t m0 = 0;
   int m_rows = a.m_rows;
+  if (MODE == GB_ROUTE) {                          // 16 tokens per CTA
+    m0 = (int64_t)blockIdx.x * MP;
+    m_rows = (int)(a.m_rows - m0 < MP ? a.m_rows - m0 : MP);
+  }
   if (MOE) {
     if ((int)blockIdx.x >= a.tiles[0]) return;     // uniform across the CTA, before any barrier
     const int e = a.tiles[1 + 2 * blockIdx.x];
@@ -96,7 +104,7 @@ __global__ void __launch_bounds__(GB_THREADS) qgemv_batch_kernel(const __grid_co
       if (lane == 0) xscale[r] = 0.0f;
       continue;
     }
-    int64_t src = MOE ? m0 + r : r;
+    int64_t src = (MOE || MODE == GB_ROUTE) ? m0 + r : r;
     if (MODE == GB_MOE_GU && a.perm) {
       const int32_t p = a.perm[src];
       src = p >= 0 ? p / a.top_k : 0;
@@ -134,8 +142,8 @@ __global__ void __launch_bounds__(GB_THREADS) qgemv_batch_kernel(const __grid_co
   const int ksp = warp % KSPLIT;
   const int64_t steps_total = K / KSTEP;
   const int64_t s_begin = steps_total * ksp / KSPLIT, s_end = steps_total * (ksp + 1) / KSPLIT;
-  const int64_t cta_rb0 = (MOE ? (int64_t)blockIdx.y : (int64_t)blockIdx.x) * RB_PER_CTA;
-  const int64_t cta_rb_stride = (MOE ? (int64_t)gridDim.y : (int64_t)gridDim.x) * RB_PER_CTA;
+  const int64_t cta_rb0 = (MODE == GB_ROUTE ? 0 : MOE ? (int64_t)blockIdx.y : (int64_t)blockIdx.x) * RB_PER_CTA;
+  const int64_t cta_rb_stride = (MODE == GB_ROUTE ? 1 : MOE ? (int64_t)gridDim.y : (int64_t)gridDim.x) * RB_PER_CTA;
 
   for (int64_t rb_base = cta_rb0; rb_base * 16 < N; rb_base += cta_rb_stride) {
     const int64_t rb = rb_base + rb_in_cta;
@@ -261,6 +269,11 @@ __global__ void __launch_bounds__(GB_THREADS) qgemv_batch_kernel(const __grid_co
           if (m < m_rows) {
             const float back = xscale[m];
             const float v0 = d[0][b][j] * back, v1 = d[0][b][2 + j] * back;        // rows g and g + 8
+            if (MODE == GB_ROUTE) {                 // logits of the CTA's tokens meet in shared memory: [token][expert]
+              if (ra < N) red[m * N + ra] = v0;
+              if (rbb < N) red[m * N + rbb] = v1;
+              continue;
+            }
             YT* yrow = reinterpret_cast<YT*>(a.y) + (m0 + m) * a.ldy;
             if (MODE == GB_DENSE || MODE == GB_MOE_DOWN) {
               if (ra < N) yrow[ra] = from_float<YT>(v0);
@@ -283,6 +296,60 @@ __global__ void __launch_bounds__(GB_THREADS) qgemv_batch_kernel(const __grid_co
     }
     if (KSPLIT > 1) __syncthreads();
   }
+  if (MODE == GB_ROUTE) {
+    // softmax over the E logits of a token, k rounds of arg-max (ties to the lower expert id), optional renormalisation:
+    // one warp per token, lane l holds experts l, l + 32, l + 64, l + 96
+    __syncthreads();
+    const int E = (int)N, top_k = a.top_k;
+    int32_t* idx_out = reinterpret_cast<int32_t*>(a.y);
+    for (int m = warp; m < m_rows; m += GB_WARPS) {
+      float v[4];
+      float mx = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int e = lane + 32 * j;
+        v[j] = e < E ? red[m * E + e] : -INFINITY;
+        mx = fmaxf(mx, v[j]);
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+      float all = 0.0f;
+      if (!a.act) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) all += (lane + 32 * j < E) ? expf(v[j] - mx) : 0.0f;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) all += __shfl_xor_sync(0xffffffffu, all, off);
+      }
+      float my_e = 0.0f, top_sum = 0.0f;
+      int my_i = 0;
+      for (int sl = 0; sl < top_k; ++sl) {
+        float best = -INFINITY;
+        int bi = 0x7fffffff;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int e = lane + 32 * j;
+          if (e < E && v[j] > best) { best = v[j]; bi = e; }
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+          const float ov = __shfl_xor_sync(0xffffffffu, best, off);
+          const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+          if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        }
+        if (bi == 0x7fffffff) bi = 0;
+        const float ex = expf(best - mx);
+        top_sum += ex;
+        if (lane == sl) { my_e = ex; my_i = bi; }
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (lane + 32 * j == bi) v[j] = -INFINITY;
+      }
+      if (lane < top_k) {
+        idx_out[(m0 + m) * top_k + lane] = my_i;
+        a.w_out[(m0 + m) * top_k + lane] = my_e / (a.act ? top_sum : all);
+      }
+    }
+  }
 }
 
 // ---- host side ------------------------------------------------------------------------------------------------
@@ -292,22 +359,42 @@ static size_t gb_smem_bytes(int nb, int64_t K, bool two) {
 }
 
 bool gemv_batch_supported(int fmt, int64_t N, int64_t K, int x_dtype, int64_t M) {
-  (void)fmt;
   if (x_dtype != BQ_DT_BF16 || M < 1 || M > 16 || N < 1 || (K % 128) != 0) return false;
-  return gb_smem_bytes(M <= 8 ? 1 : 2, K, false) <= 200 * 1024;
+  if (M > 8) {
+    // 9..16 rows need two column sets and twice the shared memory, which costs resident CTAs and L1: measured against
+    // the tcgen05 kernel it wins for 4-bit weights while the rows stay short (K <= 2048) or the matrix small, and
+    // loses for int8
+    if (fmt != BQ_FMT_Q4G32 || (K > 2048 && N > 16384)) return false;
+    return gb_smem_bytes(2, K, false) <= 200 * 1024;
+  }
+  return gb_smem_bytes(1, K, false) <= 200 * 1024;
+}
+
+// CTAs of this kernel that should share an SM: as many as the registers allow (3), fewer when the activation rows are large
+static int gb_ctas_per_sm(size_t smem) {
+  int n = (int)((200 * 1024) / (smem + 1024));
+  return n > 3 ? 3 : (n < 1 ? 1 : n);
 }
 
 template <int FMT, int NB, int KSPLIT, int MODE, typename YT>
 static int gb_launch(const GbArgs& a, dim3 grid, bool two, cudaStream_t s) {
   auto kern = qgemv_batch_kernel<FMT, NB, KSPLIT, MODE, YT>;
   const size_t smem = gb_smem_bytes(NB, a.K, two);
-  static bool configured = false;
-  if (!configured) {
-    // the activation rows take tens of KB per CTA: ask for the largest shared-memory carve-out, or the default split
-    // between L1 and shared memory limits the kernel to one CTA per SM (measured: twice the run time)
-    BQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    BQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared));
-    configured = true;
+  // Shared memory and L1 share one array.  The kernel wants both: room for gb_ctas_per_sm CTAs' activation rows AND
+  // as much L1 as is left (scales and activations are re-read through it; with the carve-out at its maximum the
+  // kernel ran at half speed, with the default one CTA per SM was resident above 48 KB).  So the carve-out asked for
+  // is exactly what those CTAs need.
+  static size_t cfg_smem = 0;
+  static int cfg_pct = -1;
+  if (smem > cfg_smem) {
+    BQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    cfg_smem = smem;
+  }
+  int pct = (int)((gb_ctas_per_sm(smem) * (smem + 1024) * 100 + 227 * 1024 - 1) / (227 * 1024));
+  if (pct > 100) pct = 100;
+  if (pct != cfg_pct) {
+    BQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, pct));
+    cfg_pct = pct;
   }
   BQ_CUDA(launch_chain(kern, grid, dim3(GB_THREADS), smem, s, 1, a));
   count_launch();
@@ -320,11 +407,7 @@ template <int FMT, int NB, int MODE, typename YT>
 static int gb_dense(const GbArgs& a, cudaStream_t s) {
   const int64_t rb = (a.N + 15) / 16;
   const int64_t want = (int64_t)sm_count() * 16;
-  const size_t smem = gb_smem_bytes(NB, a.K, false);
-  int per_sm = (int)((220 * 1024) / (smem + 2048));
-  if (per_sm > 4) per_sm = 4;
-  if (per_sm < 1) per_sm = 1;
-  const int64_t cap = (int64_t)sm_count() * per_sm;
+  const int64_t cap = (int64_t)sm_count() * gb_ctas_per_sm(gb_smem_bytes(NB, a.K, false));
   auto grid_for = [&](int ksplit) {
     int64_t gx = (rb + GB_WARPS / ksplit - 1) / (GB_WARPS / ksplit);
     return dim3((unsigned)(gx > cap ? cap : gx));
@@ -354,6 +437,25 @@ int launch_qlinear_batch(const uint8_t* codes, const __half* scales, int fmt, in
   else                     { if (M <= 8) BQ_GB_CASE(BQ_FMT_Q4G32, 1); BQ_GB_CASE(BQ_FMT_Q4G32, 2); }
 #undef BQ_GB_CASE
   return fail(BQ_ERR_ARG, "bad format");
+}
+
+bool moe_route_linear_supported(int fmt, int64_t E, int64_t K, int top_k) {
+  (void)fmt;
+  return E >= 1 && E <= 128 && top_k >= 1 && top_k <= 32 && top_k <= E && (K % 128) == 0 &&
+         gb_smem_bytes(2, K, false) <= 200 * 1024;
+}
+
+int launch_moe_route_linear(const uint8_t* codes, const __half* scales, int fmt, int64_t E, int64_t K, const void* x, int64_t T,
+                            int top_k, int renorm, int32_t* idx_out, float* w_out, cudaStream_t s) {
+  if (!moe_route_linear_supported(fmt, E, K, top_k)) return fail(BQ_ERR_UNSUPPORTED, "fused router: E <= 128, K % 128 == 0");
+  if ((reinterpret_cast<uintptr_t>(x) & 15) != 0) return fail(BQ_ERR_ARG, "activations must be 16-byte aligned");
+  GbArgs a;
+  memset(&a, 0, sizeof(a));
+  a.codes = codes; a.scales = scales; a.x = (const __nv_bfloat16*)x; a.y = idx_out; a.w_out = w_out; a.N = E; a.K = K;
+  a.m_rows = (int)T; a.top_k = top_k; a.act = renorm;
+  dim3 grid((unsigned)((T + 15) / 16));
+  return fmt == BQ_FMT_Q8G32 ? gb_launch<BQ_FMT_Q8G32, 2, 1, GB_ROUTE, float>(a, grid, false, s)
+                             : gb_launch<BQ_FMT_Q4G32, 2, 1, GB_ROUTE, float>(a, grid, false, s);
 }
 
 // ---- MoE grouped experts at decode sizes: 16-row tiles of every expert's segment ----------------------------------

@@ -126,8 +126,12 @@ qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ s
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   // Launched with programmatic stream serialization: it may start while a preceding (small, early-triggering) kernel
-  // still runs, so wait before touching x / y.  It never triggers its own successor early: CTAs of a following GEMV
-  // parked on the SMs cost this one bandwidth (measured).
+  // still runs, so wait before touching x / y.  Its own successor may be launched at once: the grid never exceeds what
+  // is resident (see gm_launch), so a successor's CTAs only ever take slots this kernel's CTAs have left for good, and
+  // they park in their own griddepcontrol.wait until this grid has completed.
+#ifndef BQ_GEMV_NO_EARLY_TRIGGER
+  pdl_launch_dependents();
+#endif
   pdl_wait();
   // PUSH: the receive-slot addresses of this call, one per rank, parked behind the reduction buffers
   float** push_dst = reinterpret_cast<float**>(cred + GM_WARPS * 16 * NV);
@@ -448,20 +452,25 @@ static int gm_launch(const uint8_t* codes, const __half* scales, const XT* x, YT
   auto kern_cl = qgemv_mma_kernel<FMT, NV, KSPLIT, XT, YT, true, OUT>;
   const size_t smem = (size_t)NV * K * 2 + 32 + 2 * (size_t)GM_WARPS * 16 * NV * sizeof(float) + (OUT == GM_OUT_PUSH ? 128 + GM_WARPS * 4 * 16 * sizeof(float) : 0);
   static size_t configured = 0;
-  if (smem > 16 * 1024 && smem > configured) {      // long K or several vectors: room for several CTAs' activations per SM
+  if (smem > 48 * 1024 && smem > configured) {
     BQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     BQ_CUDA(cudaFuncSetAttribute(kern_cl, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    BQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared));
-    BQ_CUDA(cudaFuncSetAttribute(kern_cl, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared));
     configured = 200 * 1024;
   }
   const int64_t rb = (N + 15) / 16;
   const int rb_per_cta = GM_WARPS / KSPLIT;
   int64_t grid = (rb + rb_per_cta - 1) / rb_per_cta;
-  int per_sm = (int)((220 * 1024) / (smem + 2048));
-  if (per_sm > 6) per_sm = 6;
-  if (per_sm < 1) per_sm = 1;
-  const int64_t cap = (int64_t)sm_count() * per_sm;
+  // CTAs that are resident at once (registers and shared memory decide; asked once per shared-memory size): the grid
+  // is capped there and the CTAs walk the row blocks, so the kernel is one wave whatever N is
+  static size_t occ_smem = (size_t)-1;
+  static int occ = 1;
+  if (smem != occ_smem) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, GM_THREADS, smem) != cudaSuccess || n < 1) n = 1;
+    occ = n > 6 ? 6 : n;
+    occ_smem = smem;
+  }
+  const int64_t cap = (int64_t)sm_count() * occ;
   // Few row blocks but a long K (e.g. 2048 x 16384): the CTAs above cannot fill the machine.  Split K further
   // across a thread-block cluster of kc CTAs (summed through distributed shared memory, fixed order) while every
   // warp keeps at least 4 steps to stream.

@@ -799,7 +799,7 @@ int bq_qlinear_gated(bq_weight_t weight, const void* x, int x_dtype, int64_t M, 
   cudaStream_t s = (cudaStream_t)stream;
   const bool batch_ok = x_dtype == BQ_DT_BF16 && gemv_batch_supported(w->fmt, w->N, w->K, x_dtype, M) &&
                         (reinterpret_cast<uintptr_t>(x) & 15) == 0;
-  if (batch_ok && (M > 4 || (w->fmt == BQ_FMT_Q4G32 && M >= 3))) {      // 3..16 rows: the batched GEMV, same epilogue
+  if (batch_ok && M >= 3) {                                             // 3..16 rows: the batched GEMV, same epilogue
     set_last_path(BQ_PATH_MMA);
     return launch_qlinear_batch(w->codes, w->scales, w->fmt, w->N, w->K, x, x_dtype, M, out, BQ_DT_BF16, w->N / 2, act, s);
   }
@@ -807,7 +807,13 @@ int bq_qlinear_gated(bq_weight_t weight, const void* x, int x_dtype, int64_t M, 
     set_last_path(BQ_PATH_MMA);
     return launch_qlinear_mma_gated(w->codes, w->scales, w->fmt, w->N, w->K, x, x_dtype, M, out, act, s);
   }
-  // larger batches: plain product into a scratch owned by the library (sized on the first call: before any graph
+  // larger bf16 batches: the tcgen05 kernel applies the activation in its epilogue (a gate row and its up row sit 8
+  // lanes apart in one warp), no intermediate product
+  if (x_dtype == BQ_DT_BF16 && tc_supported(w->fmt, w->N, w->K, x_dtype, M) && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    set_last_path(BQ_PATH_TENSOR);
+    return launch_qlinear_tc(w->codes, w->scales, w->fmt, w->N, w->K, x, x_dtype, M, out, BQ_DT_BF16, w->N / 2, s, act);
+  }
+  // anything else: plain product into a scratch owned by the library (sized on the first call: before any graph
   // capture), then the activation kernel reading the blocked layout
   if ((rc = scratch_ensure(&g_gu, (size_t)M * w->N * sizeof(float), s, "bq_qlinear_gated"))) return rc;
   rc = bq_qlinear(weight, x, x_dtype, M, g_gu.ptr, BQ_DT_F32, stream);

@@ -447,6 +447,22 @@ int bq_moe_route(const float* logits, int64_t T, int E, int top_k, int renormali
   return BQ_OK;
 }
 
+int bq_moe_route_linear(bq_weight_t router, const void* x_bf16, int64_t T, int top_k, int renormalise, int32_t* idx_out,
+                        float* w_out, void* stream) {
+  int rc = ready();
+  if (rc) return rc;
+  Weight* w = get_weight(router);
+  if (!w) return BQ_ERR_HANDLE;
+  if (T < 0 || top_k <= 0 || top_k > 32 || top_k > w->N) return fail(BQ_ERR_ARG, "need T >= 0, 1 <= top_k <= min(32, E)");
+  if (T >= ((int64_t)1 << 31)) return fail(BQ_ERR_ARG, "T out of range");
+  if (T == 0) return BQ_OK;
+  if (!x_bf16 || !idx_out || !w_out) return fail(BQ_ERR_ARG, "null pointer");
+  if (!moe_route_linear_supported(w->fmt, w->N, w->K, top_k))
+    return fail(BQ_ERR_UNSUPPORTED, "fused router needs E <= 128 and K a multiple of 128: use bq_qlinear + bq_moe_route");
+  return launch_moe_route_linear(w->codes, w->scales, w->fmt, w->N, w->K, x_bf16, T, top_k, renormalise, idx_out, w_out,
+                                 (cudaStream_t)stream);
+}
+
 int64_t bq_moe_permute_scratch_bytes(int64_t T, int top_k, int E) {
   if (T < 0 || top_k <= 0 || E <= 0) return 0;
   return (int64_t)perm_chunks(T * top_k) * E * (int64_t)sizeof(int32_t);
@@ -583,6 +599,26 @@ int bq_moe_experts_ex(bq_moe_t h, const void* xp_bf16, const int32_t* offsets, i
   set_last_path(BQ_PATH_SIMT);
   if ((rc = moe_ffn_simt(m, true, xp_bf16, offsets, hbuf_bf16, s))) return rc;
   return moe_ffn_simt(m, false, hbuf_bf16, offsets, out, s);
+}
+
+int bq_moe_experts_tokens(bq_moe_t h, const void* x_bf16, const int32_t* perm, int top_k, const int32_t* offsets, int64_t P,
+                          int64_t rows_hint, void* xp_work, void* hbuf_bf16, float* out, int path, void* stream) {
+  int rc = ready();
+  if (rc) return rc;
+  Moe* m = get_moe(h);
+  if (!m) return BQ_ERR_HANDLE;
+  if (P < 0 || rows_hint < 0 || rows_hint > P || top_k <= 0) return fail(BQ_ERR_ARG, "need 0 <= rows_hint <= P and top_k >= 1");
+  if (P == 0) return BQ_OK;
+  if (!x_bf16 || !perm || !offsets || !hbuf_bf16 || !out) return fail(BQ_ERR_ARG, "null pointer");
+  const bool batch_ok = moe_batch_supported(m) && ((reinterpret_cast<uintptr_t>(x_bf16) | reinterpret_cast<uintptr_t>(hbuf_bf16)) & 15) == 0;
+  if (path == BQ_PATH_MMA && !batch_ok) return fail(BQ_ERR_UNSUPPORTED, "batched-GEMV path unavailable for this expert shape");
+  if (path == BQ_PATH_MMA || (path == BQ_PATH_AUTO && batch_ok && rows_hint <= (int64_t)m->E * 20)) {
+    set_last_path(BQ_PATH_MMA);             // the kernel reads the token rows through perm: no gathered copy
+    return launch_moe_experts_batch(m, x_bf16, perm, top_k, offsets, P, hbuf_bf16, out, (cudaStream_t)stream);
+  }
+  if (!xp_work) return fail(BQ_ERR_ARG, "this path needs the gathered rows: xp_work must not be null");
+  if ((rc = bq_moe_gather(x_bf16, BQ_DT_BF16, m->H, perm, P, top_k, xp_work, stream))) return rc;
+  return bq_moe_experts_ex(h, xp_work, offsets, P, rows_hint, hbuf_bf16, out, path, stream);
 }
 
 int bq_moe_combine(const float* out, const int32_t* inv, const float* w, int64_t T, int top_k, int64_t H,

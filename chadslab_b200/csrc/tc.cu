@@ -235,6 +235,9 @@ struct T2Args {
   // (a scale tile covers two steps).  0 = no split.
   int kper;
   float* part;
+  // >= 0 (dense only): the weight is a fused gate|up projection whose 16-row blocks hold 8 gate rows followed by the 8
+  // up rows of the same outputs; the epilogue stores act(gate) * up (0 = gelu-tanh, 1 = silu) as bf16 [M, N / 2]
+  int gated_act;
 };
 
 __device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
@@ -454,6 +457,24 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tmem_kernel(const __grid_
           tc_ld16(tbase + (uint32_t)(w * BN + c0), v);
           tc_ld_wait();
           const int64_t nn = n + w * TC_ROWS;
+          if (args.gated_act >= 0) {
+            // this lane's row is a gate row (row & 8 == 0) or the up row of the same output (lane + 8): the pair
+            // meets through a shuffle and the gate lane stores act(gate) * up
+            const int64_t ncol = (nn >> 4) * 8 + (nn & 7);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int64_t m = m0 + c0 + j;
+              const float f = m < m_end ? __uint_as_float(v[j]) * args.xscale[m] : 0.0f;
+              const float up = __shfl_xor_sync(0xffffffffu, f, 8);
+              if ((lane & 8) == 0 && m < m_end && nn < args.N) {
+                float a;
+                if (args.gated_act == 0) a = 0.5f * f * (1.0f + tanhf(0.7978845608028654f * (f + 0.044715f * f * f * f)));
+                else a = f / (1.0f + __expf(-f));
+                reinterpret_cast<__nv_bfloat16*>(args.out)[m * args.ldy + ncol] = __float2bfloat16_rn(a * up);
+              }
+            }
+            continue;
+          }
           if (nn < args.N) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
@@ -476,6 +497,294 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tmem_kernel(const __grid_
   if (threadIdx.x == 0 && *abort_flag) atomicExch(args.status, BQ_ERR_TIMEOUT);
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)P::TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// =================================================================================================
+// 2-SM variant for large batches (M >= 512): the two CTAs of a cluster form one 256 x 256 UMMA tile.
+//
+// Large batches are bound by the bytes a CTA must stage per multiply-add (codes + activation tile): a 128 x 256 tile
+// needs 80 KB per 128-k step for int8 and only two stages fit.  Here CTA r of the pair converts weight rows
+// n0 + 128 r .. + 127 into ITS tensor memory and stages only ITS half of the activation tile (batch rows m0 + 128 r ..),
+// 48 KB per step, four stages; one thread of the leader (rank 0) issues tcgen05.mma.cta_group::2 (M = 256, N = 256):
+// A from each CTA's tensor memory, B = the two halves in the two CTAs' shared memory, D = 128 lanes x 256 columns in
+// each CTA's tensor memory.  No multicast anywhere: every CTA loads its own operands with plain TMA loads; the
+// leader learns that the peer's operands are ready through remote mbarrier arrivals of the peer's converter warps
+// (the barriers the issuer waits on live in the leader's shared memory), and tells the peer that its buffers are
+// free / its accumulator is complete with a second tcgen05.commit aimed at the peer's barrier.
+// Tensor memory: [0, 256) accumulator, 2 x 64 columns of A from column 256; allocated with cta_group::2 by warp 1 of
+// both CTAs.
+// =================================================================================================
+template <int FMT> struct PairPlan {
+  static constexpr int RAW_ROW = (FMT == BQ_FMT_Q8G32) ? 128 : 64;
+  static constexpr int RAW = TC_ROWS * RAW_ROW;
+  static constexpr int XT = 2 * 128 * 128;                               // this CTA's 128 batch rows, two 64-k atoms
+  static constexpr int SCT = TC_ROWS * 16;
+  static constexpr int STAGE = ((RAW + XT + 1023) / 1024) * 1024;
+  static constexpr int FIXED = TC_SC_SLOTS * SCT + 1024 + 1024;
+  static constexpr int S = 4;
+  static constexpr int SMEM = FIXED + S * STAGE;
+  static constexpr int ACOL0 = 256;
+  static constexpr int TMEM_COLS = 512;
+  static_assert(SMEM <= 227 * 1024, "shared memory plan too large");
+};
+
+__device__ __forceinline__ uint32_t pair_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void pair_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t pair_map(uint32_t local_addr, uint32_t rank) {
+  uint32_t ra;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(local_addr), "r"(rank));
+  return ra;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_cluster(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+__device__ __noinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_cluster(bar, parity, 2000u)) return true;
+  const uint64_t t0 = global_ns();
+  for (;;) {
+    for (int i = 0; i < 16; ++i)
+      if (mbar_try_cluster(bar, parity, 2000u)) return true;
+    if (*abort_flag) return false;
+    if (global_ns() - t0 > TC_WAIT_NS) { *abort_flag = 1; return false; }
+  }
+}
+__device__ __forceinline__ void tc_commit2(uint32_t cluster_bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma2_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// kind::f16 instruction descriptor of the pair: D = f32, A = B = f16, K-major, M = 256 (128 per CTA), N = 256
+__host__ __device__ constexpr uint32_t umma_idesc_pair() {
+  return (1u << 4) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+}
+
+template <int FMT>
+__global__ void __launch_bounds__(TC_THREADS, 1) qgemm_pair_kernel(const __grid_constant__ T2Args args) {
+  using P = PairPlan<FMT>;
+  constexpr int S = P::S, NA = 2;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* stages = smem;                                  // per stage: [x atom 0][x atom 1][codes tile]
+  uint8_t* sc_tiles = stages + S * P::STAGE;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sc_tiles + TC_SC_SLOTS * P::SCT);
+  uint64_t* full = bars;               // [S]  this CTA's TMA landed
+  uint64_t* empty = bars + S;          // [S]  this CTA's converter warps (8) + the leader's MMA commit (1)
+  uint64_t* a_full = bars + 2 * S;     // [NA] LEADER's copy is the one in use: 8 converter warps of each CTA
+  uint64_t* a_empty = a_full + NA;     // [NA] the leader's MMA commit (1)
+  uint64_t* acc_full = a_empty + NA;   // [1]
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(acc_full + 1);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = pair_rank();                       // 0 = leader (issues the MMAs), 1 = peer
+  // grid.y counts 128-row weight tiles (padded to an even number), cluster dimension y = 2: rank = blockIdx.y & 1
+  const int64_t n0 = (int64_t)blockIdx.y * TC_ROWS;                       // this CTA's weight rows
+  const int64_t m0 = (int64_t)blockIdx.x * 256, m_end = args.M;           // the pair's batch rows
+  const int64_t mx0 = m0 + 128 * (int64_t)rank;                            // the half of them this CTA stages
+  const int ksteps = (int)(args.K / T2_BK);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < S; ++i) { mbar_init(smem_u32(&full[i]), 1); mbar_init(smem_u32(&empty[i]), TC_CONV_WARPS + 1); }
+    for (int i = 0; i < NA; ++i) { mbar_init(smem_u32(&a_full[i]), 2 * TC_CONV_WARPS); mbar_init(smem_u32(&a_empty[i]), 1); }
+    mbar_init(smem_u32(acc_full), 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"((uint32_t)P::TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  pair_sync();                          // both CTAs' barriers are initialised before anybody arrives on them remotely
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+  pdl_wait();
+
+  if (warp == 0) {
+    // ================= producer: this CTA's codes, scales and its half of the activation tile =================
+    if (lane == 0) {
+      for (int ks = 0; ks < ksteps; ++ks) {
+        const int s = ks % S;
+        const uint32_t ph = (uint32_t)(ks / S) & 1u;
+        if (!mbar_wait_cluster(smem_u32(&empty[s]), ph ^ 1u, abort_flag)) break;
+        const bool with_scales = (ks & 1) == 0;
+        const uint32_t fb = smem_u32(&full[s]);
+        mbar_expect_tx(fb, P::RAW + P::XT + (with_scales ? P::SCT : 0));
+        uint8_t* st = stages + s * P::STAGE;
+        tma_load_2d(smem_u32(st), &args.tm_x, ks * T2_BK, (int)mx0, fb);
+        tma_load_2d(smem_u32(st + 128 * 128), &args.tm_x, ks * T2_BK + 64, (int)mx0, fb);
+        tma_load_2d(smem_u32(st + P::XT), &args.tm_w, ks * P::RAW_ROW, (int)n0, fb);
+        if (with_scales)
+          tma_load_2d(smem_u32(sc_tiles + ((ks >> 1) % TC_SC_SLOTS) * P::SCT), &args.tm_s, (ks >> 1) * 8, (int)n0, fb);
+      }
+      if (*abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ================= MMA issuer (leader only) =================
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = umma_idesc_pair();
+      const uint64_t bdesc_stage0 = umma_desc_sw128(smem_u32(stages));
+      const uint32_t peer_a_empty = pair_map(smem_u32(&a_empty[0]), 1u), peer_empty = pair_map(smem_u32(&empty[0]), 1u);
+      const uint32_t peer_acc = pair_map(smem_u32(acc_full), 1u);
+      bool ok = true;
+      for (int ks = 0; ks < ksteps && ok; ++ks) {
+        const int s = ks % S, a = ks & 1;
+        const uint32_t aph = (uint32_t)(ks >> 1) & 1u;
+        ok = mbar_wait_cluster(smem_u32(&a_full[a]), aph, abort_flag);   // both CTAs converted (hence both stages landed)
+        if (!ok) break;
+        tc_fence_after();
+        const uint64_t bdesc0 = bdesc_stage0 + (uint64_t)((uint32_t)(s * P::STAGE) >> 4);
+        const uint32_t a_tmem = tmem_base + (uint32_t)(P::ACOL0 + a * T2_ACOLS);
+#pragma unroll
+        for (int kk = 0; kk < T2_BK / 16; ++kk)
+          tc_mma2_f16_ts(tmem_base, a_tmem + (uint32_t)(8 * kk),
+                         bdesc0 + (uint64_t)((((kk >> 2) * 128 * 128) >> 4) + 2 * (kk & 3)), idesc, (ks > 0 || kk > 0) ? 1u : 0u);
+        tc_commit2(smem_u32(&a_empty[a]));
+        tc_commit2(peer_a_empty + (uint32_t)(a * 8));
+        tc_commit2(smem_u32(&empty[s]));
+        tc_commit2(peer_empty + (uint32_t)(s * 8));
+      }
+      if (ok) {
+        tc_commit2(smem_u32(acc_full));
+        tc_commit2(peer_acc);
+      }
+    }
+  } else {
+    // ================= converters (one weight row per thread), then epilogue =================
+    const int lg = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int row = lg * 32 + lane;
+    const uint32_t leader_a_full = pair_map(smem_u32(&a_full[0]), 0u);
+    bool ok = true;
+    for (int ks = 0; ks < ksteps && ok; ++ks) {
+      const int s = ks % S, a = ks & 1;
+      const uint32_t ph = (uint32_t)(ks / S) & 1u, aph = (uint32_t)(ks >> 1) & 1u;
+      ok = mbar_wait_warp(smem_u32(&full[s]), ph, abort_flag, lane);
+      if (ok) {
+        uint32_t fine = 0;
+        if (lane == 0) fine = mbar_wait_cluster(smem_u32(&a_empty[a]), aph ^ 1u, abort_flag) ? 1u : 0u;
+        ok = __shfl_sync(0xffffffffu, fine, 0) != 0;
+      }
+      if (!ok) break;
+      const uint8_t* raw = stages + s * P::STAGE + P::XT + row * P::RAW_ROW;
+      const __half* scw = reinterpret_cast<const __half*>(sc_tiles + ((ks >> 1) % TC_SC_SLOTS) * P::SCT) + row * 8 + (ks & 1) * 4;
+      uint32_t regs[32];
+      if (FMT == BQ_FMT_Q8G32) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int c = 4 * half + i;
+          const uint4 wv = *reinterpret_cast<const uint4*>(raw + ((c ^ (row & 7)) << 4));
+          uint4 lo, hi;
+          cvt_q8_chunk(wv, __half2half2(scw[c >> 1]), lo, hi);
+          regs[8 * i + 0] = lo.x; regs[8 * i + 1] = lo.y; regs[8 * i + 2] = lo.z; regs[8 * i + 3] = lo.w;
+          regs[8 * i + 4] = hi.x; regs[8 * i + 5] = hi.y; regs[8 * i + 6] = hi.z; regs[8 * i + 7] = hi.w;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int c = 2 * half + i;
+          const uint4 wv = *reinterpret_cast<const uint4*>(raw + ((c ^ ((row >> 1) & 3)) << 4));
+          const __half2 s2 = __half2half2(scw[c]);
+          const uint4 q0 = cvt_q4_word(wv.x, s2), q1 = cvt_q4_word(wv.y, s2), q2 = cvt_q4_word(wv.z, s2),
+                      q3 = cvt_q4_word(wv.w, s2);
+          uint32_t* r = regs + 16 * i;
+          r[0] = q0.x; r[1] = q0.y; r[2] = q0.z; r[3] = q0.w; r[4] = q1.x; r[5] = q1.y; r[6] = q1.z; r[7] = q1.w;
+          r[8] = q2.x; r[9] = q2.y; r[10] = q2.z; r[11] = q2.w; r[12] = q3.x; r[13] = q3.y; r[14] = q3.z; r[15] = q3.w;
+        }
+      }
+      tc_st32(tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)(P::ACOL0 + a * T2_ACOLS + 32 * half), regs);
+      tc_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive_cluster(leader_a_full + (uint32_t)(a * 8));     // the leader's issuer counts both CTAs' warps
+        mbar_arrive(smem_u32(&empty[s]));
+      }
+    }
+    if (ok) {
+      uint32_t fine = 0;
+      if (lane == 0) fine = mbar_wait_cluster(smem_u32(acc_full), 0u, abort_flag) ? 1u : 0u;
+      ok = __shfl_sync(0xffffffffu, fine, 0) != 0;
+    }
+    if (ok) {
+      tc_fence_after();
+      const int64_t nn = n0 + row;
+      const uint32_t tbase = tmem_base + ((uint32_t)(lg * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 16 * half; c0 < 256; c0 += 32) {
+        if (m0 + c0 >= m_end) break;
+        uint32_t v[16];
+        tc_ld16(tbase + (uint32_t)c0, v);
+        tc_ld_wait();
+        if (args.gated_act >= 0) {
+          const int64_t ncol = (nn >> 4) * 8 + (nn & 7);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int64_t m = m0 + c0 + j;
+            const float f = m < m_end ? __uint_as_float(v[j]) * args.xscale[m] : 0.0f;
+            const float up = __shfl_xor_sync(0xffffffffu, f, 8);
+            if ((lane & 8) == 0 && m < m_end && nn < args.N) {
+              float act;
+              if (args.gated_act == 0) act = 0.5f * f * (1.0f + tanhf(0.7978845608028654f * (f + 0.044715f * f * f * f)));
+              else act = f / (1.0f + __expf(-f));
+              reinterpret_cast<__nv_bfloat16*>(args.out)[m * args.ldy + ncol] = __float2bfloat16_rn(act * up);
+            }
+          }
+          continue;
+        }
+        if (nn < args.N) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int64_t m = m0 + c0 + j;
+            if (m < m_end) {
+              const float f = __uint_as_float(v[j]) * args.xscale[m];
+              if (args.out_dtype == BQ_DT_F32) reinterpret_cast<float*>(args.out)[m * args.ldy + nn] = f;
+              else reinterpret_cast<__nv_bfloat16*>(args.out)[m * args.ldy + nn] = __float2bfloat16_rn(f);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(args.status, BQ_ERR_TIMEOUT);
+  pair_sync();                          // neither CTA frees tensor memory or leaves while the other may still use it
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)P::TMEM_COLS)
                  : "memory");
   }
 }
@@ -554,6 +863,29 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
     for (int z = 1; z < nz; ++z) s += part[(int64_t)z * total + i];
     const int64_t m = i / N, n = i - m * N;
     out[m * ldy + n] = from_float<YT>(s);
+  }
+}
+
+// Same for a fused gate|up weight (16-column blocks = 8 gate + 8 up values of the same outputs): the slices are added
+// in order and out[m, n / 16 * 8 + n % 8] = act(gate) * up is stored as bf16 [M, N / 2].
+__global__ void __launch_bounds__(256) splitk_reduce_gated_kernel(const float* __restrict__ part, int nz, int64_t M, int64_t N,
+                                                                  __nv_bfloat16* __restrict__ out, int64_t ldy, int act) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t half = N / 2, total = M * half;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t m = i / half, c = i - m * half;
+    const int64_t ng = (c >> 3) * 16 + (c & 7);
+    float g = 0.0f, u = 0.0f;
+    for (int z = 0; z < nz; ++z) {
+      const float* p = part + ((int64_t)z * M + m) * N + ng;
+      g += p[0];
+      u += p[8];
+    }
+    float a;
+    if (act == 0) a = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    else a = g / (1.0f + __expf(-g));
+    out[m * ldy + c] = __float2bfloat16_rn(a * u);
   }
 }
 
@@ -692,6 +1024,29 @@ static int t2_launch(const T2Args& a, dim3 grid, cudaStream_t s) {
   return BQ_OK;
 }
 template <int FMT>
+static int pair_launch(const T2Args& a, dim3 grid, cudaStream_t s) {
+  using P = PairPlan<FMT>;
+  auto kern = qgemm_pair_kernel<FMT>;
+  static bool configured = false;
+  if (!configured) {
+    BQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P::SMEM));
+    configured = true;
+  }
+  BQ_CUDA(launch_chain(kern, grid, dim3(TC_THREADS), (size_t)P::SMEM, s, 2, a));      // clusters of 2 CTAs along grid.y
+  count_launch();
+  BQ_CUDA(cudaGetLastError());
+  return BQ_OK;
+}
+static int pair_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("BQ_PAIR");
+    v = e ? atoi(e) : 0;
+  }
+  return v;
+}
+
+template <int FMT>
 static int t2_dispatch(const T2Args& a, int bn, dim3 grid, cudaStream_t s) {
   switch (bn) {
     case 16:  return t2_launch<FMT, 16, 0>(a, grid, s);
@@ -704,7 +1059,7 @@ static int t2_dispatch(const T2Args& a, int bn, dim3 grid, cudaStream_t s) {
 }
 
 int launch_qlinear_tc(const uint8_t* codes, const __half* scales, int fmt, int64_t N, int64_t K, const void* x,
-                      int x_dtype, int64_t M, void* y, int y_dtype, int64_t ldy, cudaStream_t s) {
+                      int x_dtype, int64_t M, void* y, int y_dtype, int64_t ldy, cudaStream_t s, int gated_act) {
   if (x_dtype != BQ_DT_BF16) return fail(BQ_ERR_UNSUPPORTED, "tensor path takes bf16 activations");
   if ((reinterpret_cast<uintptr_t>(x) & 15) != 0) return fail(BQ_ERR_ARG, "activations must be 16-byte aligned");
   const int bn = pick_bn(M);
@@ -712,14 +1067,28 @@ int launch_qlinear_tc(const uint8_t* codes, const __half* scales, int fmt, int64
   if (rc) return rc;
   T2Args t;
   memset(&t, 0, sizeof(t));
+  if (pair_enabled() && M >= 512 && N >= 2 * TC_ROWS) {
+    // large batches: pairs of CTAs on 256 x 256 tiles (each stages half of the activation tile)
+    if ((rc = x_map(&t.tm_x, g_x16.ptr, M, K, 128))) return rc;
+    if ((rc = weight_maps(codes, scales, fmt, N, K, &t.tm_w, &t.tm_s))) return rc;
+    t.xscale = (const float*)g_xs.ptr; t.out = y; t.ldy = ldy; t.N = N; t.K = K; t.M = M; t.out_dtype = y_dtype;
+    t.status = status_word();
+    t.gated_act = gated_act;
+    const int64_t row_tiles = (N + TC_ROWS - 1) / TC_ROWS;
+    dim3 gridp((unsigned)((M + 255) / 256), (unsigned)((row_tiles + 1) / 2 * 2));
+    return fmt == BQ_FMT_Q8G32 ? pair_launch<BQ_FMT_Q8G32>(t, gridp, s) : pair_launch<BQ_FMT_Q4G32>(t, gridp, s);
+  }
   // large batches are bound by the L2 -> SM traffic of codes + activations per multiply-add: 4-bit weights do
   // better with 256 weight rows x 128 batch rows per CTA, int8 with 128 x 256 (measured)
-  const bool two = bn == 256 && fmt == BQ_FMT_Q4G32 && N >= 2 * TC_ROWS;
+  // (only when that still gives every SM a CTA; otherwise 128-row tiles, split over K below when they are few)
+  const bool two = bn == 256 && fmt == BQ_FMT_Q4G32 && N >= 2 * TC_ROWS &&
+                   ((M + 127) / 128) * ((N + 2 * TC_ROWS - 1) / (2 * TC_ROWS)) >= (int64_t)sm_count();
   const int bx = two ? 128 : bn;
   if ((rc = x_map(&t.tm_x, g_x16.ptr, M, K, bx))) return rc;
   if ((rc = weight_maps(codes, scales, fmt, N, K, &t.tm_w, &t.tm_s))) return rc;
   t.xscale = (const float*)g_xs.ptr; t.out = y; t.ldy = ldy; t.N = N; t.K = K; t.M = M; t.out_dtype = y_dtype;
   t.status = status_word();
+  t.gated_act = gated_act;
   const int rows_cta = two ? 2 * TC_ROWS : TC_ROWS;
   dim3 grid2((unsigned)((M + bx - 1) / bx), (unsigned)((N + rows_cta - 1) / rows_cta));
   const int sel = two ? 512 : bn;
@@ -738,6 +1107,7 @@ int launch_qlinear_tc(const uint8_t* codes, const __half* scales, int fmt, int64
         if ((rc = scratch_ensure(&g_part, (size_t)nz * M * N * sizeof(float), s, "tcgen05 path (split-K partial tiles)")))
           return rc;
         t.kper = (int)kper; t.part = (float*)g_part.ptr; grid2.z = (unsigned)nz;
+        t.gated_act = -1;                       // the slices are plain partial products; the reduction applies the activation
       }
     }
   }
@@ -745,7 +1115,10 @@ int launch_qlinear_tc(const uint8_t* codes, const __half* scales, int fmt, int64
   if (rc || nz <= 1) return rc;
   int64_t rg = (M * N + 255) / 256;
   if (rg > (int64_t)sm_count() * 8) rg = (int64_t)sm_count() * 8;
-  if (y_dtype == BQ_DT_F32)
+  if (gated_act >= 0)
+    BQ_CUDA(launch_chain(splitk_reduce_gated_kernel, dim3((unsigned)rg), dim3(256), 0, s, 1, (const float*)g_part.ptr, nz, M, N,
+                         (__nv_bfloat16*)y, ldy, gated_act));
+  else if (y_dtype == BQ_DT_F32)
     BQ_CUDA(launch_chain(splitk_reduce_kernel<float>, dim3((unsigned)rg), dim3(256), 0, s, 1, (const float*)g_part.ptr, nz, M, N,
                          (float*)y, ldy));
   else
@@ -832,7 +1205,7 @@ int launch_moe_experts_tc(const Moe* m, const void* xp, const int32_t* offsets, 
   if ((rc = launch_x_prep(xp, BQ_DT_BF16, P, m->H, s, offsets + m->E))) return rc;     // offsets[E] = rows in use
   if ((rc = x_map(&a.tm_x, g_x16.ptr, P, m->H, bn))) return rc;
   a.xscale = (const float*)g_xs.ptr; a.tm_list = st->gate_up; a.offsets = offsets; a.tiles = tiles; a.out = hbuf; a.ldy = m->F;
-  a.N = m->F; a.K = m->H; a.M = P; a.out_dtype = BQ_DT_BF16; a.moe = 1; a.status = status_word();
+  a.N = m->F; a.K = m->H; a.M = P; a.out_dtype = BQ_DT_BF16; a.moe = 1; a.status = status_word(); a.gated_act = -1;
   dim3 g1((unsigned)max_tiles, (unsigned)((m->F + TC_ROWS - 1) / TC_ROWS));
   rc = m->fmt == BQ_FMT_Q8G32 ? t2_moe_dispatch<BQ_FMT_Q8G32, 1>(a, bn, g1, s) : t2_moe_dispatch<BQ_FMT_Q4G32, 1>(a, bn, g1, s);
   if (rc) return rc;
@@ -841,7 +1214,7 @@ int launch_moe_experts_tc(const Moe* m, const void* xp, const int32_t* offsets, 
   if ((rc = launch_x_prep(hbuf, BQ_DT_BF16, P, m->F, s, offsets + m->E))) return rc;   // stream order: the first GEMM is done with the scratch
   if ((rc = x_map(&b.tm_x, g_x16.ptr, P, m->F, bn))) return rc;
   b.xscale = (const float*)g_xs.ptr; b.tm_list = st->down; b.offsets = offsets; b.tiles = tiles; b.out = out; b.ldy = m->H;
-  b.N = m->H; b.K = m->F; b.M = P; b.out_dtype = BQ_DT_F32; b.moe = 1; b.status = status_word();
+  b.N = m->H; b.K = m->F; b.M = P; b.out_dtype = BQ_DT_F32; b.moe = 1; b.status = status_word(); b.gated_act = -1;
   dim3 g2((unsigned)max_tiles, (unsigned)((m->H + TC_ROWS - 1) / TC_ROWS));
   return m->fmt == BQ_FMT_Q8G32 ? t2_moe_dispatch<BQ_FMT_Q8G32, 0>(b, bn, g2, s) : t2_moe_dispatch<BQ_FMT_Q4G32, 0>(b, bn, g2, s);
 }

@@ -76,17 +76,49 @@ def _headline(torch, dist, rank, world, dec, cfg, B, ctx, step, tokens, steps, m
     peaks_path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
     peak, src = (float(json.load(open(peaks_path))["hbm_gbs"]), "measured") if os.path.exists(peaks_path) else (6650.0, "fallback")
     ach = abytes / us / 1e3
-    del flush, x, y
+    quant = {"bound": "hbm", "achieved": round(ach, 1), "peak": peak, "unit": "GB/s", "frac": round(ach / peak, 4),
+             "traffic": None, "traffic_source": "not captured in this run (ncu summaries of this kernel family: profiles/)",
+             "peak_source": src, "kernel": f"lm_head {'int8' if pw.fmt == 0 else 'q4'}-g32 ({pw.N},{pw.K}) M={B}: the largest "
+                                           f"quantized-matmul launch of the step ({head_launches} kernel"
+                                           f"{'s' if head_launches != 1 else ''}: activation pre-pass + GEMM when M > 16)",
+             "algorithmic_bytes": int(abytes), "launch_us": round(us, 2), "share_of_step": round(us / (ms * 1e3), 4),
+             "frac_of_nominal_8TBs": round(ach / 8000, 4)}
+    # decode attention of one layer alone (RoPE + KV append + single-query attention over the ctx-position cache)
+    c = cfg
+    kc, vc = dec.k_cache[0], dec.v_cache[0]
+    S = kc.shape[1]
+    qkv = torch.randn((B, (dec.h_local + 2 * dec.kv_local) * c.head_dim), device="cuda")
+    att = torch.empty((B, dec.h_local, c.head_dim), dtype=kc.dtype, device="cuda")
+    pos_t = torch.tensor([ctx], device="cuda", dtype=torch.int64)
+    acall = lambda: _lib.check(lib.bq_decode_attention_rope(qkv.data_ptr(), kc.data_ptr(), vc.data_ptr(), pos_t.data_ptr(),
+                                                            att.data_ptr(), B, dec.h_local, dec.kv_local, c.head_dim, S,
+                                                            c.rope_base, 1 if kc.dtype == torch.bfloat16 else 0, st))
+    acall()
+    times = []
+    for _ in range(8):
+        _flush_l2(torch, flush)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        acall()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    aus = sorted(times)[len(times) // 2] * 1e3
+    att_bytes = 2.0 * B * (ctx + 1) * dec.kv_local * c.head_dim * kc.element_size() + B * dec.h_local * c.head_dim * (4 + kc.element_size())
+    aach = att_bytes / aus / 1e3
+    attn = {"bound": "hbm", "achieved": round(aach, 1), "peak": peak, "unit": "GB/s", "frac": round(aach / peak, 4),
+            "traffic": None, "traffic_source": "not captured in this run",
+            "peak_source": src, "kernel": f"decode attention of one layer: batch {B}, {dec.h_local} query / {dec.kv_local} KV heads x "
+                                          f"{c.head_dim}, {ctx}-position cache ({'bf16' if kc.element_size() == 2 else 'fp32'}): K and V "
+                                          "rows are the algorithmic bytes",
+            "algorithmic_bytes": int(att_bytes), "launch_us": round(aus, 2),
+            "share_of_step": round(aus * c.layers / (ms * 1e3), 4), "frac_of_nominal_8TBs": round(aach / 8000, 4)}
+    del flush, x, y, qkv, att
+    dominant, other = (attn, quant) if aus * c.layers >= us else (quant, attn)
     return {"ms_per_step": ms, "e2e_ms_per_step": e2e_ms, "launches_per_step": int(launches),
             "stream_GB_per_step_per_gpu": round((bpt + B * kv_bytes) / 1e9, 3),
             "frac_of_hbm_peak": round((bpt + B * kv_bytes) / ms / 1e6 / peak, 4),
-            "roofline": {"bound": "hbm", "achieved": round(ach, 1), "peak": peak, "unit": "GB/s", "frac": round(ach / peak, 4),
-                         "traffic": None, "traffic_source": "not captured in this run (ncu summaries of this kernel family: profiles/)",
-                         "peak_source": src, "kernel": f"lm_head {'int8' if pw.fmt == 0 else 'q4'}-g32 ({pw.N},{pw.K}) M={B}: "
-                                                       f"the largest quantized-matmul launch of the step ({head_launches} kernel"
-                                                       f"{'s' if head_launches != 1 else ''}: activation pre-pass + GEMM when M > 4)",
-                         "algorithmic_bytes": int(abytes), "launch_us": round(us, 2),
-                         "frac_of_nominal_8TBs": round(ach / 8000, 4)}}
+            "roofline": dominant, "roofline_quantized_matmul" if dominant is attn else "roofline_attention": other}
 
 
 def run(torch, dist, rank: int, world: int, shape: str = "gemma7b", batches=(1, 16, 64), ctx: int = 2048, steps: int = 16,

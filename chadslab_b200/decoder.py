@@ -166,21 +166,24 @@ class QuantDecoder:
         if self.pos + T > self.k_cache[0].shape[1] or B > self.k_cache[0].shape[0]:
             raise ValueError(f"KV cache holds {self.k_cache[0].shape[1]} positions x {self.k_cache[0].shape[0]} sequences; "
                              f"asked for positions {self.pos}..{self.pos + T - 1} of {B} sequences")
-        x = self.embed[tokens].to(self.act_dtype)
+        M = B * T
+        x = self.embed[tokens].to(self.act_dtype).reshape(M, c.hidden).contiguous()      # residual stream
+        h = torch.empty_like(x)
         pos = torch.arange(self.pos, self.pos + T, device=x.device)
         S = self.pos + T
+        nq, nkv = self.h_local * c.head_dim, self.kv_local * c.head_dim
+        rep = self.h_local // self.kv_local
+        delta = None
         for l in range(c.layers):
-            h = _rmsnorm(x, self.norms[f"l{l}.norm1"], c.eps)
-            nq, nkv = self.h_local * c.head_dim, self.kv_local * c.head_dim
-            qkv = self.lin[f"l{l}.qkv"](h).to(self.act_dtype)
-            q = qkv[..., :nq].reshape(B, T, self.h_local, c.head_dim)
-            k = qkv[..., nq:nq + nkv].reshape(B, T, self.kv_local, c.head_dim)
-            v = qkv[..., nq + nkv:].reshape(B, T, self.kv_local, c.head_dim)
+            self._add_norm(x, delta, self.norms[f"l{l}.norm1"], h)                        # x += delta; h = rmsnorm(x) * w
+            qkv = self.lin[f"l{l}.qkv"](h, out=torch.empty((M, nq + 2 * nkv), dtype=self.act_dtype, device=x.device))
+            q = qkv[:, :nq].reshape(B, T, self.h_local, c.head_dim)
+            k = qkv[:, nq:nq + nkv].reshape(B, T, self.kv_local, c.head_dim)
+            v = qkv[:, nq + nkv:].reshape(B, T, self.kv_local, c.head_dim)
             q, k = _rope(q, pos, c.rope_base), _rope(k, pos, c.rope_base)
             self.k_cache[l][:B, self.pos:S] = k
             self.v_cache[l][:B, self.pos:S] = v
             kk, vv = self.k_cache[l][:B, :S], self.v_cache[l][:B, :S]
-            rep = self.h_local // self.kv_local
             if rep > 1:
                 kk, vv = kk.repeat_interleave(rep, dim=2), vv.repeat_interleave(rep, dim=2)
             if self.pos == 0 and T > 1:      # no earlier context: plain causal attention (lets PyTorch pick a fused kernel)
@@ -188,14 +191,21 @@ class QuantDecoder:
             else:
                 mask = (torch.arange(S, device=x.device)[None, :] <= pos[:, None])      # [T, S]
                 o = F.scaled_dot_product_attention(q.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2), attn_mask=mask)
-            o = o.transpose(1, 2).reshape(B, T, self.h_local * c.head_dim)
-            x = x + self.lin[f"l{l}.o"](o.contiguous()).to(self.act_dtype)
-            h = _rmsnorm(x, self.norms[f"l{l}.norm2"], c.eps)
-            gate, up = split_gate_up(self.lin[f"l{l}.gate_up"](h))
-            a = F.gelu(gate, approximate="tanh") * up
-            x = x + self.lin[f"l{l}.down"](a.to(self.act_dtype)).to(self.act_dtype)
+            o = o.transpose(1, 2).reshape(M, self.h_local * c.head_dim)
+            delta = self.lin[f"l{l}.o"](o.contiguous())                                   # fp32 (summed over the ranks when sharded)
+            self._add_norm(x, delta, self.norms[f"l{l}.norm2"], h)
+            a = self.lin[f"l{l}.gate_up"].gated(h, 0)                                     # GeGLU applied inside the matmul kernel
+            delta = self.lin[f"l{l}.down"](a)
+        self._add_norm(x, delta, self.norms["norm_f"], h)
         self.pos = S
-        return _rmsnorm(x, self.norms["norm_f"], c.eps)
+        return h.reshape(B, T, c.hidden)
+
+    def _add_norm(self, x, delta, gamma, out):
+        """x[rows, hidden] += delta (fp32, may be None); out = rmsnorm(x) * gamma -- the library's kernel."""
+        from . import _lib
+        from .ops import _dt_of_torch, _stream_ptr
+        _lib.check(_lib.lib().bq_add_rmsnorm(x.data_ptr(), delta.data_ptr() if delta is not None else None, gamma.data_ptr(),
+                                             out.data_ptr(), x.shape[0], x.shape[1], self.cfg.eps, _dt_of_torch(x), _stream_ptr()))
 
     def logits(self, tokens):
         h = self.hidden_states(tokens)
@@ -433,16 +443,19 @@ class MoEDecoder(QuantDecoder):
         if S > self.k_cache[0].shape[1] or b0 + B > self.k_cache[0].shape[0]:
             raise ValueError(f"KV cache holds {self.k_cache[0].shape[1]} positions x {self.k_cache[0].shape[0]} sequences; "
                              f"asked for positions up to {S - 1} of sequences {b0}..{b0 + B - 1}")
-        x = self.embed[tokens].to(self.act_dtype)
+        M = B * T
+        x = self.embed[tokens].to(self.act_dtype).reshape(M, c.hidden).contiguous()
+        h = torch.empty_like(x)
         pos = torch.arange(self.pos, S, device=x.device)
         nq, nkv = c.n_heads * c.head_dim, c.n_kv_heads * c.head_dim
         rep = c.n_heads // c.n_kv_heads
+        delta = None
         for l in range(c.layers):
-            h = _rmsnorm(x, self.norms[f"l{l}.norm1"], c.eps)
-            qkv = self.lin[f"l{l}.qkv"](h).to(self.act_dtype)
-            q = qkv[..., :nq].reshape(B, T, c.n_heads, c.head_dim)
-            k = qkv[..., nq:nq + nkv].reshape(B, T, c.n_kv_heads, c.head_dim)
-            v = qkv[..., nq + nkv:].reshape(B, T, c.n_kv_heads, c.head_dim)
+            self._add_norm(x, delta, self.norms[f"l{l}.norm1"], h)
+            qkv = self.lin[f"l{l}.qkv"](h, out=torch.empty((M, nq + 2 * nkv), dtype=self.act_dtype, device=x.device))
+            q = qkv[:, :nq].reshape(B, T, c.n_heads, c.head_dim)
+            k = qkv[:, nq:nq + nkv].reshape(B, T, c.n_kv_heads, c.head_dim)
+            v = qkv[:, nq + nkv:].reshape(B, T, c.n_kv_heads, c.head_dim)
             q, k = _rope(q, pos, c.rope_base), _rope(k, pos, c.rope_base)
             self.k_cache[l][b0:b0 + B, self.pos:S] = k
             self.v_cache[l][b0:b0 + B, self.pos:S] = v
@@ -454,14 +467,14 @@ class MoEDecoder(QuantDecoder):
             else:
                 mask = (torch.arange(S, device=x.device)[None, :] <= pos[:, None])
                 o = F.scaled_dot_product_attention(q.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2), attn_mask=mask)
-            o = o.transpose(1, 2).reshape(B, T, nq)
-            x = x + self.lin[f"l{l}.o"](o.contiguous()).to(self.act_dtype)
-            h = _rmsnorm(x, self.norms[f"l{l}.norm2"], c.eps)
-            y = self.ffn[l](h.reshape(B * T, -1))                                 # fp32 [B*T, hidden]
-            x = x + y.reshape(B, T, -1).to(self.act_dtype)
+            o = o.transpose(1, 2).reshape(M, nq)
+            delta = self.lin[f"l{l}.o"](o.contiguous())
+            self._add_norm(x, delta, self.norms[f"l{l}.norm2"], h)
+            delta = self.ffn[l](h)                                                        # fp32 [M, hidden]
+        self._add_norm(x, delta, self.norms["norm_f"], h)
         if advance:
             self.pos = S
-        return _rmsnorm(x, self.norms["norm_f"], c.eps)
+        return h.reshape(B, T, c.hidden)
 
     def logits(self, tokens):
         h = self.hidden_states(tokens)

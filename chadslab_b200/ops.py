@@ -484,6 +484,24 @@ def moe_route(logits, top_k: int, renormalise: bool = True):
     return idx, w
 
 
+def moe_route_linear(router: "QuantLinear", xb, top_k: int, renormalise: bool = True):
+    """Router logits + softmax + top-k for bf16 tokens xb[T,H]: one launch when the router has at most 128 experts
+    (bq_moe_route_linear), else the router matmul followed by bq_moe_route."""
+    torch = _torch()
+    pw = router.pw
+    xb = xb.contiguous()
+    T = xb.shape[0]
+    if xb.dtype == torch.bfloat16 and pw.N <= 128 and pw.K % 128 == 0 and top_k <= min(32, pw.N):
+        idx = torch.empty((T, top_k), dtype=torch.int32, device=xb.device)
+        w = torch.empty((T, top_k), dtype=torch.float32, device=xb.device)
+        rc = _lib.lib().bq_moe_route_linear(pw.handle, xb.data_ptr(), T, top_k, int(renormalise), idx.data_ptr(), w.data_ptr(),
+                                            _stream_ptr())
+        if rc != _lib.ERR_UNSUPPORTED:
+            _lib.check(rc)
+            return idx, w
+    return moe_route(router(xb), top_k, renormalise)
+
+
 def moe_permute(idx, n_experts: int):
     torch = _torch()
     idx = idx.contiguous()
@@ -562,6 +580,18 @@ class MoEExperts:
                                              out.data_ptr(), self.path, _stream_ptr()))
         return (out, hbuf) if return_h else out
 
+    def experts_tokens(self, xb, perm, offsets):
+        """Grouped SwiGLU FFN on the TOKEN rows xb[T,H] (bf16) of a routed batch: sorted position p uses row
+        perm[p] // top_k.  -> f32 [T*k, H] in sorted order.  No gathered copy is made at decode sizes."""
+        torch = _torch()
+        P = perm.numel()
+        hbuf = torch.empty((P, self.F), dtype=torch.bfloat16, device=xb.device)
+        out = torch.empty((P, self.H), dtype=torch.float32, device=xb.device)
+        work = torch.empty((P, self.H), dtype=torch.bfloat16, device=xb.device)
+        _lib.check(_lib.lib().bq_moe_experts_tokens(self._handle, xb.data_ptr(), perm.data_ptr(), self.top_k, offsets.data_ptr(), P,
+                                                    P, work.data_ptr(), hbuf.data_ptr(), out.data_ptr(), self.path, _stream_ptr()))
+        return out
+
     def experts_received(self, ep: "PeerEP", rows_hint: int):
         """Grouped SwiGLU FFN of this rank's experts on the rows `ep.dispatch` delivered: reads the receive buffer and
         the device-side row ranges of the exchange object, writes `ep.out_rows`.  `rows_hint`: rows to expect (picks
@@ -577,10 +607,8 @@ class MoEExperts:
         torch = _torch()
         x = x.reshape(-1, self.H)
         xb = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
-        logits = self.router(xb)
-        idx, w = moe_route(logits, self.top_k, self.renormalise)
+        idx, w = moe_route_linear(self.router, xb, self.top_k, self.renormalise)
         perm, inv, offsets = moe_permute(idx, self.E)
-        xp = moe_gather(xb, perm, self.top_k)
-        out_p = self.experts(xp, offsets)
+        out_p = self.experts_tokens(xb.contiguous(), perm, offsets)
         y = moe_combine(out_p, inv, w)
         return (y, (idx, w, perm, inv, offsets)) if return_aux else y

@@ -118,7 +118,11 @@ class ExpertParallelMoE:
         be, k = self.backend, self.top_k
         El = self.E_local
         xb = x if x.dtype == self.act_dtype else x.to(self.act_dtype)
-        idx, w = be.route(self.router(xb), k, self.renormalise)                # [T,k]
+        if self.ep is not None and hasattr(self.router, "pw"):                  # router matmul + softmax + top-k in one launch
+            from . import ops
+            idx, w = ops.moe_route_linear(self.router, xb, k, self.renormalise)
+        else:
+            idx, w = be.route(self.router(xb), k, self.renormalise)            # [T,k]
         perm, inv, offsets = be.permute(idx, self.E)                            # sorted by global expert
         if self.ep is not None:
             self.ep.dispatch(xb.contiguous(), idx, perm, offsets)               # rows land in their owners' buffers

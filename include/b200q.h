@@ -170,6 +170,11 @@ int bq_gated_act(const float* gate_up, void* out, int64_t rows, int64_t F, int a
  * Limits: E <= 1024, top_k <= 32.                                                        */
 int bq_moe_route(const float* logits, int64_t T, int E, int top_k, int renormalise,
                  int32_t* idx_out, float* w_out, void* stream);
+/* Router linear + bq_moe_route in one launch: router is the packed [E, H] router weight, x the token activations
+ * (device bf16 [T, H]).  E <= 128 and H a multiple of 128, else BQ_ERR_UNSUPPORTED (use bq_qlinear + bq_moe_route).
+ * Logits are computed like every tensor-core matmul of this library (weights rounded once to fp16).        */
+int bq_moe_route_linear(bq_weight_t router, const void* x_bf16, int64_t T, int top_k, int renormalise,
+                        int32_t* idx_out, float* w_out, void* stream);
 /* Stable counting sort of the T*k assignments by expert.  perm int32[T*k]: sorted position
  * p holds flat assignment t*k+slot; inv int32[T*k] (may be NULL): inv[t*k+slot] = p;
  * offsets int32[E+1]: expert e owns positions offsets[e]..offsets[e+1].
@@ -213,6 +218,13 @@ int bq_moe_experts(bq_moe_t m, const void* xp_bf16, const int32_t* offsets, int6
  * number of rows to expect, which picks the token tile; bq_moe_experts uses rows_hint = P.          */
 int bq_moe_experts_ex(bq_moe_t m, const void* xp_bf16, const int32_t* offsets, int64_t P,
                       int64_t rows_hint, void* hbuf_bf16, float* out, int path, void* stream);
+/* bq_moe_gather + bq_moe_experts_ex in one call: x is the TOKEN activations, device bf16 [T, H]; sorted position p
+ * uses row perm[p] / top_k.  At decode sizes (about a dozen rows per expert) the expert kernel reads the token
+ * rows through perm itself and xp_work is not touched; otherwise the rows are gathered into xp_work (device bf16
+ * [P, H]) first.                                                                                          */
+int bq_moe_experts_tokens(bq_moe_t m, const void* x_bf16, const int32_t* perm, int top_k,
+                          const int32_t* offsets, int64_t P, int64_t rows_hint, void* xp_work,
+                          void* hbuf_bf16, float* out, int path, void* stream);
 /* y[t,:] = sum_{slot=0..k-1} w[t,slot] * out[inv[t*k+slot], :] in slot order (deterministic,
  * no atomics).  inv as produced by bq_moe_permute.  y dtype F32 or BF16.                 */
 int bq_moe_combine(const float* out, const int32_t* inv, const float* w, int64_t T,

@@ -163,10 +163,12 @@ def test_fused_rope_append_attention_equals_the_two_kernels(cuda_lib, adt, shape
 @pytest.mark.parametrize("fmt", [0, 1])
 @pytest.mark.parametrize("adt", ["float32", "bfloat16"])
 @pytest.mark.parametrize("act", [0, 1])
-@pytest.mark.parametrize("M", [1, 2, 16])
+@pytest.mark.parametrize("M", [1, 2, 4, 16, 200, 600])
 def test_gated_linear_equals_product_then_activation(cuda_lib, fmt, adt, act, M):
     """bq_qlinear_gated on an interleaved gate|up weight against the plain products of the two weights followed by
-    the activation: M <= 2 runs the GEMV with the activation in its epilogue, M = 16 the two-kernel route."""
+    the activation.  bf16 activations: the exact GEMV (M <= 2), the batched GEMV (up to 16 rows) and the tcgen05
+    kernel (larger batches) all apply the activation in their epilogue; fp32 activations beyond the GEMV take the
+    two-kernel route (product, then activation)."""
     import torch
     import chadslab_b200 as cb
     dt = getattr(torch, adt)
@@ -187,4 +189,28 @@ def test_gated_linear_equals_product_then_activation(cuda_lib, fmt, adt, act, M)
     # the plain product of the fused weight is the interleaved pair
     from chadslab_b200.ops import split_gate_up
     g2, u2 = split_gate_up(fused(x))
-    assert torch.equal(g2, cb.QuantLinear(gate)(x)) and torch.equal(u2, cb.QuantLinear(up)(x))
+    if M <= 2 or M > 16 or dt == torch.float32:      # same kernel, same K split for the fused and the separate weights
+        assert torch.equal(g2, cb.QuantLinear(gate)(x)) and torch.equal(u2, cb.QuantLinear(up)(x))
+    else:                                             # batched GEMV: the K split depends on the row count of the weight
+        assert _rel(g2.double().cpu().numpy(), g.cpu().numpy()) <= 1e-5 and _rel(u2.double().cpu().numpy(), u.cpu().numpy()) <= 1e-5
+
+
+@pytest.mark.parametrize("fmt", [0, 1])
+@pytest.mark.parametrize("act", [0, 1])
+def test_gated_linear_with_split_k(cuda_lib, fmt, act):
+    """Few output tiles and a long K: the tcgen05 kernel splits K over the grid and the reduction kernel applies the
+    gated activation."""
+    import torch
+    import chadslab_b200 as cb
+    F, K, M = 128, 4096, 64
+    rng = np.random.default_rng(8)
+    gate = cb.PackedWeight.from_float(rng.normal(0, 0.05, (F, K)).astype(np.float32), fmt)
+    up = cb.PackedWeight.from_float(rng.normal(0, 0.05, (F, K)).astype(np.float32), fmt)
+    fused = cb.QuantLinear(cb.interleave_gate_up(gate, up))
+    x = torch.randn((M, K), device="cuda").to(torch.bfloat16)
+    n0 = cuda_lib.bq_launch_count()
+    got = fused.gated(x, act)
+    assert cuda_lib.bq_launch_count() - n0 == 3 and cuda_lib.bq_last_path() == cb.PATH_TENSOR     # pre-pass, split GEMM, gated reduction
+    g, u = cb.QuantLinear(gate)(x).double(), cb.QuantLinear(up)(x).double()
+    a = 0.5 * g * (1.0 + torch.tanh(0.7978845608028654 * (g + 0.044715 * g ** 3))) if act == 0 else g / (1.0 + torch.exp(-g))
+    assert _rel(got.double().cpu().numpy(), (a * u).cpu().numpy()) <= _tol(torch.bfloat16)

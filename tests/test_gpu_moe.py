@@ -189,3 +189,36 @@ def test_grouped_experts_at_scale_against_simt_path(cuda_lib, fmt, T):
     assert err <= TOL, err
     y = cb.moe_combine(out_t, inv, w)
     assert bool(torch.isfinite(y).all())
+
+
+@pytest.mark.parametrize("fmt", [0, 1])
+@pytest.mark.parametrize("T,E,k,H", [(1, 8, 2, 256), (37, 128, 8, 2048), (256, 128, 8, 2048), (300, 64, 6, 512), (20, 100, 4, 384)])
+def test_fused_router_equals_linear_then_route(cuda_lib, fmt, T, E, k, H):
+    """bq_moe_route_linear (router matmul + softmax + top-k in one launch) against the router matmul of the oracle
+    followed by the oracle's routing: same expert ids wherever the oracle's own margin between the k-th and the
+    (k+1)-th logit exceeds the matmul tolerance, weights within it."""
+    import torch
+    import chadslab_b200 as cb
+    rng = np.random.default_rng(T + E + fmt)
+    Wr = rng.normal(0, 0.3, (E, H)).astype(np.float32)
+    codes, scales = spec.quantize(Wr, fmt)
+    router = cb.QuantLinear(cb.PackedWeight.from_arrays(codes, scales, fmt))
+    x = spec.bf16_round(rng.normal(0, 1, (T, H)).astype(np.float32))
+    xt = torch.from_numpy(x).cuda().to(torch.bfloat16)
+    n0 = cuda_lib.bq_launch_count()
+    idx, w = cb.ops.moe_route_linear(router, xt, k)
+    assert cuda_lib.bq_launch_count() - n0 == 1
+    logits = spec.qlinear(x, codes, scales, fmt, f64=True)
+    ridx, rw = spec.moe_route_from_logits(logits.astype(np.float32), k)
+    srt = np.sort(logits, axis=-1)[:, ::-1]
+    margin = (srt[:, :k] - srt[:, 1:k + 1]).min(axis=-1) / np.abs(logits).max()       # smallest gap among the top k+1
+    clear = margin > 2 * TOL
+    got = idx.cpu().numpy()
+    assert clear.mean() > 0.5 and np.array_equal(got[clear], ridx[clear])
+    assert np.allclose(w.cpu().numpy()[clear], rw[clear], rtol=0, atol=5e-3)
+    # every row: the chosen ids are distinct, in range, and the weights sum to one
+    assert (np.sort(got, axis=1)[:, 1:] != np.sort(got, axis=1)[:, :-1]).all() and got.min() >= 0 and got.max() < E
+    assert np.allclose(w.cpu().numpy().sum(-1), 1.0, atol=1e-5)
+    # and it agrees with the library's own two-step route wherever that one is clear, too
+    idx2, w2 = cb.moe_route(router(xt), k)
+    assert np.array_equal(idx2.cpu().numpy()[clear], got[clear])
