@@ -561,6 +561,42 @@ def run_one_qlinear(args):
     _lib.check(lib.bq_status_poll())
 
 
+def run_one_attention(args):
+    """`--only attention`: the decode-attention kernel alone (RoPE + KV append + single-query attention) on a synthetic
+    cache: `--batch` sequences, `--heads` query / `--kv-heads` KV heads of `--head-dim`, `--ctx` positions, bf16."""
+    import torch
+    from chadslab_b200 import _lib
+    torch.cuda.set_device(0)
+    lib = _lib.init(0)
+    B, Hq, Hkv, D, ctx = args.batch, args.heads, args.kv_heads, args.head_dim, args.ctx
+    S = ctx + 8
+    g = torch.Generator(device="cuda").manual_seed(0)
+    kc = torch.randn((B, S, Hkv, D), device="cuda", generator=g).to(torch.bfloat16)
+    vc = torch.randn((B, S, Hkv, D), device="cuda", generator=g).to(torch.bfloat16)
+    qkv = torch.randn((B, (Hq + 2 * Hkv) * D), device="cuda", generator=g)
+    out = torch.empty((B, Hq, D), dtype=torch.bfloat16, device="cuda")
+    pos = torch.tensor([ctx], device="cuda", dtype=torch.int64)
+    st = torch.cuda.current_stream().cuda_stream
+    call = lambda: _lib.check(lib.bq_decode_attention_rope(qkv.data_ptr(), kc.data_ptr(), vc.data_ptr(), pos.data_ptr(),
+                                                           out.data_ptr(), B, Hq, Hkv, D, S, 10000.0, 1, st))
+    flush = torch.empty((256 << 20,), dtype=torch.uint8, device="cuda")
+    call()
+    times = []
+    for _ in range(args.reps):
+        flush.zero_()
+        a, b = _events(torch)
+        a.record()
+        call()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b) * 1e3)
+    us = sorted(times)[len(times) // 2]
+    nbytes = 2.0 * B * (ctx + 1) * Hkv * D * 2
+    print(json.dumps({"kernel": "decode attention", "batch": B, "heads": Hq, "kv_heads": Hkv, "head_dim": D, "ctx": ctx,
+                      "us": round(us, 2), "kv_bytes": int(nbytes), "GBps": round(nbytes / us / 1e3, 1)}))
+    _lib.check(lib.bq_status_poll())
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -569,7 +605,13 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--extras", type=int, default=1, help="also run the other configs, the parity check and the sweep")
     ap.add_argument("--cpu", type=int, default=1, help="N = 1: also time the numpy oracle sample (cpu_baseline)")
-    ap.add_argument("--only", default="", choices=["", "qlinear"], help="qlinear: time one weight shape instead of the benchmark")
+    ap.add_argument("--only", default="", choices=["", "qlinear", "attention"],
+                    help="qlinear / attention: time one kernel on one shape instead of the benchmark")
+    ap.add_argument("--batch", type=int, default=16)
+    ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--kv-heads", type=int, default=16)
+    ap.add_argument("--head-dim", type=int, default=256)
+    ap.add_argument("--ctx", type=int, default=2048)
     ap.add_argument("--n", type=int, default=65536)
     ap.add_argument("--k", type=int, default=2048)
     ap.add_argument("--fmt", default="int8,q4")
@@ -580,6 +622,8 @@ def main():
     args = ap.parse_args()
     if args.only == "qlinear":
         run_one_qlinear(args)
+    elif args.only == "attention":
+        run_one_attention(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

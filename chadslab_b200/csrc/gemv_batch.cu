@@ -110,12 +110,28 @@ __global__ void __launch_bounds__(GB_THREADS) qgemv_batch_kernel(const __grid_co
       src = p >= 0 ? p / a.top_k : 0;
     }
     const __nv_bfloat16* xrow = a.x + src * K;
+    // the row arrives in batches of GB_PC 16-byte pieces per lane, all requested before any is used (a loop with one
+    // load in flight per trip made this prologue longer than the weight stream of a small expert tile); rows of up
+    // to 32 * 8 * GB_PC elements stay in registers between the maximum and the conversion
+    constexpr int GB_PC = 8;
+    const int64_t nchunks = K / 8;
+    uint4 raw[GB_PC];
     float mx = 0.0f;
-    for (int64_t c = lane; c < K / 8; c += 32) {
-      float f[8];
-      load8<__nv_bfloat16>(xrow + c * 8, f);
+    for (int64_t c0 = 0; c0 < nchunks; c0 += 32 * GB_PC) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(f[i]));
+      for (int i = 0; i < GB_PC; ++i) {
+        const int64_t c = c0 + i * 32 + lane;
+        raw[i] = c < nchunks ? *reinterpret_cast<const uint4*>(xrow + c * 8) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int i = 0; i < GB_PC; ++i) {
+        const uint32_t wds[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          mx = fmaxf(mx, fabsf(__uint_as_float(wds[j] << 16)));
+          mx = fmaxf(mx, fabsf(__uint_as_float(wds[j] & 0xFFFF0000u)));
+        }
+      }
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
@@ -124,13 +140,27 @@ __global__ void __launch_bounds__(GB_THREADS) qgemv_batch_kernel(const __grid_co
     if (e < -100) e = -100;
     const float down = __uint_as_float((uint32_t)(127 - e) << 23);
     __half* xr = xs + (int64_t)r * xstride;
-    for (int64_t c = lane; c < K / 8; c += 32) {
-      float f[8];
-      load8<__nv_bfloat16>(xrow + c * 8, f);
-      __half h[8];
+    const bool cached = nchunks <= 32 * GB_PC;           // the single batch above is still in `raw`
+    for (int64_t c0 = 0; c0 < nchunks; c0 += 32 * GB_PC) {
+      if (!cached) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) h[i] = __float2half_rn(f[i] * down);
-      *reinterpret_cast<uint4*>(xr + gb_xoffset<Q8>(c)) = *reinterpret_cast<const uint4*>(h);
+        for (int i = 0; i < GB_PC; ++i) {
+          const int64_t c = c0 + i * 32 + lane;
+          raw[i] = c < nchunks ? *reinterpret_cast<const uint4*>(xrow + c * 8) : make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < GB_PC; ++i) {
+        const int64_t c = c0 + i * 32 + lane;
+        if (c < nchunks) {
+          const uint32_t wds[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+          __half2 h[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            h[j] = __floats2half2_rn(__uint_as_float(wds[j] << 16) * down, __uint_as_float(wds[j] & 0xFFFF0000u) * down);
+          *reinterpret_cast<uint4*>(xr + gb_xoffset<Q8>(c)) = *reinterpret_cast<const uint4*>(h);
+        }
+      }
     }
     if (lane == 0) xscale[r] = __uint_as_float((uint32_t)(127 + e) << 23);
   }

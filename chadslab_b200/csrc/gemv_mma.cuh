@@ -126,12 +126,9 @@ qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ s
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   // Launched with programmatic stream serialization: it may start while a preceding (small, early-triggering) kernel
-  // still runs, so wait before touching x / y.  Its own successor may be launched at once: the grid never exceeds what
-  // is resident (see gm_launch), so a successor's CTAs only ever take slots this kernel's CTAs have left for good, and
-  // they park in their own griddepcontrol.wait until this grid has completed.
-#ifndef BQ_GEMV_NO_EARLY_TRIGGER
-  pdl_launch_dependents();
-#endif
+  // still runs, so wait before touching x / y.  It never triggers its own successor early: a successor whose CTAs
+  // become resident while this grid streams takes registers and shared memory away from it, and measured (256000-row
+  // head, q4: 58 against 63 us) that costs more than the launch latency it hides.
   pdl_wait();
   // PUSH: the receive-slot addresses of this call, one per rank, parked behind the reduction buffers
   float** push_dst = reinterpret_cast<float**>(cred + GM_WARPS * 16 * NV);

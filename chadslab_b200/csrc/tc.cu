@@ -1032,6 +1032,21 @@ static int pair_launch(const T2Args& a, dim3 grid, cudaStream_t s) {
     BQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P::SMEM));
     configured = true;
   }
+  if (getenv("BQ_PAIR_PROBE")) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = dim3(TC_THREADS); cfg.dynamicSmemBytes = P::SMEM; cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension; at[0].val.clusterDim.x = 1; at[0].val.clusterDim.y = 2; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    int ncl = -1, csz = -1;
+    cudaError_t e1 = cudaOccupancyMaxActiveClusters(&ncl, kern, &cfg);
+    cfg.numAttrs = 0;
+    cudaError_t e2 = cudaOccupancyMaxPotentialClusterSize(&csz, kern, &cfg);
+    cudaFuncAttributes fa; cudaFuncGetAttributes(&fa, kern);
+    fprintf(stderr, "pair probe: grid %u %u smem %d regs %d maxdyn %d active clusters %d (%s) potential size %d (%s)\n", grid.x, grid.y,
+            (int)P::SMEM, fa.numRegs, fa.maxDynamicSharedSizeBytes, ncl, cudaGetErrorName(e1), csz, cudaGetErrorName(e2));
+    cudaGetLastError();
+  }
   BQ_CUDA(launch_chain(kern, grid, dim3(TC_THREADS), (size_t)P::SMEM, s, 2, a));      // clusters of 2 CTAs along grid.y
   count_launch();
   BQ_CUDA(cudaGetLastError());
