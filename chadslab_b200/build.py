@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "_obj")
 LIB = os.path.join(HERE, "libb200q.so")
-SOURCES = ["api.cu", "simt.cu", "gemv_mma.cu", "gemv_push.cu", "gemv_gated.cu", "gemv_batch.cu", "moe.cu", "tc.cu", "glue.cu", "comm.cu", "ep.cu", "quant.cu"]
+SOURCES = ["api.cu", "simt.cu", "gemv_mma.cu", "gemv_push.cu", "gemv_gated.cu", "gemv_batch.cu", "moe.cu", "tc.cu", "glue.cu", "attn_mma.cu", "comm.cu", "ep.cu", "quant.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC",

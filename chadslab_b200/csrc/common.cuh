@@ -145,11 +145,17 @@ int launch_moe_experts_tc(const Moe* m, const void* xp, const int32_t* offsets, 
 int launch_device_encode(uint8_t* codes, size_t bytes, int fmt, bool to_device_layout, cudaStream_t s);
 // out[m] = argmax of row m (ties -> lower index); vout (optional): the maximum itself
 int launch_argmax(const void* logits, int dtype, int64_t M, int64_t N, int32_t* out, cudaStream_t s, float* vout = nullptr);
+// grouped-query decode attention on mma.sync (bf16 caches, head_dim 64 / 128 / 256): hp = query heads per CTA
+bool attention_mma_supported(int Hq, int Hkv, int D, int* hp_out);
+int launch_attention_mma(const void* q, const float* qkv, void* k_cache, void* v_cache, const int64_t* pos, void* out, int64_t B,
+                         int Hq, int Hkv, int D, int64_t S, float rope_base, int hp, int nsplit, float* part, unsigned* counters,
+                         cudaStream_t s);
 bool pdl_enabled();     // BQ_PDL environment switch (default on)
 
 #ifdef __CUDACC__
 // Launch with the programmatic-stream-serialization attribute (the kernel must call pdl_wait() before it reads or
-// writes anything a preceding kernel on the stream may still be using).  `cluster_y` > 1 adds a cluster dimension.
+// writes anything a preceding kernel on the stream may still be using).  `cluster_y` > 1 adds a cluster dimension
+// along y; `cluster_y` < -1 one of -cluster_y CTAs along x (CTA pairs of tcgen05 cta_group::2 are neighbours in x).
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_chain(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, int cluster_y,
                                 Args... args) {
@@ -165,6 +171,10 @@ inline cudaError_t launch_chain(void (*kern)(KArgs...), dim3 grid, dim3 block, s
   if (cluster_y > 1) {
     attr[n].id = cudaLaunchAttributeClusterDimension;
     attr[n].val.clusterDim.x = 1; attr[n].val.clusterDim.y = (unsigned)cluster_y; attr[n].val.clusterDim.z = 1;
+    ++n;
+  } else if (cluster_y < -1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = (unsigned)(-cluster_y); attr[n].val.clusterDim.y = 1; attr[n].val.clusterDim.z = 1;
     ++n;
   }
   cfg.attrs = attr; cfg.numAttrs = n;
@@ -255,6 +265,15 @@ template <> __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16*
     w[i] = *reinterpret_cast<const uint32_t*>(&v);
   }
   *reinterpret_cast<uint4*>(p) = r;
+}
+
+// element d of a head taken from the fp32 projection output, rotated like rope_kv_append_kernel does
+template <typename T>
+__device__ __forceinline__ float rope_elem(const float* __restrict__ src, int d, int D, const float* cs, const float* sn, bool rotate) {
+  if (!rotate) return to_float<T>(from_float<T>(src[d]));
+  const int half = D / 2, j = d < half ? d : d - half;
+  const float x1 = to_float<T>(from_float<T>(src[j])), x2 = to_float<T>(from_float<T>(src[j + half]));
+  return to_float<T>(from_float<T>(d < half ? x1 * cs[j] - x2 * sn[j] : x2 * cs[j] + x1 * sn[j]));
 }
 
 // Exact integer-code -> fp32 conversions without the (slow) I2F pipe.

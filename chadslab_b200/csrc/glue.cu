@@ -423,14 +423,6 @@ template <int N> __device__ __forceinline__ void unpack_rawvec(const RawVec<__nv
     }
   }
 }
-// element d of a head taken from the fp32 projection output, rotated like rope_kv_append_kernel does
-template <typename T>
-__device__ __forceinline__ float rope_elem(const float* __restrict__ src, int d, int D, const float* cs, const float* sn, bool rotate) {
-  if (!rotate) return to_float<T>(from_float<T>(src[d]));
-  const int half = D / 2, j = d < half ? d : d - half;
-  const float x1 = to_float<T>(from_float<T>(src[j])), x2 = to_float<T>(from_float<T>(src[j + half]));
-  return to_float<T>(from_float<T>(d < half ? x1 * cs[j] - x2 * sn[j] : x2 * cs[j] + x1 * sn[j]));
-}
 constexpr int GQA_MAX_HD = 512;          // hpw * D handled by one warp (EPLN <= 16)
 template <typename T, bool FUSED, int EPLN, int PB>      // PB positions per warp and trip (K and V rows of a trip in flight)
 __global__ void __launch_bounds__(ATT_WARPS * 32)
@@ -660,7 +652,12 @@ static int launch_attention(const void* q, const float* qkv, void* k_cache, void
   const bool gqa = hpw > 1 && (D * hpw) % 32 == 0 && (epln == 8 || epln == 16) &&
                    ((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) | reinterpret_cast<uintptr_t>(q) |
                      reinterpret_cast<uintptr_t>(out)) & 15) == 0;
-  const int64_t ctas_xy = gqa ? B * Hkv * (rep / hpw) : B * Hq;
+  // bf16 caches with several query heads per KV head: the tensor-path kernel (attn_mma.cu), which keeps up with HBM
+  int hp = 0;
+  const bool mma = dtype == BQ_DT_BF16 && attention_mma_supported(Hq, Hkv, D, &hp) &&
+                   ((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) | reinterpret_cast<uintptr_t>(q) |
+                     reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  const int64_t ctas_xy = mma ? B * Hkv * (rep / hp) : gqa ? B * Hkv * (rep / hpw) : B * Hq;
   // few CTAs and a long cache: split the positions so that several CTAs per SM stream K/V
   int64_t nsplit = (4 * (int64_t)sm_count() + ctas_xy - 1) / ctas_xy;
   if (nsplit > S / 128) nsplit = S / 128;        // at least 128 cache positions per split (measured: finer is slower)
@@ -674,6 +671,7 @@ static int launch_attention(const void* q, const float* qkv, void* k_cache, void
   }
   float* part = (float*)g_att_part.ptr;
   unsigned* counters = (unsigned*)g_att_count.ptr;
+  if (mma) return launch_attention_mma(q, qkv, k_cache, v_cache, pos, out, B, Hq, Hkv, D, S, rope_base, hp, (int)nsplit, part, counters, s);
   if (gqa) {
     dim3 grid((unsigned)(Hkv * (rep / hpw)), (unsigned)B, (unsigned)nsplit);
 #define BQ_GQA_LAUNCH(TT, FUSED, EP)                                                                                       \

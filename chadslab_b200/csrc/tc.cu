@@ -603,9 +603,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_pair_kernel(const __grid_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = pair_rank();                       // 0 = leader (issues the MMAs), 1 = peer
-  // grid.y counts 128-row weight tiles (padded to an even number), cluster dimension y = 2: rank = blockIdx.y & 1
-  const int64_t n0 = (int64_t)blockIdx.y * TC_ROWS;                       // this CTA's weight rows
-  const int64_t m0 = (int64_t)blockIdx.x * 256, m_end = args.M;           // the pair's batch rows
+  // grid.x counts 128-row weight tiles (padded to an even number), cluster dimension x = 2: rank = blockIdx.x & 1
+  const int64_t n0 = (int64_t)blockIdx.x * TC_ROWS;                       // this CTA's weight rows
+  const int64_t m0 = (int64_t)blockIdx.y * 256, m_end = args.M;           // the pair's batch rows
   const int64_t mx0 = m0 + 128 * (int64_t)rank;                            // the half of them this CTA stages
   const int ksteps = (int)(args.K / T2_BK);
 
@@ -1032,22 +1032,7 @@ static int pair_launch(const T2Args& a, dim3 grid, cudaStream_t s) {
     BQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P::SMEM));
     configured = true;
   }
-  if (getenv("BQ_PAIR_PROBE")) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid; cfg.blockDim = dim3(TC_THREADS); cfg.dynamicSmemBytes = P::SMEM; cfg.stream = s;
-    cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeClusterDimension; at[0].val.clusterDim.x = 1; at[0].val.clusterDim.y = 2; at[0].val.clusterDim.z = 1;
-    cfg.attrs = at; cfg.numAttrs = 1;
-    int ncl = -1, csz = -1;
-    cudaError_t e1 = cudaOccupancyMaxActiveClusters(&ncl, kern, &cfg);
-    cfg.numAttrs = 0;
-    cudaError_t e2 = cudaOccupancyMaxPotentialClusterSize(&csz, kern, &cfg);
-    cudaFuncAttributes fa; cudaFuncGetAttributes(&fa, kern);
-    fprintf(stderr, "pair probe: grid %u %u smem %d regs %d maxdyn %d active clusters %d (%s) potential size %d (%s)\n", grid.x, grid.y,
-            (int)P::SMEM, fa.numRegs, fa.maxDynamicSharedSizeBytes, ncl, cudaGetErrorName(e1), csz, cudaGetErrorName(e2));
-    cudaGetLastError();
-  }
-  BQ_CUDA(launch_chain(kern, grid, dim3(TC_THREADS), (size_t)P::SMEM, s, 2, a));      // clusters of 2 CTAs along grid.y
+  BQ_CUDA(launch_chain(kern, grid, dim3(TC_THREADS), (size_t)P::SMEM, s, -2, a));      // clusters of 2 CTAs along grid.x
   count_launch();
   BQ_CUDA(cudaGetLastError());
   return BQ_OK;
@@ -1090,7 +1075,7 @@ int launch_qlinear_tc(const uint8_t* codes, const __half* scales, int fmt, int64
     t.status = status_word();
     t.gated_act = gated_act;
     const int64_t row_tiles = (N + TC_ROWS - 1) / TC_ROWS;
-    dim3 gridp((unsigned)((M + 255) / 256), (unsigned)((row_tiles + 1) / 2 * 2));
+    dim3 gridp((unsigned)((row_tiles + 1) / 2 * 2), (unsigned)((M + 255) / 256));
     return fmt == BQ_FMT_Q8G32 ? pair_launch<BQ_FMT_Q8G32>(t, gridp, s) : pair_launch<BQ_FMT_Q4G32>(t, gridp, s);
   }
   // large batches are bound by the L2 -> SM traffic of codes + activations per multiply-add: 4-bit weights do

@@ -214,7 +214,7 @@ def test_fused_router_equals_linear_then_route(cuda_lib, fmt, T, E, k, H):
     margin = (srt[:, :k] - srt[:, 1:k + 1]).min(axis=-1) / np.abs(logits).max()       # smallest gap among the top k+1
     clear = margin > 2 * TOL
     got = idx.cpu().numpy()
-    assert (T < 16 or clear.mean() > 0.5) and np.array_equal(got[clear], ridx[clear])
+    assert (T < 16 or clear.mean() > 0.25) and np.array_equal(got[clear], ridx[clear])
     # rows with a near tie: every chosen expert's logit is within the tolerance of the k-th best
     chosen = np.take_along_axis(logits, got.astype(np.int64), axis=1)
     assert (chosen >= srt[:, k - 1:k] - 2 * TOL * np.abs(logits).max()).all()
