@@ -64,6 +64,8 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __
   const int rep = Hq / Hkv, gpk = rep / hp;
   const int b = blockIdx.y, kv = blockIdx.x / gpk, hg = blockIdx.x % gpk;
   const int nsplit = gridDim.z, z = blockIdx.z;
+  // position slices leave (max, sum) pairs behind the [B * Hq][nsplit][D] accumulators of `part`
+  float* stats = part + (int64_t)gridDim.y * Hq * nsplit * D;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
   const int h0 = kv * rep + hg * hp;                       // first query head of this CTA
   pdl_launch_dependents();
@@ -83,6 +85,7 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __
       sincosf((float)(n_all - 1) * inv, &s_sin[j], &s_cos[j]);
     }
     __syncthreads();
+#pragma unroll 4
     for (int e = threadIdx.x; e < ROWS * D; e += AM_THREADS) {
       const int hl = e / D, d = e - hl * D;
       float v = 0.0f;
@@ -122,8 +125,11 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __
   const __nv_bfloat16* kb = k_cache + ((int64_t)b * S * Hkv + kv) * D + 8 * t;
   const __nv_bfloat16* vb = v_cache + ((int64_t)b * S * Hkv + kv) * D + 8 * g;
 
-  for (int64_t p0 = p_lo + (int64_t)warp * 16; p0 < n_pos; p0 += AM_WARPS * 16) {
-    uint4 kr[2][D / 32], vr[4][D / 64];
+  // Software pipeline without extra registers: the K rows of the next block are requested as soon as the scores of this
+  // one are done (their registers are free then), the V rows of the next block as soon as this block's P V is done, so
+  // one of the two is always in flight while the warp computes.
+  uint4 kr[2][D / 32], vr[4][D / 64];
+  auto load_k = [&](int64_t p0) {
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt) {
       int64_t row = p0 + 8 * nt + g;
@@ -131,6 +137,8 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __
 #pragma unroll
       for (int L = 0; L < D / 32; ++L) kr[nt][L] = *reinterpret_cast<const uint4*>(kb + row * row_stride + 32 * L);
     }
+  };
+  auto load_v = [&](int64_t p0) {
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
       int64_t row = p0 + 2 * t + (r & 1) + 8 * (r >> 1);
@@ -138,6 +146,11 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __
 #pragma unroll
       for (int i = 0; i < D / 64; ++i) vr[r][i] = *reinterpret_cast<const uint4*>(vb + row * row_stride + 64 * i);
     }
+  };
+  const int64_t p_first = p_lo + (int64_t)warp * 16;
+  if (p_first < n_pos) { load_k(p_first); load_v(p_first); }
+  for (int64_t p0 = p_first; p0 < n_pos; p0 += AM_WARPS * 16) {
+    const int64_t p_next = p0 + AM_WARPS * 16;
     // ---- scores of 16 positions x the CTA's heads -------------------------------------------------------------
     float sc[2][NC];
 #pragma unroll
@@ -155,6 +168,7 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __
         am_mma<HI>(sc[nt], qa.z, qb.z, qa.w, qb.w, kr[nt][L].z, kr[nt][L].w);
       }
     }
+    if (p_next < n_pos) load_k(p_next);
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
@@ -193,6 +207,7 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __
         if (HI) { acc[j][2] *= corr[1]; acc[j][3] *= corr[1]; }
         am_mma<HI>(acc[j], pa[0], pa[1], pa[2], pa[3], b0, b1);
       }
+    if (p_next < n_pos) load_v(p_next);
   }
 
   // ---- merge the warps (per head), then the position slices -------------------------------------------------------------
@@ -228,9 +243,12 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __
     if (nsplit == 1) {
       out[(bh0 + eh) * D + ed] = __float2bfloat16_rn(o / gs);
     } else {
-      float* mine = part + ((bh0 + eh) * nsplit + z) * (D + 2);
-      mine[2 + ed] = o;
-      if (ed == 0) { mine[0] = gm; mine[1] = gs; }
+      part[((bh0 + eh) * nsplit + z) * D + ed] = o;
+      if (ed == 0) {
+        float* st = stats + ((bh0 + eh) * nsplit + z) * 2;
+        st[0] = gm;
+        st[1] = gs;
+      }
     }
   }
   if (nsplit == 1) return;
@@ -246,19 +264,41 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  for (int e = threadIdx.x; e < HD; e += AM_THREADS) {
-    const int eh = e / D, ed = e - eh * D;
-    const float* all = part + (bh0 + eh) * nsplit * (D + 2);
+  // the last slice to arrive merges: per head the weights exp2(m_i - max) / sum first (shared memory, reusing the
+  // warps' accumulator area), then every output element is a weighted sum of nsplit independent loads
+  float* s_f = &s_acc[0][0][0];                                         // [hp][nsplit]; hp * nsplit <= 16 * 64 floats
+  for (int eh = warp; eh < hp; eh += AM_WARPS) {
+    const float* st = stats + (bh0 + eh) * nsplit * 2;
     float tm = -INFINITY;
-    for (int i = 0; i < nsplit; ++i) tm = fmaxf(tm, __ldcg(all + (int64_t)i * (D + 2)));
-    float ts = 0.0f, o = 0.0f;
-    for (int i = 0; i < nsplit; ++i) {
-      const float m_i = __ldcg(all + (int64_t)i * (D + 2));
+    for (int i = lane; i < nsplit; i += 32) tm = fmaxf(tm, __ldcg(st + 2 * i));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, off));
+    float ts = 0.0f;
+    for (int i = lane; i < nsplit; i += 32) {
+      const float m_i = __ldcg(st + 2 * i);
       const float f = m_i == -INFINITY ? 0.0f : exp2f(m_i - tm);
-      ts += __ldcg(all + (int64_t)i * (D + 2) + 1) * f;
-      o += __ldcg(all + (int64_t)i * (D + 2) + 2 + ed) * f;
+      s_f[eh * nsplit + i] = f;
+      ts += __ldcg(st + 2 * i + 1) * f;
     }
-    out[(bh0 + eh) * D + ed] = __float2bfloat16_rn(o / ts);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) ts += __shfl_xor_sync(0xffffffffu, ts, off);
+    __syncwarp();
+    const float inv = 1.0f / ts;
+    for (int i = lane; i < nsplit; i += 32) s_f[eh * nsplit + i] *= inv;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < HD / 4; e += AM_THREADS) {
+    const int eh = e / (D / 4), e4 = e - eh * (D / 4);
+    const float4* all = reinterpret_cast<const float4*>(part + (bh0 + eh) * nsplit * D) + e4;
+    float4 o = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll 8
+    for (int i = 0; i < nsplit; ++i) {
+      const float4 v = __ldcg(all + (int64_t)i * (D / 4));
+      const float f = s_f[eh * nsplit + i];
+      o.x += v.x * f; o.y += v.y * f; o.z += v.z * f; o.w += v.w * f;
+    }
+    __nv_bfloat16* dst = out + (bh0 + eh) * D + 4 * e4;
+    *reinterpret_cast<uint2*>(dst) = make_uint2(am_pack(o.x, o.y), am_pack(o.z, o.w));
   }
 }
 

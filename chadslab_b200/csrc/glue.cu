@@ -660,8 +660,11 @@ static int launch_attention(const void* q, const float* qkv, void* k_cache, void
   const int64_t ctas_xy = mma ? B * Hkv * (rep / hp) : gqa ? B * Hkv * (rep / hpw) : B * Hq;
   // few CTAs and a long cache: split the positions so that several CTAs per SM stream K/V
   int64_t nsplit = (4 * (int64_t)sm_count() + ctas_xy - 1) / ctas_xy;
-  if (nsplit > S / 128) nsplit = S / 128;        // at least 128 cache positions per split (measured: finer is slower)
-  if (nsplit > 32) nsplit = 32;
+  // at least 128 cache positions per split (measured: finer is slower); the tensor-path kernel has half the warps per
+  // CTA and takes 64 (one 16-position block per warp)
+  const int64_t min_pos = mma ? 64 : 128, max_split = mma ? 64 : 32;
+  if (nsplit > S / min_pos) nsplit = S / min_pos;
+  if (nsplit > max_split) nsplit = max_split;
   if (nsplit < 1) nsplit = 1;
   cudaStream_t s = (cudaStream_t)stream;
   if (nsplit > 1) {

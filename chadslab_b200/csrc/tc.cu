@@ -513,8 +513,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tmem_kernel(const __grid_
 // leader learns that the peer's operands are ready through remote mbarrier arrivals of the peer's converter warps
 // (the barriers the issuer waits on live in the leader's shared memory), and tells the peer that its buffers are
 // free / its accumulator is complete with a second tcgen05.commit aimed at the peer's barrier.
-// Tensor memory: [0, 256) accumulator, 2 x 64 columns of A from column 256; allocated with cta_group::2 by warp 1 of
-// both CTAs.
+// Tensor memory: [0, 256) accumulator, 4 x 64 columns of A from column 256 (the converters run up to three k-steps
+// ahead of the MMAs, so that their latency - wake-up, unpack, tcgen05.st, arrive - is off the critical path); allocated
+// with cta_group::2 by warp 1 of both CTAs.
 // =================================================================================================
 template <int FMT> struct PairPlan {
   static constexpr int RAW_ROW = (FMT == BQ_FMT_Q8G32) ? 128 : 64;
@@ -524,9 +525,11 @@ template <int FMT> struct PairPlan {
   static constexpr int STAGE = ((RAW + XT + 1023) / 1024) * 1024;
   static constexpr int FIXED = TC_SC_SLOTS * SCT + 1024 + 1024;
   static constexpr int S = 4;
+  static constexpr int NA = 4;                                           // A buffers in tensor memory (64 columns each)
   static constexpr int SMEM = FIXED + S * STAGE;
   static constexpr int ACOL0 = 256;
   static constexpr int TMEM_COLS = 512;
+  static_assert(ACOL0 + NA * T2_ACOLS <= TMEM_COLS, "tensor memory plan too large");
   static_assert(SMEM <= 227 * 1024, "shared memory plan too large");
 };
 
@@ -587,7 +590,7 @@ __host__ __device__ constexpr uint32_t umma_idesc_pair() {
 template <int FMT>
 __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_pair_kernel(const __grid_constant__ T2Args args) {
   using P = PairPlan<FMT>;
-  constexpr int S = P::S, NA = 2;
+  constexpr int S = P::S, NA = P::NA;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* stages = smem;                                  // per stage: [x atom 0][x atom 1][codes tile]
@@ -660,8 +663,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_pair_kernel(const __grid_
       const uint32_t peer_acc = pair_map(smem_u32(acc_full), 1u);
       bool ok = true;
       for (int ks = 0; ks < ksteps && ok; ++ks) {
-        const int s = ks % S, a = ks & 1;
-        const uint32_t aph = (uint32_t)(ks >> 1) & 1u;
+        const int s = ks % S, a = ks % NA;
+        const uint32_t aph = (uint32_t)(ks / NA) & 1u;
         ok = mbar_wait_cluster(smem_u32(&a_full[a]), aph, abort_flag);   // both CTAs converted (hence both stages landed)
         if (!ok) break;
         tc_fence_after();
@@ -689,8 +692,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_pair_kernel(const __grid_
     const uint32_t leader_a_full = pair_map(smem_u32(&a_full[0]), 0u);
     bool ok = true;
     for (int ks = 0; ks < ksteps && ok; ++ks) {
-      const int s = ks % S, a = ks & 1;
-      const uint32_t ph = (uint32_t)(ks / S) & 1u, aph = (uint32_t)(ks >> 1) & 1u;
+      const int s = ks % S, a = ks % NA;
+      const uint32_t ph = (uint32_t)(ks / S) & 1u, aph = (uint32_t)(ks / NA) & 1u;
       ok = mbar_wait_warp(smem_u32(&full[s]), ph, abort_flag, lane);
       if (ok) {
         uint32_t fine = 0;
