@@ -33,12 +33,17 @@
 namespace bq {
 
 constexpr int TC_ROWS = 128;        // weight rows per tile (UMMA M)
-constexpr int TC_CONV_THREADS = 256;   // 8 converter warps
+// 16 converter warps: four per tensor-memory lane quarter, each converting 32 k of its 32 rows per step.  With 8 (64 k
+// per thread) a step took ~3000 cycles at every batch size although no unit was busy: a converter warp issues one
+// instruction per ~5 cycles (dependent PRMT / HSUB2 / HMUL2 chains), and two warps per scheduler cannot hide that.
+constexpr int TC_CONV_THREADS = 512;
 constexpr int TC_THREADS = 64 + TC_CONV_THREADS;
 constexpr int TC_SC_SLOTS = 3;      // scale tiles in flight (each covers 2 k-steps)
 constexpr size_t TC_PART_BYTES = (size_t)64 << 20;   // split-K partial tiles never exceed this
 constexpr uint64_t TC_WAIT_NS = 2000000000ull;   // every device-side wait gives up after 2 s
 constexpr int TC_CONV_WARPS = TC_CONV_THREADS / 32;
+constexpr int TC_KQ = TC_CONV_WARPS / 4;            // converter warps that share a row block: k slices of a 128-k step
+constexpr int TC_CPT = 64 / TC_KQ;                  // tensor-memory columns (2 fp16 each) a thread writes per step
 
 // ---- PTX wrappers -----------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -179,6 +184,37 @@ __device__ __forceinline__ uint4 cvt_q4_word(const uint32_t v, const __half2 s2)
                     *reinterpret_cast<uint32_t*>(&h45), *reinterpret_cast<uint32_t*>(&h67));
 }
 
+// One converter thread's share of a 128-k step of its weight row: TC_CPT * 2 codes -> code * scale as fp16 pairs.
+// `raw` = the row's packed codes of the step in the (swizzled) stage, `scw` = its 4 scales of the step.
+template <int FMT>
+__device__ __forceinline__ void convert_row_slice(const uint8_t* raw, const __half* scw, int row, int kq, uint32_t* regs) {
+  if (FMT == BQ_FMT_Q8G32) {
+    // 16 codes per 16-byte chunk; chunk c of the row sits at 16-byte slot c ^ (row & 7)
+#pragma unroll
+    for (int i = 0; i < 8 / TC_KQ; ++i) {
+      const int c = (8 / TC_KQ) * kq + i;
+      const uint4 wv = *reinterpret_cast<const uint4*>(raw + ((c ^ (row & 7)) << 4));
+      uint4 lo, hi;
+      cvt_q8_chunk(wv, __half2half2(scw[c >> 1]), lo, hi);
+      regs[8 * i + 0] = lo.x; regs[8 * i + 1] = lo.y; regs[8 * i + 2] = lo.z; regs[8 * i + 3] = lo.w;
+      regs[8 * i + 4] = hi.x; regs[8 * i + 5] = hi.y; regs[8 * i + 6] = hi.z; regs[8 * i + 7] = hi.w;
+    }
+  } else {
+    // 32 codes (one group) per 16-byte chunk; chunk c sits at 16-byte slot c ^ ((row >> 1) & 3)
+#pragma unroll
+    for (int i = 0; i < 4 / TC_KQ; ++i) {
+      const int c = (4 / TC_KQ) * kq + i;
+      const uint4 wv = *reinterpret_cast<const uint4*>(raw + ((c ^ ((row >> 1) & 3)) << 4));
+      const __half2 s2 = __half2half2(scw[c]);
+      const uint4 q0 = cvt_q4_word(wv.x, s2), q1 = cvt_q4_word(wv.y, s2), q2 = cvt_q4_word(wv.z, s2),
+                  q3 = cvt_q4_word(wv.w, s2);
+      uint32_t* r = regs + 16 * i;
+      r[0] = q0.x; r[1] = q0.y; r[2] = q0.z; r[3] = q0.w; r[4] = q1.x; r[5] = q1.y; r[6] = q1.z; r[7] = q1.w;
+      r[8] = q2.x; r[9] = q2.y; r[10] = q2.z; r[11] = q2.w; r[12] = q3.x; r[13] = q3.y; r[14] = q3.z; r[15] = q3.w;
+    }
+  }
+}
+
 // =================================================================================================
 // The converted fp16 weights never touch shared memory: shared memory only holds packed codes, activations and
 // scales, so two CTAs fit on an SM up to BN = 128.
@@ -259,10 +295,21 @@ __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t* v) {
         "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
       : "memory");
 }
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
+// one converter thread's TC_CPT columns of a step
+__device__ __forceinline__ void tc_st_cols(uint32_t taddr, const uint32_t* v) {
+  if (TC_CPT == 32) tc_st32(taddr, v); else tc_st16(taddr, v);
+}
 __device__ __forceinline__ void tc_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 template <int FMT, int BN, int MODE>
-__global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tmem_kernel(const __grid_constant__ T2Args args) {
+__global__ void __launch_bounds__(TC_THREADS, (T2Plan<FMT, BN, MODE>::TMEM_COLS == 256 ? 2 : 1)) qgemm_tmem_kernel(const __grid_constant__ T2Args args) {
   using P = T2Plan<FMT, BN, MODE>;
   constexpr int S = P::S, NA = 2, NW = P::NW;
   constexpr bool GATED = MODE == 1, DUAL = MODE == 2;
@@ -375,7 +422,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tmem_kernel(const __grid_
   } else {
     // ================= converters (one weight row per thread), then epilogue =================
     const int lg = warp & 3;                 // TMEM lane group this warp may touch
-    const int half = (warp - 2) >> 2;        // which 64 k of the 128-k step this warp converts
+    const int kq = (warp - 2) >> 2;          // which slice of the 128-k step this warp converts
     const int row = lg * 32 + lane;
     bool ok = true;
     for (int ks = 0; ks < ksteps && ok; ++ks) {
@@ -388,33 +435,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tmem_kernel(const __grid_
       for (int w = 0; w < NW; ++w) {
       const uint8_t* raw = stages + s * P::STAGE + P::XT + w * P::RAW + row * P::RAW_ROW;
       const __half* scw = reinterpret_cast<const __half*>(sc_tiles + (((ks >> 1) % TC_SC_SLOTS) * NW + w) * P::SCT) + row * 8 + (ks & 1) * 4;
-      uint32_t regs[32];
-      if (FMT == BQ_FMT_Q8G32) {
-        // 64 codes = 4 chunks of 16; chunk c of the row sits at 16-byte slot c ^ (row & 7)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int c = 4 * half + i;
-          const uint4 wv = *reinterpret_cast<const uint4*>(raw + ((c ^ (row & 7)) << 4));
-          uint4 lo, hi;
-          cvt_q8_chunk(wv, __half2half2(scw[c >> 1]), lo, hi);
-          regs[8 * i + 0] = lo.x; regs[8 * i + 1] = lo.y; regs[8 * i + 2] = lo.z; regs[8 * i + 3] = lo.w;
-          regs[8 * i + 4] = hi.x; regs[8 * i + 5] = hi.y; regs[8 * i + 6] = hi.z; regs[8 * i + 7] = hi.w;
-        }
-      } else {
-        // 64 codes = 2 chunks of 32 (one group each); chunk c sits at 16-byte slot c ^ ((row >> 1) & 3)
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const int c = 2 * half + i;
-          const uint4 wv = *reinterpret_cast<const uint4*>(raw + ((c ^ ((row >> 1) & 3)) << 4));
-          const __half2 s2 = __half2half2(scw[c]);
-          const uint4 q0 = cvt_q4_word(wv.x, s2), q1 = cvt_q4_word(wv.y, s2), q2 = cvt_q4_word(wv.z, s2),
-                      q3 = cvt_q4_word(wv.w, s2);
-          uint32_t* r = regs + 16 * i;
-          r[0] = q0.x; r[1] = q0.y; r[2] = q0.z; r[3] = q0.w; r[4] = q1.x; r[5] = q1.y; r[6] = q1.z; r[7] = q1.w;
-          r[8] = q2.x; r[9] = q2.y; r[10] = q2.z; r[11] = q2.w; r[12] = q3.x; r[13] = q3.y; r[14] = q3.z; r[15] = q3.w;
-        }
-      }
-      tc_st32(tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)(P::ACOL0 + (w * NA + a) * T2_ACOLS + 32 * half), regs);
+      uint32_t regs[TC_CPT];
+      convert_row_slice<FMT>(raw, scw, row, kq, regs);
+      tc_st_cols(tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)(P::ACOL0 + (w * NA + a) * T2_ACOLS + TC_CPT * kq), regs);
       }
       tc_st_wait();
       tc_fence_before();
@@ -430,7 +453,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tmem_kernel(const __grid_
       const int64_t n = n0 + row;
       const uint32_t tbase = tmem_base + ((uint32_t)(lg * 32) << 16);
 #pragma unroll 1
-      for (int c0 = 16 * half; c0 < BN; c0 += 32) {
+      for (int c0 = 16 * kq; c0 < BN; c0 += 16 * TC_KQ) {
         if (m0 + c0 >= m_end) break;
         if (GATED) {                               // h = silu(gate) * up, rounded to bf16
           uint32_t v[16], u[16];
@@ -687,7 +710,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_pair_kernel(const __grid_
   } else {
     // ================= converters (one weight row per thread), then epilogue =================
     const int lg = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int kq = (warp - 2) >> 2;
     const int row = lg * 32 + lane;
     const uint32_t leader_a_full = pair_map(smem_u32(&a_full[0]), 0u);
     bool ok = true;
@@ -703,31 +726,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_pair_kernel(const __grid_
       if (!ok) break;
       const uint8_t* raw = stages + s * P::STAGE + P::XT + row * P::RAW_ROW;
       const __half* scw = reinterpret_cast<const __half*>(sc_tiles + ((ks >> 1) % TC_SC_SLOTS) * P::SCT) + row * 8 + (ks & 1) * 4;
-      uint32_t regs[32];
-      if (FMT == BQ_FMT_Q8G32) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int c = 4 * half + i;
-          const uint4 wv = *reinterpret_cast<const uint4*>(raw + ((c ^ (row & 7)) << 4));
-          uint4 lo, hi;
-          cvt_q8_chunk(wv, __half2half2(scw[c >> 1]), lo, hi);
-          regs[8 * i + 0] = lo.x; regs[8 * i + 1] = lo.y; regs[8 * i + 2] = lo.z; regs[8 * i + 3] = lo.w;
-          regs[8 * i + 4] = hi.x; regs[8 * i + 5] = hi.y; regs[8 * i + 6] = hi.z; regs[8 * i + 7] = hi.w;
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const int c = 2 * half + i;
-          const uint4 wv = *reinterpret_cast<const uint4*>(raw + ((c ^ ((row >> 1) & 3)) << 4));
-          const __half2 s2 = __half2half2(scw[c]);
-          const uint4 q0 = cvt_q4_word(wv.x, s2), q1 = cvt_q4_word(wv.y, s2), q2 = cvt_q4_word(wv.z, s2),
-                      q3 = cvt_q4_word(wv.w, s2);
-          uint32_t* r = regs + 16 * i;
-          r[0] = q0.x; r[1] = q0.y; r[2] = q0.z; r[3] = q0.w; r[4] = q1.x; r[5] = q1.y; r[6] = q1.z; r[7] = q1.w;
-          r[8] = q2.x; r[9] = q2.y; r[10] = q2.z; r[11] = q2.w; r[12] = q3.x; r[13] = q3.y; r[14] = q3.z; r[15] = q3.w;
-        }
-      }
-      tc_st32(tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)(P::ACOL0 + a * T2_ACOLS + 32 * half), regs);
+      uint32_t regs[TC_CPT];
+      convert_row_slice<FMT>(raw, scw, row, kq, regs);
+      tc_st_cols(tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)(P::ACOL0 + a * T2_ACOLS + TC_CPT * kq), regs);
       tc_st_wait();
       tc_fence_before();
       __syncwarp();
@@ -746,7 +747,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_pair_kernel(const __grid_
       const int64_t nn = n0 + row;
       const uint32_t tbase = tmem_base + ((uint32_t)(lg * 32) << 16);
 #pragma unroll 1
-      for (int c0 = 16 * half; c0 < 256; c0 += 32) {
+      for (int c0 = 16 * kq; c0 < 256; c0 += 16 * TC_KQ) {
         if (m0 + c0 >= m_end) break;
         uint32_t v[16];
         tc_ld16(tbase + (uint32_t)c0, v);
