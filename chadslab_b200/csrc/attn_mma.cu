@@ -25,7 +25,6 @@ namespace bq {
 
 constexpr int AM_WARPS = 4;
 constexpr int AM_THREADS = AM_WARPS * 32;
-constexpr int AM_PF = 3;                    // 16-position blocks a warp requests from L2 ahead of its register loads
 
 // d[0..1] (+ d[2..3] when HI) += A x B; without HI the rows 8..15 of A are zero and their sums are dropped
 template <bool HI>
@@ -148,22 +147,10 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __
       for (int i = 0; i < D / 64; ++i) vr[r][i] = *reinterpret_cast<const uint4*>(vb + row * row_stride + 64 * i);
     }
   };
-  // and further ahead the rows are only requested from L2 (no registers): lane l asks for K row l, lane 16 + l for V
-  // row l of the block AM_PF rounds ahead, so that the register loads above find their rows in L2
-  auto prefetch_block = [&](int64_t p0) {
-    const int64_t row = p0 + (lane & 15);
-    if (row < n_pos) {
-      const __nv_bfloat16* base = (lane < 16 ? k_cache : v_cache) + ((int64_t)b * S * Hkv + kv) * D;
-      l2_prefetch_bulk(base + row * row_stride, (uint32_t)(D * sizeof(__nv_bfloat16)));
-    }
-  };
   const int64_t p_first = p_lo + (int64_t)warp * 16;
-#pragma unroll
-  for (int j = 1; j <= AM_PF; ++j) prefetch_block(p_first + (int64_t)j * AM_WARPS * 16);
   if (p_first < n_pos) { load_k(p_first); load_v(p_first); }
   for (int64_t p0 = p_first; p0 < n_pos; p0 += AM_WARPS * 16) {
     const int64_t p_next = p0 + AM_WARPS * 16;
-    prefetch_block(p0 + (int64_t)(AM_PF + 1) * AM_WARPS * 16);
     // ---- scores of 16 positions x the CTA's heads -------------------------------------------------------------
     float sc[2][NC];
 #pragma unroll

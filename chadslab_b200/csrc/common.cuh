@@ -210,13 +210,6 @@ __device__ __forceinline__ void comm_deposit4(float* p, float4 v) {      // p 16
 // predecessor (completion + memory visibility) before it touches anything the predecessor may have written.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-// L2 prefetch of `bytes` from a global address; a hint: no registers, no completion.  The instruction wants a 16-byte
-// aligned address and a multiple of 16 bytes: anything else (a row-sliced view can start on an 8-byte boundary) is
-// simply not prefetched.
-__device__ __forceinline__ void l2_prefetch_bulk(const void* p, uint32_t bytes) {
-  if ((reinterpret_cast<uintptr_t>(p) & 15) != 0 || (bytes & 15u) != 0 || bytes == 0) return;
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
-}
 __device__ __forceinline__ uint4 ldg_stream16(const void* p) {
   uint4 v;
   asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"

@@ -42,7 +42,6 @@ struct GbArgs {
   float* w_out;                      // GB_ROUTE: f32 routing weights [T, top_k]
   int64_t ldy, N, K;
   int m_rows, top_k, act;            // GB_ROUTE: m_rows = T (all tokens), act = renormalise
-  int prefetch;                      // dense: request each warp's next 16-row block from L2 ahead of its use
 };
 
 // 8 fp16 values of a row, k = 8c .. 8c+7, go to this offset (in halves) of the row's shared-memory image: inside a
@@ -78,18 +77,6 @@ __global__ void __launch_bounds__(GB_THREADS) qgemv_batch_kernel(const __grid_co
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
 
-  const int64_t row_bytes = Q8 ? K : K / 2;
-  const int64_t groups = K / GROUP;
-  const int rb_in_cta = warp / KSPLIT;
-  const int ksp = warp % KSPLIT;
-  const int64_t steps_total = K / KSTEP;
-  const int64_t s_begin = steps_total * ksp / KSPLIT, s_end = steps_total * (ksp + 1) / KSPLIT;
-  const int64_t cta_rb0 = (MODE == GB_ROUTE ? 0 : MOE ? (int64_t)blockIdx.y : (int64_t)blockIdx.x) * RB_PER_CTA;
-  const int64_t cta_rb_stride = (MODE == GB_ROUTE ? 1 : MOE ? (int64_t)gridDim.y : (int64_t)gridDim.x) * RB_PER_CTA;
-  // the weight is a constant of the model: its first block may be requested while the preceding kernel still runs
-  if (!MOE && a.prefetch)
-    wq_prefetch_block(KSPLIT == 1, a.codes, a.scales, cta_rb0 + rb_in_cta, N, row_bytes, groups, s_begin, s_end, ksp == 0, lane);
-
   pdl_wait();                                      // activations, tile list and row ranges come from preceding kernels
   const uint8_t* codesA = a.codes;
   const __half* scalesA = a.scales;
@@ -109,9 +96,6 @@ __global__ void __launch_bounds__(GB_THREADS) qgemv_batch_kernel(const __grid_co
     m_rows = (int)(m_end - m0 < MP ? m_end - m0 : MP);
     codesA = a.codesA[e]; scalesA = a.scalesA[e];
     if (TWO) { codesB = a.codesB[e]; scalesB = a.scalesB[e]; }
-    // the expert is known now: its rows stream into L2 while the activation rows are staged below
-    wq_prefetch_block(KSPLIT == 1, codesA, scalesA, cta_rb0 + rb_in_cta, N, row_bytes, groups, s_begin, s_end, ksp == 0, lane);
-    if (TWO) wq_prefetch_block(KSPLIT == 1, codesB, scalesB, cta_rb0 + rb_in_cta, N, row_bytes, groups, s_begin, s_end, ksp == 0, lane);
   }
 
   // ---- activations -> scaled fp16 rows in shared memory (one warp per row, two passes over the row) ----------
@@ -182,13 +166,18 @@ __global__ void __launch_bounds__(GB_THREADS) qgemv_batch_kernel(const __grid_co
   }
   __syncthreads();
 
+  const int64_t row_bytes = Q8 ? K : K / 2;
+  const int64_t groups = K / GROUP;
+  const int rb_in_cta = warp / KSPLIT;
+  const int ksp = warp % KSPLIT;
+  const int64_t steps_total = K / KSTEP;
+  const int64_t s_begin = steps_total * ksp / KSPLIT, s_end = steps_total * (ksp + 1) / KSPLIT;
+  const int64_t cta_rb0 = (MODE == GB_ROUTE ? 0 : MOE ? (int64_t)blockIdx.y : (int64_t)blockIdx.x) * RB_PER_CTA;
+  const int64_t cta_rb_stride = (MODE == GB_ROUTE ? 1 : MOE ? (int64_t)gridDim.y : (int64_t)gridDim.x) * RB_PER_CTA;
+
   for (int64_t rb_base = cta_rb0; rb_base * 16 < N; rb_base += cta_rb_stride) {
     const int64_t rb = rb_base + rb_in_cta;
     const bool active = rb * 16 < N;               // warp-uniform
-    if (MOE || a.prefetch) {                       // the block this warp takes next
-      wq_prefetch_block(KSPLIT == 1, codesA, scalesA, rb + cta_rb_stride, N, row_bytes, groups, s_begin, s_end, ksp == 0, lane);
-      if (TWO) wq_prefetch_block(KSPLIT == 1, codesB, scalesB, rb + cta_rb_stride, N, row_bytes, groups, s_begin, s_end, ksp == 0, lane);
-    }
     int64_t r0 = rb * 16 + g, r1 = r0 + 8;
     if (r0 >= N) r0 = N - 1;
     if (r1 >= N) r1 = N - 1;
@@ -453,19 +442,10 @@ static int gb_dense(const GbArgs& a, cudaStream_t s) {
     int64_t gx = (rb + GB_WARPS / ksplit - 1) / (GB_WARPS / ksplit);
     return dim3((unsigned)(gx > cap ? cap : gx));
   };
-  // L2 prefetch one block ahead per warp, unless the blocks of all resident warps together would crowd L2 (the large
-  // matrices that reach this limit stream at 0.7-0.9 of the HBM rate without it)
-  auto with_prefetch = [&](int ksplit) {
-    GbArgs b = a;
-    const int64_t row_bytes = FMT == BQ_FMT_Q8G32 ? a.K : a.K / 2;
-    const int64_t ahead = (int64_t)grid_for(ksplit).x * (GB_WARPS / ksplit) * 16 * row_bytes;
-    b.prefetch = ahead <= (48ll << 20) ? 1 : 0;
-    return b;
-  };
-  if (rb >= want || a.K < 1024) return gb_launch<FMT, NB, 1, MODE, YT>(with_prefetch(1), grid_for(1), false, s);
-  if (rb * 2 >= want || a.K < 2048) return gb_launch<FMT, NB, 2, MODE, YT>(with_prefetch(2), grid_for(2), false, s);
-  if (rb * 4 >= want || a.K < 4096) return gb_launch<FMT, NB, 4, MODE, YT>(with_prefetch(4), grid_for(4), false, s);
-  return gb_launch<FMT, NB, 8, MODE, YT>(with_prefetch(8), grid_for(8), false, s);
+  if (rb >= want || a.K < 1024) return gb_launch<FMT, NB, 1, MODE, YT>(a, grid_for(1), false, s);
+  if (rb * 2 >= want || a.K < 2048) return gb_launch<FMT, NB, 2, MODE, YT>(a, grid_for(2), false, s);
+  if (rb * 4 >= want || a.K < 4096) return gb_launch<FMT, NB, 4, MODE, YT>(a, grid_for(4), false, s);
+  return gb_launch<FMT, NB, 8, MODE, YT>(a, grid_for(8), false, s);
 }
 
 int launch_qlinear_batch(const uint8_t* codes, const __half* scales, int fmt, int64_t N, int64_t K, const void* x,

@@ -86,31 +86,6 @@ __device__ __forceinline__ void q4_word_to_h2(uint32_t v, uint32_t* o) {
   o[3] = *reinterpret_cast<uint32_t*>(&h3);
 }
 
-// Ask L2 for the 16-row block `rb` of a weight (codes of steps [s_begin, s_end) and the rows' scales) ahead of its use:
-// cp.async.bulk.prefetch.L2 takes no registers and no shared memory, so a warp has a whole block in flight where the
-// register-direct loads of the main loop reach two to four steps; those loads then hit L2.  Lanes 0..15 take one row
-// each when the warp streams a K range of the rows, lanes 0..3 a quarter of the (contiguous) block when it streams
-// whole rows.  Weights are constants of the model, so this may run before griddepcontrol.wait.
-__device__ __forceinline__ void wq_prefetch_block(bool whole_rows, const uint8_t* codes, const __half* scales, int64_t rb, int64_t N,
-                                                  int64_t row_bytes, int64_t groups, int64_t s_begin, int64_t s_end,
-                                                  bool with_scales, int lane) {
-  const int64_t r_first = rb * 16;
-  if (r_first >= N) return;
-  const int64_t nrows = N - r_first < 16 ? N - r_first : 16;
-  if (whole_rows) {
-    if (lane < 4) {
-      const int64_t r_lo = lane * 4, r_hi = r_lo + 4 < nrows ? r_lo + 4 : nrows;
-      if (r_lo < r_hi) l2_prefetch_bulk(codes + (r_first + r_lo) * row_bytes, (uint32_t)((r_hi - r_lo) * row_bytes));
-    }
-  } else if (lane < nrows && s_end > s_begin) {
-    l2_prefetch_bulk(codes + (r_first + lane) * row_bytes + s_begin * 64, (uint32_t)((s_end - s_begin) * 64));
-  }
-  if (with_scales && lane == 16) {
-    const uint32_t bytes = (uint32_t)(nrows * groups * 2) & ~15u;        // the block starts on a 16-byte boundary (16 rows x K/16 bytes)
-    if (bytes) l2_prefetch_bulk(scales + r_first * groups, bytes);
-  }
-}
-
 // FMT        weight format
 // NV         fp16 activation vectors held in shared memory (bf16: one per row; fp32: two per row)
 // KSPLIT     warps that split K for one 16-row block (1, 2, 4 or 8); GM_WARPS/KSPLIT row blocks per CTA
@@ -154,20 +129,6 @@ qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ s
   // still runs, so wait before touching x / y.  It never triggers its own successor early: a successor whose CTAs
   // become resident while this grid streams takes registers and shared memory away from it, and measured (256000-row
   // head, q4: 58 against 63 us) that costs more than the launch latency it hides.
-  const int64_t row_bytes = Q8 ? K : K / 2;
-  const int64_t groups = K / GROUP;
-  const int rb_in_cta = warp / KSPLIT;
-  const int ksp = warp % KSPLIT;
-  const int64_t steps_total = K / KSTEP;
-  const int64_t cs_begin = steps_total * cy / kc, cs_end = steps_total * (cy + 1) / kc;   // this CTA's steps
-  const int64_t s_begin = cs_begin + (cs_end - cs_begin) * ksp / KSPLIT;
-  const int64_t s_end = cs_begin + (cs_end - cs_begin) * (ksp + 1) / KSPLIT;
-  // L2 prefetch one block ahead per warp, unless the blocks of all resident warps together would crowd L2 (the large
-  // matrices that reach this limit stream at 0.8-0.9 of the HBM rate without it)
-  const bool pf = (int64_t)gridDim.x * RB_PER_CTA * 16 * row_bytes <= (48ll << 20);
-  const bool pf_whole = KSPLIT == 1 && kc == 1;
-  if (pf) wq_prefetch_block(pf_whole, codes, scales, (int64_t)blockIdx.x * RB_PER_CTA + rb_in_cta, N, row_bytes, groups, s_begin, s_end,
-                            ksp == 0 && cy == 0, lane);
   pdl_wait();
   // PUSH: the receive-slot addresses of this call, one per rank, parked behind the reduction buffers
   float** push_dst = reinterpret_cast<float**>(cred + GM_WARPS * 16 * NV);
@@ -250,6 +211,15 @@ qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ s
     __syncthreads();
   }
 
+  const int64_t row_bytes = Q8 ? K : K / 2;
+  const int64_t groups = K / GROUP;
+  const int rb_in_cta = warp / KSPLIT;
+  const int ksp = warp % KSPLIT;
+  const int64_t steps_total = K / KSTEP;
+  const int64_t cs_begin = steps_total * cy / kc, cs_end = steps_total * (cy + 1) / kc;   // this CTA's steps
+  const int64_t s_begin = cs_begin + (cs_end - cs_begin) * ksp / KSPLIT;
+  const int64_t s_end = cs_begin + (cs_end - cs_begin) * (ksp + 1) / KSPLIT;
+
   // which activation vector / group-column this lane feeds into B: column n = g.
   //   Q8: column n = 2*v + h, h = group half (0/1); this lane's k-slots are in half (t >> 1)
   //   Q4: column n = 4*v + q, q = group (0..3);     this lane's k-slots are in group t
@@ -261,8 +231,6 @@ qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ s
   for (int64_t rb_base = (int64_t)blockIdx.x * RB_PER_CTA; rb_base * 16 < N; rb_base += (int64_t)gridDim.x * RB_PER_CTA) {
     const int64_t rb = rb_base + rb_in_cta;
     const bool active = rb * 16 < N;            // warp-uniform; inactive warps only keep the barriers company
-    if (pf) wq_prefetch_block(pf_whole, codes, scales, rb + (int64_t)gridDim.x * RB_PER_CTA, N, row_bytes, groups, s_begin, s_end,
-                              ksp == 0 && cy == 0, lane);
     int64_t r0 = rb * 16 + g, r1 = r0 + 8;
     if (r0 >= N) r0 = N - 1;
     if (r1 >= N) r1 = N - 1;

@@ -259,18 +259,7 @@ decode_attention_kernel(const T* __restrict__ q, const float* __restrict__ qkv, 
   const int64_t row_stride = (int64_t)Hkv * D;
   const T* kbase = k_cache + ((int64_t)b * S * Hkv + kv) * D + d0;
   const T* vbase = v_cache + ((int64_t)b * S * Hkv + kv) * D + d0;
-  // rows of the trips ATT_PF rounds ahead are requested from L2 (no registers): lane j asks for K row j, lane ATT_PB + j
-  // for V row j of that trip, so the register loads below mostly find their rows in L2
-  auto prefetch_trip = [&](int64_t s0) {
-    const int64_t sidx = s0 + (lane % ATT_PB);
-    if (lane < 2 * ATT_PB && sidx < n_pos)
-      l2_prefetch_bulk((lane < ATT_PB ? k_cache : v_cache) + ((int64_t)b * S * Hkv + kv) * D + sidx * row_stride,
-                       (uint32_t)(D * sizeof(T)));
-  };
-#pragma unroll
-  for (int j = 1; j <= ATT_PF; ++j) prefetch_trip(p_lo + (int64_t)warp * ATT_PB + (int64_t)j * ATT_WARPS * ATT_PB);
   for (int64_t s0 = p_lo + (int64_t)warp * ATT_PB; s0 < n_pos; s0 += ATT_WARPS * ATT_PB) {
-    prefetch_trip(s0 + (int64_t)(ATT_PF + 1) * ATT_WARPS * ATT_PB);
     // all K and V rows of the trip are requested before anything is computed
     RawRow<T> kr[ATT_PB], vr[ATT_PB];
     float dot[ATT_PB];

@@ -33,17 +33,16 @@
 namespace bq {
 
 constexpr int TC_ROWS = 128;        // weight rows per tile (UMMA M)
-// 16 converter warps: four per tensor-memory lane quarter, each converting 32 k of its 32 rows per step.  With 8 (64 k
-// per thread) a step took ~3000 cycles at every batch size although no unit was busy: a converter warp issues one
-// instruction per ~5 cycles (dependent PRMT / HSUB2 / HMUL2 chains), and two warps per scheduler cannot hide that.
-constexpr int TC_CONV_THREADS = 512;
-constexpr int TC_THREADS = 64 + TC_CONV_THREADS;
+// Converter warps: 4 * KQ per CTA, KQ per tensor-memory lane quarter, each converting 128 / KQ k of its 32 rows per step.
+// Tiles of 128 batch rows and more use KQ = 4 (16 warps): with 8 warps a step took ~3000 cycles although no unit was
+// busy, because a converter warp issues one instruction per ~5 cycles (dependent PRMT / HSUB2 / HMUL2 chains) and two
+// warps per scheduler cannot hide that.  Smaller tiles (two CTAs per SM, little to convert per MMA) keep KQ = 2:
+// measured, 16 warps made M = 64 slower.
+__host__ __device__ constexpr int tc_kq(int bn) { return bn >= 128 ? 4 : 2; }
+__host__ __device__ constexpr int tc_threads(int kq) { return 64 + 128 * kq; }
 constexpr int TC_SC_SLOTS = 3;      // scale tiles in flight (each covers 2 k-steps)
 constexpr size_t TC_PART_BYTES = (size_t)64 << 20;   // split-K partial tiles never exceed this
 constexpr uint64_t TC_WAIT_NS = 2000000000ull;   // every device-side wait gives up after 2 s
-constexpr int TC_CONV_WARPS = TC_CONV_THREADS / 32;
-constexpr int TC_KQ = TC_CONV_WARPS / 4;            // converter warps that share a row block: k slices of a 128-k step
-constexpr int TC_CPT = 64 / TC_KQ;                  // tensor-memory columns (2 fp16 each) a thread writes per step
 
 // ---- PTX wrappers -----------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -184,15 +183,15 @@ __device__ __forceinline__ uint4 cvt_q4_word(const uint32_t v, const __half2 s2)
                     *reinterpret_cast<uint32_t*>(&h45), *reinterpret_cast<uint32_t*>(&h67));
 }
 
-// One converter thread's share of a 128-k step of its weight row: TC_CPT * 2 codes -> code * scale as fp16 pairs.
+// One converter thread's share of a 128-k step of its weight row: 128 / KQ codes -> code * scale as fp16 pairs.
 // `raw` = the row's packed codes of the step in the (swizzled) stage, `scw` = its 4 scales of the step.
-template <int FMT>
+template <int FMT, int KQ>
 __device__ __forceinline__ void convert_row_slice(const uint8_t* raw, const __half* scw, int row, int kq, uint32_t* regs) {
   if (FMT == BQ_FMT_Q8G32) {
     // 16 codes per 16-byte chunk; chunk c of the row sits at 16-byte slot c ^ (row & 7)
 #pragma unroll
-    for (int i = 0; i < 8 / TC_KQ; ++i) {
-      const int c = (8 / TC_KQ) * kq + i;
+    for (int i = 0; i < 8 / KQ; ++i) {
+      const int c = (8 / KQ) * kq + i;
       const uint4 wv = *reinterpret_cast<const uint4*>(raw + ((c ^ (row & 7)) << 4));
       uint4 lo, hi;
       cvt_q8_chunk(wv, __half2half2(scw[c >> 1]), lo, hi);
@@ -202,8 +201,8 @@ __device__ __forceinline__ void convert_row_slice(const uint8_t* raw, const __ha
   } else {
     // 32 codes (one group) per 16-byte chunk; chunk c sits at 16-byte slot c ^ ((row >> 1) & 3)
 #pragma unroll
-    for (int i = 0; i < 4 / TC_KQ; ++i) {
-      const int c = (4 / TC_KQ) * kq + i;
+    for (int i = 0; i < 4 / KQ; ++i) {
+      const int c = (4 / KQ) * kq + i;
       const uint4 wv = *reinterpret_cast<const uint4*>(raw + ((c ^ ((row >> 1) & 3)) << 4));
       const __half2 s2 = __half2half2(scw[c]);
       const uint4 q0 = cvt_q4_word(wv.x, s2), q1 = cvt_q4_word(wv.y, s2), q2 = cvt_q4_word(wv.z, s2),
@@ -302,16 +301,17 @@ __device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t* v) {
         "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
       : "memory");
 }
-// one converter thread's TC_CPT columns of a step
-__device__ __forceinline__ void tc_st_cols(uint32_t taddr, const uint32_t* v) {
-  if (TC_CPT == 32) tc_st32(taddr, v); else tc_st16(taddr, v);
+// one converter thread's CPT (32 or 16) columns of a step
+template <int CPT> __device__ __forceinline__ void tc_st_cols(uint32_t taddr, const uint32_t* v) {
+  if (CPT == 32) tc_st32(taddr, v); else tc_st16(taddr, v);
 }
 __device__ __forceinline__ void tc_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 template <int FMT, int BN, int MODE>
-__global__ void __launch_bounds__(TC_THREADS, (T2Plan<FMT, BN, MODE>::TMEM_COLS == 256 ? 2 : 1)) qgemm_tmem_kernel(const __grid_constant__ T2Args args) {
+__global__ void __launch_bounds__(tc_threads(tc_kq(BN)), (T2Plan<FMT, BN, MODE>::TMEM_COLS == 256 ? 2 : 1)) qgemm_tmem_kernel(const __grid_constant__ T2Args args) {
   using P = T2Plan<FMT, BN, MODE>;
   constexpr int S = P::S, NA = 2, NW = P::NW;
+  constexpr int KQ = tc_kq(BN), CONV_WARPS = 4 * KQ, CPT = 64 / KQ;
   constexpr bool GATED = MODE == 1, DUAL = MODE == 2;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -345,8 +345,8 @@ __global__ void __launch_bounds__(TC_THREADS, (T2Plan<FMT, BN, MODE>::TMEM_COLS 
   const int ksteps = args.kper ? (ksteps_all - k0 < args.kper ? ksteps_all - k0 : args.kper) : ksteps_all;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < S; ++i) { mbar_init(smem_u32(&full[i]), 1); mbar_init(smem_u32(&empty[i]), TC_CONV_WARPS + 1); }
-    for (int i = 0; i < NA; ++i) { mbar_init(smem_u32(&a_full[i]), TC_CONV_WARPS); mbar_init(smem_u32(&a_empty[i]), 1); }
+    for (int i = 0; i < S; ++i) { mbar_init(smem_u32(&full[i]), 1); mbar_init(smem_u32(&empty[i]), CONV_WARPS + 1); }
+    for (int i = 0; i < NA; ++i) { mbar_init(smem_u32(&a_full[i]), CONV_WARPS); mbar_init(smem_u32(&a_empty[i]), 1); }
     mbar_init(smem_u32(acc_full), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -435,9 +435,9 @@ __global__ void __launch_bounds__(TC_THREADS, (T2Plan<FMT, BN, MODE>::TMEM_COLS 
       for (int w = 0; w < NW; ++w) {
       const uint8_t* raw = stages + s * P::STAGE + P::XT + w * P::RAW + row * P::RAW_ROW;
       const __half* scw = reinterpret_cast<const __half*>(sc_tiles + (((ks >> 1) % TC_SC_SLOTS) * NW + w) * P::SCT) + row * 8 + (ks & 1) * 4;
-      uint32_t regs[TC_CPT];
-      convert_row_slice<FMT>(raw, scw, row, kq, regs);
-      tc_st_cols(tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)(P::ACOL0 + (w * NA + a) * T2_ACOLS + TC_CPT * kq), regs);
+      uint32_t regs[CPT];
+      convert_row_slice<FMT, KQ>(raw, scw, row, kq, regs);
+      tc_st_cols<CPT>(tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)(P::ACOL0 + (w * NA + a) * T2_ACOLS + CPT * kq), regs);
       }
       tc_st_wait();
       tc_fence_before();
@@ -453,7 +453,7 @@ __global__ void __launch_bounds__(TC_THREADS, (T2Plan<FMT, BN, MODE>::TMEM_COLS 
       const int64_t n = n0 + row;
       const uint32_t tbase = tmem_base + ((uint32_t)(lg * 32) << 16);
 #pragma unroll 1
-      for (int c0 = 16 * kq; c0 < BN; c0 += 16 * TC_KQ) {
+      for (int c0 = 16 * kq; c0 < BN; c0 += 16 * KQ) {
         if (m0 + c0 >= m_end) break;
         if (GATED) {                               // h = silu(gate) * up, rounded to bf16
           uint32_t v[16], u[16];
@@ -611,9 +611,10 @@ __host__ __device__ constexpr uint32_t umma_idesc_pair() {
 }
 
 template <int FMT>
-__global__ void __launch_bounds__(TC_THREADS, 1) qgemm_pair_kernel(const __grid_constant__ T2Args args) {
+__global__ void __launch_bounds__(tc_threads(4), 1) qgemm_pair_kernel(const __grid_constant__ T2Args args) {
   using P = PairPlan<FMT>;
   constexpr int S = P::S, NA = P::NA;
+  constexpr int KQ = 4, CONV_WARPS = 4 * KQ, CPT = 64 / KQ;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* stages = smem;                                  // per stage: [x atom 0][x atom 1][codes tile]
@@ -636,8 +637,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_pair_kernel(const __grid_
   const int ksteps = (int)(args.K / T2_BK);
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < S; ++i) { mbar_init(smem_u32(&full[i]), 1); mbar_init(smem_u32(&empty[i]), TC_CONV_WARPS + 1); }
-    for (int i = 0; i < NA; ++i) { mbar_init(smem_u32(&a_full[i]), 2 * TC_CONV_WARPS); mbar_init(smem_u32(&a_empty[i]), 1); }
+    for (int i = 0; i < S; ++i) { mbar_init(smem_u32(&full[i]), 1); mbar_init(smem_u32(&empty[i]), CONV_WARPS + 1); }
+    for (int i = 0; i < NA; ++i) { mbar_init(smem_u32(&a_full[i]), 2 * CONV_WARPS); mbar_init(smem_u32(&a_empty[i]), 1); }
     mbar_init(smem_u32(acc_full), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -726,9 +727,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_pair_kernel(const __grid_
       if (!ok) break;
       const uint8_t* raw = stages + s * P::STAGE + P::XT + row * P::RAW_ROW;
       const __half* scw = reinterpret_cast<const __half*>(sc_tiles + ((ks >> 1) % TC_SC_SLOTS) * P::SCT) + row * 8 + (ks & 1) * 4;
-      uint32_t regs[TC_CPT];
-      convert_row_slice<FMT>(raw, scw, row, kq, regs);
-      tc_st_cols(tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)(P::ACOL0 + a * T2_ACOLS + TC_CPT * kq), regs);
+      uint32_t regs[CPT];
+      convert_row_slice<FMT, KQ>(raw, scw, row, kq, regs);
+      tc_st_cols<CPT>(tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)(P::ACOL0 + a * T2_ACOLS + CPT * kq), regs);
       tc_st_wait();
       tc_fence_before();
       __syncwarp();
@@ -747,7 +748,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_pair_kernel(const __grid_
       const int64_t nn = n0 + row;
       const uint32_t tbase = tmem_base + ((uint32_t)(lg * 32) << 16);
 #pragma unroll 1
-      for (int c0 = 16 * kq; c0 < 256; c0 += 16 * TC_KQ) {
+      for (int c0 = 16 * kq; c0 < 256; c0 += 16 * KQ) {
         if (m0 + c0 >= m_end) break;
         uint32_t v[16];
         tc_ld16(tbase + (uint32_t)c0, v);
@@ -1022,7 +1023,7 @@ static int t2_launch(const T2Args& a, dim3 grid, cudaStream_t s) {
     BQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P::SMEM));
     configured = true;
   }
-  BQ_CUDA(launch_chain(kern, grid, dim3(TC_THREADS), (size_t)P::SMEM, s, 1, a));
+  BQ_CUDA(launch_chain(kern, grid, dim3(tc_threads(tc_kq(BN))), (size_t)P::SMEM, s, 1, a));
   count_launch();
   BQ_CUDA(cudaGetLastError());
   return BQ_OK;
@@ -1036,7 +1037,7 @@ static int pair_launch(const T2Args& a, dim3 grid, cudaStream_t s) {
     BQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P::SMEM));
     configured = true;
   }
-  BQ_CUDA(launch_chain(kern, grid, dim3(TC_THREADS), (size_t)P::SMEM, s, -2, a));      // clusters of 2 CTAs along grid.x
+  BQ_CUDA(launch_chain(kern, grid, dim3(tc_threads(4)), (size_t)P::SMEM, s, -2, a));      // clusters of 2 CTAs along grid.x
   count_launch();
   BQ_CUDA(cudaGetLastError());
   return BQ_OK;
