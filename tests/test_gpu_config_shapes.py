@@ -57,3 +57,30 @@ def test_decode_batches_on_the_head_shape_sampled_rows(cuda_lib, fmt):
         ref = spec.qlinear(x.float().cpu().numpy(), c_np, s_np, fmt, f64=True)
         assert spec.rel_err(y[:, rows].cpu().numpy(), ref) <= TOL, (fmt, M)
     lin.pw.close()
+
+
+@pytest.mark.parametrize("fmt", [0, 1])
+@pytest.mark.parametrize("N,K,M", [(3000, 1024, 1800), (1536, 3072, 2050), (12288, 3072, 700)])
+def test_large_batches_ragged_shapes_all_rows(cuda_lib, fmt, N, K, M):
+    """Large batches on shapes whose row and batch counts are not multiples of the tile sizes (the last weight tile, the
+    last 256-row batch tile and - for int8, which runs on pairs of CTAs here - the second CTA of the last pair are
+    partly or wholly outside the matrix): every output against the float64 oracle, plain and gated epilogue."""
+    import torch
+    import chadslab_b200 as cb
+    from chadslab_b200.synth import make_device_weight
+    g = torch.Generator(device="cuda").manual_seed(N + M + fmt)
+    codes, scales = make_device_weight(torch, N, K, fmt, g)
+    lin = cb.QuantLinear(cb.PackedWeight.from_device(codes, scales, fmt))
+    x = torch.randn((M, K), device="cuda", generator=g).to(torch.bfloat16)
+    y = lin(x)
+    assert cuda_lib.bq_last_path() == cb.PATH_TENSOR
+    ref = spec.qlinear(x.float().cpu().numpy(), codes.cpu().numpy(), scales.cpu().numpy(), fmt, f64=True)
+    assert spec.rel_err(y.cpu().numpy(), ref) <= TOL
+    if N % 16 == 0:
+        h = lin.gated(x, 1)                                                # silu(gate) * up on interleaved 8 + 8 row blocks
+        gate = ref.reshape(M, N // 16, 2, 8)[:, :, 0, :].reshape(M, N // 2)
+        up = ref.reshape(M, N // 16, 2, 8)[:, :, 1, :].reshape(M, N // 2)
+        want = gate / (1.0 + np.exp(-gate)) * up
+        assert spec.rel_err(h.float().cpu().numpy(), want) <= 2.0 ** -7
+    lin.pw.close()
+    assert cuda_lib.bq_status_poll() == 0
