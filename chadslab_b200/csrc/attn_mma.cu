@@ -8,19 +8,14 @@
 //   scores  S[head, pos] = Q[head, :] . K[pos, :]      A = Q (heads x d), B = K rows as they lie in the cache
 //   output  O[head, :]  += P[head, pos] * V[pos, :]    A = P (the score fragment, rounded to bf16), B = V
 //
-// One CTA = (batch row, KV head, up to 16 query heads, one slice of the positions); its warps (8, or 4 for head_dim 256)
-// take 16-position blocks in turn and keep their own running (max, sum, O); shared memory merges the warps, and - when positions are
+// One CTA = (batch row, KV head, up to 16 query heads, one slice of the positions); its 4 warps take 16-position
+// blocks in turn and keep their own running (max, sum, O); shared memory merges the warps, and - when positions are
 // split over CTAs - the last CTA to arrive merges the slices (same scheme as the CUDA-core kernel).
 //
-// The cache rows travel through a per-warp ring in shared memory filled with cp.async (16 bytes per lane and copy): a
-// warp requests the K and V rows of its next two 16-position blocks while it computes the current one, without holding
-// a register for them, so that 16-32 KB per warp are in flight all the time (with register-direct loads the long
-// MMA / softmax chain of a block left the memory system idle and the kernel reached 0.4 of the HBM rate).  Every lane
-// copies exactly the 16-byte pieces it later feeds into its own fragments, so no barrier is needed between the copy
-// and the read, only cp.async.wait_group:
+// Operand fragments are filled with 16-byte loads straight from the cache, no shared-memory staging:
 //   * the k index of S is a permutation of d (lane t of a quad owns d = 32 L + 8 t .. + 7 of every 32-wide chunk L and
-//     feeds two k16 steps from one piece); Q sits in shared memory under the same permutation, so the sum is the same;
-//   * for O the lane takes 8 consecutive d of cache rows 2t, 2t+1, 2t+8, 2t+9 of the block and pairs rows with PRMT
+//     feeds two k16 steps from one load); Q sits in shared memory under the same permutation, so the sum is the same;
+//   * for O the lane loads 8 consecutive d of cache rows 2t, 2t+1, 2t+8, 2t+9 of the block and pairs rows with PRMT
 //     (B wants two consecutive k = positions per register); n-tile j = 8 i + e of the output then holds
 //     d = 64 i + 8 n + e at column n, which is undone when the accumulators go to shared memory.
 // Softmax runs in the exp2 domain (scores scaled by log2(e) / sqrt(d)).  Heads beyond `hp` are zero rows of Q.
@@ -28,16 +23,8 @@
 
 namespace bq {
 
-constexpr int AM_STAGES = 3;                // ring slots per warp: one being computed, two in flight
-__host__ __device__ constexpr int am_warps(int d) { return d > 128 ? 4 : 8; }
-__host__ __device__ constexpr int am_ring_bytes(int d) { return am_warps(d) * AM_STAGES * 64 * d; }
-
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+constexpr int AM_WARPS = 4;
+constexpr int AM_THREADS = AM_WARPS * 32;
 
 // d[0..1] (+ d[2..3] when HI) += A x B; without HI the rows 8..15 of A are zero and their sums are dropped
 template <bool HI>
@@ -60,7 +47,7 @@ __device__ __forceinline__ uint32_t am_pack(float lo, float hi) {
 }
 
 template <bool FUSED, int D, bool HI>
-__global__ void __launch_bounds__(am_warps(D) * 32, 1)
+__global__ void __launch_bounds__(AM_THREADS, (D > 128 ? 2 : 3))
 decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __restrict__ qkv, __nv_bfloat16* k_cache,
                             __nv_bfloat16* v_cache, const int64_t* __restrict__ pos_p, __nv_bfloat16* __restrict__ out, int Hq,
                             int Hkv, int64_t S, float rope_base, float* __restrict__ part, unsigned* __restrict__ counters,
@@ -69,15 +56,10 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __
   constexpr int NC = HI ? 4 : 2;             // accumulator registers per n-tile
   constexpr int QSTR = D + 32;               // q row pitch in shared memory (64 bytes of padding: conflict-free 16-byte reads)
   constexpr int NT = D / 8;
-  constexpr int AM_WARPS = am_warps(D), AM_THREADS = AM_WARPS * 32;
-  constexpr int NL = D / 8;                  // 16-byte pieces per lane and block: D/16 of K, then D/16 of V
-  constexpr int SB = NL * 512;               // bytes of one ring slot
-  extern __shared__ __align__(16) uint8_t am_ring[];         // [AM_WARPS][AM_STAGES][NL][32 lanes][16 bytes]
   __shared__ __align__(16) __nv_bfloat16 qs[ROWS * QSTR];
   __shared__ float s_cos[D / 2], s_sin[D / 2];
   __shared__ float s_mx[AM_WARPS][ROWS], s_sum[AM_WARPS][ROWS];
-  float (*s_acc)[ROWS][D] = reinterpret_cast<float (*)[ROWS][D]>(am_ring);   // the warps' results reuse the ring
-  static_assert(sizeof(float) * AM_WARPS * ROWS * D <= (size_t)am_ring_bytes(D), "merge area must fit in the ring");
+  __shared__ float s_acc[AM_WARPS][ROWS][D];
 
   const int rep = Hq / Hkv, gpk = rep / hp;
   const int b = blockIdx.y, kv = blockIdx.x / gpk, hg = blockIdx.x % gpk;
@@ -121,7 +103,6 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __
         kd[d] = __float2bfloat16_rn(rope_elem<__nv_bfloat16>(ksrc, d, D, s_cos, s_sin, true));
         vd[d] = __float2bfloat16_rn(rope_elem<__nv_bfloat16>(vsrc, d, D, s_cos, s_sin, false));
       }
-      __threadfence();
     }
   } else {
     for (int e = threadIdx.x; e < ROWS * (D / 8); e += AM_THREADS) {
@@ -144,41 +125,32 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __
   const __nv_bfloat16* kb = k_cache + ((int64_t)b * S * Hkv + kv) * D + 8 * t;
   const __nv_bfloat16* vb = v_cache + ((int64_t)b * S * Hkv + kv) * D + 8 * g;
 
-  const uint32_t ring = smem_addr(am_ring) + (uint32_t)(warp * AM_STAGES * SB) + (uint32_t)(lane * 16);
-  const uint8_t* ring_g = am_ring + warp * AM_STAGES * SB + lane * 16;
-  const int64_t p_first = p_lo + (int64_t)warp * 16;
-  const int nblk = p_first < n_pos ? (int)((n_pos - p_first + AM_WARPS * 16 - 1) / (AM_WARPS * 16)) : 0;
-  // block j of this warp -> ring slot j % AM_STAGES; one commit group per block (empty past the end, so that the group
-  // count a wait refers to is the same for every block)
-  auto issue = [&](int j) {
-    if (j < nblk) {
-      const int64_t p0 = p_first + (int64_t)j * AM_WARPS * 16;
-      const uint32_t slot = ring + (uint32_t)((j % AM_STAGES) * SB);
+  // Software pipeline without extra registers: the K rows of the next block are requested as soon as the scores of this
+  // one are done (their registers are free then), the V rows of the next block as soon as this block's P V is done, so
+  // one of the two is always in flight while the warp computes.
+  uint4 kr[2][D / 32], vr[4][D / 64];
+  auto load_k = [&](int64_t p0) {
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt) {
-        int64_t row = p0 + 8 * nt + g;
-        if (row >= n_pos) row = n_pos - 1;                // masked below; a row that exists is read instead
+    for (int nt = 0; nt < 2; ++nt) {
+      int64_t row = p0 + 8 * nt + g;
+      if (row >= n_pos) row = n_pos - 1;                  // masked below; a row that exists is read instead
 #pragma unroll
-        for (int L = 0; L < D / 32; ++L) cp_async16(slot + (uint32_t)((nt * (D / 32) + L) * 512), kb + row * row_stride + 32 * L);
-      }
-#pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        int64_t row = p0 + 2 * t + (r & 1) + 8 * (r >> 1);
-        if (row >= n_pos) row = n_pos - 1;
-#pragma unroll
-        for (int i = 0; i < D / 64; ++i)
-          cp_async16(slot + (uint32_t)((D / 16 + r * (D / 64) + i) * 512), vb + row * row_stride + 64 * i);
-      }
+      for (int L = 0; L < D / 32; ++L) kr[nt][L] = *reinterpret_cast<const uint4*>(kb + row * row_stride + 32 * L);
     }
-    cp_async_commit();
   };
-  issue(0);
-  issue(1);
-  for (int blk = 0; blk < nblk; ++blk) {
-    const int64_t p0 = p_first + (int64_t)blk * AM_WARPS * 16;
-    issue(blk + 2);
-    cp_async_wait<2>();                                   // this block's copies (two younger groups may be pending)
-    const uint8_t* slot = ring_g + (blk % AM_STAGES) * SB;
+  auto load_v = [&](int64_t p0) {
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      int64_t row = p0 + 2 * t + (r & 1) + 8 * (r >> 1);
+      if (row >= n_pos) row = n_pos - 1;
+#pragma unroll
+      for (int i = 0; i < D / 64; ++i) vr[r][i] = *reinterpret_cast<const uint4*>(vb + row * row_stride + 64 * i);
+    }
+  };
+  const int64_t p_first = p_lo + (int64_t)warp * 16;
+  if (p_first < n_pos) { load_k(p_first); load_v(p_first); }
+  for (int64_t p0 = p_first; p0 < n_pos; p0 += AM_WARPS * 16) {
+    const int64_t p_next = p0 + AM_WARPS * 16;
     // ---- scores of 16 positions x the CTA's heads -------------------------------------------------------------
     float sc[2][NC];
 #pragma unroll
@@ -192,11 +164,11 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __
       if (HI) qb = *reinterpret_cast<const uint4*>(&qs[(g + 8) * QSTR + 32 * L + 8 * t]);
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
-        const uint4 kf = *reinterpret_cast<const uint4*>(slot + (nt * (D / 32) + L) * 512);
-        am_mma<HI>(sc[nt], qa.x, qb.x, qa.y, qb.y, kf.x, kf.y);
-        am_mma<HI>(sc[nt], qa.z, qb.z, qa.w, qb.w, kf.z, kf.w);
+        am_mma<HI>(sc[nt], qa.x, qb.x, qa.y, qb.y, kr[nt][L].x, kr[nt][L].y);
+        am_mma<HI>(sc[nt], qa.z, qb.z, qa.w, qb.w, kr[nt][L].z, kr[nt][L].w);
       }
     }
+    if (p_next < n_pos) load_k(p_next);
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
@@ -223,25 +195,20 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const float* __
     }
     // ---- O += P V ----------------------------------------------------------------------------------------------------
 #pragma unroll
-    for (int i = 0; i < D / 64; ++i) {
-      uint4 vf[4];
-#pragma unroll
-      for (int r = 0; r < 4; ++r) vf[r] = *reinterpret_cast<const uint4*>(slot + (D / 16 + r * (D / 64) + i) * 512);
+    for (int i = 0; i < D / 64; ++i)
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         const int j = 8 * i + e;
         const uint32_t sel = (e & 1) ? 0x7632u : 0x5410u;
-        const uint32_t b0 = __byte_perm(am_word(vf[0], e >> 1), am_word(vf[1], e >> 1), sel);
-        const uint32_t b1 = __byte_perm(am_word(vf[2], e >> 1), am_word(vf[3], e >> 1), sel);
+        const uint32_t b0 = __byte_perm(am_word(vr[0][i], e >> 1), am_word(vr[1][i], e >> 1), sel);
+        const uint32_t b1 = __byte_perm(am_word(vr[2][i], e >> 1), am_word(vr[3][i], e >> 1), sel);
         acc[j][0] *= corr[0];
         acc[j][1] *= corr[0];
         if (HI) { acc[j][2] *= corr[1]; acc[j][3] *= corr[1]; }
         am_mma<HI>(acc[j], pa[0], pa[1], pa[2], pa[3], b0, b1);
       }
-    }
+    if (p_next < n_pos) load_v(p_next);
   }
-  cp_async_wait<0>();
-  __syncthreads();                                        // every warp is done with its ring: the merge area reuses it
 
   // ---- merge the warps (per head), then the position slices -------------------------------------------------------------
 #pragma unroll
@@ -348,33 +315,16 @@ bool attention_mma_supported(int Hq, int Hkv, int D, int* hp_out) {
   return true;
 }
 
-template <bool FUSED, int D, bool HI>
-static int am_launch(dim3 grid, cudaStream_t s, const void* q, const float* qkv, void* k_cache, void* v_cache, const int64_t* pos,
-                     void* out, int Hq, int Hkv, int64_t S, float rope_base, float* part, unsigned* counters, int hp) {
-  auto kern = decode_attention_mma_kernel<FUSED, D, HI>;
-  static bool configured = false;
-  if (!configured) {
-    BQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, am_ring_bytes(D)));
-    configured = true;
-  }
-  BQ_CUDA(launch_chain(kern, grid, dim3(am_warps(D) * 32), (size_t)am_ring_bytes(D), s, 1, (const __nv_bfloat16*)q, qkv,
-                       (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, pos, (__nv_bfloat16*)out, Hq, Hkv, S, rope_base, part,
-                       counters, status_word(), hp));
-  return BQ_OK;
-}
-
-// positions per slice the kernel wants at least: two 16-position blocks per warp
-int attention_mma_min_positions(int D) { return am_warps(D) * 32; }
-
 int launch_attention_mma(const void* q, const float* qkv, void* k_cache, void* v_cache, const int64_t* pos, void* out, int64_t B,
                          int Hq, int Hkv, int D, int64_t S, float rope_base, int hp, int nsplit, float* part, unsigned* counters,
                          cudaStream_t s) {
   const int gpk = (Hq / Hkv) / hp;
   dim3 grid((unsigned)(Hkv * gpk), (unsigned)B, (unsigned)nsplit);
   const bool hi = hp > 8;
-  int rc;
-#define BQ_AM_LAUNCH(FUSED, DD, HI) \
-  rc = am_launch<FUSED, DD, HI>(grid, s, q, qkv, k_cache, v_cache, pos, out, Hq, Hkv, S, rope_base, part, counters, hp)
+#define BQ_AM_LAUNCH(FUSED, DD, HI)                                                                                        \
+  BQ_CUDA(launch_chain(decode_attention_mma_kernel<FUSED, DD, HI>, grid, dim3(AM_THREADS), 0, s, 1, (const __nv_bfloat16*)q, qkv, \
+                       (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, pos, (__nv_bfloat16*)out, Hq, Hkv, S, rope_base, part,    \
+                       counters, status_word(), hp))
 #define BQ_AM_PICK(FUSED)                                                          \
   do {                                                                             \
     if (D == 64) { if (hi) BQ_AM_LAUNCH(FUSED, 64, true); else BQ_AM_LAUNCH(FUSED, 64, false); }        \
@@ -384,7 +334,6 @@ int launch_attention_mma(const void* q, const float* qkv, void* k_cache, void* v
   if (qkv) BQ_AM_PICK(true); else BQ_AM_PICK(false);
 #undef BQ_AM_PICK
 #undef BQ_AM_LAUNCH
-  if (rc) return rc;
   count_launch();
   BQ_CUDA(cudaGetLastError());
   return BQ_OK;

@@ -659,11 +659,10 @@ static int launch_attention(const void* q, const float* qkv, void* k_cache, void
                      reinterpret_cast<uintptr_t>(out)) & 15) == 0;
   const int64_t ctas_xy = mma ? B * Hkv * (rep / hp) : gqa ? B * Hkv * (rep / hpw) : B * Hq;
   // few CTAs and a long cache: split the positions so that several CTAs per SM stream K/V
-  // (the tensor-path kernel runs one CTA per SM: two waves of it are enough)
-  int64_t nsplit = ((mma ? 2 : 4) * (int64_t)sm_count() + ctas_xy - 1) / ctas_xy;
-  // at least 128 cache positions per split (measured: finer is slower); the tensor-path kernel wants two 16-position
-  // blocks per warp
-  const int64_t min_pos = mma ? attention_mma_min_positions(D) : 128, max_split = mma ? 64 : 32;
+  int64_t nsplit = (4 * (int64_t)sm_count() + ctas_xy - 1) / ctas_xy;
+  // at least 128 cache positions per split (measured: finer is slower); the tensor-path kernel has half the warps per
+  // CTA and takes 64 (one 16-position block per warp)
+  const int64_t min_pos = mma ? 64 : 128, max_split = mma ? 64 : 32;
   if (nsplit > S / min_pos) nsplit = S / min_pos;
   if (nsplit > max_split) nsplit = max_split;
   if (nsplit < 1) nsplit = 1;

@@ -1122,12 +1122,14 @@ int launch_qlinear_tc(const uint8_t* codes, const __half* scales, int fmt, int64
   const int rows_cta = two ? 2 * TC_ROWS : TC_ROWS;
   dim3 grid2((unsigned)((M + bx - 1) / bx), (unsigned)((N + rows_cta - 1) / rows_cta));
   const int sel = two ? 512 : bn;
-  // Few output tiles and a long K (e.g. 2048 x 16384, or a down projection at decode batch sizes): split K over
-  // grid.z so that about two CTAs per SM stream weights, each with at least 4 steps; partial tiles are summed in order.
+  // Fewer output tiles than half the resident CTAs and a long K (e.g. 2048 x 16384, a down projection at decode batch
+  // sizes, or any projection of a tensor-parallel shard): split K over grid.z into one wave of slices, each with at
+  // least 4 steps; partial tiles are summed in order.
   const int64_t ctas = (int64_t)grid2.x * grid2.y, ksteps_all = K / T2_BK;
   int nz = 1;
-  if (!two && ctas * 2 <= sm_count() && ksteps_all >= 8) {
-    int64_t want = (2 * (int64_t)sm_count() + ctas - 1) / ctas;
+  const int64_t slots = (int64_t)sm_count() * (bn <= 64 ? 2 : 1);       // CTAs of this tile size that are resident at once
+  if (!two && slots / ctas >= 2 && ksteps_all >= 8) {
+    int64_t want = slots / ctas;                                       // one wave of slices
     if (want > ksteps_all / 4) want = ksteps_all / 4;
     while (want > 1 && (size_t)want * M * N * sizeof(float) > TC_PART_BYTES) --want;
     if (want > 1) {
