@@ -315,6 +315,29 @@ bool attention_mma_supported(int Hq, int Hkv, int D, int* hp_out) {
   return true;
 }
 
+// CTAs of the kernel instance that are resident on an SM (registers decide), asked once per instance
+int attention_mma_ctas_per_sm(bool fused, int D, bool hi) {
+  static int cache[2][3][2] = {};
+  const int di = D == 64 ? 0 : D == 128 ? 1 : 2;
+  int& c = cache[fused ? 1 : 0][di][hi ? 1 : 0];
+  if (c == 0) {
+    int n = 0;
+    cudaError_t e = cudaErrorInvalidValue;
+#define BQ_AM_OCC(FUSED, DD, HI) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, decode_attention_mma_kernel<FUSED, DD, HI>, AM_THREADS, 0)
+#define BQ_AM_OCC_PICK(FUSED)                                                                    \
+  do {                                                                                           \
+    if (D == 64) { if (hi) BQ_AM_OCC(FUSED, 64, true); else BQ_AM_OCC(FUSED, 64, false); }        \
+    else if (D == 128) { if (hi) BQ_AM_OCC(FUSED, 128, true); else BQ_AM_OCC(FUSED, 128, false); } \
+    else BQ_AM_OCC(FUSED, 256, false);                                                           \
+  } while (0)
+    if (fused) BQ_AM_OCC_PICK(true); else BQ_AM_OCC_PICK(false);
+#undef BQ_AM_OCC_PICK
+#undef BQ_AM_OCC
+    c = (e == cudaSuccess && n >= 1) ? n : 1;
+  }
+  return c;
+}
+
 int launch_attention_mma(const void* q, const float* qkv, void* k_cache, void* v_cache, const int64_t* pos, void* out, int64_t B,
                          int Hq, int Hkv, int D, int64_t S, float rope_base, int hp, int nsplit, float* part, unsigned* counters,
                          cudaStream_t s) {

@@ -147,6 +147,7 @@ int launch_device_encode(uint8_t* codes, size_t bytes, int fmt, bool to_device_l
 int launch_argmax(const void* logits, int dtype, int64_t M, int64_t N, int32_t* out, cudaStream_t s, float* vout = nullptr);
 // grouped-query decode attention on mma.sync (bf16 caches, head_dim 64 / 128 / 256): hp = query heads per CTA
 bool attention_mma_supported(int Hq, int Hkv, int D, int* hp_out);
+int attention_mma_ctas_per_sm(bool fused, int D, bool hi);
 int launch_attention_mma(const void* q, const float* qkv, void* k_cache, void* v_cache, const int64_t* pos, void* out, int64_t B,
                          int Hq, int Hkv, int D, int64_t S, float rope_base, int hp, int nsplit, float* part, unsigned* counters,
                          cudaStream_t s);

@@ -666,6 +666,19 @@ static int launch_attention(const void* q, const float* qkv, void* k_cache, void
   if (nsplit > S / min_pos) nsplit = S / min_pos;
   if (nsplit > max_split) nsplit = max_split;
   if (nsplit < 1) nsplit = 1;
+  if (mma) {
+    // The tensor-path kernel is latency-bound, so a partly filled last wave costs a whole wave, and every CTA pays a
+    // fixed prologue + merge worth about 96 positions: take the slice count that minimises
+    // waves x (positions per slice + 96) instead of just filling the machine.
+    const int64_t slots = (int64_t)sm_count() * attention_mma_ctas_per_sm(qkv != nullptr, D, hp > 8);
+    int64_t best = 1, best_cost = -1;
+    for (int64_t ns = 1; ns <= nsplit; ++ns) {
+      const int64_t waves = (ctas_xy * ns + slots - 1) / slots;
+      const int64_t cost = waves * ((S + ns - 1) / ns + 96);
+      if (best_cost < 0 || cost < best_cost) { best = ns; best_cost = cost; }
+    }
+    nsplit = best;
+  }
   cudaStream_t s = (cudaStream_t)stream;
   if (nsplit > 1) {
     if ((rc = scratch_ensure(&g_att_part, (size_t)B * Hq * nsplit * (D + 2) * sizeof(float), s, "split-position attention")))

@@ -552,9 +552,10 @@ __global__ void __launch_bounds__(tc_threads(tc_kq(BN)), (T2Plan<FMT, BN, MODE>:
 // 48 KB per step, four stages; one thread of the leader (rank 0) issues tcgen05.mma.cta_group::2 (M = 256, N = 256):
 // A from each CTA's tensor memory, B = the two halves in the two CTAs' shared memory, D = 128 lanes x 256 columns in
 // each CTA's tensor memory.  No multicast anywhere: every CTA loads its own operands with plain TMA loads; the
-// leader learns that the peer's operands are ready through remote mbarrier arrivals of the peer's converter warps
-// (the barriers the issuer waits on live in the leader's shared memory), and tells the peer that its buffers are
-// free / its accumulator is complete with a second tcgen05.commit aimed at the peer's barrier.
+// leader learns that the peer's operands are ready through one remote mbarrier arrival per step, forwarded by a thread
+// of the peer once the peer's converter warps have arrived on a barrier of their own CTA (the barrier the issuer waits
+// on lives in the leader's shared memory), and tells the peer that its buffers are free / its accumulator is complete
+// with a second tcgen05.commit aimed at the peer's barrier.
 // Tensor memory: [0, 256) accumulator, 4 x 64 columns of A from column 256 (the converters run up to three k-steps
 // ahead of the MMAs, so that their latency - wake-up, unpack, tcgen05.st, arrive - is off the critical path); allocated
 // with cta_group::2 by warp 1 of both CTAs.
@@ -670,7 +671,12 @@ __global__ void __launch_bounds__(tc_threads(4), 1) qgemm_pair_kernel(const __gr
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S; ++i) { mbar_init(smem_u32(&full[i]), 1); mbar_init(smem_u32(&empty[i]), CONV_WARPS + 1); }
-    for (int i = 0; i < NA; ++i) { mbar_init(smem_u32(&a_full[i]), 2 * CONV_WARPS); mbar_init(smem_u32(&a_empty[i]), 1); }
+    // a_full: the leader's copy gates the MMAs (its own converter warps + one arrival forwarded from the peer); the
+    // peer's copy collects the peer's converter warps for its forwarder
+    for (int i = 0; i < NA; ++i) {
+      mbar_init(smem_u32(&a_full[i]), rank == 0 ? CONV_WARPS + 1 : CONV_WARPS);
+      mbar_init(smem_u32(&a_empty[i]), 1);
+    }
     mbar_init(smem_u32(acc_full), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -739,13 +745,26 @@ __global__ void __launch_bounds__(tc_threads(4), 1) qgemm_pair_kernel(const __gr
         tc_commit2(smem_u32(acc_full));
         tc_commit2(peer_acc);
       }
+    } else if (lane == 0) {
+      // ================= forwarder (peer only) =================
+      // The peer's converter warps arrive on a barrier of their own CTA; this thread passes each completed phase on to
+      // the leader as ONE cluster-scope arrival.  (With every converter warp arriving remotely, the release fence of
+      // a cluster-scope arrive sat in the converter loop 16 times per step: ncu showed the warps stalled on it.)
+      const uint32_t leader_a_full = pair_map(smem_u32(&a_full[0]), 0u);
+      for (int ks = 0; ks < ksteps; ++ks) {
+        const int a = ks % NA;
+        const uint32_t aph = (uint32_t)(ks / NA) & 1u;
+        if (!mbar_wait(smem_u32(&a_full[a]), aph, abort_flag)) break;
+        tc_fence_after();
+        tc_fence_before();
+        mbar_arrive_cluster(leader_a_full + (uint32_t)(a * 8));
+      }
     }
   } else {
     // ================= converters (one weight row per thread), then epilogue =================
     const int lg = warp & 3;
     const int kq = (warp - 2) >> 2;
     const int row = lg * 32 + lane;
-    const uint32_t leader_a_full = pair_map(smem_u32(&a_full[0]), 0u);
     bool ok = true;
     for (int ks = 0; ks < ksteps && ok; ++ks) {
       const int s = ks % S, a = ks % NA;
@@ -766,7 +785,7 @@ __global__ void __launch_bounds__(tc_threads(4), 1) qgemm_pair_kernel(const __gr
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive_cluster(leader_a_full + (uint32_t)(a * 8));     // the leader's issuer counts both CTAs' warps
+        mbar_arrive(smem_u32(&a_full[a]));        // own CTA's barrier: the leader's gates the MMAs, the peer's its forwarder
         mbar_arrive(smem_u32(&empty[s]));
       }
     }
