@@ -129,6 +129,50 @@ qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ s
   // still runs, so wait before touching x / y.  It never triggers its own successor early: a successor whose CTAs
   // become resident while this grid streams takes registers and shared memory away from it, and measured (256000-row
   // head, q4: 58 against 63 us) that costs more than the launch latency it hides.
+  const int64_t row_bytes = Q8 ? K : K / 2;
+  const int64_t groups = K / GROUP;
+  const int rb_in_cta = warp / KSPLIT;
+  const int ksp = warp % KSPLIT;
+  const int64_t steps_total = K / KSTEP;
+  const int64_t cs_begin = steps_total * cy / kc, cs_end = steps_total * (cy + 1) / kc;   // this CTA's steps
+  const int64_t s_begin = cs_begin + (cs_end - cs_begin) * ksp / KSPLIT;
+  const int64_t s_end = cs_begin + (cs_end - cs_begin) * (ksp + 1) / KSPLIT;
+
+  // One step of a warp's weight stream as it sits in registers: 16 bytes of codes of rows g and g + 8 and the rows' group
+  // scales of the step (Q8: 2 fp16 = one word per row; Q4: 4 fp16 = two words per row).
+  struct StepRegs { uint4 w0, w1; uint32_t sa[2], sb[2]; };
+  auto fetch = [&](const uint8_t* p0, const uint8_t* p1, const __half* sc0, const __half* sc1, int64_t st, StepRegs& r) {
+    r.w0 = ldg_stream16(p0 + st * 64);
+    r.w1 = ldg_stream16(p1 + st * 64);
+    if (Q8) {
+      r.sa[0] = *reinterpret_cast<const uint32_t*>(sc0 + st * 2);
+      r.sb[0] = *reinterpret_cast<const uint32_t*>(sc1 + st * 2);
+    } else {
+      const uint2 a = *reinterpret_cast<const uint2*>(sc0 + st * 4), b = *reinterpret_cast<const uint2*>(sc1 + st * 4);
+      r.sa[0] = a.x; r.sa[1] = a.y; r.sb[0] = b.x; r.sb[1] = b.y;
+    }
+  };
+  // 4-bit weights: the weight stream is software-pipelined one step deep (the loads and the MMAs are `asm volatile` and
+  // keep their program order, so otherwise a warp requests the codes of a step only after it has issued the MMAs of the
+  // step before), and the first step of the CTA's first row block is requested here, BEFORE griddepcontrol.wait:
+  // weights are constants of the model, so their first trip to HBM overlaps the tail of the preceding kernel and the
+  // activation staging below.  Measured: head shape 0.78 -> 0.80 of HBM, batch-1 decode step of the 7B shape -3%.
+  // int8 weights keep the plain loop: with any pipelining depth the extra registers cost a resident CTA and the
+  // kernel lost 10-50% (depths 1-3 measured on the same box); deeper than one step also lost for 4-bit.
+  constexpr int PD = Q8 ? 0 : 1;
+  StepRegs ring[PD + 1];
+  if (PD > 0) {
+    const int64_t rb = (int64_t)blockIdx.x * RB_PER_CTA + rb_in_cta;
+    if (rb * 16 < N) {
+      int64_t r0 = rb * 16 + g, r1 = r0 + 8;
+      if (r0 >= N) r0 = N - 1;
+      if (r1 >= N) r1 = N - 1;
+#pragma unroll
+      for (int j = 0; j < PD; ++j)
+        if (s_begin + j < s_end)
+          fetch(codes + r0 * row_bytes + t * 16, codes + r1 * row_bytes + t * 16, scales + r0 * groups, scales + r1 * groups, s_begin + j, ring[j]);
+    }
+  }
   pdl_wait();
   // PUSH: the receive-slot addresses of this call, one per rank, parked behind the reduction buffers
   float** push_dst = reinterpret_cast<float**>(cred + GM_WARPS * 16 * NV);
@@ -211,15 +255,6 @@ qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ s
     __syncthreads();
   }
 
-  const int64_t row_bytes = Q8 ? K : K / 2;
-  const int64_t groups = K / GROUP;
-  const int rb_in_cta = warp / KSPLIT;
-  const int ksp = warp % KSPLIT;
-  const int64_t steps_total = K / KSTEP;
-  const int64_t cs_begin = steps_total * cy / kc, cs_end = steps_total * (cy + 1) / kc;   // this CTA's steps
-  const int64_t s_begin = cs_begin + (cs_end - cs_begin) * ksp / KSPLIT;
-  const int64_t s_end = cs_begin + (cs_end - cs_begin) * (ksp + 1) / KSPLIT;
-
   // which activation vector / group-column this lane feeds into B: column n = g.
   //   Q8: column n = 2*v + h, h = group half (0/1); this lane's k-slots are in half (t >> 1)
   //   Q4: column n = 4*v + q, q = group (0..3);     this lane's k-slots are in group t
@@ -245,24 +280,23 @@ qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ s
 #pragma unroll
     for (int b = 0; b < NB; ++b) acc0[b][0] = acc1[b][0] = 0.0f;
 
-    // KSPLIT == 8 is the small-N / long-K case: a warp has only a dozen steps, so more of them are kept in flight
-    constexpr int UNR = KSPLIT == 8 ? 4 : 2;
-#pragma unroll UNR
-    for (int64_t s = active ? s_begin : s_end; s < s_end; ++s) {
-      const uint4 w0 = ldg_stream16(p0 + s * 64);
-      const uint4 w1 = ldg_stream16(p1 + s * 64);
-      // group scales of this step for both rows: Q8 2 fp16 (one 32-bit load), Q4 4 fp16 (one 64-bit load)
+    const bool first_block = rb_base == (int64_t)blockIdx.x * RB_PER_CTA;      // its first PD steps are already in flight
+    if (PD > 0 && active && !first_block) {
+#pragma unroll
+      for (int j = 0; j < PD; ++j)
+        if (s_begin + j < s_end) fetch(p0, p1, sc0, sc1, s_begin + j, ring[j]);
+    }
+    auto consume = [&](int64_t s, const StepRegs& rg) {
+      const uint4 w0 = rg.w0, w1 = rg.w1;
       float s0[GROUPS_PER_STEP], s1[GROUPS_PER_STEP];
       if (Q8) {
-        const __half2 a = *reinterpret_cast<const __half2*>(sc0 + s * 2);
-        const __half2 b = *reinterpret_cast<const __half2*>(sc1 + s * 2);
+        const __half2 a = *reinterpret_cast<const __half2*>(&rg.sa[0]);
+        const __half2 b = *reinterpret_cast<const __half2*>(&rg.sb[0]);
         s0[0] = __low2float(a); s0[1] = __high2float(a);
         s1[0] = __low2float(b); s1[1] = __high2float(b);
       } else {
-        const uint2 a = *reinterpret_cast<const uint2*>(sc0 + s * 4);
-        const uint2 b = *reinterpret_cast<const uint2*>(sc1 + s * 4);
-        const __half2 a0 = *reinterpret_cast<const __half2*>(&a.x), a1 = *reinterpret_cast<const __half2*>(&a.y);
-        const __half2 b0 = *reinterpret_cast<const __half2*>(&b.x), b1 = *reinterpret_cast<const __half2*>(&b.y);
+        const __half2 a0 = *reinterpret_cast<const __half2*>(&rg.sa[0]), a1 = *reinterpret_cast<const __half2*>(&rg.sa[1]);
+        const __half2 b0 = *reinterpret_cast<const __half2*>(&rg.sb[0]), b1 = *reinterpret_cast<const __half2*>(&rg.sb[1]);
         s0[0] = __low2float(a0); s0[1] = __high2float(a0); s0[2] = __low2float(a1); s0[3] = __high2float(a1);
         s1[0] = __low2float(b0); s1[1] = __high2float(b0); s1[2] = __low2float(b1); s1[3] = __high2float(b1);
       }
@@ -321,6 +355,25 @@ qgemv_mma_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ s
           acc0[b][0] = fmaf(q0 ? s0[3] : s0[1], d[1], acc0[b][0]);
           acc1[b][0] = fmaf(q0 ? s1[2] : s1[0], d[2], acc1[b][0]);
           acc1[b][0] = fmaf(q0 ? s1[3] : s1[1], d[3], acc1[b][0]);
+        }
+      }
+    };
+    if (PD == 0) {
+      // KSPLIT == 8 is the small-N / long-K case: a warp has only a dozen steps, so the loop is unrolled further
+      constexpr int UNR = KSPLIT == 8 ? 4 : 2;
+#pragma unroll UNR
+      for (int64_t s = active ? s_begin : s_end; s < s_end; ++s) {
+        fetch(p0, p1, sc0, sc1, s, ring[0]);
+        consume(s, ring[0]);
+      }
+    } else {
+      for (int64_t s = active ? s_begin : s_end; s < s_end; s += PD + 1) {
+#pragma unroll
+        for (int u = 0; u <= PD; ++u) {
+          if (s + u < s_end) {
+            if (s + u + PD < s_end) fetch(p0, p1, sc0, sc1, s + u + PD, ring[(u + PD) % (PD + 1)]);
+            consume(s + u, ring[u]);
+          }
         }
       }
     }

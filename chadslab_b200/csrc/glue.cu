@@ -658,26 +658,21 @@ static int launch_attention(const void* q, const float* qkv, void* k_cache, void
                    ((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) | reinterpret_cast<uintptr_t>(q) |
                      reinterpret_cast<uintptr_t>(out)) & 15) == 0;
   const int64_t ctas_xy = mma ? B * Hkv * (rep / hp) : gqa ? B * Hkv * (rep / hpw) : B * Hq;
-  // few CTAs and a long cache: split the positions so that several CTAs per SM stream K/V
-  int64_t nsplit = (4 * (int64_t)sm_count() + ctas_xy - 1) / ctas_xy;
-  // at least 128 cache positions per split (measured: finer is slower); the tensor-path kernel has half the warps per
-  // CTA and takes 64 (one 16-position block per warp)
+  // Positions are split over nsplit CTAs per (batch row, head group).  A partly filled last wave costs (nearly) a whole
+  // wave - fully so for the latency-bound tensor-path kernel - and every CTA pays a fixed prologue + merge worth about 96
+  // positions, so the slice count minimises waves x (positions per slice + 96).  Measured on batch 64 x 2048
+  // positions: 16 heads x 256 -> 2-3 slices (367-371 us against 377 with one), 2 heads x 256 (a tensor-parallel rank)
+  // -> 3 slices (71 us against 78 with the 5 that merely fill the machine).  At least 128 positions per slice (64 for
+  // the tensor-path kernel, which has half the warps).
   const int64_t min_pos = mma ? 64 : 128, max_split = mma ? 64 : 32;
-  if (nsplit > S / min_pos) nsplit = S / min_pos;
-  if (nsplit > max_split) nsplit = max_split;
-  if (nsplit < 1) nsplit = 1;
-  if (mma) {
-    // The tensor-path kernel is latency-bound, so a partly filled last wave costs a whole wave, and every CTA pays a
-    // fixed prologue + merge worth about 96 positions: take the slice count that minimises
-    // waves x (positions per slice + 96) instead of just filling the machine.
-    const int64_t slots = (int64_t)sm_count() * attention_mma_ctas_per_sm(qkv != nullptr, D, hp > 8);
-    int64_t best = 1, best_cost = -1;
-    for (int64_t ns = 1; ns <= nsplit; ++ns) {
-      const int64_t waves = (ctas_xy * ns + slots - 1) / slots;
-      const int64_t cost = waves * ((S + ns - 1) / ns + 96);
-      if (best_cost < 0 || cost < best_cost) { best = ns; best_cost = cost; }
-    }
-    nsplit = best;
+  int64_t ns_max = S / min_pos < max_split ? S / min_pos : max_split;
+  if (ns_max < 1) ns_max = 1;
+  const int64_t slots = (int64_t)sm_count() * (mma ? attention_mma_ctas_per_sm(qkv != nullptr, D, hp > 8) : 3);
+  int64_t nsplit = 1, best_cost = -1;
+  for (int64_t ns = 1; ns <= ns_max; ++ns) {
+    const int64_t waves = (ctas_xy * ns + slots - 1) / slots;
+    const int64_t cost = waves * ((S + ns - 1) / ns + 96);
+    if (best_cost < 0 || cost < best_cost) { nsplit = ns; best_cost = cost; }
   }
   cudaStream_t s = (cudaStream_t)stream;
   if (nsplit > 1) {

@@ -15,6 +15,12 @@ import json
 import os
 
 
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one decode_attention_kernel launch under ncu, and the K/V
+# bytes that launch streams: batch 8, 16 query / 16 KV heads x 256, 2048 positions, bf16 cache.
+NCU_ATT_TRAFFIC_MB = 272.96
+NCU_ATT_ALGORITHMIC_MB = 268.57
+
+
 def _flush_l2(torch, buf):
     buf.zero_()
 
@@ -77,7 +83,7 @@ def _headline(torch, dist, rank, world, dec, cfg, B, ctx, step, tokens, steps, m
     peak, src = (float(json.load(open(peaks_path))["hbm_gbs"]), "measured") if os.path.exists(peaks_path) else (6650.0, "fallback")
     ach = abytes / us / 1e3
     quant = {"bound": "hbm", "achieved": round(ach, 1), "peak": peak, "unit": "GB/s", "frac": round(ach / peak, 4),
-             "traffic": None, "traffic_source": "not captured in this run (ncu summaries of this kernel family: profiles/)",
+             "traffic": None, "traffic_source": "not captured in this run",
              "peak_source": src, "kernel": f"lm_head {'int8' if pw.fmt == 0 else 'q4'}-g32 ({pw.N},{pw.K}) M={B}: the largest "
                                            f"quantized-matmul launch of the step ({head_launches} kernel"
                                            f"{'s' if head_launches != 1 else ''}: activation pre-pass + GEMM when M > 16)",
@@ -107,7 +113,10 @@ def _headline(torch, dist, rank, world, dec, cfg, B, ctx, step, tokens, steps, m
     att_bytes = 2.0 * B * (ctx + 1) * dec.kv_local * c.head_dim * kc.element_size() + B * dec.h_local * c.head_dim * (4 + kc.element_size())
     aach = att_bytes / aus / 1e3
     attn = {"bound": "hbm", "achieved": round(aach, 1), "peak": peak, "unit": "GB/s", "frac": round(aach / peak, 4),
-            "traffic": None, "traffic_source": "not captured in this run",
+            "traffic": int(att_bytes * NCU_ATT_TRAFFIC_MB / NCU_ATT_ALGORITHMIC_MB),
+            "traffic_source": (f"scaled, not re-measured in this run: one ncu capture of this kernel at batch 8 (16 heads x 256, 2048 positions) "
+                               f"read + wrote {NCU_ATT_TRAFFIC_MB} MB of DRAM for {NCU_ATT_ALGORITHMIC_MB} MB of K/V rows; the traffic is "
+                               "proportional to the rows streamed"),
             "peak_source": src, "kernel": f"decode attention of one layer: batch {B}, {dec.h_local} query / {dec.kv_local} KV heads x "
                                           f"{c.head_dim}, {ctx}-position cache ({'bf16' if kc.element_size() == 2 else 'fp32'}): K and V "
                                           "rows are the algorithmic bytes",
