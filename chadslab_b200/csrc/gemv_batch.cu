@@ -58,7 +58,7 @@ template <bool Q8> __device__ __forceinline__ int64_t gb_xoffset(int64_t c) {
   }
 }
 
-template <int FMT, int NB, int KSPLIT, int MODE, typename YT>
+template <int FMT, int NB, int KSPLIT, int MODE, typename YT, bool PIPE>
 __global__ void __launch_bounds__(GB_THREADS) qgemv_batch_kernel(const __grid_constant__ GbArgs a) {
   constexpr bool Q8 = FMT == BQ_FMT_Q8G32;
   constexpr int KSTEP = Q8 ? 64 : 128;
@@ -76,6 +76,50 @@ __global__ void __launch_bounds__(GB_THREADS) qgemv_batch_kernel(const __grid_co
   float* red = xscale + MP;                                                         // [NACC][GB_WARPS][16][MP]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
+
+  const int64_t row_bytes = Q8 ? K : K / 2;
+  const int64_t groups = K / GROUP;
+  const int rb_in_cta = warp / KSPLIT;
+  const int ksp = warp % KSPLIT;
+  const int64_t steps_total = K / KSTEP;
+  const int64_t s_begin = steps_total * ksp / KSPLIT, s_end = steps_total * (ksp + 1) / KSPLIT;
+  const int64_t cta_rb0 = (MODE == GB_ROUTE ? 0 : MOE ? (int64_t)blockIdx.y : (int64_t)blockIdx.x) * RB_PER_CTA;
+  const int64_t cta_rb_stride = (MODE == GB_ROUTE ? 1 : MOE ? (int64_t)gridDim.y : (int64_t)gridDim.x) * RB_PER_CTA;
+
+  // One step of a warp's weight stream in registers: 16 bytes of codes of rows g and g + 8 of each matrix and the two
+  // rows' scale of this lane's group.  PIPE (4-bit weights, 12 and more steps per warp): the stream is software-
+  // pipelined one step deep (loads and MMAs are `asm volatile` and keep their program order), and the first step of the
+  // first row block is requested before the activation rows are staged - for the dense modes even before
+  // griddepcontrol.wait, weights being constants.  Measured: (256000, 2048) at 4-8 rows 70 -> 63 us, the 128-expert
+  // layer's gate|up 174 -> 162 us; with a handful of steps per warp (16384 x 2048: 9.4 -> 10.7 us) and for int8 (the
+  // exact GEMV lost 10-50% with the extra registers) the plain loop is faster.
+  struct StepRegs { uint4 wq[NACC][2]; __half sc[NACC][2]; };
+  constexpr int PD = (!Q8 && PIPE) ? 1 : 0;
+  StepRegs ring[PD + 1];
+  auto fetch = [&](const uint8_t* cA, const __half* sA, const uint8_t* cB, const __half* sB, int64_t r0, int64_t r1, int64_t st,
+                   StepRegs& r) {
+    const int64_t so = st * (Q8 ? 2 : 4) + (Q8 ? (t >> 1) : t);
+    r.wq[0][0] = ldg_stream16(cA + r0 * row_bytes + t * 16 + st * 64);
+    r.wq[0][1] = ldg_stream16(cA + r1 * row_bytes + t * 16 + st * 64);
+    r.sc[0][0] = sA[r0 * groups + so];
+    r.sc[0][1] = sA[r1 * groups + so];
+    if (TWO) {
+      r.wq[NACC - 1][0] = ldg_stream16(cB + r0 * row_bytes + t * 16 + st * 64);
+      r.wq[NACC - 1][1] = ldg_stream16(cB + r1 * row_bytes + t * 16 + st * 64);
+      r.sc[NACC - 1][0] = sB[r0 * groups + so];
+      r.sc[NACC - 1][1] = sB[r1 * groups + so];
+    }
+  };
+  auto preload_first = [&](const uint8_t* cA, const __half* sA, const uint8_t* cB, const __half* sB) {
+    const int64_t rb = cta_rb0 + rb_in_cta;
+    if (PD > 0 && rb * 16 < N && s_begin < s_end) {
+      int64_t r0 = rb * 16 + g, r1 = r0 + 8;
+      if (r0 >= N) r0 = N - 1;
+      if (r1 >= N) r1 = N - 1;
+      fetch(cA, sA, cB, sB, r0, r1, s_begin, ring[0]);
+    }
+  };
+  if (!MOE) preload_first(a.codes, a.scales, nullptr, nullptr);
 
   pdl_wait();                                      // activations, tile list and row ranges come from preceding kernels
   const uint8_t* codesA = a.codes;
@@ -96,6 +140,7 @@ __global__ void __launch_bounds__(GB_THREADS) qgemv_batch_kernel(const __grid_co
     m_rows = (int)(m_end - m0 < MP ? m_end - m0 : MP);
     codesA = a.codesA[e]; scalesA = a.scalesA[e];
     if (TWO) { codesB = a.codesB[e]; scalesB = a.scalesB[e]; }
+    preload_first(codesA, scalesA, codesB, scalesB);      // the expert is known: its first step travels while the rows are staged
   }
 
   // ---- activations -> scaled fp16 rows in shared memory (one warp per row, two passes over the row) ----------
@@ -166,49 +211,26 @@ __global__ void __launch_bounds__(GB_THREADS) qgemv_batch_kernel(const __grid_co
   }
   __syncthreads();
 
-  const int64_t row_bytes = Q8 ? K : K / 2;
-  const int64_t groups = K / GROUP;
-  const int rb_in_cta = warp / KSPLIT;
-  const int ksp = warp % KSPLIT;
-  const int64_t steps_total = K / KSTEP;
-  const int64_t s_begin = steps_total * ksp / KSPLIT, s_end = steps_total * (ksp + 1) / KSPLIT;
-  const int64_t cta_rb0 = (MODE == GB_ROUTE ? 0 : MOE ? (int64_t)blockIdx.y : (int64_t)blockIdx.x) * RB_PER_CTA;
-  const int64_t cta_rb_stride = (MODE == GB_ROUTE ? 1 : MOE ? (int64_t)gridDim.y : (int64_t)gridDim.x) * RB_PER_CTA;
-
   for (int64_t rb_base = cta_rb0; rb_base * 16 < N; rb_base += cta_rb_stride) {
     const int64_t rb = rb_base + rb_in_cta;
     const bool active = rb * 16 < N;               // warp-uniform
     int64_t r0 = rb * 16 + g, r1 = r0 + 8;
     if (r0 >= N) r0 = N - 1;
     if (r1 >= N) r1 = N - 1;
-    const uint8_t* pA0 = codesA + r0 * row_bytes + t * 16;
-    const uint8_t* pA1 = codesA + r1 * row_bytes + t * 16;
-    const __half* sA0 = scalesA + r0 * groups + (Q8 ? (t >> 1) : t);
-    const __half* sA1 = scalesA + r1 * groups + (Q8 ? (t >> 1) : t);
-    const uint8_t* pB0 = TWO ? codesB + r0 * row_bytes + t * 16 : nullptr;
-    const uint8_t* pB1 = TWO ? codesB + r1 * row_bytes + t * 16 : nullptr;
-    const __half* sB0 = TWO ? scalesB + r0 * groups + (Q8 ? (t >> 1) : t) : nullptr;
-    const __half* sB1 = TWO ? scalesB + r1 * groups + (Q8 ? (t >> 1) : t) : nullptr;
     float d[NACC][NB][4];
 #pragma unroll
     for (int w = 0; w < NACC; ++w)
 #pragma unroll
       for (int b = 0; b < NB; ++b) d[w][b][0] = d[w][b][1] = d[w][b][2] = d[w][b][3] = 0.0f;
 
-#pragma unroll 2
-    for (int64_t s = active ? s_begin : s_end; s < s_end; ++s) {
+    if (PD > 0 && active && rb_base != cta_rb0 && s_begin < s_end) fetch(codesA, scalesA, codesB, scalesB, r0, r1, s_begin, ring[0]);
+    auto consume = [&](int64_t s, const StepRegs& rg) {
       uint4 wq[NACC][2];
       __half2 sc[NACC][2];
-      wq[0][0] = ldg_stream16(pA0 + s * 64);
-      wq[0][1] = ldg_stream16(pA1 + s * 64);
-      sc[0][0] = __half2half2(sA0[s * (Q8 ? 2 : 4)]);
-      sc[0][1] = __half2half2(sA1[s * (Q8 ? 2 : 4)]);
-      if (TWO) {
-        wq[NACC - 1][0] = ldg_stream16(pB0 + s * 64);
-        wq[NACC - 1][1] = ldg_stream16(pB1 + s * 64);
-        sc[NACC - 1][0] = __half2half2(sB0[s * (Q8 ? 2 : 4)]);
-        sc[NACC - 1][1] = __half2half2(sB1[s * (Q8 ? 2 : 4)]);
-      }
+#pragma unroll
+      for (int w = 0; w < NACC; ++w)
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) { wq[w][rr] = rg.wq[w][rr]; sc[w][rr] = __half2half2(rg.sc[w][rr]); }
       // A fragments (code * scale as fp16): afr[j] = {row g slots 2t..; row g+8 slots 2t..; row g slots 2t+8..; row g+8 ..}
       uint32_t afr[NACC][MMAS][4];
 #pragma unroll
@@ -254,6 +276,23 @@ __global__ void __launch_bounds__(GB_THREADS) qgemv_batch_kernel(const __grid_co
         for (int w = 0; w < NACC; ++w)
 #pragma unroll
           for (int j = 0; j < MMAS; ++j) mma_f16_16816(d[w][b], afr[w][j], bfr[j][0], bfr[j][1]);
+      }
+    };
+    if (PD == 0) {
+#pragma unroll 2
+      for (int64_t s = active ? s_begin : s_end; s < s_end; ++s) {
+        fetch(codesA, scalesA, codesB, scalesB, r0, r1, s, ring[0]);
+        consume(s, ring[0]);
+      }
+    } else {
+      for (int64_t s = active ? s_begin : s_end; s < s_end; s += PD + 1) {
+#pragma unroll
+        for (int u = 0; u <= PD; ++u) {
+          if (s + u < s_end) {
+            if (s + u + PD < s_end) fetch(codesA, scalesA, codesB, scalesB, r0, r1, s + u + PD, ring[(u + PD) % (PD + 1)]);
+            consume(s + u, ring[u]);
+          }
+        }
       }
     }
 
@@ -406,9 +445,21 @@ static int gb_ctas_per_sm(size_t smem) {
   return n > 3 ? 3 : (n < 1 ? 1 : n);
 }
 
+template <int FMT, int NB, int KSPLIT, int MODE, typename YT, bool PIPE>
+static int gb_launch_impl(const GbArgs& a, dim3 grid, bool two, cudaStream_t s);
+
+// PIPE: the pipelined variant pays off from about 12 steps per warp (4-bit weights only)
 template <int FMT, int NB, int KSPLIT, int MODE, typename YT>
 static int gb_launch(const GbArgs& a, dim3 grid, bool two, cudaStream_t s) {
-  auto kern = qgemv_batch_kernel<FMT, NB, KSPLIT, MODE, YT>;
+  if constexpr (FMT == BQ_FMT_Q4G32) {
+    if (a.K / 128 / KSPLIT >= 12) return gb_launch_impl<FMT, NB, KSPLIT, MODE, YT, true>(a, grid, two, s);
+  }
+  return gb_launch_impl<FMT, NB, KSPLIT, MODE, YT, false>(a, grid, two, s);
+}
+
+template <int FMT, int NB, int KSPLIT, int MODE, typename YT, bool PIPE>
+static int gb_launch_impl(const GbArgs& a, dim3 grid, bool two, cudaStream_t s) {
+  auto kern = qgemv_batch_kernel<FMT, NB, KSPLIT, MODE, YT, PIPE>;
   const size_t smem = gb_smem_bytes(NB, a.K, two);
   // Shared memory and L1 share one array.  The kernel wants both: room for gb_ctas_per_sm CTAs' activation rows AND
   // as much L1 as is left (scales and activations are re-read through it; with the carve-out at its maximum the

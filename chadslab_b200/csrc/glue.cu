@@ -660,7 +660,9 @@ static int launch_attention(const void* q, const float* qkv, void* k_cache, void
   const int64_t ctas_xy = mma ? B * Hkv * (rep / hp) : gqa ? B * Hkv * (rep / hpw) : B * Hq;
   // Positions are split over nsplit CTAs per (batch row, head group).  A partly filled last wave costs (nearly) a whole
   // wave - fully so for the latency-bound tensor-path kernel - and every CTA pays a fixed prologue + merge worth about 96
-  // positions, so the slice count minimises waves x (positions per slice + 96).  Measured on batch 64 x 2048
+  // positions (256 for the tensor-path kernel: with 96 the sparse-MoE decoder, batch 256 x 512 positions, took two
+  // slices and its step grew from 17.7 to 18.5 ms), so the slice count minimises waves x (positions per slice + fixed).
+  // Measured on batch 64 x 2048
   // positions: 16 heads x 256 -> 2-3 slices (367-371 us against 377 with one), 2 heads x 256 (a tensor-parallel rank)
   // -> 3 slices (71 us against 78 with the 5 that merely fill the machine).  At least 128 positions per slice (64 for
   // the tensor-path kernel, which has half the warps).
@@ -668,10 +670,11 @@ static int launch_attention(const void* q, const float* qkv, void* k_cache, void
   int64_t ns_max = S / min_pos < max_split ? S / min_pos : max_split;
   if (ns_max < 1) ns_max = 1;
   const int64_t slots = (int64_t)sm_count() * (mma ? attention_mma_ctas_per_sm(qkv != nullptr, D, hp > 8) : 3);
+  const int64_t fixed = mma ? 256 : 96;      // the tensor-path CTA rotates and stages up to 16 query heads and merges 4 warps x 16 heads
   int64_t nsplit = 1, best_cost = -1;
   for (int64_t ns = 1; ns <= ns_max; ++ns) {
     const int64_t waves = (ctas_xy * ns + slots - 1) / slots;
-    const int64_t cost = waves * ((S + ns - 1) / ns + 96);
+    const int64_t cost = waves * ((S + ns - 1) / ns + fixed);
     if (best_cost < 0 || cost < best_cost) { nsplit = ns; best_cost = cost; }
   }
   cudaStream_t s = (cudaStream_t)stream;

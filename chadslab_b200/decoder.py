@@ -52,11 +52,6 @@ GEMMA_7B_SHAPE = DecoderConfig(28, 3072, 16, 16, 256, 24576, 256000, fmt=1)
 MOE_SHAPE = DecoderConfig(48, 2048, 32, 4, 128, 0, 32000, fmt=1, n_experts=128, top_k=8, moe_ffn=768)
 
 
-def _rmsnorm(x, w, eps):
-    xf = x.float()
-    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w).to(x.dtype)
-
-
 def _rope(x, pos, base):
     """x [B, T, heads, d], pos [T]."""
     d = x.shape[-1]
