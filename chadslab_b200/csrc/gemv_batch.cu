@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(GB_THREADS) qgemv_batch_kernel(const __grid_co
   const int64_t cta_rb_stride = (MODE == GB_ROUTE ? 1 : MOE ? (int64_t)gridDim.y : (int64_t)gridDim.x) * RB_PER_CTA;
 
   // One step of a warp's weight stream in registers: 16 bytes of codes of rows g and g + 8 of each matrix and the two
-  // rows' scale of this lane's group.  PIPE (4-bit weights, 12 and more steps per warp): the stream is software-
+  // rows' scale of this lane's group.  PIPE (4-bit weights; 12 and more steps per warp, or an expert tile): the stream is software-
   // pipelined one step deep (loads and MMAs are `asm volatile` and keep their program order), and the first step of the
   // first row block is requested before the activation rows are staged - for the dense modes even before
   // griddepcontrol.wait, weights being constants.  Measured: (256000, 2048) at 4-8 rows 70 -> 63 us, the 128-expert
@@ -448,11 +448,13 @@ static int gb_ctas_per_sm(size_t smem) {
 template <int FMT, int NB, int KSPLIT, int MODE, typename YT, bool PIPE>
 static int gb_launch_impl(const GbArgs& a, dim3 grid, bool two, cudaStream_t s);
 
-// PIPE: the pipelined variant pays off from about 12 steps per warp (4-bit weights only)
+// PIPE (4-bit weights only): the pipelined variant pays off from about 12 steps per warp, and for the expert modes at
+// any length, because there the first step travels while the 16 token rows are gathered and converted
 template <int FMT, int NB, int KSPLIT, int MODE, typename YT>
 static int gb_launch(const GbArgs& a, dim3 grid, bool two, cudaStream_t s) {
   if constexpr (FMT == BQ_FMT_Q4G32) {
-    if (a.K / 128 / KSPLIT >= 12) return gb_launch_impl<FMT, NB, KSPLIT, MODE, YT, true>(a, grid, two, s);
+    if (MODE == GB_MOE_GU || MODE == GB_MOE_DOWN || a.K / 128 / KSPLIT >= 12)
+      return gb_launch_impl<FMT, NB, KSPLIT, MODE, YT, true>(a, grid, two, s);
   }
   return gb_launch_impl<FMT, NB, KSPLIT, MODE, YT, false>(a, grid, two, s);
 }
