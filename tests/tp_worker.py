@@ -111,14 +111,20 @@ def main():
     err = spec.rel_err(y, ref)
     assert err <= 4e-3, err      # layer-level bound (bf16 hidden activation between the expert matmuls)
     # the same layer with both exchanges on the device (peer-memory stores, no collective call, no host step):
-    # bit-identical to the route through the process group, eagerly and from a replayed CUDA graph
+    # bit-identical to the route through the process group, eagerly and from a replayed CUDA graph.  (The router is
+    # passed as a plain callable here so that both routes compute the routing weights with the same two kernels; with
+    # a QuantLinear the device route fuses router matmul + softmax + top-k into one launch, checked below.)
     ep = cb.PeerEP(E, H, max_send_rows=64)
     local2 = cb.MoEExperts(None, [mk(g) for g in lg_], [mk(u) for u in lu_], [mk(d) for d in ld_], top_k=k)
-    layer2 = parallel.ExpertParallelMoE(cb.QuantLinear(mk(router)), None, E, k, ep=ep, local_moe=local2)
+    router_lin = cb.QuantLinear(mk(router))
+    layer2 = parallel.ExpertParallelMoE(lambda t: router_lin(t), None, E, k, ep=ep, local_moe=local2)
     xt = torch.from_numpy(x).cuda().to(torch.bfloat16)
     for _ in range(3):
         y2 = layer2(xt)
         assert np.array_equal(y2.cpu().numpy(), y)
+    layer3 = parallel.ExpertParallelMoE(router_lin, None, E, k, ep=ep, local_moe=local2)       # fused router
+    y3 = layer3(xt).cpu().numpy()
+    assert spec.rel_err(y3, ref) <= 4e-3 and spec.rel_err(y3, y) <= 1e-3
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     graph = torch.cuda.CUDAGraph()
