@@ -4,7 +4,8 @@
     torchrun --nproc-per-node N ... -m chadslab_b200.moe_bench ...   (expert parallel: E/N experts and tokens/N per rank)
 
 Random-init packed weights generated on the device; router logits come from x . Wr^T with x ~ N(0,1).  Per token
-count: microseconds of the whole layer and of its stages (CUDA events, `--reps` launches after 2), the expert
+count: microseconds of the whole layer (replays of one captured CUDA graph, as a decode step runs it; the eager figure
+beside it includes the host time between launches) and of its stages (CUDA events, `--reps` launches after 2), the expert
 weight bytes one pass streams (every expert that received a token), the resulting GB/s, and TFLOP/s of the expert
 matmuls.  Prints one JSON object on rank 0.
 """
@@ -24,6 +25,29 @@ def _timed(torch, fn, reps):
         fn()
     b.record()
     torch.cuda.synchronize()
+    return a.elapsed_time(b) * 1e3 / reps
+
+
+def _timed_graph(torch, fn, reps):
+    """The same launches captured once and replayed (how a decode step runs them): no host time between kernels."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            fn()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        keep = fn()
+    for _ in range(2):
+        graph.replay()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        graph.replay()
+    b.record()
+    torch.cuda.synchronize()
+    del keep, graph
     return a.elapsed_time(b) * 1e3 / reps
 
 
@@ -56,8 +80,9 @@ def run(torch, dist, rank, world, tokens=(256,), E=128, H=2048, F=768, top_k=8, 
     for T in tokens:
         T_loc = T // world
         x = torch.randn((T_loc, H), device="cuda", generator=gen).to(torch.bfloat16)
-        us = _timed(torch, lambda: layer(x), reps)
-        case = {"tokens": T, "tokens_per_rank": T_loc, "layer_us": round(us, 1)}
+        eager_us = _timed(torch, lambda: layer(x), reps)
+        us = _timed_graph(torch, lambda: layer(x), reps)            # the headline figure: one captured layer, replayed
+        case = {"tokens": T, "tokens_per_rank": T_loc, "layer_us": round(us, 1), "layer_us_eager": round(eager_us, 1)}
         if world == 1:
             logits = moe.router(x)
             idx, w = ops.moe_route(logits, top_k)
@@ -76,10 +101,10 @@ def run(torch, dist, rank, world, tokens=(256,), E=128, H=2048, F=768, top_k=8, 
             wbytes = touched * bytes_per_expert
             case["expert_weight_gbs"] = round(wbytes / case["stages_us"]["experts"] / 1e3, 1)
             case["expert_tflops"] = round(2.0 * T * top_k * 3 * H * F / case["stages_us"]["experts"] / 1e6, 1)
-        t = torch.tensor([us], device="cuda")
+        t = torch.tensor([us, eager_us], device="cuda")
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            case["layer_us"] = round(float(t[0]), 1)
+            case["layer_us"], case["layer_us_eager"] = round(float(t[0]), 1), round(float(t[1]), 1)
         case["tokens_per_s_per_layer"] = round(T / float(t[0]) * 1e6, 1)
         out["cases"].append(case)
         del x
