@@ -132,7 +132,7 @@ int launch_moe_route_linear(const uint8_t* codes, const __half* scales, int fmt,
                             int top_k, int renorm, int32_t* idx_out, float* w_out, cudaStream_t s);
 bool moe_batch_supported(const Moe* m);
 int launch_moe_experts_batch(const Moe* m, const void* x, const int32_t* perm, int top_k, const int32_t* offsets, int64_t P,
-                             void* hbuf, float* out, cudaStream_t s);
+                             int64_t rows_hint, void* hbuf, float* out, cudaStream_t s);
 bool moe_tc_supported(const Moe* m);
 int moe_tc_prepare(Moe* m, const std::vector<const uint8_t*>* codes, const std::vector<const __half*>* scales);
 void moe_tc_release(Moe* m);

@@ -422,9 +422,10 @@ __global__ void __launch_bounds__(GB_THREADS) qgemv_batch_kernel(const __grid_co
 }
 
 // ---- host side ------------------------------------------------------------------------------------------------
-static size_t gb_smem_bytes(int nb, int64_t K, bool two) {
+// `with_red`: the area where K-split partials (or the router's logits) meet; a launch without either does not need it
+static size_t gb_smem_bytes(int nb, int64_t K, bool two, bool with_red = true) {
   const int mp = 8 * nb;
-  return (size_t)mp * (K + 32) * 2 + (size_t)mp * 4 + (size_t)(two ? 2 : 1) * GB_WARPS * 16 * mp * 4;
+  return (size_t)mp * (K + 32) * 2 + (size_t)mp * 4 + (with_red ? (size_t)(two ? 2 : 1) * GB_WARPS * 16 * mp * 4 : 0);
 }
 
 bool gemv_batch_supported(int fmt, int64_t N, int64_t K, int x_dtype, int64_t M) {
@@ -441,7 +442,7 @@ bool gemv_batch_supported(int fmt, int64_t N, int64_t K, int x_dtype, int64_t M)
 
 // CTAs of this kernel that should share an SM: as many as the registers allow (3), fewer when the activation rows are large
 static int gb_ctas_per_sm(size_t smem) {
-  int n = (int)((200 * 1024) / (smem + 1024));
+  int n = (int)((210 * 1024) / (smem + 1024));
   return n > 3 ? 3 : (n < 1 ? 1 : n);
 }
 
@@ -462,7 +463,7 @@ static int gb_launch(const GbArgs& a, dim3 grid, bool two, cudaStream_t s) {
 template <int FMT, int NB, int KSPLIT, int MODE, typename YT, bool PIPE>
 static int gb_launch_impl(const GbArgs& a, dim3 grid, bool two, cudaStream_t s) {
   auto kern = qgemv_batch_kernel<FMT, NB, KSPLIT, MODE, YT, PIPE>;
-  const size_t smem = gb_smem_bytes(NB, a.K, two);
+  const size_t smem = gb_smem_bytes(NB, a.K, two, KSPLIT > 1 || MODE == GB_ROUTE);
   // Shared memory and L1 share one array.  The kernel wants both: room for gb_ctas_per_sm CTAs' activation rows AND
   // as much L1 as is left (scales and activations are re-read through it; with the carve-out at its maximum the
   // kernel ran at half speed, with the default one CTA per SM was resident above 48 KB).  So the carve-out asked for
@@ -541,14 +542,15 @@ int launch_moe_route_linear(const uint8_t* codes, const __half* scales, int fmt,
                              : gb_launch<BQ_FMT_Q4G32, 2, 1, GB_ROUTE, float>(a, grid, false, s);
 }
 
-// ---- MoE grouped experts at decode sizes: 16-row tiles of every expert's segment ----------------------------------
-__global__ void __launch_bounds__(1024) moe_tile16_kernel(const int32_t* __restrict__ offsets, int E, int32_t* __restrict__ tiles) {
+// ---- MoE grouped experts at decode sizes: 8-, 16- or 24-row tiles of every expert's segment ------------------------
+__global__ void __launch_bounds__(1024) moe_tile_kernel(const int32_t* __restrict__ offsets, int E, int tile_rows,
+                                                        int32_t* __restrict__ tiles) {
   __shared__ int32_t pre[1024];
   const int e = threadIdx.x;
   pdl_launch_dependents();
   pdl_wait();
   int32_t cnt = 0;
-  if (e < E) cnt = (offsets[e + 1] - offsets[e] + 15) / 16;
+  if (e < E) cnt = (offsets[e + 1] - offsets[e] + tile_rows - 1) / tile_rows;
   pre[e] = cnt;
   __syncthreads();
   for (int off = 1; off < 1024; off <<= 1) {
@@ -561,7 +563,7 @@ __global__ void __launch_bounds__(1024) moe_tile16_kernel(const int32_t* __restr
     const int32_t base = pre[e] - cnt, first = offsets[e];
     for (int i = 0; i < cnt; ++i) {
       tiles[1 + 2 * (base + i)] = e;
-      tiles[2 + 2 * (base + i)] = first + i * 16;
+      tiles[2 + 2 * (base + i)] = first + i * tile_rows;
     }
   }
   if (e == E - 1) tiles[0] = pre[e];
@@ -574,44 +576,60 @@ bool moe_batch_supported(const Moe* m) {
 
 static Scratch g_tiles16;      // tile list of the current call (library scratch: see common.cuh)
 
-int launch_moe_experts_batch(const Moe* m, const void* x, const int32_t* perm, int top_k, const int32_t* offsets, int64_t P,
-                             void* hbuf, float* out, cudaStream_t s) {
-  if (!moe_batch_supported(m)) return fail(BQ_ERR_UNSUPPORTED, "batched-GEMV expert path unavailable for this expert shape");
-  if ((reinterpret_cast<uintptr_t>(x) & 15) != 0 || (reinterpret_cast<uintptr_t>(hbuf) & 15) != 0)
-    return fail(BQ_ERR_ARG, "activation buffers must be 16-byte aligned");
-  const int64_t max_tiles = (P + 15) / 16 + m->E;
-  int rc = scratch_ensure(&g_tiles16, sizeof(int32_t) * (size_t)(2 * max_tiles + 1 + 64), s, "bq_moe_experts (tile list)");
-  if (rc) return rc;
-  int32_t* tiles = (int32_t*)g_tiles16.ptr;
-  BQ_CUDA(launch_chain(moe_tile16_kernel, dim3(1), dim3(1024), 0, s, 1, offsets, m->E, tiles));
-  count_launch();
-  GbArgs a;
-  memset(&a, 0, sizeof(a));
-  a.codesA = m->gate_codes; a.scalesA = m->gate_scales; a.codesB = m->up_codes; a.scalesB = m->up_scales;
-  a.x = (const __nv_bfloat16*)x; a.perm = perm; a.top_k = top_k > 0 ? top_k : 1; a.offsets = offsets; a.tiles = tiles;
-  a.y = hbuf; a.ldy = m->F; a.N = m->F; a.K = m->H;
-  // gate|up: a warp streams 16 gate rows and the 16 up rows of the same outputs; 8 row blocks per CTA pass
+template <int NB>
+static int moe_batch_launch(const Moe* m, const GbArgs& a, const GbArgs& b, int64_t max_tiles, cudaStream_t s) {
+  int rc;
   {
+    // gate|up: a warp streams 16 gate rows and the 16 up rows of the same outputs; 8 row blocks per CTA pass
     const int64_t rb = (m->F + 15) / 16;
     dim3 grid((unsigned)max_tiles, (unsigned)((rb + GB_WARPS - 1) / GB_WARPS));
-    rc = m->fmt == BQ_FMT_Q8G32 ? gb_launch<BQ_FMT_Q8G32, 2, 1, GB_MOE_GU, __nv_bfloat16>(a, grid, true, s)
-                                : gb_launch<BQ_FMT_Q4G32, 2, 1, GB_MOE_GU, __nv_bfloat16>(a, grid, true, s);
+    rc = m->fmt == BQ_FMT_Q8G32 ? gb_launch<BQ_FMT_Q8G32, NB, 1, GB_MOE_GU, __nv_bfloat16>(a, grid, true, s)
+                                : gb_launch<BQ_FMT_Q4G32, NB, 1, GB_MOE_GU, __nv_bfloat16>(a, grid, true, s);
     if (rc) return rc;
   }
-  GbArgs b;
-  memset(&b, 0, sizeof(b));
-  b.codesA = m->down_codes; b.scalesA = m->down_scales; b.x = (const __nv_bfloat16*)hbuf; b.offsets = offsets; b.tiles = tiles;
-  b.y = out; b.ldy = m->H; b.N = m->H; b.K = m->F; b.top_k = 1;
   {
     // down: short K (a handful of steps per warp): every warp walks several row blocks
     const int64_t rb = (m->H + 15) / 16;
     int64_t gy = (rb + GB_WARPS * 4 - 1) / (GB_WARPS * 4);
     if (gy < 1) gy = 1;
     dim3 grid((unsigned)max_tiles, (unsigned)gy);
-    rc = m->fmt == BQ_FMT_Q8G32 ? gb_launch<BQ_FMT_Q8G32, 2, 1, GB_MOE_DOWN, float>(b, grid, false, s)
-                                : gb_launch<BQ_FMT_Q4G32, 2, 1, GB_MOE_DOWN, float>(b, grid, false, s);
+    rc = m->fmt == BQ_FMT_Q8G32 ? gb_launch<BQ_FMT_Q8G32, NB, 1, GB_MOE_DOWN, float>(b, grid, false, s)
+                                : gb_launch<BQ_FMT_Q4G32, NB, 1, GB_MOE_DOWN, float>(b, grid, false, s);
   }
   return rc;
+}
+
+// rows_hint: rows the experts are expected to hold in total (<= P, the rows the buffers hold).  It picks the tile
+// height: a tile streams its expert's weights and pays the whole unpack arithmetic once whatever it holds, so the tile
+// should cover an expert's segment in one piece without carrying many empty columns: 8 rows up to an average of 5 rows
+// per expert, 16 up to 11, 24 beyond (when two CTAs of 24 rows still share an SM).
+int launch_moe_experts_batch(const Moe* m, const void* x, const int32_t* perm, int top_k, const int32_t* offsets, int64_t P,
+                             int64_t rows_hint, void* hbuf, float* out, cudaStream_t s) {
+  if (!moe_batch_supported(m)) return fail(BQ_ERR_UNSUPPORTED, "batched-GEMV expert path unavailable for this expert shape");
+  if ((reinterpret_cast<uintptr_t>(x) & 15) != 0 || (reinterpret_cast<uintptr_t>(hbuf) & 15) != 0)
+    return fail(BQ_ERR_ARG, "activation buffers must be 16-byte aligned");
+  const int64_t avg = (rows_hint + m->E - 1) / m->E;
+  const int64_t kmax = m->H > m->F ? m->H : m->F;
+  int nb = avg <= 5 ? 1 : avg <= 11 ? 2 : 3;
+  if (nb == 3 && gb_ctas_per_sm(gb_smem_bytes(3, kmax, true, false)) < 2) nb = 2;
+  const int tile_rows = 8 * nb;
+  const int64_t max_tiles = (P + tile_rows - 1) / tile_rows + m->E;
+  int rc = scratch_ensure(&g_tiles16, sizeof(int32_t) * (size_t)(2 * ((P + 7) / 8 + m->E) + 1 + 64), s, "bq_moe_experts (tile list)");
+  if (rc) return rc;
+  int32_t* tiles = (int32_t*)g_tiles16.ptr;
+  BQ_CUDA(launch_chain(moe_tile_kernel, dim3(1), dim3(1024), 0, s, 1, offsets, m->E, tile_rows, tiles));
+  count_launch();
+  GbArgs a;
+  memset(&a, 0, sizeof(a));
+  a.codesA = m->gate_codes; a.scalesA = m->gate_scales; a.codesB = m->up_codes; a.scalesB = m->up_scales;
+  a.x = (const __nv_bfloat16*)x; a.perm = perm; a.top_k = top_k > 0 ? top_k : 1; a.offsets = offsets; a.tiles = tiles;
+  a.y = hbuf; a.ldy = m->F; a.N = m->F; a.K = m->H;
+  GbArgs b;
+  memset(&b, 0, sizeof(b));
+  b.codesA = m->down_codes; b.scalesA = m->down_scales; b.x = (const __nv_bfloat16*)hbuf; b.offsets = offsets; b.tiles = tiles;
+  b.y = out; b.ldy = m->H; b.N = m->H; b.K = m->F; b.top_k = 1;
+  return nb == 1 ? moe_batch_launch<1>(m, a, b, max_tiles, s) : nb == 2 ? moe_batch_launch<2>(m, a, b, max_tiles, s)
+                                                                          : moe_batch_launch<3>(m, a, b, max_tiles, s);
 }
 
 }  // namespace bq

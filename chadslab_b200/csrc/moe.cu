@@ -590,7 +590,7 @@ int bq_moe_experts_ex(bq_moe_t h, const void* xp_bf16, const int32_t* offsets, i
   if (path == BQ_PATH_MMA && !batch_ok) return fail(BQ_ERR_UNSUPPORTED, "batched-GEMV path unavailable for this expert shape");
   if (path == BQ_PATH_MMA || (path == BQ_PATH_AUTO && batch_ok && rows_hint <= (int64_t)m->E * 20)) {
     set_last_path(BQ_PATH_MMA);
-    return launch_moe_experts_batch(m, xp_bf16, nullptr, 1, offsets, P, hbuf_bf16, out, s);
+    return launch_moe_experts_batch(m, xp_bf16, nullptr, 1, offsets, P, rows_hint, hbuf_bf16, out, s);
   }
   if ((path == BQ_PATH_AUTO && tc_ok) || path == BQ_PATH_TENSOR) {
     set_last_path(BQ_PATH_TENSOR);
@@ -614,7 +614,7 @@ int bq_moe_experts_tokens(bq_moe_t h, const void* x_bf16, const int32_t* perm, i
   if (path == BQ_PATH_MMA && !batch_ok) return fail(BQ_ERR_UNSUPPORTED, "batched-GEMV path unavailable for this expert shape");
   if (path == BQ_PATH_MMA || (path == BQ_PATH_AUTO && batch_ok && rows_hint <= (int64_t)m->E * 20)) {
     set_last_path(BQ_PATH_MMA);             // the kernel reads the token rows through perm: no gathered copy
-    return launch_moe_experts_batch(m, x_bf16, perm, top_k, offsets, P, hbuf_bf16, out, (cudaStream_t)stream);
+    return launch_moe_experts_batch(m, x_bf16, perm, top_k, offsets, P, rows_hint, hbuf_bf16, out, (cudaStream_t)stream);
   }
   if (!xp_work) return fail(BQ_ERR_ARG, "this path needs the gathered rows: xp_work must not be null");
   if ((rc = bq_moe_gather(x_bf16, BQ_DT_BF16, m->H, perm, P, top_k, xp_work, stream))) return rc;
