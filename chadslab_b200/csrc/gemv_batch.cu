@@ -442,7 +442,7 @@ bool gemv_batch_supported(int fmt, int64_t N, int64_t K, int x_dtype, int64_t M)
 
 // CTAs of this kernel that should share an SM: as many as the registers allow (3), fewer when the activation rows are large
 static int gb_ctas_per_sm(size_t smem) {
-  int n = (int)((210 * 1024) / (smem + 1024));
+  int n = (int)((200 * 1024) / (smem + 1024));
   return n > 3 ? 3 : (n < 1 ? 1 : n);
 }
 
@@ -542,7 +542,7 @@ int launch_moe_route_linear(const uint8_t* codes, const __half* scales, int fmt,
                              : gb_launch<BQ_FMT_Q4G32, 2, 1, GB_ROUTE, float>(a, grid, false, s);
 }
 
-// ---- MoE grouped experts at decode sizes: 8-, 16- or 24-row tiles of every expert's segment ------------------------
+// ---- MoE grouped experts at decode sizes: 8- or 16-row tiles of every expert's segment ------------------------------
 __global__ void __launch_bounds__(1024) moe_tile_kernel(const int32_t* __restrict__ offsets, int E, int tile_rows,
                                                         int32_t* __restrict__ tiles) {
   __shared__ int32_t pre[1024];
@@ -600,18 +600,17 @@ static int moe_batch_launch(const Moe* m, const GbArgs& a, const GbArgs& b, int6
 }
 
 // rows_hint: rows the experts are expected to hold in total (<= P, the rows the buffers hold).  It picks the tile
-// height: a tile streams its expert's weights and pays the whole unpack arithmetic once whatever it holds, so the tile
-// should cover an expert's segment in one piece without carrying many empty columns: 8 rows up to an average of 5 rows
-// per expert, 16 up to 11, 24 beyond (when two CTAs of 24 rows still share an SM).
+// height: a tile streams its expert's weights and pays the whole unpack arithmetic once whatever it holds, and the MMA
+// work grows with its height: 8 rows up to an average of 5 rows per expert (64 tokens, 128 experts, top-8: experts stage
+// 121 -> 103 us), 16 rows beyond.  24-row tiles lost (256 tokens: 162 -> 193 us): two such CTAs take 200 KB of the
+// shared-memory / L1 array and 127 registers.
 int launch_moe_experts_batch(const Moe* m, const void* x, const int32_t* perm, int top_k, const int32_t* offsets, int64_t P,
                              int64_t rows_hint, void* hbuf, float* out, cudaStream_t s) {
   if (!moe_batch_supported(m)) return fail(BQ_ERR_UNSUPPORTED, "batched-GEMV expert path unavailable for this expert shape");
   if ((reinterpret_cast<uintptr_t>(x) & 15) != 0 || (reinterpret_cast<uintptr_t>(hbuf) & 15) != 0)
     return fail(BQ_ERR_ARG, "activation buffers must be 16-byte aligned");
   const int64_t avg = (rows_hint + m->E - 1) / m->E;
-  const int64_t kmax = m->H > m->F ? m->H : m->F;
-  int nb = avg <= 5 ? 1 : avg <= 11 ? 2 : 3;
-  if (nb == 3 && gb_ctas_per_sm(gb_smem_bytes(3, kmax, true, false)) < 2) nb = 2;
+  const int nb = avg <= 5 ? 1 : 2;
   const int tile_rows = 8 * nb;
   const int64_t max_tiles = (P + tile_rows - 1) / tile_rows + m->E;
   int rc = scratch_ensure(&g_tiles16, sizeof(int32_t) * (size_t)(2 * ((P + 7) / 8 + m->E) + 1 + 64), s, "bq_moe_experts (tile list)");
@@ -628,8 +627,7 @@ int launch_moe_experts_batch(const Moe* m, const void* x, const int32_t* perm, i
   memset(&b, 0, sizeof(b));
   b.codesA = m->down_codes; b.scalesA = m->down_scales; b.x = (const __nv_bfloat16*)hbuf; b.offsets = offsets; b.tiles = tiles;
   b.y = out; b.ldy = m->H; b.N = m->H; b.K = m->F; b.top_k = 1;
-  return nb == 1 ? moe_batch_launch<1>(m, a, b, max_tiles, s) : nb == 2 ? moe_batch_launch<2>(m, a, b, max_tiles, s)
-                                                                          : moe_batch_launch<3>(m, a, b, max_tiles, s);
+  return nb == 1 ? moe_batch_launch<1>(m, a, b, max_tiles, s) : moe_batch_launch<2>(m, a, b, max_tiles, s);
 }
 
 }  // namespace bq
