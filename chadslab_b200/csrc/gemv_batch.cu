@@ -422,10 +422,12 @@ __global__ void __launch_bounds__(GB_THREADS) qgemv_batch_kernel(const __grid_co
 }
 
 // ---- host side ------------------------------------------------------------------------------------------------
-// `with_red`: the area where K-split partials (or the router's logits) meet; a launch without either does not need it
-static size_t gb_smem_bytes(int nb, int64_t K, bool two, bool with_red = true) {
+// (The area where K-split partials meet is part of every launch's request, also of the expert modes that never split K:
+// without it the 16-row expert tile asked for 67 instead of 83 KB, landed on another shared-memory / L1 split and ran
+// 163 -> 210 us on the 128-expert layer at 256 tokens, with either way of rounding the carve-out request.)
+static size_t gb_smem_bytes(int nb, int64_t K, bool two) {
   const int mp = 8 * nb;
-  return (size_t)mp * (K + 32) * 2 + (size_t)mp * 4 + (with_red ? (size_t)(two ? 2 : 1) * GB_WARPS * 16 * mp * 4 : 0);
+  return (size_t)mp * (K + 32) * 2 + (size_t)mp * 4 + (size_t)(two ? 2 : 1) * GB_WARPS * 16 * mp * 4;
 }
 
 bool gemv_batch_supported(int fmt, int64_t N, int64_t K, int x_dtype, int64_t M) {
@@ -463,7 +465,7 @@ static int gb_launch(const GbArgs& a, dim3 grid, bool two, cudaStream_t s) {
 template <int FMT, int NB, int KSPLIT, int MODE, typename YT, bool PIPE>
 static int gb_launch_impl(const GbArgs& a, dim3 grid, bool two, cudaStream_t s) {
   auto kern = qgemv_batch_kernel<FMT, NB, KSPLIT, MODE, YT, PIPE>;
-  const size_t smem = gb_smem_bytes(NB, a.K, two, KSPLIT > 1 || MODE == GB_ROUTE);
+  const size_t smem = gb_smem_bytes(NB, a.K, two);
   // Shared memory and L1 share one array.  The kernel wants both: room for gb_ctas_per_sm CTAs' activation rows AND
   // as much L1 as is left (scales and activations are re-read through it; with the carve-out at its maximum the
   // kernel ran at half speed, with the default one CTA per SM was resident above 48 KB).  So the carve-out asked for
