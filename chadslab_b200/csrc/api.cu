@@ -29,14 +29,7 @@ int fail_cuda(cudaError_t e, const char* what) {
 }
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 void set_last_path(int p) { t_last_path = p; }
-bool pdl_enabled() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("BQ_PDL");
-    v = e ? (atoi(e) != 0) : 1;
-  }
-  return v != 0;
-}
+bool pdl_enabled() { return true; }      // every launch of the library carries the programmatic-serialization attribute
 int device_id() { return g_device; }
 int sm_count() { return g_sms > 0 ? g_sms : SM_COUNT_B200; }
 int* status_word() { return g_status; }

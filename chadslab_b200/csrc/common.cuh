@@ -151,7 +151,7 @@ int attention_mma_ctas_per_sm(bool fused, int D, bool hi);
 int launch_attention_mma(const void* q, const float* qkv, void* k_cache, void* v_cache, const int64_t* pos, void* out, int64_t B,
                          int Hq, int Hkv, int D, int64_t S, float rope_base, int hp, int nsplit, float* part, unsigned* counters,
                          cudaStream_t s);
-bool pdl_enabled();     // BQ_PDL environment switch (default on)
+bool pdl_enabled();     // programmatic dependent launch on every launch of the library
 
 #ifdef __CUDACC__
 // Launch with the programmatic-stream-serialization attribute (the kernel must call pdl_wait() before it reads or
