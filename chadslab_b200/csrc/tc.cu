@@ -1114,18 +1114,19 @@ int launch_qlinear_tc(const uint8_t* codes, const __half* scales, int fmt, int64
   if (rc) return rc;
   T2Args t;
   memset(&t, 0, sizeof(t));
-  // Large batches of int8 weights: pairs of CTAs on 256 x 256 tiles (each stages half of the activation tile), when the
-  // pairs fill at least half the machine.  Measured on the prefill of the 7B shape (8 x 4096 tokens, int8): 956 ms
-  // against 1178 ms with one CTA per tile.  4-bit weights do better with two weight tiles per CTA (below).
+  // Large batches: pairs of CTAs on 256 x 256 tiles (each stages half of the activation tile), when the pairs fill at
+  // least half the machine.  Measured at M = 4096 against one CTA per tile (int8) / two weight tiles per CTA (4-bit):
+  // (12288, 3072) int8 875 TFLOP/s, 4-bit 896 against 823; (16384, 8192) 4-bit 1137 against 1050; the int8 prefill of the
+  // 7B shape (8 x 4096 tokens) 860 ms against 1178 ms.
   const int64_t row_tiles = (N + TC_ROWS - 1) / TC_ROWS;
-  if (fmt == BQ_FMT_Q8G32 && M >= 512 && N >= 2 * TC_ROWS && ((row_tiles + 1) / 2) * ((M + 255) / 256) * 2 >= (int64_t)sm_count()) {
+  if (M >= 512 && N >= 2 * TC_ROWS && ((row_tiles + 1) / 2) * ((M + 255) / 256) * 2 >= (int64_t)sm_count()) {
     if ((rc = x_map(&t.tm_x, g_x16.ptr, M, K, 128))) return rc;
     if ((rc = weight_maps(codes, scales, fmt, N, K, &t.tm_w, &t.tm_s))) return rc;
     t.xscale = (const float*)g_xs.ptr; t.out = y; t.ldy = ldy; t.N = N; t.K = K; t.M = M; t.out_dtype = y_dtype;
     t.status = status_word();
     t.gated_act = gated_act;
     dim3 gridp((unsigned)((row_tiles + 1) / 2 * 2), (unsigned)((M + 255) / 256));
-    return pair_launch<BQ_FMT_Q8G32>(t, gridp, s);
+    return fmt == BQ_FMT_Q8G32 ? pair_launch<BQ_FMT_Q8G32>(t, gridp, s) : pair_launch<BQ_FMT_Q4G32>(t, gridp, s);
   }
   // large batches are bound by the L2 -> SM traffic of codes + activations per multiply-add: 4-bit weights do
   // better with 256 weight rows x 128 batch rows per CTA, int8 with 128 x 256 (measured)
