@@ -292,6 +292,7 @@ struct T2Args {
   // >= 0 (dense only): the weight is a fused gate|up projection whose 16-row blocks hold 8 gate rows followed by the 8
   // up rows of the same outputs; the epilogue stores act(gate) * up (0 = gelu-tanh, 1 = silu) as bf16 [M, N / 2]
   int gated_act;
+  int tile_order;        // pair kernel: which tile index varies fastest over the grid (see the kernel)
 };
 
 __device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
@@ -663,9 +664,12 @@ __global__ void __launch_bounds__(tc_threads(4), 1) qgemm_pair_kernel(const __gr
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = pair_rank();                       // 0 = leader (issues the MMAs), 1 = peer
-  // grid.x counts 128-row weight tiles (padded to an even number), cluster dimension x = 2: rank = blockIdx.x & 1
-  const int64_t n0 = (int64_t)blockIdx.x * TC_ROWS;                       // this CTA's weight rows
-  const int64_t m0 = (int64_t)blockIdx.y * 256, m_end = args.M;           // the pair's batch rows
+  // Cluster dimension x = 2: rank = blockIdx.x & 1.  grid.x / 2 is the index that varies fastest among the pairs that
+  // run together: the 256-row weight tile (tile_order 0: they share an activation tile, right when the weights fit in
+  // L2) or the 256-row batch tile (tile_order 1: they share weight rows, right for a matrix larger than L2 - the head)
+  const int64_t fast = (int64_t)(blockIdx.x >> 1), slow = (int64_t)blockIdx.y;
+  const int64_t n0 = ((args.tile_order ? slow : fast) * 2 + rank) * TC_ROWS;      // this CTA's weight rows
+  const int64_t m0 = (args.tile_order ? fast : slow) * 256, m_end = args.M;       // the pair's batch rows
   const int64_t mx0 = m0 + 128 * (int64_t)rank;                            // the half of them this CTA stages
   const int ksteps = (int)(args.K / T2_BK);
 
@@ -1125,7 +1129,11 @@ int launch_qlinear_tc(const uint8_t* codes, const __half* scales, int fmt, int64
     t.xscale = (const float*)g_xs.ptr; t.out = y; t.ldy = ldy; t.N = N; t.K = K; t.M = M; t.out_dtype = y_dtype;
     t.status = status_word();
     t.gated_act = gated_act;
-    dim3 gridp((unsigned)((row_tiles + 1) / 2 * 2), (unsigned)((M + 255) / 256));
+    // weights that do not fit in L2 while the activations do: batch tiles vary fastest, so a weight tile is read once
+    const int64_t w_bytes = N * (fmt == BQ_FMT_Q8G32 ? K : K / 2), x_bytes = M * K * 2;
+    t.tile_order = (w_bytes > ((int64_t)64 << 20) && x_bytes <= ((int64_t)64 << 20)) ? 1 : 0;
+    const int64_t pairs_n = (row_tiles + 1) / 2, tiles_m = (M + 255) / 256;
+    dim3 gridp((unsigned)(2 * (t.tile_order ? tiles_m : pairs_n)), (unsigned)(t.tile_order ? pairs_n : tiles_m));
     return fmt == BQ_FMT_Q8G32 ? pair_launch<BQ_FMT_Q8G32>(t, gridp, s) : pair_launch<BQ_FMT_Q4G32>(t, gridp, s);
   }
   // large batches are bound by the L2 -> SM traffic of codes + activations per multiply-add: 4-bit weights do
