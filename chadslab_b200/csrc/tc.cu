@@ -121,6 +121,19 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int 
       ::"r"(dst), "l"(tmap), "r"(c0), "r"(c1), "r"(bar)
       : "memory");
 }
+// Tile store shared -> global (bulk async group of the issuing thread).  Rows / columns of the box that fall outside
+// the tensor are not written.
+__device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
+               ::"l"(tmap), "r"(c0), "r"(c1), "r"(src)
+               : "memory");
+}
+// ends the group and waits until the stores issued so far have READ their shared-memory source
+__device__ __forceinline__ void tma_store_drain() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+__device__ __forceinline__ void prefetch_l1(const void* p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -293,6 +306,14 @@ struct T2Args {
   // up rows of the same outputs; the epilogue stores act(gate) * up (0 = gelu-tanh, 1 = silu) as bf16 [M, N / 2]
   int gated_act;
   int tile_order;        // pair kernel: which tile index varies fastest over the grid (see the kernel)
+  // Output through a tile store (dense calls whose output rows are 16-byte aligned): the epilogue transposes the
+  // accumulator into shared memory ([batch row][weight row], the layout of y) and one thread stores the tile with
+  // cp.async.bulk.tensor.  tm_y covers y [M, N] (or [M, N / 2] for a gated call, or the split-K partial slices as
+  // [nz * part_rows, N]); box = 128 (64 gated) x batch rows of a tile.  Plain st.global from the epilogue warps
+  // cost ~130 cycles per warp store (the SM keeps few writes in flight), 2.6 us of a 128 x 64 tile.
+  CUtensorMap tm_y;
+  int tma_store;
+  int64_t part_rows;     // rows per split-K slice in `part` (M rounded up to whole batch tiles when tma_store)
 };
 
 __device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
@@ -333,6 +354,7 @@ __global__ void __launch_bounds__(tc_threads(tc_kq(BN)), (T2Plan<FMT, BN, MODE>:
   constexpr int S = P::S, NA = 2, NW = P::NW;
   constexpr int KQ = tc_kq(BN), CONV_WARPS = 4 * KQ, CPT = 64 / KQ;
   constexpr bool GATED = MODE == 1, DUAL = MODE == 2;
+  static_assert(GATED || NW * BN * 512 <= S * P::STAGE, "the output tile is staged in the stage ring");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* stages = smem;                                  // per stage: [x atom 0][x atom 1][codes tile 0][codes tile 1]
@@ -467,14 +489,63 @@ __global__ void __launch_bounds__(tc_threads(tc_kq(BN)), (T2Plan<FMT, BN, MODE>:
         mbar_arrive(smem_u32(&empty[s]));
       }
     }
+    if (lane < (BN + 31) / 32 && m0 + 32 * lane < m_end) prefetch_l1(args.xscale + m0 + 32 * lane);   // for the epilogue
     if (ok) ok = mbar_wait_warp(smem_u32(acc_full), 0u, abort_flag, lane);
     if (ok) {
       tc_fence_after();
       const int64_t n = n0 + row;
       const uint32_t tbase = tmem_base + ((uint32_t)(lg * 32) << 16);
+      if (!GATED && args.tma_store) {
+        // Transposed tile(s) in the stage ring, which is idle by now (every load has landed and every MMA has
+        // completed): [batch row][128 weight rows] in the output type, or [batch row][64 outputs] bf16 for a gated
+        // call.  Consecutive lanes write consecutive words: no bank conflicts.  One thread stores the tile below.
+        const bool gated = args.gated_act >= 0, f32 = args.kper || args.out_dtype == BQ_DT_F32;
+#pragma unroll 1
+        for (int c0 = 16 * kq; c0 < BN; c0 += 16 * KQ) {
+          if (m0 + c0 >= m_end) break;
+          float xs[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) xs[j] = m0 + c0 + j < m_end ? __ldg(args.xscale + m0 + c0 + j) : 0.0f;
+#pragma unroll
+          for (int w = 0; w < NW; ++w) {
+            uint32_t v[16];
+            tc_ld16(tbase + (uint32_t)(w * BN + c0), v);
+            tc_ld_wait();
+            uint8_t* tile = stages + (size_t)w * BN * 512;
+            if (gated) {
+              __nv_bfloat16* t16 = reinterpret_cast<__nv_bfloat16*>(tile) + (size_t)c0 * 64 + ((row >> 4) * 8 + (row & 7));
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const float f = __uint_as_float(v[j]) * xs[j];
+                const float up = __shfl_xor_sync(0xffffffffu, f, 8);
+                if ((lane & 8) == 0) {
+                  float a;
+                  if (args.gated_act == 0) a = 0.5f * f * (1.0f + tanhf(0.7978845608028654f * (f + 0.044715f * f * f * f)));
+                  else a = f / (1.0f + __expf(-f));
+                  t16[j * 64] = __float2bfloat16_rn(a * up);
+                }
+              }
+            } else if (f32) {
+              float* t32 = reinterpret_cast<float*>(tile) + (size_t)c0 * 128 + row;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) t32[j * 128] = __uint_as_float(v[j]) * xs[j];
+            } else {
+              __nv_bfloat16* t16 = reinterpret_cast<__nv_bfloat16*>(tile) + (size_t)c0 * 128 + row;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) t16[j * 128] = __float2bfloat16_rn(__uint_as_float(v[j]) * xs[j]);
+            }
+          }
+        }
+        fence_async_smem();                     // the tile store below reads these writes through the async proxy
+      } else {
 #pragma unroll 1
       for (int c0 = 16 * kq; c0 < BN; c0 += 16 * KQ) {
         if (m0 + c0 >= m_end) break;
+        // the 16 row back-scales of this chunk, loaded before any store (a load behind a store to memory that may
+        // alias cannot be hoisted by the compiler, and 16 exposed load latencies tripled the epilogue time)
+        float xs[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) xs[j] = m0 + c0 + j < m_end ? __ldg(args.xscale + m0 + c0 + j) : 0.0f;
         if (GATED) {                               // h = silu(gate) * up, rounded to bf16
           uint32_t v[16], u[16];
           tc_ld16(tbase + (uint32_t)c0, v);
@@ -485,7 +556,7 @@ __global__ void __launch_bounds__(tc_threads(tc_kq(BN)), (T2Plan<FMT, BN, MODE>:
             for (int j = 0; j < 16; ++j) {
               const int64_t m = m0 + c0 + j;
               if (m < m_end) {
-                const float rs = args.xscale[m];
+                const float rs = xs[j];
                 const float f = __uint_as_float(v[j]) * rs;
                 const float h = f / (1.0f + __expf(-f)) * (__uint_as_float(u[j]) * rs);
                 reinterpret_cast<__nv_bfloat16*>(args.out)[m * args.ldy + n] = __float2bfloat16_rn(h);
@@ -507,7 +578,7 @@ __global__ void __launch_bounds__(tc_threads(tc_kq(BN)), (T2Plan<FMT, BN, MODE>:
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int64_t m = m0 + c0 + j;
-              const float f = m < m_end ? __uint_as_float(v[j]) * args.xscale[m] : 0.0f;
+              const float f = m < m_end ? __uint_as_float(v[j]) * xs[j] : 0.0f;
               const float up = __shfl_xor_sync(0xffffffffu, f, 8);
               if ((lane & 8) == 0 && m < m_end && nn < args.N) {
                 float a;
@@ -523,8 +594,8 @@ __global__ void __launch_bounds__(tc_threads(tc_kq(BN)), (T2Plan<FMT, BN, MODE>:
             for (int j = 0; j < 16; ++j) {
               const int64_t m = m0 + c0 + j;
               if (m < m_end) {
-                const float f = __uint_as_float(v[j]) * args.xscale[m];
-                if (args.kper) args.part[((int64_t)blockIdx.z * args.M + m) * args.N + nn] = f;
+                const float f = __uint_as_float(v[j]) * xs[j];
+                if (args.kper) args.part[((int64_t)blockIdx.z * args.part_rows + m) * args.N + nn] = f;
                 else if (args.out_dtype == BQ_DT_F32) reinterpret_cast<float*>(args.out)[m * args.ldy + nn] = f;
                 else reinterpret_cast<__nv_bfloat16*>(args.out)[m * args.ldy + nn] = __float2bfloat16_rn(f);
               }
@@ -532,12 +603,22 @@ __global__ void __launch_bounds__(tc_threads(tc_kq(BN)), (T2Plan<FMT, BN, MODE>:
           }
         }
       }
+      }
     }
   }
 
   tc_fence_before();
   __syncthreads();
   if (threadIdx.x == 0 && *abort_flag) atomicExch(args.status, BQ_ERR_TIMEOUT);
+  if (!GATED && args.tma_store && threadIdx.x == 64 && !*abort_flag) {
+    // rows past M and weight rows past N are clipped by the tensor map; a split-K slice keeps whole batch tiles
+    const int ydiv = args.gated_act >= 0 ? 2 : 1;
+    const int yrow = (int)((args.kper ? (int64_t)blockIdx.z * args.part_rows : 0) + m0);
+#pragma unroll
+    for (int w = 0; w < NW; ++w)
+      tma_store_2d(&args.tm_y, smem_u32(stages + (size_t)w * BN * 512), (int)((n0 + w * TC_ROWS) / ydiv), yrow);
+    tma_store_drain();                          // the shared-memory tile must outlive the store's reads
+  }
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)P::TMEM_COLS)
                  : "memory");
@@ -648,6 +729,7 @@ template <int FMT>
 __global__ void __launch_bounds__(tc_threads(4), 1) qgemm_pair_kernel(const __grid_constant__ T2Args args) {
   using P = PairPlan<FMT>;
   constexpr int S = P::S, NA = P::NA;
+  static_assert(256 * 512 <= S * P::STAGE, "the output tile is staged in the stage ring");
   constexpr int KQ = 4, CONV_WARPS = 4 * KQ, CPT = 64 / KQ;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -793,6 +875,7 @@ __global__ void __launch_bounds__(tc_threads(4), 1) qgemm_pair_kernel(const __gr
         mbar_arrive(smem_u32(&empty[s]));
       }
     }
+    if (lane < 8 && m0 + 32 * lane < m_end) prefetch_l1(args.xscale + m0 + 32 * lane);   // for the epilogue
     if (ok) {
       uint32_t fine = 0;
       if (lane == 0) fine = mbar_wait_cluster(smem_u32(acc_full), 0u, abort_flag) ? 1u : 0u;
@@ -802,9 +885,50 @@ __global__ void __launch_bounds__(tc_threads(4), 1) qgemm_pair_kernel(const __gr
       tc_fence_after();
       const int64_t nn = n0 + row;
       const uint32_t tbase = tmem_base + ((uint32_t)(lg * 32) << 16);
+      if (args.tma_store) {
+        // transposed tile in the idle stage ring ([256 batch rows][this CTA's 128 weight rows], or [256][64] bf16 for a
+        // gated call), stored by one thread below: see the single-CTA kernel
+        const bool gated = args.gated_act >= 0, f32 = args.out_dtype == BQ_DT_F32;
+#pragma unroll 1
+        for (int c0 = 16 * kq; c0 < 256; c0 += 16 * KQ) {
+          if (m0 + c0 >= m_end) break;
+          float xs[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) xs[j] = m0 + c0 + j < m_end ? __ldg(args.xscale + m0 + c0 + j) : 0.0f;
+          uint32_t v[16];
+          tc_ld16(tbase + (uint32_t)c0, v);
+          tc_ld_wait();
+          if (gated) {
+            __nv_bfloat16* t16 = reinterpret_cast<__nv_bfloat16*>(stages) + (size_t)c0 * 64 + ((row >> 4) * 8 + (row & 7));
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float f = __uint_as_float(v[j]) * xs[j];
+              const float up = __shfl_xor_sync(0xffffffffu, f, 8);
+              if ((lane & 8) == 0) {
+                float act;
+                if (args.gated_act == 0) act = 0.5f * f * (1.0f + tanhf(0.7978845608028654f * (f + 0.044715f * f * f * f)));
+                else act = f / (1.0f + __expf(-f));
+                t16[j * 64] = __float2bfloat16_rn(act * up);
+              }
+            }
+          } else if (f32) {
+            float* t32 = reinterpret_cast<float*>(stages) + (size_t)c0 * 128 + row;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) t32[j * 128] = __uint_as_float(v[j]) * xs[j];
+          } else {
+            __nv_bfloat16* t16 = reinterpret_cast<__nv_bfloat16*>(stages) + (size_t)c0 * 128 + row;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) t16[j * 128] = __float2bfloat16_rn(__uint_as_float(v[j]) * xs[j]);
+          }
+        }
+        fence_async_smem();
+      } else {
 #pragma unroll 1
       for (int c0 = 16 * kq; c0 < 256; c0 += 16 * KQ) {
         if (m0 + c0 >= m_end) break;
+        float xs[16];                            // back-scales first: see the single-CTA kernel
+#pragma unroll
+        for (int j = 0; j < 16; ++j) xs[j] = m0 + c0 + j < m_end ? __ldg(args.xscale + m0 + c0 + j) : 0.0f;
         uint32_t v[16];
         tc_ld16(tbase + (uint32_t)c0, v);
         tc_ld_wait();
@@ -813,7 +937,7 @@ __global__ void __launch_bounds__(tc_threads(4), 1) qgemm_pair_kernel(const __gr
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int64_t m = m0 + c0 + j;
-            const float f = m < m_end ? __uint_as_float(v[j]) * args.xscale[m] : 0.0f;
+            const float f = m < m_end ? __uint_as_float(v[j]) * xs[j] : 0.0f;
             const float up = __shfl_xor_sync(0xffffffffu, f, 8);
             if ((lane & 8) == 0 && m < m_end && nn < args.N) {
               float act;
@@ -829,12 +953,13 @@ __global__ void __launch_bounds__(tc_threads(4), 1) qgemm_pair_kernel(const __gr
           for (int j = 0; j < 16; ++j) {
             const int64_t m = m0 + c0 + j;
             if (m < m_end) {
-              const float f = __uint_as_float(v[j]) * args.xscale[m];
+              const float f = __uint_as_float(v[j]) * xs[j];
               if (args.out_dtype == BQ_DT_F32) reinterpret_cast<float*>(args.out)[m * args.ldy + nn] = f;
               else reinterpret_cast<__nv_bfloat16*>(args.out)[m * args.ldy + nn] = __float2bfloat16_rn(f);
             }
           }
         }
+      }
       }
     }
   }
@@ -842,6 +967,10 @@ __global__ void __launch_bounds__(tc_threads(4), 1) qgemm_pair_kernel(const __gr
   tc_fence_before();
   __syncthreads();
   if (threadIdx.x == 0 && *abort_flag) atomicExch(args.status, BQ_ERR_TIMEOUT);
+  if (args.tma_store && threadIdx.x == 64 && !*abort_flag) {
+    tma_store_2d(&args.tm_y, smem_u32(stages), (int)(n0 / (args.gated_act >= 0 ? 2 : 1)), (int)m0);
+    tma_store_drain();
+  }
   pair_sync();                          // neither CTA frees tensor memory or leaves while the other may still use it
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)P::TMEM_COLS)
@@ -914,13 +1043,13 @@ __global__ void __launch_bounds__(256) x_prep_kernel(const XT* __restrict__ x, i
 // out[m, n] = sum over z of part[z][m][n], slices added in order (deterministic), stored in the output type
 template <typename YT>
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ part, int nz, int64_t M, int64_t N,
-                                                            YT* __restrict__ out, int64_t ldy) {
+                                                            int64_t part_rows, YT* __restrict__ out, int64_t ldy) {
   pdl_launch_dependents();
   pdl_wait();
-  const int64_t total = M * N;
+  const int64_t total = M * N, zstride = part_rows * N;          // a slice holds part_rows >= M rows
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     float s = part[i];
-    for (int z = 1; z < nz; ++z) s += part[(int64_t)z * total + i];
+    for (int z = 1; z < nz; ++z) s += part[(int64_t)z * zstride + i];
     const int64_t m = i / N, n = i - m * N;
     out[m * ldy + n] = from_float<YT>(s);
   }
@@ -929,7 +1058,8 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
 // Same for a fused gate|up weight (16-column blocks = 8 gate + 8 up values of the same outputs): the slices are added
 // in order and out[m, n / 16 * 8 + n % 8] = act(gate) * up is stored as bf16 [M, N / 2].
 __global__ void __launch_bounds__(256) splitk_reduce_gated_kernel(const float* __restrict__ part, int nz, int64_t M, int64_t N,
-                                                                  __nv_bfloat16* __restrict__ out, int64_t ldy, int act) {
+                                                                  int64_t part_rows, __nv_bfloat16* __restrict__ out, int64_t ldy,
+                                                                  int act) {
   pdl_launch_dependents();
   pdl_wait();
   const int64_t half = N / 2, total = M * half;
@@ -938,7 +1068,7 @@ __global__ void __launch_bounds__(256) splitk_reduce_gated_kernel(const float* _
     const int64_t ng = (c >> 3) * 16 + (c & 7);
     float g = 0.0f, u = 0.0f;
     for (int z = 0; z < nz; ++z) {
-      const float* p = part + ((int64_t)z * M + m) * N + ng;
+      const float* p = part + ((int64_t)z * part_rows + m) * N + ng;
       g += p[0];
       u += p[8];
     }
@@ -963,7 +1093,7 @@ int tc_reserve(int64_t rows, int64_t K, int64_t N) {
   int rc = ensure_x_scratch(rows, K, 0);
   if (rc) return rc;
   // split-K partial tiles are bounded by TC_PART_BYTES whatever the shape
-  size_t part = (size_t)rows * N * 4 * sizeof(float);
+  size_t part = (size_t)((rows + 255) / 256 * 256) * N * 4 * sizeof(float);      // slices hold whole batch tiles
   if (part > TC_PART_BYTES) part = TC_PART_BYTES;
   return scratch_ensure(&g_part, part, 0, "tcgen05 path (split-K partial tiles)");
 }
@@ -1109,6 +1239,18 @@ static int t2_dispatch(const T2Args& a, int bn, dim3 grid, cudaStream_t s) {
   }
 }
 
+// Tensor map of the output for the epilogue's tile store: `cols` elements per row (fp32 or bf16), row stride ld
+// elements, box = box_cols x box_rows.  Returns false (plain stores are used) when the rows are not 16-byte aligned.
+static bool out_map(CUtensorMap* tm, void* base, bool f32, int64_t cols, int64_t rows, int64_t ld, int box_cols, int box_rows,
+                    int* rc) {
+  const int es = f32 ? 4 : 2;
+  *rc = BQ_OK;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (ld * es) % 16 != 0) return false;
+  *rc = make_map_2d(tm, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, base, (uint64_t)cols,
+                    (uint64_t)rows, (uint64_t)ld * es, (uint32_t)box_cols, (uint32_t)box_rows, CU_TENSOR_MAP_SWIZZLE_NONE);
+  return *rc == BQ_OK;
+}
+
 int launch_qlinear_tc(const uint8_t* codes, const __half* scales, int fmt, int64_t N, int64_t K, const void* x,
                       int x_dtype, int64_t M, void* y, int y_dtype, int64_t ldy, cudaStream_t s, int gated_act) {
   if (x_dtype != BQ_DT_BF16) return fail(BQ_ERR_UNSUPPORTED, "tensor path takes bf16 activations");
@@ -1129,6 +1271,9 @@ int launch_qlinear_tc(const uint8_t* codes, const __half* scales, int fmt, int64
     t.xscale = (const float*)g_xs.ptr; t.out = y; t.ldy = ldy; t.N = N; t.K = K; t.M = M; t.out_dtype = y_dtype;
     t.status = status_word();
     t.gated_act = gated_act;
+    t.tma_store = out_map(&t.tm_y, y, gated_act < 0 && y_dtype == BQ_DT_F32, gated_act >= 0 ? N / 2 : N, M, ldy,
+                          gated_act >= 0 ? 64 : 128, 256, &rc) ? 1 : 0;
+    if (rc) return rc;
     // weights that do not fit in L2 while the activations do: batch tiles vary fastest, so a weight tile is read once
     const int64_t w_bytes = N * (fmt == BQ_FMT_Q8G32 ? K : K / 2), x_bytes = M * K * 2;
     t.tile_order = (w_bytes > ((int64_t)64 << 20) && x_bytes <= ((int64_t)64 << 20)) ? 1 : 0;
@@ -1156,20 +1301,32 @@ int launch_qlinear_tc(const uint8_t* codes, const __half* scales, int fmt, int64
   const int64_t ctas = (int64_t)grid2.x * grid2.y, ksteps_all = K / T2_BK;
   int nz = 1;
   const int64_t slots = (int64_t)sm_count() * (bn <= 64 ? 2 : 1);       // CTAs of this tile size that are resident at once
+  // a slice of partial products holds whole batch tiles when the tiles are stored with the tile-store epilogue
+  const int64_t part_rows = (N % 4 == 0) ? (int64_t)grid2.x * bx : M;
+  t.part_rows = part_rows;
   if (!two && slots / ctas >= 2 && ksteps_all >= 8) {
     int64_t want = slots / ctas;                                       // one wave of slices
     if (want > ksteps_all / 4) want = ksteps_all / 4;
-    while (want > 1 && (size_t)want * M * N * sizeof(float) > TC_PART_BYTES) --want;
+    while (want > 1 && (size_t)want * part_rows * N * sizeof(float) > TC_PART_BYTES) --want;
     if (want > 1) {
       int64_t kper = ((ksteps_all + want - 1) / want + 1) & ~(int64_t)1;
       nz = (int)((ksteps_all + kper - 1) / kper);
       if (nz > 1) {
-        if ((rc = scratch_ensure(&g_part, (size_t)nz * M * N * sizeof(float), s, "tcgen05 path (split-K partial tiles)")))
+        if ((rc = scratch_ensure(&g_part, (size_t)nz * part_rows * N * sizeof(float), s, "tcgen05 path (split-K partial tiles)")))
           return rc;
         t.kper = (int)kper; t.part = (float*)g_part.ptr; grid2.z = (unsigned)nz;
         t.gated_act = -1;                       // the slices are plain partial products; the reduction applies the activation
+        t.tma_store = (N % 4 == 0 && out_map(&t.tm_y, g_part.ptr, true, N, (int64_t)nz * part_rows, N, 128, bx, &rc)) ? 1 : 0;
+        if (rc) return rc;
       }
     }
+  }
+  // (a single wave of 256-row batch tiles ends with one thread storing 128 KB while nothing else runs: measured
+  // slower than plain stores there, faster everywhere else)
+  if (nz <= 1 && !(bx == 256 && ctas < 2 * slots)) {
+    t.tma_store = out_map(&t.tm_y, y, gated_act < 0 && y_dtype == BQ_DT_F32, gated_act >= 0 ? N / 2 : N, M, ldy,
+                          gated_act >= 0 ? 64 : 128, bx, &rc) ? 1 : 0;
+    if (rc) return rc;
   }
   rc = fmt == BQ_FMT_Q8G32 ? t2_dispatch<BQ_FMT_Q8G32>(t, sel, grid2, s) : t2_dispatch<BQ_FMT_Q4G32>(t, sel, grid2, s);
   if (rc || nz <= 1) return rc;
@@ -1177,13 +1334,13 @@ int launch_qlinear_tc(const uint8_t* codes, const __half* scales, int fmt, int64
   if (rg > (int64_t)sm_count() * 8) rg = (int64_t)sm_count() * 8;
   if (gated_act >= 0)
     BQ_CUDA(launch_chain(splitk_reduce_gated_kernel, dim3((unsigned)rg), dim3(256), 0, s, 1, (const float*)g_part.ptr, nz, M, N,
-                         (__nv_bfloat16*)y, ldy, gated_act));
+                         part_rows, (__nv_bfloat16*)y, ldy, gated_act));
   else if (y_dtype == BQ_DT_F32)
     BQ_CUDA(launch_chain(splitk_reduce_kernel<float>, dim3((unsigned)rg), dim3(256), 0, s, 1, (const float*)g_part.ptr, nz, M, N,
-                         (float*)y, ldy));
+                         part_rows, (float*)y, ldy));
   else
     BQ_CUDA(launch_chain(splitk_reduce_kernel<__nv_bfloat16>, dim3((unsigned)rg), dim3(256), 0, s, 1, (const float*)g_part.ptr, nz, M,
-                         N, (__nv_bfloat16*)y, ldy));
+                         N, part_rows, (__nv_bfloat16*)y, ldy));
   count_launch();
   BQ_CUDA(cudaGetLastError());
   return BQ_OK;
