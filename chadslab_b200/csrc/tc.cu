@@ -133,7 +133,6 @@ __device__ __forceinline__ void tma_store_drain() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
   asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
-__device__ __forceinline__ void prefetch_l1(const void* p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -406,6 +405,29 @@ __global__ void __launch_bounds__(tc_threads(tc_kq(BN)), (T2Plan<FMT, BN, MODE>:
   // Programmatic dependent launch: barriers and tensor memory are set up while the preceding kernel drains; nothing
   // it wrote (activations, tile list) has been read yet, and nothing is written before this point.
   pdl_launch_dependents();
+  // The weights do not depend on the preceding kernel: a dense call requests the codes and scales of its first stages
+  // before waiting for it, so that their latency runs under its tail (the activations follow after the wait).
+  auto load_weights = [&](int ks, uint32_t fb) {
+    const int s = ks % S, kg = k0 + ks;               // kg: step index in the whole K (k0 is even)
+    uint8_t* st = stages + s * P::STAGE;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) {
+      const int nrow = (int)n0 + (DUAL ? w * TC_ROWS : 0);
+      tma_load_2d(smem_u32(st + P::XT + w * P::RAW), tmw[w], kg * P::RAW_ROW, nrow, fb);
+      if ((ks & 1) == 0)
+        tma_load_2d(smem_u32(sc_tiles + (((ks >> 1) % TC_SC_SLOTS) * NW + w) * P::SCT), tms[w], (kg >> 1) * 8, nrow, fb);
+    }
+  };
+  auto stage_bytes = [&](int ks) { return (uint32_t)(NW * P::RAW + P::XT + ((ks & 1) == 0 ? NW * P::SCT : 0)); };
+  int early = 0;
+  if (warp == 0 && lane == 0 && !args.moe) {
+    early = ksteps < S ? ksteps : S;
+    for (int ks = 0; ks < early; ++ks) {
+      const uint32_t fb = smem_u32(&full[ks % S]);
+      mbar_expect_tx(fb, stage_bytes(ks));
+      load_weights(ks, fb);
+    }
+  }
   pdl_wait();
 
   if (warp == 0) {
@@ -414,21 +436,16 @@ __global__ void __launch_bounds__(tc_threads(tc_kq(BN)), (T2Plan<FMT, BN, MODE>:
       for (int ks = 0; ks < ksteps; ++ks) {
         const int s = ks % S;
         const uint32_t ph = (uint32_t)(ks / S) & 1u;
-        if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1u, abort_flag)) break;
-        const bool with_scales = (ks & 1) == 0;
         const uint32_t fb = smem_u32(&full[s]);
-        mbar_expect_tx(fb, NW * P::RAW + P::XT + (with_scales ? NW * P::SCT : 0));
+        if (ks >= early) {
+          if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1u, abort_flag)) break;
+          mbar_expect_tx(fb, stage_bytes(ks));
+        }
         uint8_t* st = stages + s * P::STAGE;
-        const int kg = k0 + ks;                       // step index in the whole K (k0 is even)
+        const int kg = k0 + ks;
         tma_load_2d(smem_u32(st), &args.tm_x, kg * T2_BK, (int)m0, fb);
         tma_load_2d(smem_u32(st + BN * 128), &args.tm_x, kg * T2_BK + 64, (int)m0, fb);
-#pragma unroll
-        for (int w = 0; w < NW; ++w) {
-          const int nrow = (int)n0 + (DUAL ? w * TC_ROWS : 0);
-          tma_load_2d(smem_u32(st + P::XT + w * P::RAW), tmw[w], kg * P::RAW_ROW, nrow, fb);
-          if (with_scales)
-            tma_load_2d(smem_u32(sc_tiles + (((ks >> 1) % TC_SC_SLOTS) * NW + w) * P::SCT), tms[w], (kg >> 1) * 8, nrow, fb);
-        }
+        if (ks >= early) load_weights(ks, fb);
       }
       if (*abort_flag) {
         for (int i = 0; i < 64; ++i) __nanosleep(1000);
@@ -489,7 +506,6 @@ __global__ void __launch_bounds__(tc_threads(tc_kq(BN)), (T2Plan<FMT, BN, MODE>:
         mbar_arrive(smem_u32(&empty[s]));
       }
     }
-    if (lane < (BN + 31) / 32 && m0 + 32 * lane < m_end) prefetch_l1(args.xscale + m0 + 32 * lane);   // for the epilogue
     if (ok) ok = mbar_wait_warp(smem_u32(acc_full), 0u, abort_flag, lane);
     if (ok) {
       tc_fence_after();
@@ -779,6 +795,22 @@ __global__ void __launch_bounds__(tc_threads(4), 1) qgemm_pair_kernel(const __gr
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   pdl_launch_dependents();
+  // codes and scales of the first stages are requested before the wait for the preceding kernel (see the single-CTA kernel)
+  auto load_weights = [&](int ks, uint32_t fb) {
+    tma_load_2d(smem_u32(stages + (ks % S) * P::STAGE + P::XT), &args.tm_w, ks * P::RAW_ROW, (int)n0, fb);
+    if ((ks & 1) == 0)
+      tma_load_2d(smem_u32(sc_tiles + ((ks >> 1) % TC_SC_SLOTS) * P::SCT), &args.tm_s, (ks >> 1) * 8, (int)n0, fb);
+  };
+  auto stage_bytes = [&](int ks) { return (uint32_t)(P::RAW + P::XT + ((ks & 1) == 0 ? P::SCT : 0)); };
+  int early = 0;
+  if (warp == 0 && lane == 0) {
+    early = ksteps < S ? ksteps : S;
+    for (int ks = 0; ks < early; ++ks) {
+      const uint32_t fb = smem_u32(&full[ks % S]);
+      mbar_expect_tx(fb, stage_bytes(ks));
+      load_weights(ks, fb);
+    }
+  }
   pdl_wait();
 
   if (warp == 0) {
@@ -787,16 +819,15 @@ __global__ void __launch_bounds__(tc_threads(4), 1) qgemm_pair_kernel(const __gr
       for (int ks = 0; ks < ksteps; ++ks) {
         const int s = ks % S;
         const uint32_t ph = (uint32_t)(ks / S) & 1u;
-        if (!mbar_wait_cluster(smem_u32(&empty[s]), ph ^ 1u, abort_flag)) break;
-        const bool with_scales = (ks & 1) == 0;
         const uint32_t fb = smem_u32(&full[s]);
-        mbar_expect_tx(fb, P::RAW + P::XT + (with_scales ? P::SCT : 0));
+        if (ks >= early) {
+          if (!mbar_wait_cluster(smem_u32(&empty[s]), ph ^ 1u, abort_flag)) break;
+          mbar_expect_tx(fb, stage_bytes(ks));
+        }
         uint8_t* st = stages + s * P::STAGE;
         tma_load_2d(smem_u32(st), &args.tm_x, ks * T2_BK, (int)mx0, fb);
         tma_load_2d(smem_u32(st + 128 * 128), &args.tm_x, ks * T2_BK + 64, (int)mx0, fb);
-        tma_load_2d(smem_u32(st + P::XT), &args.tm_w, ks * P::RAW_ROW, (int)n0, fb);
-        if (with_scales)
-          tma_load_2d(smem_u32(sc_tiles + ((ks >> 1) % TC_SC_SLOTS) * P::SCT), &args.tm_s, (ks >> 1) * 8, (int)n0, fb);
+        if (ks >= early) load_weights(ks, fb);
       }
       if (*abort_flag) {
         for (int i = 0; i < 64; ++i) __nanosleep(1000);
@@ -875,7 +906,6 @@ __global__ void __launch_bounds__(tc_threads(4), 1) qgemm_pair_kernel(const __gr
         mbar_arrive(smem_u32(&empty[s]));
       }
     }
-    if (lane < 8 && m0 + 32 * lane < m_end) prefetch_l1(args.xscale + m0 + 32 * lane);   // for the epilogue
     if (ok) {
       uint32_t fine = 0;
       if (lane == 0) fine = mbar_wait_cluster(smem_u32(acc_full), 0u, abort_flag) ? 1u : 0u;
