@@ -259,20 +259,23 @@ decode_attention_kernel(const T* __restrict__ q, const float* __restrict__ qkv, 
   const int64_t row_stride = (int64_t)Hkv * D;
   const T* kbase = k_cache + ((int64_t)b * S * Hkv + kv) * D + d0;
   const T* vbase = v_cache + ((int64_t)b * S * Hkv + kv) * D + d0;
-  for (int64_t s0 = p_lo + (int64_t)warp * ATT_PB; s0 < n_pos; s0 += ATT_WARPS * ATT_PB) {
+  // positions and the row stride as 32-bit values: one widening multiply-add per row address
+  const int n_pos32 = (int)n_pos, rs32 = (int)row_stride;
+  const bool b16 = (lane & 16) != 0, b8 = (lane & 8) != 0;
+  for (int s0 = (int)p_lo + warp * ATT_PB; s0 < n_pos32; s0 += ATT_WARPS * ATT_PB) {
     // all K and V rows of the trip are requested before anything is computed
     RawRow<T> kr[ATT_PB], vr[ATT_PB];
     float dot[ATT_PB];
     if (live) {
 #pragma unroll
       for (int j = 0; j < ATT_PB; ++j) {
-        const int64_t sidx = s0 + j < n_pos ? s0 + j : n_pos - 1;       // clamp: masked below
-        kr[j] = load_raw(kbase + sidx * row_stride);
+        const int sidx = s0 + j < n_pos32 ? s0 + j : n_pos32 - 1;       // clamp: masked below
+        kr[j] = load_raw(kbase + (int64_t)sidx * rs32);
       }
 #pragma unroll
       for (int j = 0; j < ATT_PB; ++j) {
-        const int64_t sidx = s0 + j < n_pos ? s0 + j : n_pos - 1;
-        vr[j] = load_raw(vbase + sidx * row_stride);
+        const int sidx = s0 + j < n_pos32 ? s0 + j : n_pos32 - 1;
+        vr[j] = load_raw(vbase + (int64_t)sidx * rs32);
       }
     }
 #pragma unroll
@@ -284,9 +287,28 @@ decode_attention_kernel(const T* __restrict__ q, const float* __restrict__ qkv, 
 #pragma unroll
         for (int i = 0; i < ATT_EPL; ++i) dsum += qv[i] * kf[i];
       }
+      dot[j] = dsum;
+    }
+    // The 4 partial dot products of a lane are summed over the warp together: two halving exchanges leave each group
+    // of 8 lanes with one row, three more steps sum it, four broadcasts hand every lane all 4 sums (10 shuffles
+    // instead of 20).
+    static_assert(ATT_PB == 4, "the warp reduction folds exactly 4 rows");
+    {
+      float a0 = b16 ? dot[2] : dot[0], a1 = b16 ? dot[3] : dot[1];
+      const float t0 = b16 ? dot[0] : dot[2], t1 = b16 ? dot[1] : dot[3];
+      a0 += __shfl_xor_sync(0xffffffffu, t0, 16);
+      a1 += __shfl_xor_sync(0xffffffffu, t1, 16);
+      float c = b8 ? a1 : a0;
+      const float t = b8 ? a0 : a1;
+      c += __shfl_xor_sync(0xffffffffu, t, 8);
+      c += __shfl_xor_sync(0xffffffffu, c, 4);
+      c += __shfl_xor_sync(0xffffffffu, c, 2);
+      c += __shfl_xor_sync(0xffffffffu, c, 1);
 #pragma unroll
-      for (int off = 16; off > 0; off >>= 1) dsum += __shfl_xor_sync(0xffffffffu, dsum, off);
-      dot[j] = s0 + j < n_pos ? dsum : -INFINITY;
+      for (int j = 0; j < ATT_PB; ++j) {
+        const float d = __shfl_sync(0xffffffffu, c, (j >> 1) * 16 + (j & 1) * 8);
+        dot[j] = s0 + j < n_pos32 ? d : -INFINITY;
+      }
     }
     float nm = mx;
 #pragma unroll
@@ -641,8 +663,9 @@ static int launch_attention(const void* q, const float* qkv, void* k_cache, void
                             int64_t B, int Hq, int Hkv, int D, int64_t S, float rope_base, int dtype, void* stream) {
   int rc = glue_ready(dtype);
   if (rc) return rc;
-  if (B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || D <= 0 || D > ATT_MAXD || (D % 8) || S <= 0)
-    return fail(BQ_ERR_ARG, "bad sizes (head_dim <= 256 and a multiple of 8, Hq a multiple of Hkv)");
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || D <= 0 || D > ATT_MAXD || (D % 8) || S <= 0 || S >= ((int64_t)1 << 31) ||
+      (int64_t)Hkv * D >= ((int64_t)1 << 31))
+    return fail(BQ_ERR_ARG, "bad sizes (head_dim <= 256 and a multiple of 8, Hq a multiple of Hkv, fewer than 2^31 positions)");
   if (!k_cache || !v_cache || !pos || !out) return fail(BQ_ERR_ARG, "null pointer");
   // grouped-query attention: one CTA serves hpw query heads of a KV head (K / V rows fetched once for all of them)
   const int rep = Hq / Hkv;
