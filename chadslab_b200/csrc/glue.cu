@@ -160,7 +160,6 @@ __global__ void __launch_bounds__(128) rope_kv_append_kernel(const float* __rest
 constexpr int ATT_WARPS = 8;
 constexpr int ATT_MAXD = 256;
 constexpr int ATT_EPL = 8;
-constexpr int ATT_PB = 4;
 // a row's 8 elements as loaded (converted to fp32 only where they are used, so that the K and V rows of a whole
 // trip can be in flight together without a register per element)
 template <typename T> struct RawRow;
@@ -211,8 +210,8 @@ __device__ __forceinline__ void rope8(const float* __restrict__ src, int d0, int
 // [B, (Hq + 2 Hkv) D], the fused projection's output), rotated here; the cache supplies positions < pos only and
 // the CTA of the first query head of each KV group appends the new rows to it.  One launch instead of
 // rope_kv_append_kernel + this kernel.
-template <typename T, bool FUSED>
-__global__ void __launch_bounds__(ATT_WARPS * 32)
+template <typename T, bool FUSED, int PB>
+__global__ void __launch_bounds__(ATT_WARPS * 32, (PB == 8 || sizeof(T) == 4) ? 2 : 3)
 decode_attention_kernel(const T* __restrict__ q, const float* __restrict__ qkv, T* __restrict__ k_cache,
                         T* __restrict__ v_cache, const int64_t* __restrict__ pos_p, T* __restrict__ out, int Hq, int Hkv,
                         int D, int64_t S, float rope_base, float* __restrict__ part, unsigned* __restrict__ counters,
@@ -238,7 +237,7 @@ decode_attention_kernel(const T* __restrict__ q, const float* __restrict__ qkv, 
     }
     __syncthreads();
   }
-  const int64_t per = ((n_all + nsplit - 1) / nsplit + ATT_PB - 1) / ATT_PB * ATT_PB;
+  const int64_t per = ((n_all + nsplit - 1) / nsplit + PB - 1) / PB * PB;
   const int64_t p_lo = (int64_t)z * per;
   const int64_t n_own = p_lo + per < n_all ? p_lo + per : n_all;        // this CTA covers [p_lo, n_own)
   // FUSED: the current position (n_all - 1) is not in the cache yet; the CTA that owns it adds it after the loop
@@ -262,24 +261,24 @@ decode_attention_kernel(const T* __restrict__ q, const float* __restrict__ qkv, 
   // positions and the row stride as 32-bit values: one widening multiply-add per row address
   const int n_pos32 = (int)n_pos, rs32 = (int)row_stride;
   const bool b16 = (lane & 16) != 0, b8 = (lane & 8) != 0;
-  for (int s0 = (int)p_lo + warp * ATT_PB; s0 < n_pos32; s0 += ATT_WARPS * ATT_PB) {
+  for (int s0 = (int)p_lo + warp * PB; s0 < n_pos32; s0 += ATT_WARPS * PB) {
     // all K and V rows of the trip are requested before anything is computed
-    RawRow<T> kr[ATT_PB], vr[ATT_PB];
-    float dot[ATT_PB];
+    RawRow<T> kr[PB], vr[PB];
+    float dot[PB];
     if (live) {
 #pragma unroll
-      for (int j = 0; j < ATT_PB; ++j) {
+      for (int j = 0; j < PB; ++j) {
         const int sidx = s0 + j < n_pos32 ? s0 + j : n_pos32 - 1;       // clamp: masked below
         kr[j] = load_raw(kbase + (int64_t)sidx * rs32);
       }
 #pragma unroll
-      for (int j = 0; j < ATT_PB; ++j) {
+      for (int j = 0; j < PB; ++j) {
         const int sidx = s0 + j < n_pos32 ? s0 + j : n_pos32 - 1;
         vr[j] = load_raw(vbase + (int64_t)sidx * rs32);
       }
     }
 #pragma unroll
-    for (int j = 0; j < ATT_PB; ++j) {
+    for (int j = 0; j < PB; ++j) {
       float dsum = 0.0f;
       if (live) {
         float kf[ATT_EPL];
@@ -289,13 +288,14 @@ decode_attention_kernel(const T* __restrict__ q, const float* __restrict__ qkv, 
       }
       dot[j] = dsum;
     }
-    // The 4 partial dot products of a lane are summed over the warp together: two halving exchanges leave each group
-    // of 8 lanes with one row, three more steps sum it, four broadcasts hand every lane all 4 sums (10 shuffles
-    // instead of 20).
-    static_assert(ATT_PB == 4, "the warp reduction folds exactly 4 rows");
-    {
-      float a0 = b16 ? dot[2] : dot[0], a1 = b16 ? dot[3] : dot[1];
-      const float t0 = b16 ? dot[0] : dot[2], t1 = b16 ? dot[1] : dot[3];
+    // The partial dot products of a lane are summed over the warp four rows at a time: two halving exchanges leave
+    // each group of 8 lanes with one row, three more steps sum it, four broadcasts hand every lane all 4 sums (10
+    // shuffles instead of 20).
+    static_assert(PB % 4 == 0, "the warp reduction folds 4 rows at a time");
+#pragma unroll
+    for (int q4 = 0; q4 < PB; q4 += 4) {
+      float a0 = b16 ? dot[q4 + 2] : dot[q4 + 0], a1 = b16 ? dot[q4 + 3] : dot[q4 + 1];
+      const float t0 = b16 ? dot[q4 + 0] : dot[q4 + 2], t1 = b16 ? dot[q4 + 1] : dot[q4 + 3];
       a0 += __shfl_xor_sync(0xffffffffu, t0, 16);
       a1 += __shfl_xor_sync(0xffffffffu, t1, 16);
       float c = b8 ? a1 : a0;
@@ -305,20 +305,20 @@ decode_attention_kernel(const T* __restrict__ q, const float* __restrict__ qkv, 
       c += __shfl_xor_sync(0xffffffffu, c, 2);
       c += __shfl_xor_sync(0xffffffffu, c, 1);
 #pragma unroll
-      for (int j = 0; j < ATT_PB; ++j) {
+      for (int j = 0; j < 4; ++j) {
         const float d = __shfl_sync(0xffffffffu, c, (j >> 1) * 16 + (j & 1) * 8);
-        dot[j] = s0 + j < n_pos32 ? d : -INFINITY;
+        dot[q4 + j] = s0 + q4 + j < n_pos32 ? d : -INFINITY;
       }
     }
     float nm = mx;
 #pragma unroll
-    for (int j = 0; j < ATT_PB; ++j) nm = fmaxf(nm, dot[j]);
+    for (int j = 0; j < PB; ++j) nm = fmaxf(nm, dot[j]);
     const float corr = __expf(mx - nm);
     sum *= corr;
 #pragma unroll
     for (int i = 0; i < ATT_EPL; ++i) acc[i] *= corr;
 #pragma unroll
-    for (int j = 0; j < ATT_PB; ++j) {
+    for (int j = 0; j < PB; ++j) {
       const float p = __expf(dot[j] - nm);                                   // 0 for masked positions
       sum += p;
       if (live) {
@@ -417,7 +417,7 @@ decode_attention_kernel(const T* __restrict__ q, const float* __restrict__ qkv, 
 // Grouped-query variant: one CTA serves `hpw` query heads of one KV head, so a K / V row is fetched once for all of
 // them instead of once per query head.  A warp's lanes are split as (head hl, chunk c): lane = hl * (32 / hpw) + c
 // owns EPLN = D * hpw / 32 consecutive head-dim elements of head hl; the lanes of different heads read the same K / V
-// bytes (one transaction).  Positions are walked as in the kernel above (a warp takes ATT_PB per trip, online softmax,
+// bytes (one transaction).  Positions are walked as in the kernel above (a warp takes PB per trip, online softmax,
 // the 8 warps' states merge through shared memory, optional split over gridDim.z with a last-arrival merge).
 // grid.x = Hkv * (rep / hpw): KV head kv = blockIdx.x / (rep / hpw), query heads kv * rep + hg * hpw + hl.
 template <typename T, int N> struct RawVec { uint4 v[N * (int)sizeof(T) / 16]; };
@@ -692,13 +692,22 @@ static int launch_attention(const void* q, const float* qkv, void* k_cache, void
   const int64_t min_pos = mma ? 64 : 128, max_split = mma ? 64 : 32;
   int64_t ns_max = S / min_pos < max_split ? S / min_pos : max_split;
   if (ns_max < 1) ns_max = 1;
-  const int64_t slots = (int64_t)sm_count() * (mma ? attention_mma_ctas_per_sm(qkv != nullptr, D, hp > 8) : 3);
+  // The one-head-per-CTA kernel on bf16 caches with at least a full wave of (batch row, head) pairs keeps 8 positions
+  // (16 rows) per warp in flight: 120 registers, two CTAs per SM, and being bound by memory then it pays for a partly
+  // filled wave only while there are fewer than two of them.  Same box, step of the 7B shape at 2048 positions:
+  // batch 64 13.15 -> 12.90 ms, batch 32 8.27 -> 8.21; smaller grids lose with it (batch 16 5.85 -> 5.97, batch 8
+  // 3.88 -> 4.32: fewer warps to overlap arithmetic with loads) and keep 4 positions per trip, three CTAs per SM.
+  const bool wide = !mma && !gqa && dtype == BQ_DT_BF16 && ctas_xy >= 3 * (int64_t)sm_count();
+  const int64_t slots = (int64_t)sm_count() * (mma ? attention_mma_ctas_per_sm(qkv != nullptr, D, hp > 8) : wide ? 2 : 3);
   const int64_t fixed = mma ? 256 : 96;      // the tensor-path CTA rotates and stages up to 16 query heads and merges 4 warps x 16 heads
-  int64_t nsplit = 1, best_cost = -1;
+  int64_t nsplit = 1;
+  double best_cost = -1.0;
   for (int64_t ns = 1; ns <= ns_max; ++ns) {
-    const int64_t waves = (ctas_xy * ns + slots - 1) / slots;
-    const int64_t cost = waves * ((S + ns - 1) / ns + fixed);
-    if (best_cost < 0 || cost < best_cost) { nsplit = ns; best_cost = cost; }
+    const int64_t whole = (ctas_xy * ns + slots - 1) / slots;
+    const double frac = (double)(ctas_xy * ns) / (double)slots;
+    const double waves = wide && frac >= 2.0 ? frac : (double)whole;
+    const double cost = waves * (double)((S + ns - 1) / ns + fixed);
+    if (best_cost < 0.0 || cost < best_cost) { nsplit = ns; best_cost = cost; }
   }
   cudaStream_t s = (cudaStream_t)stream;
   if (nsplit > 1) {
@@ -727,13 +736,15 @@ static int launch_attention(const void* q, const float* qkv, void* k_cache, void
     return BQ_OK;
   }
   dim3 grid((unsigned)Hq, (unsigned)B, (unsigned)nsplit);
-#define BQ_ATT_LAUNCH(TT, FUSED)                                                                                        \
-  BQ_CUDA(launch_chain(decode_attention_kernel<TT, FUSED>, grid, dim3(ATT_WARPS * 32), 0, s, 1, (const TT*)q, qkv, (TT*)k_cache, \
+#define BQ_ATT_LAUNCH(TT, FUSED, PB)                                                                                    \
+  BQ_CUDA(launch_chain(decode_attention_kernel<TT, FUSED, PB>, grid, dim3(ATT_WARPS * 32), 0, s, 1, (const TT*)q, qkv, (TT*)k_cache, \
                        (TT*)v_cache, pos, (TT*)out, Hq, Hkv, D, S, rope_base, part, counters, status_word()))
   if (dtype == BQ_DT_F32) {
-    if (qkv) BQ_ATT_LAUNCH(float, true); else BQ_ATT_LAUNCH(float, false);
+    if (qkv) BQ_ATT_LAUNCH(float, true, 4); else BQ_ATT_LAUNCH(float, false, 4);
+  } else if (wide) {
+    if (qkv) BQ_ATT_LAUNCH(__nv_bfloat16, true, 8); else BQ_ATT_LAUNCH(__nv_bfloat16, false, 8);
   } else {
-    if (qkv) BQ_ATT_LAUNCH(__nv_bfloat16, true); else BQ_ATT_LAUNCH(__nv_bfloat16, false);
+    if (qkv) BQ_ATT_LAUNCH(__nv_bfloat16, true, 4); else BQ_ATT_LAUNCH(__nv_bfloat16, false, 4);
   }
 #undef BQ_ATT_LAUNCH
   count_launch();
