@@ -16,9 +16,10 @@ import os
 
 
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one decode_attention_kernel launch under ncu, and the K/V
-# bytes that launch streams: batch 8, 16 query / 16 KV heads x 256, 2048 positions, bf16 cache.
-NCU_ATT_TRAFFIC_MB = 272.96
-NCU_ATT_ALGORITHMIC_MB = 268.57
+# bytes that launch streams: batch 32, 16 query / 16 KV heads x 256, 2048 positions, bf16 cache (the 8-positions-per-trip
+# variant the headline step runs).
+NCU_ATT_TRAFFIC_MB = 1081.77
+NCU_ATT_ALGORITHMIC_MB = 1074.27
 
 
 def _flush_l2(torch, buf):
@@ -114,7 +115,7 @@ def _headline(torch, dist, rank, world, dec, cfg, B, ctx, step, tokens, steps, m
     aach = att_bytes / aus / 1e3
     attn = {"bound": "hbm", "achieved": round(aach, 1), "peak": peak, "unit": "GB/s", "frac": round(aach / peak, 4),
             "traffic": int(att_bytes * NCU_ATT_TRAFFIC_MB / NCU_ATT_ALGORITHMIC_MB),
-            "traffic_source": (f"scaled, not re-measured in this run: one ncu capture of this kernel at batch 8 (16 heads x 256, 2048 positions) "
+            "traffic_source": (f"scaled, not re-measured in this run: one ncu capture of this kernel at batch 32 (16 heads x 256, 2048 positions) "
                                f"read + wrote {NCU_ATT_TRAFFIC_MB} MB of DRAM for {NCU_ATT_ALGORITHMIC_MB} MB of K/V rows; the traffic is "
                                "proportional to the rows streamed"),
             "peak_source": src, "kernel": f"decode attention of one layer: batch {B}, {dec.h_local} query / {dec.kv_local} KV heads x "
