@@ -273,3 +273,39 @@ def test_tensor_path_split_k_for_few_output_tiles(cuda_lib, fmt, odt):
             tol = TOL if odt == "float32" else TOL + 2.0 ** -8
             assert spec.rel_err(y1.float().cpu().numpy(), ref) <= tol, (N, K, M)
     assert cuda_lib.bq_status_poll() == 0
+
+
+@pytest.mark.parametrize("fmt", [0, 1])
+def test_tile_store_epilogue_output_types_and_edges(cuda_lib, fmt):
+    """The tcgen05 kernels store their output tile through shared memory and one bulk tensor store: fp32, bf16 and gated
+    (bf16, half the columns) outputs, with batch rows and weight rows that end inside a tile, on the one-CTA kernel
+    (no split over K here: K = 512) and on the 2-SM kernel (M >= 512).  bf16 output must be the rounding of the fp32
+    output of the same call; the gated output is checked against the two separate products."""
+    import torch
+    import chadslab_b200 as cb
+    rng = np.random.default_rng(31 + fmt)
+    K, N = 512, 8200                                         # 64 whole 128-row tiles + 8 rows
+    W = rng.normal(0, 0.02, (N, K)).astype(np.float32)
+    codes, scales = spec.quantize(W, fmt)
+    pw = cb.PackedWeight.from_arrays(codes, scales, fmt)
+    lin32, lin16 = cb.QuantLinear(pw, path=cb.PATH_TENSOR), cb.QuantLinear(pw, out_dtype=torch.bfloat16, path=cb.PATH_TENSOR)
+    F = 4104                                                 # gate|up: 8208 rows, the last 16-row block ends a tile early
+    g_w, u_w = rng.normal(0, 0.05, (F, K)).astype(np.float32), rng.normal(0, 0.05, (F, K)).astype(np.float32)
+    gate, up = cb.PackedWeight.from_float(g_w, fmt), cb.PackedWeight.from_float(u_w, fmt)
+    fused = cb.QuantLinear(cb.interleave_gate_up(gate, up))
+    for M in (64, 201, 601, 1030):
+        x = spec.bf16_round(rng.normal(0, 1, (M, K)).astype(np.float32))
+        xt = torch.from_numpy(x).cuda().to(torch.bfloat16)
+        y32 = lin32(xt)
+        assert cuda_lib.bq_last_path() == cb.PATH_TENSOR
+        rows = rng.choice(M, size=min(M, 48), replace=False)
+        ref = spec.qlinear(x[rows], codes, scales, fmt, f64=True)
+        assert spec.rel_err(y32[torch.from_numpy(rows).cuda()].cpu().numpy(), ref) <= TOL, M
+        y16 = lin16(xt)
+        assert torch.equal(y16, y32.to(torch.bfloat16)), M
+        got = fused.gated(xt, 1).float()
+        g, u = cb.QuantLinear(gate)(xt).double(), cb.QuantLinear(up)(xt).double()
+        want = (g / (1.0 + torch.exp(-g)) * u).float()
+        assert tuple(got.shape) == (M, F)
+        assert spec.rel_err(got.cpu().numpy(), want.cpu().numpy()) <= 6e-3, M
+    assert cuda_lib.bq_status_poll() == 0
