@@ -303,6 +303,12 @@ def test_tile_store_epilogue_output_types_and_edges(cuda_lib, fmt):
         assert spec.rel_err(y32[torch.from_numpy(rows).cuda()].cpu().numpy(), ref) <= TOL, M
         y16 = lin16(xt)
         assert torch.equal(y16, y32.to(torch.bfloat16)), M
+        # an output that does not start on a 16-byte boundary takes the plain-store epilogue: same bits
+        buf = torch.empty((M * N + 1,), dtype=torch.float32, device="cuda")
+        yo = buf[1:].view(M, N)
+        assert yo.data_ptr() % 16 == 4
+        lin32(xt, out=yo)
+        assert torch.equal(yo, y32), M
         got = fused.gated(xt, 1).float()
         g, u = cb.QuantLinear(gate)(xt).double(), cb.QuantLinear(up)(xt).double()
         want = (g / (1.0 + torch.exp(-g)) * u).float()
