@@ -499,8 +499,9 @@ def run_gpu(args):
             "roofline_quantized_matmul": hb.get("roofline_quantized_matmul"),
             "e2e": {"value": round(HEADLINE_BATCH * 1e3 / e2e_ms, 1) if e2e_ms else None, "unit": "tokens/s",
                     "h2d_bytes_per_step": HEADLINE_BATCH * 8, "d2h_bytes_per_step": HEADLINE_BATCH * 8,
-                    "how": "every step: token ids copied from pinned host memory, one graph replay, new ids copied back to "
-                           "pinned host memory, stream synchronised"},
+                    "how": "every step: ONE graph launch that holds the copy of the token ids from pinned host memory, the "
+                           "step's kernels and the copy of the new ids back to pinned host memory; stream synchronised, "
+                           "wall clock over the steps"},
             "gpu_launches": int(hb.get("launches_per_step", 0)) * steps, "clocks": clocks,
             "step": {"launches_per_step": hb.get("launches_per_step"), "stream_GB_per_step_per_gpu": hb.get("stream_GB_per_step_per_gpu"),
                      "frac_of_hbm_peak": hb.get("frac_of_hbm_peak"), "peak_gbs": peaks["hbm_gbs"], "peak_source": peaks["source"]},

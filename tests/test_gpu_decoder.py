@@ -75,6 +75,18 @@ def test_cuda_graph_decode_matches_eager(cuda_lib, fmt, adt):
         step()
         got.append(tokens.cpu().numpy().copy())
     assert np.array_equal(np.stack(got, axis=1), eager)
+    # the same step with its host copies inside the graph: ids in from pinned memory, new ids out, one launch per token
+    dec.reset()
+    first = dec.next_tokens(prompt)
+    h_in, h_out = first.cpu().pin_memory(), torch.empty((2,), dtype=torch.int64).pin_memory()
+    step, _ = dec.make_graph_stepper(2, first, start_pos=dec.pos, host_in=h_in, host_out=h_out)
+    got = [first.cpu().numpy()]
+    for _ in range(5):
+        step()
+        torch.cuda.current_stream().synchronize()
+        got.append(h_out.numpy().copy())
+        h_in.copy_(h_out)                                # the host feeds the new ids back
+    assert np.array_equal(np.stack(got, axis=1), eager)
 
 
 MOE_SMALL = dict(layers=2, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=0, vocab=1024, fmt=1, n_experts=8, top_k=2,
