@@ -24,7 +24,10 @@ def _rel(a, b):
                                    (3, 4, 4, 128, 512, 5), (1, 16, 16, 256, 2112, 2048), (2, 4, 1, 64, 64, 40),
                                    (2, 32, 4, 128, 600, 531), (1, 16, 1, 128, 300, 299), (1, 32, 1, 64, 200, 77),
                                    (2, 12, 4, 128, 2048, 1999), (1, 8, 1, 256, 8192, 8000), (1, 6, 2, 64, 64, 15),
-                                   (1, 32, 2, 256, 700, 16)])
+                                   (1, 32, 2, 256, 700, 16),
+                                   # at least a full wave of (batch row, head) pairs: the 8-positions-per-trip variant (bf16),
+                                   # unsplit with a ragged last trip, and split over two CTAs per head
+                                   (32, 16, 16, 64, 300, 259), (40, 12, 12, 128, 1100, 1090)])
 def test_decode_attention_matches_softmax_attention(cuda_lib, adt, shape):
     import torch
     from chadslab_b200 import _lib
@@ -132,7 +135,8 @@ def test_gated_activation(cuda_lib, adt, act):
 @pytest.mark.parametrize("adt", ["float32", "bfloat16"])
 @pytest.mark.parametrize("shape", [(2, 4, 2, 64, 64, 0), (1, 8, 1, 256, 1024, 700), (2, 4, 4, 128, 512, 511),
                                    (1, 16, 16, 256, 2112, 2048), (3, 2, 1, 64, 4096, 128), (2, 32, 4, 128, 600, 531),
-                                   (1, 16, 1, 128, 4096, 3000), (1, 32, 1, 64, 200, 0), (1, 32, 2, 256, 700, 16)])
+                                   (1, 16, 1, 128, 4096, 3000), (1, 32, 1, 64, 200, 0), (1, 32, 2, 256, 700, 16),
+                                   (32, 16, 16, 64, 300, 259), (40, 12, 12, 128, 1100, 1090)])
 def test_fused_rope_append_attention_equals_the_two_kernels(cuda_lib, adt, shape):
     """bq_decode_attention_rope against bq_rope_kv_append + bq_decode_attention: the appended cache rows are
     bit-identical, the attention output agrees to rounding (the current position joins the softmax last)."""
