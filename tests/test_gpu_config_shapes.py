@@ -27,7 +27,7 @@ def test_prefill_batches_on_config_shapes_sampled_rows(cuda_lib, fmt, shape):
     lin = cb.QuantLinear(pw)
     rows = torch.randint(0, N, (128,), device="cuda", generator=g)
     c_np, s_np = codes[rows].cpu().numpy(), scales[rows].cpu().numpy()
-    for M in (512, 4096):
+    for M in (300, 512, 4096):           # 300: one-CTA kernels (two weight tiles per CTA for 4-bit codes), 512+: the 2-SM kernel
         x = torch.randn((M, K), device="cuda", generator=g).to(torch.bfloat16)
         y = lin(x)
         assert cuda_lib.bq_last_path() == cb.PATH_TENSOR                   # the tcgen05 kernel, not a fallback
