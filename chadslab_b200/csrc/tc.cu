@@ -17,12 +17,16 @@
 //   warp 1      issuer   : one thread issues 8 x tcgen05.mma (K = 16 each, kind::f16, A from TMEM, B = fp16
 //                          activations from shared memory, D = fp32 in TMEM) per step and commits to the barriers
 //                          that free the A buffer and the stage
-//   epilogue             : tcgen05.ld of the 128 x BN fp32 tile, row back-scale, stores of y[m, n]
-// Every mbarrier wait is bounded; on expiry a status word is set and all roles drain and exit.
+//   epilogue             : tcgen05.ld of the 128 x BN fp32 tile, row back-scale, transposed into the (idle) stage ring
+//                          and written with one bulk tensor store (cp.async.bulk.tensor, shared -> global); plain
+//                          st.global for MoE tiles and outputs whose rows are not 16-byte aligned
+// A dense call requests the codes and scales of its first stages before griddepcontrol.wait (weights do not depend
+// on the preceding kernel).  Every mbarrier wait is bounded; on expiry a status word is set and all roles drain and exit.
 //
 // Activations reach the tensor core as fp16: a pre-pass kernel scales every activation row by a power of two that
 // puts its largest magnitude in [2^14, 2^15) and rounds to fp16 (exact for bf16 inputs down to 2^-29 of the row
-// maximum); the epilogue multiplies the row back.  Both MMA operands then have the same type.
+// maximum); the epilogue multiplies the row back.  Both MMA operands then have the same type (an fp16 A with a bf16 B
+// in one kind::f16 MMA raises an illegal-instruction error on this GPU).
 //
 // MODE 1 (GATED; MoE experts / SwiGLU): the gate and up matrices share the activation tile, two accumulators, the
 // epilogue writes silu(g) * u as bf16.  MODE 2 (DUAL): rows n0.. and n0+128.. of one matrix share the activation tile.
