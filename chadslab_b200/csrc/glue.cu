@@ -155,8 +155,10 @@ __global__ void __launch_bounds__(128) rope_kv_append_kernel(const float* __rest
 
 // Single-query attention: out[b, h, :] = softmax(q[b,h,:] . K[b, 0..pos, kv(h), :] / sqrt(D)) . V[b, 0..pos, kv(h), :]
 // One block (8 warps) per (b, h).  A lane owns 8 consecutive head-dim elements (D <= 256, D % 8 == 0), so a warp
-// reads one K or V row with a single coalesced vector load per lane; a warp takes 4 positions per trip (4 K rows and
-// 4 V rows in flight) and keeps an online softmax; the 8 partial (max, sum, acc) states merge through shared memory.
+// reads one K or V row with a single coalesced vector load per lane; a warp takes PB positions per trip (PB K rows and
+// PB V rows in flight: 4, or 8 for bf16 caches on grids of at least a full wave of heads, where two CTAs of 120
+// registers per SM stream faster than three of 80) and keeps an online softmax; the 8 partial (max, sum, acc) states
+// merge through shared memory.
 constexpr int ATT_WARPS = 8;
 constexpr int ATT_MAXD = 256;
 constexpr int ATT_EPL = 8;
